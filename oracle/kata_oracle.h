@@ -1,0 +1,61 @@
+/* CPU oracle for the KataGo neural-net forward pass.  TEST INFRASTRUCTURE ONLY:
+ * the shipped library never links, loads or calls anything declared here.
+ *
+ * It restates, in plain fp32 C++ with direct convolutions, the arithmetic of the
+ * reference's Eigen backend (cpp/neuralnet/eigenbackend.cpp), which the reference
+ * treats as the source of truth for all other backends (cpp/tests/tests.h:96-100).
+ * Parity is pinned by running the reference's own known-answer tests against it:
+ * tests/testnn.cpp (layer vectors) and tests/tinymodel.cpp (whole-net vector); the
+ * recipe in oracle/Makefile links the reference's unmodified test sources with
+ * oracle/oraclebackend.cpp.
+ *
+ * All tensors are fp32, NHWC: spatial[n][y][x][c].  Models arrive as the blob
+ * described in include/kb_modelblob.h.  Every function returns 0 on success and
+ * a non-zero code on failure, with a message available from ko_last_error().
+ */
+#ifndef KATA_ORACLE_H_
+#define KATA_ORACLE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct ko_model ko_model;
+
+/* Message of the last failure on the calling thread. */
+const char* ko_last_error(void);
+
+/* Parses a model blob for boards of nnXLen x nnYLen.  *out is NULL on failure. */
+int ko_model_create(const void* blob, size_t nbytes, int nnXLen, int nnYLen, ko_model** out);
+void ko_model_destroy(ko_model* m);
+
+/* info[0..8] = modelVersion, inC, inGlobalC, policyC, valueC, scoreValueC, ownershipC, trunkC, numBlocks */
+int ko_model_info(const ko_model* m, int32_t info[9]);
+
+/* Whole-network forward (eigenbackend.cpp:2150-2204 Model::apply).
+ * spatial [n][Y][X][inC], global [n][inGlobalC].
+ * Outputs (any may be NULL): policy [n][Y*X][policyC], policyPass [n][policyC],
+ * value [n][valueC], scoreValue [n][scoreValueC], ownership [n][Y*X],
+ * trunkOut [n][Y*X][trunkC] = trunk after the final norm+activation. */
+int ko_forward(
+  const ko_model* m, int n, const float* spatial, const float* global,
+  float* policy, float* policyPass, float* value, float* scoreValue, float* ownership,
+  float* trunkOut);
+
+/* Single-layer evaluation for the reference's layer tests (nninterface.h:134-180).
+ * The blob holds exactly one CONV, BN, BLOCK_ORDINARY or BLOCK_GPOOL construct.
+ * in [n][Y][X][inC], mask [n][Y][X] (ignored for CONV), out [n][Y][X][outC]. */
+int ko_eval_layer(
+  const void* blob, size_t nbytes, int n, int nnXLen, int nnYLen,
+  const float* in, const float* mask, float* out);
+
+/* Number of OpenMP threads the oracle will use (for reporting CPU baselines). */
+int ko_num_threads(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

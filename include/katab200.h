@@ -1,0 +1,127 @@
+/* C ABI of libkatab200.so: the B200 (sm_100a) implementation of the KataGo neural-net
+ * forward pass that sits below the reference's backend interface
+ * (cpp/neuralnet/nninterface.h:32-182).  The reference-side backend
+ * (katago_b200/host/b200backend.cpp) and the Python harness (katago_b200/capi.py) both
+ * bind exactly these entry points.
+ *
+ * Conventions: plain pointers and sizes only; every function returns 0 on success and a
+ * non-zero code on failure, never throws; the message of the last failure on the calling
+ * thread is available from kb_last_error().  A kb_handle is bound to one GPU and must be
+ * used by one thread at a time (nninterface.h:19-21).  There is no CPU fallback: without
+ * a CUDA device every compute entry point fails.
+ */
+#ifndef KATAB200_H_
+#define KATAB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct kb_model kb_model;   /* parsed network, host memory, device independent */
+typedef struct kb_handle kb_handle; /* one GPU replica: device weights, activations, stream */
+
+enum { KB_PRECISION_FP32 = 0, KB_PRECISION_FP16 = 1, KB_PRECISION_BF16 = 2 };
+
+/* Message of the last failure on the calling thread (never NULL). */
+const char* kb_last_error(void);
+
+/* Library version string. */
+const char* kb_version(void);
+
+/* Replaces NeuralNet::printDevices / device selection (nninterface.h:39, cudabackend.cpp:3333). */
+int kb_device_count(int* count);
+int kb_device_name(int device, char* buf, size_t buflen);
+
+/* Replaces the construction of the backend's Model from a ModelDesc
+ * (nninterface.h:43-46 loadModelFile/getModelDesc feed it; cudabackend.cpp:2852-2963).
+ * `blob` is the record stream of include/kb_modelblob.h. */
+int kb_model_create(const void* blob, size_t nbytes, kb_model** out);
+void kb_model_destroy(kb_model* m);
+
+/* info[0..8] = modelVersion, inC, inGlobalC, policyC, valueC, scoreValueC, ownershipC, trunkC, numBlocks */
+int kb_model_info(const kb_model* m, int32_t info[9]);
+
+/* Replaces NeuralNet::createComputeHandle / freeComputeHandle (nninterface.h:76-86):
+ * binds the calling thread to `device` (-1 = current default), uploads the weights in the
+ * chosen precision and allocates every activation buffer for batches up to maxBatch.
+ * requireExactNNLen != 0 promises that every board is exactly nnXLen x nnYLen. */
+int kb_handle_create(
+  const kb_model* m, int device, int maxBatch, int nnXLen, int nnYLen, int precision, int requireExactNNLen,
+  kb_handle** out);
+void kb_handle_destroy(kb_handle* h);
+
+/* Replaces NeuralNet::isUsingFP16 (nninterface.h:88): returns the precision in *precision. */
+int kb_handle_precision(const kb_handle* h, int* precision);
+
+/* Replaces the device part of NeuralNet::getOutput (nninterface.h:117-123; cudabackend.cpp:3556-3795):
+ * host buffers in, host buffers out, synchronous.
+ *   spatial  [n][nnYLen][nnXLen][inC] fp32 NHWC, as filled by NNEvaluator (not yet symmetrised)
+ *   global   [n][inGlobalC] fp32
+ *   symmetry [n] values 0..7 (SymmetryHelpers, nninputs.cpp:529-597) or NULL for identity; applied to the
+ *            inputs on the device and inverted on policy/ownership outputs
+ * Outputs are raw logits (nninterface.h:116); any output pointer may be NULL:
+ *   policy [n][nnYLen*nnXLen][policyC], policyPass [n][policyC], value [n][valueC],
+ *   scoreValue [n][scoreValueC], ownership [n][nnYLen*nnXLen]. */
+int kb_forward_host(
+  kb_handle* h, int n, const float* spatial, const float* global, const int32_t* symmetry,
+  float* policy, float* policyPass, float* value, float* scoreValue, float* ownership);
+
+/* The three stages of kb_forward_host as separate calls, for measurements with the inputs
+ * already resident in device memory: upload (host->device, asynchronous on the handle's stream),
+ * run (all kernels of one forward pass), download (device->host, synchronises). */
+int kb_upload_inputs(kb_handle* h, int n, const float* spatial, const float* global, const int32_t* symmetry);
+int kb_forward_resident(kb_handle* h, int n);
+int kb_download_outputs(
+  kb_handle* h, int n, float* policy, float* policyPass, float* value, float* scoreValue, float* ownership);
+
+/* Runs `iters` forward passes on resident inputs and returns the mean device time of one pass
+ * in milliseconds, measured with CUDA events on the handle's stream. */
+int kb_time_forward_resident(kb_handle* h, int n, int iters, float* msPerIter);
+
+/* Times `steps` forward passes one by one: before each pass `flushBytes` bytes of scratch device memory are
+ * overwritten (0 = no flush) so that the pass starts with a cold L2; the pass itself is bracketed by its own pair
+ * of CUDA events on the handle's stream.  msEach[i] receives the device time of pass i in milliseconds. */
+int kb_time_forward_steps(kb_handle* h, int n, int steps, size_t flushBytes, float* msEach);
+
+/* Per-kernel-class device timing.  When enabled, every launch of kb_forward_resident is bracketed
+ * by CUDA events on the handle's stream; kb_profile_read synchronises and returns, for up to `cap`
+ * kernel classes, the class name (<=47 chars), number of launches and total milliseconds since the
+ * last reset, and per-class algorithmic flops and bytes summed over those launches. */
+typedef struct kb_profile_entry {
+  char name[48];
+  int64_t launches;
+  double ms;
+  double flops;
+  double bytes;
+} kb_profile_entry;
+int kb_profile_enable(kb_handle* h, int enabled);
+int kb_profile_reset(kb_handle* h);
+int kb_profile_read(kb_handle* h, kb_profile_entry* entries, int cap, int* count);
+
+/* Number of kernel launches one forward pass of batch n issues (for the harness's launch count). */
+int kb_launches_per_forward(const kb_handle* h, int* launches);
+
+/* Trunk output after the final norm+activation, [n][nnYLen*nnXLen][trunkC] fp32 (debugging aid;
+ * mirrors the reference's DEBUG_INTERMEDIATE_VALUES dumps, cudabackend.cpp:46). */
+int kb_debug_read_trunk(kb_handle* h, int n, float* trunkOut);
+
+/* Page-locked host memory for the staging buffers the caller fills (replaces the plain `new float[]`
+ * staging of the reference's InputBuffers, cudabackend.cpp:3438-3551): copies from/to such memory are
+ * asynchronous DMA transfers.  Usable from any thread, with or without a bound device. */
+int kb_host_alloc(size_t bytes, void** out);
+void kb_host_free(void* p);
+
+/* Replaces NeuralNet::testEvaluateConv / BatchNorm / ResidualBlock / GlobalPoolingResidualBlock
+ * (nninterface.h:134-180).  The blob holds one CONV, BN, BLOCK_ORDINARY or BLOCK_GPOOL construct.
+ * in [n][Y][X][inC] NHWC fp32, mask [n][Y][X] (may be NULL for CONV), out [n][Y][X][outC]. */
+int kb_eval_layer(
+  const void* blob, size_t nbytes, int device, int precision, int n, int nnXLen, int nnYLen,
+  const float* in, const float* mask, float* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KATAB200_H_ */

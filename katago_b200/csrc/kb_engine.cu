@@ -1,0 +1,734 @@
+// Engine: flattens a kb::Model into a static list of fused launches and replays it.
+//
+// Fusion scheme.  Every convolution reads an ALREADY ACTIVATED tensor and its epilogue produces what its
+// consumers need: the updated residual stream (accumulator + residual, stored raw) and/or the NEXT
+// layer's batch-norm + activation + mask of that value.  So the reference's separate passes
+// (BatchNormLayer::apply before every conv, the residual add, addNCBiasInplace; eigenbackend.cpp:1026-1303)
+// disappear into the conv kernels; what remains besides convolutions is the gpool reduction, a few
+// per-board matmuls and one elementwise pass per gpool block.
+#include "kb_engine.h"
+
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+
+namespace kb {
+
+void cudaCheck(cudaError_t e, const char* what) {
+  if(e != cudaSuccess) throw CudaError(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+static bool isConvBlock(const BlockW& b) { return b.kind == BLOCK_ORDINARY || b.kind == BLOCK_GPOOL || b.kind == BLOCK_NESTED; }
+
+// host fp32 -> device dtype conversion
+static void convertTo(int dt, const std::vector<float>& src, std::vector<uint8_t>& dst) {
+  dst.resize(src.size() * dtypeSize(dt));
+  if(dt == DT_F32) std::memcpy(dst.data(), src.data(), src.size() * 4);
+  else if(dt == DT_F16) {
+    __half* o = reinterpret_cast<__half*>(dst.data());
+    for(size_t i = 0; i < src.size(); i++) o[i] = __float2half_rn(src[i]);
+  }
+  else {
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(dst.data());
+    for(size_t i = 0; i < src.size(); i++) o[i] = __float2bfloat16_rn(src[i]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+
+void* Engine::alloc(size_t bytes) {
+  void* p = nullptr;
+  if(bytes == 0) bytes = 16;
+  cudaCheck(cudaMalloc(&p, bytes), "cudaMalloc");
+  allocations_.push_back(p);
+  cudaCheck(cudaMemsetAsync(p, 0, bytes, stream_), "cudaMemset");
+  return p;
+}
+
+void* Engine::scratch(const std::string& key, size_t bytes) {
+  auto it = scratch_.find(key);
+  if(it != scratch_.end()) {
+    if(it->second.bytes < bytes) throw std::runtime_error("internal: scratch buffer " + key + " requested with two sizes");
+    return it->second.p;
+  }
+  DevBuf b;
+  b.p = alloc(bytes);
+  b.bytes = bytes;
+  scratch_[key] = b;
+  return b.p;
+}
+
+float* Engine::uploadF32(const std::vector<float>& v) {
+  float* p = static_cast<float*>(alloc(v.size() * sizeof(float)));
+  cudaCheck(cudaMemcpyAsync(p, v.data(), v.size() * sizeof(float), cudaMemcpyHostToDevice, stream_), "upload f32");
+  cudaCheck(cudaStreamSynchronize(stream_), "upload sync");
+  return p;
+}
+
+void* Engine::uploadConvWeights(const std::vector<const ConvW*>& parts, int inCdev, bool tcLayout) {
+  const int kY = parts[0]->kY, kX = parts[0]->kX, inC = parts[0]->inC;
+  int outC = 0;
+  for(const ConvW* p : parts) {
+    if(p->kY != kY || p->kX != kX || p->inC != inC) throw std::runtime_error("internal: merged convolutions differ in shape");
+    outC += p->outC;
+  }
+  const int taps = kY * kX;
+  std::vector<float> packed((size_t)taps * inCdev * outC, 0.0f);
+  int oc0 = 0;
+  for(const ConvW* p : parts) {
+    for(int oc = 0; oc < p->outC; oc++)
+      for(int ic = 0; ic < inC; ic++)
+        for(int y = 0; y < kY; y++)
+          for(int x = 0; x < kX; x++) {
+            const float v = p->w[(((size_t)oc * inC + ic) * kY + y) * kX + x];
+            const int tap = y * kX + x;
+            const size_t dst = tcLayout ? ((size_t)tap * outC + (oc0 + oc)) * inCdev + ic
+                                        : ((size_t)tap * inCdev + ic) * outC + (oc0 + oc);
+            packed[dst] = v;
+          }
+    oc0 += p->outC;
+  }
+  std::vector<uint8_t> bytes;
+  convertTo(dt_, packed, bytes);
+  void* d = alloc(bytes.size());
+  cudaCheck(cudaMemcpyAsync(d, bytes.data(), bytes.size(), cudaMemcpyHostToDevice, stream_), "upload conv weights");
+  cudaCheck(cudaStreamSynchronize(stream_), "upload sync");
+  return d;
+}
+
+Engine::ConvDev Engine::makeConv(const std::vector<const ConvW*>& parts, const void* in, int inStride, int inCdev) {
+  ConvDev c;
+  c.kY = parts[0]->kY; c.kX = parts[0]->kX; c.inC = inCdev; c.inCReal = parts[0]->inC;
+  c.outC = 0;
+  bool aligned = true;
+  for(const ConvW* p : parts) { c.outC += p->outC; if(p->outC % 16) aligned = false; }
+  c.in = in; c.inStride = inStride;
+  c.tc = !forceSimt_ && aligned && convTcEligible(dt_, inCdev, c.outC, c.kY, c.kX) && (inStride % 8) == 0;
+  c.w = uploadConvWeights(parts, inCdev, c.tc);
+  if(c.tc) {
+    c.plan = convTcCreate(dt_, in, inStride, inCdev, c.w, c.outC, c.kY, c.kX, X_, Y_, rowsPadMax_);
+    if(!c.plan) throw std::runtime_error("failed to create the tensor-core convolution plan (TMA descriptor encoding)");
+    tcPlans_.push_back(c.plan);
+  }
+  return c;
+}
+
+Engine::BNDev Engine::makeBN(const std::vector<const BNW*>& parts) {
+  std::vector<float> s, b;
+  BNDev d;
+  d.act = parts[0]->act;
+  for(const BNW* p : parts) {
+    if(p->act != d.act) throw std::runtime_error("internal: merged norms differ in activation");
+    s.insert(s.end(), p->scale.begin(), p->scale.end());
+    b.insert(b.end(), p->bias.begin(), p->bias.end());
+  }
+  d.C = (int)s.size();
+  d.scale = uploadF32(s);
+  d.bias = uploadF32(b);
+  return d;
+}
+
+int Engine::classId(const std::string& name) {
+  for(size_t i = 0; i < classes_.size(); i++)
+    if(classes_[i].name == name) return (int)i;
+  OpClass c;
+  c.name = name;
+  classes_.push_back(c);
+  return (int)classes_.size() - 1;
+}
+
+void Engine::addOp(const std::string& cls, double flops, double bytes, std::function<cudaError_t(cudaStream_t, const Geom&)> f) {
+  Op op;
+  op.cls = classId(cls);
+  op.flops = flops;
+  op.bytes = bytes;
+  op.run = std::move(f);
+  ops_.push_back(std::move(op));
+}
+
+void Engine::addConvOp(const ConvDev& c, Epilogue ep, const std::string& tag) {
+  ep.mask = mask_;
+  const double S = (double)X_ * Y_;
+  const double es = (double)dtypeSize(dt_);
+  double flops = 2.0 * c.kY * c.kX * c.inCReal * c.outC * S;
+  double bytes = S * c.inCReal * es;
+  if(ep.residual) bytes += S * c.outC * es;
+  if(ep.outRaw) bytes += S * (ep.rawC1 - ep.rawC0) * es;
+  if(ep.outAct) bytes += S * (ep.actC1 - ep.actC0) * es;
+  std::string name = "conv" + std::to_string(c.kY) + "x" + std::to_string(c.kX) + " " + std::to_string(c.inCReal) + "->" +
+                     std::to_string(c.outC) + (c.tc ? " tcgen05" : " simt") + (tag.empty() ? "" : " " + tag);
+  const int dt = dt_;
+  int* status = statusWord_;
+  if(c.tc) {
+    const ConvTcPlan* plan = c.plan;
+    addOp(name, flops, bytes, [plan, ep, status](cudaStream_t st, const Geom& g) { return launchConvTc(st, plan, g, ep, status); });
+  }
+  else {
+    ConvDev cc = c;
+    addOp(name, flops, bytes, [cc, ep, dt](cudaStream_t st, const Geom& g) {
+      return launchConvSimt(st, dt, cc.in, cc.inStride, cc.inC, cc.w, cc.outC, cc.kY, cc.kX, g, ep);
+    });
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Block graph -> launches
+
+void Engine::emitStack(const std::vector<BlockW>& blocks, int C, void* raw, void* act, const BNW* tail, int depth) {
+  for(size_t i = 0; i < blocks.size(); i++) {
+    const BNW* next = tail;
+    if(i + 1 < blocks.size()) next = isConvBlock(blocks[i + 1]) ? &blocks[i + 1].preBN : nullptr;
+    emitBlock(blocks[i], C, raw, act, next, depth);
+  }
+}
+
+void Engine::emitBlock(const BlockW& b, int C, void* raw, void* act, const BNW* next, int depth) {
+  const size_t es = dtypeSize(dt_);
+  const std::string d = "_d" + std::to_string(depth);
+  auto finishEp = [&](Epilogue& ep) {
+    // residual add into the stream + (optionally) the next block's norm/activation
+    ep.residual = raw; ep.resStride = C;
+    ep.outRaw = raw; ep.rawStride = C; ep.rawC0 = 0; ep.rawC1 = C;
+    if(next) {
+      BNDev nb = makeBN({next});
+      ep.outAct = act; ep.actStride = C; ep.actC0 = 0; ep.actC1 = C;
+      ep.scale = nb.scale; ep.bias = nb.bias; ep.act = nb.act;
+    }
+  };
+
+  if(b.kind == BLOCK_ORDINARY) {
+    const int mid = b.conv1.outC;
+    void* tmp = scratch("tmp" + d + "_c" + std::to_string(mid), (size_t)rowsPadMax_ * mid * es);
+    ConvDev c1 = makeConv({&b.conv1}, act, C, C);
+    BNDev mb = makeBN({&b.midBN});
+    Epilogue e1;
+    e1.outAct = tmp; e1.actStride = mid; e1.actC0 = 0; e1.actC1 = mid; e1.scale = mb.scale; e1.bias = mb.bias; e1.act = mb.act;
+    addConvOp(c1, e1, "");
+    ConvDev c2 = makeConv({&b.conv2}, tmp, mid, mid);
+    Epilogue e2;
+    finishEp(e2);
+    addConvOp(c2, e2, "+res");
+  }
+  else if(b.kind == BLOCK_GPOOL) {
+    const int reg = b.conv1.outC, gp = b.gpoolConv.outC;
+    void* R = scratch("gpR" + d + "_c" + std::to_string(reg), (size_t)rowsPadMax_ * reg * es);
+    void* G = scratch("gpG" + d + "_c" + std::to_string(gp), (size_t)rowsPadMax_ * gp * es);
+    void* Ract = scratch("gpRact" + d + "_c" + std::to_string(reg), (size_t)rowsPadMax_ * reg * es);
+    float* pooled = static_cast<float*>(scratch("gpPooled" + d + "_c" + std::to_string(gp), (size_t)maxBatch_ * 3 * gp * sizeof(float)));
+    float* gbias = static_cast<float*>(scratch("gpBias" + d + "_c" + std::to_string(reg), (size_t)maxBatch_ * reg * sizeof(float)));
+    BNDev gb = makeBN({&b.gpoolBN});
+    if(b.conv1.kY == b.gpoolConv.kY && b.conv1.kX == b.gpoolConv.kX) {
+      // regular and gpool convolutions read the same tensor: one launch, outputs split by channel range
+      ConvDev c1 = makeConv({&b.conv1, &b.gpoolConv}, act, C, C);
+      Epilogue e1;
+      e1.outRaw = R; e1.rawStride = reg; e1.rawC0 = 0; e1.rawC1 = reg;
+      e1.outAct = G; e1.actStride = gp; e1.actC0 = reg; e1.actC1 = reg + gp; e1.scale = gb.scale; e1.bias = gb.bias; e1.act = gb.act;
+      addConvOp(c1, e1, "reg|gpool");
+    }
+    else {
+      ConvDev cr = makeConv({&b.conv1}, act, C, C);
+      Epilogue er;
+      er.outRaw = R; er.rawStride = reg; er.rawC0 = 0; er.rawC1 = reg;
+      addConvOp(cr, er, "reg");
+      ConvDev cg = makeConv({&b.gpoolConv}, act, C, C);
+      Epilogue eg;
+      eg.outAct = G; eg.actStride = gp; eg.actC0 = 0; eg.actC1 = gp; eg.scale = gb.scale; eg.bias = gb.bias; eg.act = gb.act;
+      addConvOp(cg, eg, "gpool");
+    }
+    const int dt = dt_;
+    float* mask = mask_; float* maskSum = maskSum_;
+    const double S = (double)X_ * Y_;
+    addOp("gpool", 0.0, S * gp * es, [=](cudaStream_t st, const Geom& g) {
+      return launchGPool(st, dt, G, gp, 0, gp, mask, maskSum, pooled, 0, g);
+    });
+    float* wBias = uploadF32(b.gpoolToBias.w);
+    addOp("matmul small", 2.0 * 3 * gp * reg, 0.0, [=](cudaStream_t st, const Geom& g) {
+      return launchMatMulSmall(st, pooled, 3 * gp, wBias, reg, nullptr, KB_ACT_IDENTITY, gbias, g.n);
+    });
+    BNDev mb = makeBN({&b.midBN});
+    addOp("bias+norm+act", 0.0, 2.0 * S * reg * es, [=](cudaStream_t st, const Geom& g) {
+      return launchBiasBnAct(st, dt, R, reg, gbias, mb.scale, mb.bias, mb.act, mask, Ract, reg, reg, g);
+    });
+    ConvDev c2 = makeConv({&b.conv2}, Ract, reg, reg);
+    Epilogue e2;
+    finishEp(e2);
+    addConvOp(c2, e2, "+res");
+  }
+  else if(b.kind == BLOCK_NESTED) {
+    const int mid = b.conv1.outC;
+    const std::string d1 = "_d" + std::to_string(depth + 1);
+    void* midRaw = scratch("nRaw" + d1 + "_c" + std::to_string(mid), (size_t)rowsPadMax_ * mid * es);
+    void* midAct = scratch("nAct" + d1 + "_c" + std::to_string(mid), (size_t)rowsPadMax_ * mid * es);
+    ConvDev c1 = makeConv({&b.conv1}, act, C, C);
+    Epilogue e1;
+    e1.outRaw = midRaw; e1.rawStride = mid; e1.rawC0 = 0; e1.rawC1 = mid;
+    if(!isConvBlock(b.inner[0])) throw std::runtime_error("transformer blocks are not supported by this build yet");
+    BNDev ib = makeBN({&b.inner[0].preBN});
+    e1.outAct = midAct; e1.actStride = mid; e1.actC0 = 0; e1.actC1 = mid; e1.scale = ib.scale; e1.bias = ib.bias; e1.act = ib.act;
+    addConvOp(c1, e1, "");
+    emitStack(b.inner, mid, midRaw, midAct, &b.midBN, depth + 1);
+    ConvDev c2 = makeConv({&b.conv2}, midAct, mid, mid);
+    Epilogue e2;
+    finishEp(e2);
+    addConvOp(c2, e2, "+res");
+  }
+  else {
+    throw std::runtime_error("transformer blocks are not supported by this build yet");
+  }
+}
+
+void Engine::emitHeads(const Model& m, const void* trunkAct) {
+  const size_t es = dtypeSize(dt_);
+  const int P1 = m.p1Conv.outC, G1 = m.g1Conv.outC, V1 = m.v1Conv.outC, C = m.trunkC;
+  const int dt = dt_;
+  float* mask = mask_; float* maskSum = maskSum_;
+  const double S = (double)X_ * Y_;
+  void* Praw = scratch("headP", (size_t)rowsPadMax_ * P1 * es);
+  void* Pact = scratch("headPact", (size_t)rowsPadMax_ * P1 * es);
+  void* GV = scratch("headGV", (size_t)rowsPadMax_ * (G1 + V1) * es);
+  float* gpooled = static_cast<float*>(scratch("headGPooled", (size_t)maxBatch_ * 3 * G1 * sizeof(float)));
+  float* vpooled = static_cast<float*>(scratch("headVPooled", (size_t)maxBatch_ * 3 * V1 * sizeof(float)));
+  float* pbias = static_cast<float*>(scratch("headPBias", (size_t)maxBatch_ * P1 * sizeof(float)));
+
+  if(m.g1BN.act == m.v1BN.act) {
+    // the three 1x1 convolutions that read the trunk run as one GEMM (reference: three cuDNN calls,
+    // cudabackend.cpp:2603-2692, 2788-2846)
+    ConvDev hc = makeConv({&m.p1Conv, &m.g1Conv, &m.v1Conv}, trunkAct, C, C);
+    BNDev gv = makeBN({&m.g1BN, &m.v1BN});
+    Epilogue e;
+    e.outRaw = Praw; e.rawStride = P1; e.rawC0 = 0; e.rawC1 = P1;
+    e.outAct = GV; e.actStride = G1 + V1; e.actC0 = P1; e.actC1 = P1 + G1 + V1; e.scale = gv.scale; e.bias = gv.bias; e.act = gv.act;
+    addConvOp(hc, e, "heads p1|g1|v1");
+  }
+  else {
+    ConvDev pc = makeConv({&m.p1Conv}, trunkAct, C, C);
+    Epilogue ep;
+    ep.outRaw = Praw; ep.rawStride = P1; ep.rawC0 = 0; ep.rawC1 = P1;
+    addConvOp(pc, ep, "head p1");
+    ConvDev gc = makeConv({&m.g1Conv}, trunkAct, C, C);
+    BNDev gb = makeBN({&m.g1BN});
+    Epilogue eg;
+    eg.outAct = GV; eg.actStride = G1 + V1; eg.actC0 = 0; eg.actC1 = G1; eg.scale = gb.scale; eg.bias = gb.bias; eg.act = gb.act;
+    addConvOp(gc, eg, "head g1");
+    ConvDev vc = makeConv({&m.v1Conv}, trunkAct, C, C);
+    BNDev vb = makeBN({&m.v1BN});
+    Epilogue ev;
+    ev.outAct = static_cast<uint8_t*>(GV) + (size_t)G1 * es; ev.actStride = G1 + V1; ev.actC0 = 0; ev.actC1 = V1;
+    ev.scale = vb.scale; ev.bias = vb.bias; ev.act = vb.act;
+    addConvOp(vc, ev, "head v1");
+  }
+
+  addOp("gpool", 0.0, S * G1 * es, [=](cudaStream_t st, const Geom& g) {
+    return launchGPool(st, dt, GV, G1 + V1, 0, G1, mask, maskSum, gpooled, 0, g);
+  });
+  addOp("gpool", 0.0, S * V1 * es, [=](cudaStream_t st, const Geom& g) {
+    return launchGPool(st, dt, GV, G1 + V1, G1, V1, mask, maskSum, vpooled, 1, g);
+  });
+  float* wGB = uploadF32(m.gpoolToBias.w);
+  addOp("matmul small", 2.0 * 3 * G1 * P1, 0.0, [=](cudaStream_t st, const Geom& g) {
+    return launchMatMulSmall(st, gpooled, 3 * G1, wGB, P1, nullptr, KB_ACT_IDENTITY, pbias, g.n);
+  });
+  // pass logit (eigenbackend.cpp:2013-2022)
+  float* dPass = dPolicyPass_;
+  const int Pc = m.policyC;
+  float* wPass = uploadF32(m.passMul.w);
+  if(m.hasPassMlp) {
+    const int H = m.passMul.outC;
+    float* hidden = static_cast<float*>(scratch("headPassHidden", (size_t)maxBatch_ * H * sizeof(float)));
+    float* bPass = uploadF32(m.passBias.b);
+    float* wPass2 = uploadF32(m.passMul2.w);
+    const int passAct = m.passAct;
+    addOp("matmul small", 2.0 * 3 * G1 * H, 0.0, [=](cudaStream_t st, const Geom& g) {
+      return launchMatMulSmall(st, gpooled, 3 * G1, wPass, H, bPass, passAct, hidden, g.n);
+    });
+    addOp("matmul small", 2.0 * H * Pc, 0.0, [=](cudaStream_t st, const Geom& g) {
+      return launchMatMulSmall(st, hidden, H, wPass2, Pc, nullptr, KB_ACT_IDENTITY, dPass, g.n);
+    });
+  }
+  else {
+    addOp("matmul small", 2.0 * 3 * G1 * Pc, 0.0, [=](cudaStream_t st, const Geom& g) {
+      return launchMatMulSmall(st, gpooled, 3 * G1, wPass, Pc, nullptr, KB_ACT_IDENTITY, dPass, g.n);
+    });
+  }
+  BNDev pb = makeBN({&m.p1BN});
+  addOp("bias+norm+act", 0.0, 2.0 * S * P1 * es, [=](cudaStream_t st, const Geom& g) {
+    return launchBiasBnAct(st, dt, Praw, P1, pbias, pb.scale, pb.bias, pb.act, mask, Pact, P1, P1, g);
+  });
+  // value MLP (eigenbackend.cpp:2089-2099)
+  const int V2 = m.v2Mul.outC, Vc = m.valueC, Sv = m.scoreValueC;
+  float* v2 = static_cast<float*>(scratch("headV2", (size_t)maxBatch_ * V2 * sizeof(float)));
+  float* wV2 = uploadF32(m.v2Mul.w); float* bV2 = uploadF32(m.v2Bias.b);
+  float* wV3 = uploadF32(m.v3Mul.w); float* bV3 = uploadF32(m.v3Bias.b);
+  float* wSV = uploadF32(m.sv3Mul.w); float* bSV = uploadF32(m.sv3Bias.b);
+  float* dValue = dValue_; float* dScore = dScore_;
+  const int v2Act = m.v2Act;
+  addOp("matmul small", 2.0 * 3 * V1 * V2, 0.0, [=](cudaStream_t st, const Geom& g) {
+    return launchMatMulSmall(st, vpooled, 3 * V1, wV2, V2, bV2, v2Act, v2, g.n);
+  });
+  addOp("matmul small", 2.0 * V2 * Vc, 0.0, [=](cudaStream_t st, const Geom& g) {
+    return launchMatMulSmall(st, v2, V2, wV3, Vc, bV3, KB_ACT_IDENTITY, dValue, g.n);
+  });
+  addOp("matmul small", 2.0 * V2 * Sv, 0.0, [=](cudaStream_t st, const Geom& g) {
+    return launchMatMulSmall(st, v2, V2, wSV, Sv, bSV, KB_ACT_IDENTITY, dScore, g.n);
+  });
+  // p2Conv [oc][ic][1][1] -> [ic][oc]; ownership conv [1][ic][1][1] -> [ic]
+  std::vector<float> w2((size_t)P1 * Pc);
+  for(int oc = 0; oc < Pc; oc++)
+    for(int ic = 0; ic < P1; ic++) w2[(size_t)ic * Pc + oc] = m.p2Conv.w[(size_t)oc * P1 + ic];
+  float* dW2 = uploadF32(w2);
+  float* dWOwn = uploadF32(m.ownConv.w);
+  float* dPolicy = dPolicy_; float* dOwn = dOwnership_;
+  addOp("head outputs", 2.0 * S * (P1 * Pc + V1), S * (P1 + V1) * es + S * (Pc + 1) * 4.0, [=](cudaStream_t st, const Geom& g) {
+    return launchHeadFinal(st, dt, Pact, P1, P1, dW2, Pc, GV, G1 + V1, G1, V1, dWOwn, haveSym_ ? dSym_ : nullptr, dPolicy, dOwn, g);
+  });
+}
+
+// ---------------------------------------------------------------------------------------------
+
+static int pickDevice(int device) {
+  int count = 0;
+  cudaCheck(cudaGetDeviceCount(&count), "cudaGetDeviceCount");
+  if(count <= 0) throw CudaError("no CUDA device is available");
+  if(device < 0) {
+    cudaCheck(cudaGetDevice(&device), "cudaGetDevice");
+  }
+  if(device >= count) throw CudaError("device index " + std::to_string(device) + " is out of range (" + std::to_string(count) + " devices)");
+  cudaCheck(cudaSetDevice(device), "cudaSetDevice");
+  return device;
+}
+
+Engine::Engine(const Model& m, int device, int maxBatch, int X, int Y, int precision, bool requireExactNNLen) {
+  (void)requireExactNNLen;  // masks are folded into epilogues that run anyway; exact-size boards need no special path
+  if(maxBatch < 1 || maxBatch > 65536) throw std::runtime_error("maxBatch out of range");
+  if(X < 2 || Y < 2 || X > 50 || Y > 50) throw std::runtime_error("board size out of range");
+  if(precision != DT_F32 && precision != DT_F16 && precision != DT_BF16) throw std::runtime_error("unknown precision");
+  if(m.normKind != 0) throw std::runtime_error("RMSNorm trunk tips are not supported by this build yet");
+  device_ = pickDevice(device);
+  dt_ = precision; X_ = X; Y_ = Y; maxBatch_ = maxBatch;
+  forceSimt_ = getenv("KB_FORCE_SIMT") != nullptr && atoi(getenv("KB_FORCE_SIMT")) != 0;
+  cudaCheck(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate");
+  const Geom gmax = makeGeom(X, Y, maxBatch);
+  rowsPadMax_ = gmax.rowsPad;
+  const size_t es = dtypeSize(dt_);
+  const size_t S = (size_t)X * Y;
+  inC_ = m.inC; inGlobalC_ = m.inGlobalC; trunkC_ = m.trunkC; policyC_ = m.policyC; valueC_ = m.valueC; scoreValueC_ = m.scoreValueC;
+  statusWord_ = static_cast<int*>(alloc(sizeof(int)));
+  cudaCheck(cudaHostAlloc(reinterpret_cast<void**>(&statusHost_), sizeof(int), cudaHostAllocDefault), "cudaHostAlloc");
+  *statusHost_ = 0;
+
+  const bool tcInit = !forceSimt_ && dt_ != DT_F32 && convTcEligible(dt_, 64, m.trunkC, m.initialConv.kY, m.initialConv.kX);
+  inCdev_ = tcInit ? (m.inC + 63) / 64 * 64 : m.inC;
+
+  dSpatial_ = static_cast<float*>(alloc((size_t)maxBatch * S * m.inC * sizeof(float)));
+  dGlobal_ = static_cast<float*>(alloc((size_t)maxBatch * m.inGlobalC * sizeof(float)));
+  dSym_ = static_cast<int32_t*>(alloc((size_t)maxBatch * sizeof(int32_t)));
+  mask_ = static_cast<float*>(alloc((size_t)rowsPadMax_ * sizeof(float)));
+  maskSum_ = static_cast<float*>(alloc((size_t)maxBatch * sizeof(float)));
+  inputBuf_ = alloc((size_t)rowsPadMax_ * inCdev_ * es);
+  void* trunkRaw = alloc((size_t)rowsPadMax_ * m.trunkC * es);
+  trunkAct_ = alloc((size_t)rowsPadMax_ * m.trunkC * es);
+  float* gbias = static_cast<float*>(alloc((size_t)maxBatch * m.trunkC * sizeof(float)));
+  dPolicy_ = static_cast<float*>(alloc((size_t)maxBatch * S * m.policyC * sizeof(float)));
+  dPolicyPass_ = static_cast<float*>(alloc((size_t)maxBatch * m.policyC * sizeof(float)));
+  dValue_ = static_cast<float*>(alloc((size_t)maxBatch * m.valueC * sizeof(float)));
+  dScore_ = static_cast<float*>(alloc((size_t)maxBatch * m.scoreValueC * sizeof(float)));
+  dOwnership_ = static_cast<float*>(alloc((size_t)maxBatch * S * sizeof(float)));
+
+  // input packing (symmetry, mask, maskSum)
+  {
+    const int dt = dt_, inC = inC_, inCdev = inCdev_;
+    addOp("pack input", 0.0, (double)S * inC * 4.0 + (double)S * inCdev * es, [=](cudaStream_t st, const Geom& g) {
+      return launchPackInput(st, dt, dSpatial_, haveSym_ ? dSym_ : nullptr, inC, inputBuf_, inCdev, mask_, maskSum_, g);
+    });
+  }
+  // global features -> per-board bias (eigenbackend.cpp:1913-1915)
+  {
+    float* wG = uploadF32(m.initialMatMul.w);
+    const int inG = m.inGlobalC, tc = m.trunkC;
+    addOp("matmul small", 2.0 * inG * tc, 0.0, [=](cudaStream_t st, const Geom& g) {
+      return launchMatMulSmall(st, dGlobal_, inG, wG, tc, nullptr, KB_ACT_IDENTITY, gbias, g.n);
+    });
+  }
+  // initial convolution + global bias, producing the stream and the first block's activated input
+  {
+    ConvDev c0 = makeConv({&m.initialConv}, inputBuf_, inCdev_, inCdev_);
+    Epilogue e;
+    e.biasNC = gbias;
+    e.outRaw = trunkRaw; e.rawStride = m.trunkC; e.rawC0 = 0; e.rawC1 = m.trunkC;
+    if(!isConvBlock(m.blocks[0])) throw std::runtime_error("transformer blocks are not supported by this build yet");
+    BNDev b0 = makeBN({&m.blocks[0].preBN});
+    e.outAct = trunkAct_; e.actStride = m.trunkC; e.actC0 = 0; e.actC1 = m.trunkC; e.scale = b0.scale; e.bias = b0.bias; e.act = b0.act;
+    addConvOp(c0, e, "initial");
+  }
+  emitStack(m.blocks, m.trunkC, trunkRaw, trunkAct_, &m.tipBN, 0);
+  emitHeads(m, trunkAct_);
+  cudaCheck(cudaStreamSynchronize(stream_), "engine setup");
+}
+
+Engine::~Engine() {
+  cudaSetDevice(device_);
+  if(stream_) cudaStreamSynchronize(stream_);
+  for(cudaEvent_t e : events_) cudaEventDestroy(e);
+  for(ConvTcPlan* p : tcPlans_) convTcDestroy(p);
+  for(void* p : allocations_) cudaFree(p);
+  if(statusHost_) cudaFreeHost(statusHost_);
+  if(flushBuf_) cudaFree(flushBuf_);
+  if(stream_) cudaStreamDestroy(stream_);
+}
+
+void Engine::sync() {
+  cudaCheck(cudaStreamSynchronize(stream_), "stream synchronize");
+  if(statusHost_ && *statusHost_ != 0) {
+    int code = *statusHost_;
+    *statusHost_ = 0;
+    cudaMemsetAsync(statusWord_, 0, sizeof(int), stream_);
+    throw CudaError("a device-side wait timed out in the tensor-core convolution (status " + std::to_string(code) + ")");
+  }
+}
+
+void Engine::runOps(int n) {
+  if(n < 1 || n > maxBatch_) throw std::runtime_error("batch size out of range for this handle");
+  const Geom g = makeGeom(X_, Y_, n);
+  if(profiling_ && events_.size() < 2 * ops_.size()) {
+    size_t old = events_.size();
+    events_.resize(2 * ops_.size());
+    for(size_t i = old; i < events_.size(); i++) cudaCheck(cudaEventCreate(&events_[i]), "cudaEventCreate");
+  }
+  for(size_t i = 0; i < ops_.size(); i++) {
+    if(profiling_) cudaCheck(cudaEventRecord(events_[2 * i], stream_), "event record");
+    cudaError_t e = ops_[i].run(stream_, g);
+    if(e != cudaSuccess) throw CudaError("launch of '" + classes_[ops_[i].cls].name + "' failed: " + cudaGetErrorString(e));
+    if(profiling_) cudaCheck(cudaEventRecord(events_[2 * i + 1], stream_), "event record");
+  }
+  cudaCheck(cudaMemcpyAsync(statusHost_, statusWord_, sizeof(int), cudaMemcpyDeviceToHost, stream_), "status copy");
+  if(profiling_) {
+    sync();
+    for(size_t i = 0; i < ops_.size(); i++) {
+      float ms = 0.0f;
+      cudaCheck(cudaEventElapsedTime(&ms, events_[2 * i], events_[2 * i + 1]), "event elapsed");
+      OpClass& c = classes_[ops_[i].cls];
+      c.launches += 1;
+      c.ms += ms;
+      c.flops += ops_[i].flops * n;
+      c.bytes += ops_[i].bytes * n;
+    }
+  }
+}
+
+void Engine::uploadInputs(int n, const float* spatial, const float* global, const int32_t* symmetry) {
+  if(n < 1 || n > maxBatch_) throw std::runtime_error("batch size out of range for this handle");
+  if(!spatial || !global) throw std::runtime_error("NULL input pointer");
+  cudaCheck(cudaSetDevice(device_), "cudaSetDevice");
+  const size_t S = (size_t)X_ * Y_;
+  cudaCheck(cudaMemcpyAsync(dSpatial_, spatial, (size_t)n * S * inC_ * sizeof(float), cudaMemcpyHostToDevice, stream_), "H2D spatial");
+  cudaCheck(cudaMemcpyAsync(dGlobal_, global, (size_t)n * inGlobalC_ * sizeof(float), cudaMemcpyHostToDevice, stream_), "H2D global");
+  haveSym_ = symmetry != nullptr;
+  if(symmetry) {
+    for(int i = 0; i < n; i++)
+      if(symmetry[i] < 0 || symmetry[i] > 7) throw std::runtime_error("symmetry index out of range");
+    cudaCheck(cudaMemcpyAsync(dSym_, symmetry, (size_t)n * sizeof(int32_t), cudaMemcpyHostToDevice, stream_), "H2D symmetry");
+  }
+}
+
+void Engine::forwardResident(int n) {
+  cudaCheck(cudaSetDevice(device_), "cudaSetDevice");
+  runOps(n);
+}
+
+void Engine::downloadOutputs(int n, float* policy, float* policyPass, float* value, float* scoreValue, float* ownership) {
+  if(n < 1 || n > maxBatch_) throw std::runtime_error("batch size out of range for this handle");
+  cudaCheck(cudaSetDevice(device_), "cudaSetDevice");
+  const size_t S = (size_t)X_ * Y_;
+  if(policy) cudaCheck(cudaMemcpyAsync(policy, dPolicy_, (size_t)n * S * policyC_ * 4, cudaMemcpyDeviceToHost, stream_), "D2H policy");
+  if(policyPass) cudaCheck(cudaMemcpyAsync(policyPass, dPolicyPass_, (size_t)n * policyC_ * 4, cudaMemcpyDeviceToHost, stream_), "D2H pass");
+  if(value) cudaCheck(cudaMemcpyAsync(value, dValue_, (size_t)n * valueC_ * 4, cudaMemcpyDeviceToHost, stream_), "D2H value");
+  if(scoreValue) cudaCheck(cudaMemcpyAsync(scoreValue, dScore_, (size_t)n * scoreValueC_ * 4, cudaMemcpyDeviceToHost, stream_), "D2H score");
+  if(ownership) cudaCheck(cudaMemcpyAsync(ownership, dOwnership_, (size_t)n * S * 4, cudaMemcpyDeviceToHost, stream_), "D2H ownership");
+  sync();
+}
+
+float Engine::timeForwardResident(int n, int iters) {
+  if(iters < 1) throw std::runtime_error("iters must be positive");
+  cudaCheck(cudaSetDevice(device_), "cudaSetDevice");
+  cudaEvent_t a, b;
+  cudaCheck(cudaEventCreate(&a), "cudaEventCreate");
+  cudaCheck(cudaEventCreate(&b), "cudaEventCreate");
+  const bool wasProfiling = profiling_;
+  profiling_ = false;
+  cudaCheck(cudaEventRecord(a, stream_), "event record");
+  for(int i = 0; i < iters; i++) runOps(n);
+  cudaCheck(cudaEventRecord(b, stream_), "event record");
+  profiling_ = wasProfiling;
+  sync();
+  float ms = 0.0f;
+  cudaCheck(cudaEventElapsedTime(&ms, a, b), "event elapsed");
+  cudaEventDestroy(a);
+  cudaEventDestroy(b);
+  return ms / iters;
+}
+
+void Engine::timeForwardSteps(int n, int steps, size_t flushBytes, float* msEach) {
+  if(steps < 1 || steps > 100000) throw std::runtime_error("steps out of range");
+  cudaCheck(cudaSetDevice(device_), "cudaSetDevice");
+  if(flushBytes > flushBytes_) {
+    if(flushBuf_) cudaFree(flushBuf_);
+    flushBuf_ = nullptr;
+    flushBytes_ = 0;
+    cudaCheck(cudaMalloc(&flushBuf_, flushBytes), "cudaMalloc flush buffer");
+    flushBytes_ = flushBytes;
+  }
+  std::vector<cudaEvent_t> ev(2 * (size_t)steps);
+  for(auto& e : ev) cudaCheck(cudaEventCreate(&e), "cudaEventCreate");
+  const bool wasProfiling = profiling_;
+  profiling_ = false;
+  for(int i = 0; i < steps; i++) {
+    if(flushBytes > 0) cudaCheck(cudaMemsetAsync(flushBuf_, i & 0xff, flushBytes, stream_), "L2 flush");
+    cudaCheck(cudaEventRecord(ev[2 * i], stream_), "event record");
+    runOps(n);
+    cudaCheck(cudaEventRecord(ev[2 * i + 1], stream_), "event record");
+  }
+  profiling_ = wasProfiling;
+  sync();
+  for(int i = 0; i < steps; i++) cudaCheck(cudaEventElapsedTime(&msEach[i], ev[2 * i], ev[2 * i + 1]), "event elapsed");
+  for(auto& e : ev) cudaEventDestroy(e);
+}
+
+void Engine::readTrunk(int n, float* out) {
+  if(!trunkAct_ || !out) throw std::runtime_error("no trunk buffer");
+  cudaCheck(cudaSetDevice(device_), "cudaSetDevice");
+  const Geom g = makeGeom(X_, Y_, n);
+  float* tmp = nullptr;
+  const size_t bytes = (size_t)n * g.S * trunkC_ * sizeof(float);
+  cudaCheck(cudaMalloc(&tmp, bytes), "cudaMalloc");
+  cudaError_t e = launchFromPadded(stream_, dt_, trunkAct_, trunkC_, trunkC_, tmp, g);
+  if(e == cudaSuccess) e = cudaMemcpyAsync(out, tmp, bytes, cudaMemcpyDeviceToHost, stream_);
+  if(e == cudaSuccess) e = cudaStreamSynchronize(stream_);
+  cudaFree(tmp);
+  cudaCheck(e, "read trunk");
+}
+
+void Engine::profileReset() {
+  for(OpClass& c : classes_) { c.launches = 0; c.ms = 0.0; c.flops = 0.0; c.bytes = 0.0; }
+}
+
+int Engine::profileRead(OpClass* out, int cap) {
+  int k = 0;
+  for(const OpClass& c : classes_) {
+    if(k >= cap) break;
+    out[k++] = c;
+  }
+  return k;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Single-layer mode
+
+Engine::Engine(const void* layerBlob, size_t nbytes, int device, int n, int X, int Y, int precision) {
+  if(n < 1 || n > 65536) throw std::runtime_error("batch size out of range");
+  if(X < 1 || Y < 1 || X > 50 || Y > 50) throw std::runtime_error("board size out of range");
+  if(precision != DT_F32 && precision != DT_F16 && precision != DT_BF16) throw std::runtime_error("unknown precision");
+  device_ = pickDevice(device);
+  dt_ = precision; X_ = X; Y_ = Y; maxBatch_ = n; layerN_ = n;
+  forceSimt_ = getenv("KB_FORCE_SIMT") != nullptr && atoi(getenv("KB_FORCE_SIMT")) != 0;
+  cudaCheck(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate");
+  const Geom g = makeGeom(X, Y, n);
+  rowsPadMax_ = g.rowsPad;
+  const size_t es = dtypeSize(dt_);
+  const size_t S = (size_t)X * Y;
+  statusWord_ = static_cast<int*>(alloc(sizeof(int)));
+  cudaCheck(cudaHostAlloc(reinterpret_cast<void**>(&statusHost_), sizeof(int), cudaHostAllocDefault), "cudaHostAlloc");
+  *statusHost_ = 0;
+  mask_ = static_cast<float*>(alloc((size_t)rowsPadMax_ * sizeof(float)));
+  maskSum_ = static_cast<float*>(alloc((size_t)n * sizeof(float)));
+  layerMaskIn_ = static_cast<float*>(alloc((size_t)n * S * sizeof(float)));
+
+  kbblob::Reader rd(layerBlob, nbytes);
+  const uint32_t tag = rd.peekTag();
+  const int dt = dt_;
+  if(tag == KB_TAG_CONV) {
+    ConvW cw;
+    parseConv(rd, cw);
+    layerInC_ = cw.inC; layerOutC_ = cw.outC;
+    // pad the channel stride so that the tensor-core path is exercised when the shape allows it
+    const bool tcOk = !forceSimt_ && dt_ != DT_F32 && convTcEligible(dt_, (cw.inC + 63) / 64 * 64, cw.outC, cw.kY, cw.kX);
+    const int inCdev = tcOk ? (cw.inC + 63) / 64 * 64 : cw.inC;
+    void* inBuf = alloc((size_t)rowsPadMax_ * inCdev * es);
+    void* outBuf = alloc((size_t)rowsPadMax_ * cw.outC * es);
+    layerIn_ = static_cast<float*>(alloc((size_t)n * S * cw.inC * sizeof(float)));
+    layerOut_ = static_cast<float*>(alloc((size_t)n * S * cw.outC * sizeof(float)));
+    const int inC = cw.inC, outC = cw.outC;
+    float* lin = layerIn_; float* lout = layerOut_;
+    addOp("to padded", 0, 0, [=](cudaStream_t st, const Geom& gg) { return launchToPadded(st, dt, lin, inC, inBuf, inCdev, gg); });
+    ConvDev c = makeConv({&cw}, inBuf, inCdev, inCdev);
+    Epilogue e;
+    e.outRaw = outBuf; e.rawStride = outC; e.rawC0 = 0; e.rawC1 = outC;
+    addConvOp(c, e, "layer");
+    addOp("from padded", 0, 0, [=](cudaStream_t st, const Geom& gg) { return launchFromPadded(st, dt, outBuf, outC, outC, lout, gg); });
+    // a bare convolution has no mask: the epilogue must not read one
+    layerNeedsMask_ = false;
+  }
+  else if(tag == KB_TAG_BN) {
+    BNW bw;
+    parseBN(rd, bw);
+    layerInC_ = bw.C; layerOutC_ = bw.C;
+    const int C = bw.C;
+    void* inBuf = alloc((size_t)rowsPadMax_ * C * es);
+    void* outBuf = alloc((size_t)rowsPadMax_ * C * es);
+    layerIn_ = static_cast<float*>(alloc((size_t)n * S * C * sizeof(float)));
+    layerOut_ = static_cast<float*>(alloc((size_t)n * S * C * sizeof(float)));
+    BNDev b = makeBN({&bw});
+    float* lin = layerIn_; float* lout = layerOut_; float* mask = mask_;
+    addOp("to padded", 0, 0, [=](cudaStream_t st, const Geom& gg) { return launchToPadded(st, dt, lin, C, inBuf, C, gg); });
+    addOp("norm+act", 0, 0, [=](cudaStream_t st, const Geom& gg) {
+      return launchBnAct(st, dt, inBuf, C, b.scale, b.bias, b.act, mask, dt, outBuf, C, C, gg);
+    });
+    addOp("from padded", 0, 0, [=](cudaStream_t st, const Geom& gg) { return launchFromPadded(st, dt, outBuf, C, C, lout, gg); });
+    layerNeedsMask_ = true;
+  }
+  else {
+    BlockW bw;
+    parseBlock(rd, bw);
+    if(!isConvBlock(bw)) throw std::runtime_error("transformer blocks are not supported by this build yet");
+    const int C = bw.channels();
+    layerInC_ = C; layerOutC_ = C;
+    void* raw = alloc((size_t)rowsPadMax_ * C * es);
+    void* act = alloc((size_t)rowsPadMax_ * C * es);
+    layerIn_ = static_cast<float*>(alloc((size_t)n * S * C * sizeof(float)));
+    layerOut_ = static_cast<float*>(alloc((size_t)n * S * C * sizeof(float)));
+    BNDev pb = makeBN({&bw.preBN});
+    float* lin = layerIn_; float* lout = layerOut_; float* mask = mask_;
+    addOp("to padded", 0, 0, [=](cudaStream_t st, const Geom& gg) { return launchToPadded(st, dt, lin, C, raw, C, gg); });
+    addOp("norm+act", 0, 0, [=](cudaStream_t st, const Geom& gg) {
+      return launchBnAct(st, dt, raw, C, pb.scale, pb.bias, pb.act, mask, dt, act, C, C, gg);
+    });
+    emitBlock(bw, C, raw, act, nullptr, 0);
+    addOp("from padded", 0, 0, [=](cudaStream_t st, const Geom& gg) { return launchFromPadded(st, dt, raw, C, C, lout, gg); });
+    layerNeedsMask_ = true;
+  }
+  cudaCheck(cudaStreamSynchronize(stream_), "engine setup");
+}
+
+void Engine::evalLayer(const float* in, const float* mask, float* out) {
+  if(!in || !out) throw std::runtime_error("NULL pointer");
+  if(layerNeedsMask_ && !mask) throw std::runtime_error("this layer needs a mask");
+  cudaCheck(cudaSetDevice(device_), "cudaSetDevice");
+  const Geom g = makeGeom(X_, Y_, layerN_);
+  const size_t S = (size_t)X_ * Y_;
+  cudaCheck(cudaMemcpyAsync(layerIn_, in, (size_t)layerN_ * S * layerInC_ * 4, cudaMemcpyHostToDevice, stream_), "H2D layer input");
+  if(mask) {
+    cudaCheck(cudaMemcpyAsync(layerMaskIn_, mask, (size_t)layerN_ * S * 4, cudaMemcpyHostToDevice, stream_), "H2D layer mask");
+    cudaCheck(launchMaskToPadded(stream_, layerMaskIn_, mask_, maskSum_, g), "mask to padded");
+  }
+  else {
+    // all-ones mask on board points (padding rows stay 0)
+    std::vector<float> ones((size_t)layerN_ * S, 1.0f);
+    cudaCheck(cudaMemcpyAsync(layerMaskIn_, ones.data(), ones.size() * 4, cudaMemcpyHostToDevice, stream_), "H2D ones");
+    cudaCheck(cudaStreamSynchronize(stream_), "sync");
+    cudaCheck(launchMaskToPadded(stream_, layerMaskIn_, mask_, maskSum_, g), "mask to padded");
+  }
+  runOps(layerN_);
+  cudaCheck(cudaMemcpyAsync(out, layerOut_, (size_t)layerN_ * S * layerOutC_ * 4, cudaMemcpyDeviceToHost, stream_), "D2H layer output");
+  sync();
+}
+
+}  // namespace kb

@@ -1,0 +1,128 @@
+// One GPU replica of a network: device weights, activation buffers and the static launch list
+// ("program") that one forward pass replays.  Mirrors the role of the reference CUDA backend's
+// ComputeHandle + Model + Buffers (cpp/neuralnet/cudabackend.cpp:2852-3406) without its per-layer
+// objects: the block graph is flattened once, at creation, into a list of fused launches.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <functional>
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "kb_kernels.cuh"
+#include "kb_model.h"
+
+namespace kb {
+
+struct CudaError : std::runtime_error {
+  using std::runtime_error::runtime_error;
+};
+void cudaCheck(cudaError_t e, const char* what);
+
+// One launch of the program.
+struct Op {
+  int cls = 0;                                   // index into Engine::classes (profiling bucket)
+  double flops = 0.0, bytes = 0.0;               // algorithmic, per board (scaled by n when accounted)
+  std::function<cudaError_t(cudaStream_t, const Geom&)> run;
+};
+
+struct OpClass {
+  std::string name;
+  int64_t launches = 0;
+  double ms = 0.0, flops = 0.0, bytes = 0.0;
+};
+
+class Engine {
+ public:
+  // Whole network.
+  Engine(const Model& m, int device, int maxBatch, int X, int Y, int precision, bool requireExactNNLen);
+  // Single layer (test entry points): blob holds one CONV / BN / block.
+  Engine(const void* layerBlob, size_t nbytes, int device, int n, int X, int Y, int precision);
+  ~Engine();
+  Engine(const Engine&) = delete;
+  Engine& operator=(const Engine&) = delete;
+
+  int precision() const { return dt_; }
+  int launchesPerForward() const { return (int)ops_.size(); }
+
+  void uploadInputs(int n, const float* spatial, const float* global, const int32_t* symmetry);
+  void forwardResident(int n);
+  void downloadOutputs(int n, float* policy, float* policyPass, float* value, float* scoreValue, float* ownership);
+  float timeForwardResident(int n, int iters);
+  void timeForwardSteps(int n, int steps, size_t flushBytes, float* msEach);
+  void readTrunk(int n, float* out);
+
+  // single-layer mode
+  void evalLayer(const float* in, const float* mask, float* out);
+
+  void profileEnable(bool on) { profiling_ = on; }
+  void profileReset();
+  int profileRead(OpClass* out, int cap);
+
+  void sync();
+
+ private:
+  struct DevBuf { void* p = nullptr; size_t bytes = 0; };
+  struct ConvDev {
+    int kY = 1, kX = 1, inC = 0, outC = 0;  // inC as seen on the device (possibly zero-padded)
+    int inCReal = 0;                         // the layer's own input channel count
+    void* w = nullptr;
+    bool tc = false;
+    ConvTcPlan* plan = nullptr;
+    const void* in = nullptr;
+    int inStride = 0;
+  };
+  struct BNDev { const float* scale = nullptr; const float* bias = nullptr; int act = 0; int C = 0; };
+
+  void* alloc(size_t bytes);                               // zero-initialised device memory
+  void* scratch(const std::string& key, size_t bytes);     // named, reused across the plan
+  float* uploadF32(const std::vector<float>& v);
+  void* uploadConvWeights(const std::vector<const ConvW*>& parts, int inCdev, bool tcLayout);
+  ConvDev makeConv(const std::vector<const ConvW*>& parts, const void* in, int inStride, int inCdev);
+  BNDev makeBN(const std::vector<const BNW*>& parts);
+  int classId(const std::string& name);
+  void addConvOp(const ConvDev& c, Epilogue ep, const std::string& tag);
+  void addOp(const std::string& cls, double flops, double bytes, std::function<cudaError_t(cudaStream_t, const Geom&)> f);
+
+  // Emits the launches of a block stack.  On entry `raw` holds the residual stream ([rows][C]) and, if the
+  // first block wants it, `act` holds preBN+activation of it.  On exit `raw` is updated and `act` holds
+  // tail-norm(raw) if `tail` is given.
+  void emitStack(const std::vector<BlockW>& blocks, int C, void* raw, void* act, const BNW* tail, int depth);
+  void emitBlock(const BlockW& b, int C, void* raw, void* act, const BNW* next, int depth);
+  void emitHeads(const Model& m, const void* trunkAct);
+  void runOps(int n);
+
+  int device_ = 0, dt_ = DT_F32, X_ = 19, Y_ = 19, maxBatch_ = 1, rowsPadMax_ = 0;
+  bool forceSimt_ = false;
+  cudaStream_t stream_ = nullptr;
+  std::vector<void*> allocations_;
+  std::map<std::string, DevBuf> scratch_;
+  std::vector<ConvTcPlan*> tcPlans_;
+  std::vector<Op> ops_;
+  std::vector<OpClass> classes_;
+  bool profiling_ = false;
+  std::vector<cudaEvent_t> events_;
+  int* statusWord_ = nullptr;  // device
+  int* statusHost_ = nullptr;  // pinned
+  void* flushBuf_ = nullptr;
+  size_t flushBytes_ = 0;
+
+  // whole-network state
+  int inC_ = 0, inCdev_ = 0, inGlobalC_ = 0, trunkC_ = 0, policyC_ = 0, valueC_ = 0, scoreValueC_ = 0;
+  float *dSpatial_ = nullptr, *dGlobal_ = nullptr, *mask_ = nullptr, *maskSum_ = nullptr;
+  int32_t* dSym_ = nullptr;
+  bool haveSym_ = false;
+  void* inputBuf_ = nullptr;
+  void* trunkAct_ = nullptr;
+  float *dPolicy_ = nullptr, *dPolicyPass_ = nullptr, *dValue_ = nullptr, *dScore_ = nullptr, *dOwnership_ = nullptr;
+
+  // single-layer state
+  int layerN_ = 0, layerInC_ = 0, layerOutC_ = 0;
+  float *layerIn_ = nullptr, *layerMaskIn_ = nullptr, *layerOut_ = nullptr;
+  bool layerNeedsMask_ = false;
+};
+
+}  // namespace kb

@@ -1,0 +1,432 @@
+// CUDA-core kernels: input packing, the generic convolution used for fp32 and for shapes the
+// tensor-core kernel does not take, masked global pooling, the fused bias+norm+activation pass of
+// the gpool blocks, the small per-board matmuls and the head outputs.  All are bandwidth-bound
+// except the convolution; rows are channel-contiguous (NHWC), so adjacent threads read adjacent
+// channels.
+#include "kb_kernels.cuh"
+#include "../../include/kb_modelblob.h"
+
+namespace kb {
+
+// ---------------------------------------------------------------------------------------------
+// dtype helpers
+
+template <typename T> __device__ __forceinline__ float toF(T v);
+template <> __device__ __forceinline__ float toF<float>(float v) { return v; }
+template <> __device__ __forceinline__ float toF<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float toF<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T fromF(float v);
+template <> __device__ __forceinline__ float fromF<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half fromF<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 fromF<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Activation functions (eigenbackend.cpp:749-760; MISH_SCALE8 from desc.cpp:402-432).
+__device__ __forceinline__ float mishF(float x) {
+  // x * tanh(softplus(x)), softplus linear above 20
+  float sp = (x > 20.0f) ? x : log1pf(expf(x));
+  return x * tanhf(sp);
+}
+__device__ __forceinline__ float applyActF(float x, int act) {
+  switch(act) {
+    case KB_ACT_RELU: return fmaxf(x, 0.0f);
+    case KB_ACT_MISH: return mishF(x);
+    case KB_ACT_SILU: return x / (1.0f + expf(-x));
+    case KB_ACT_MISH_SCALE8: {
+      float x8 = 8.0f * x;
+      float sp = (x8 > 20.0f) ? x8 : log1pf(expf(x8));
+      return x * tanhf(sp);
+    }
+    default: return x;
+  }
+}
+
+// Board symmetry as a point map (h,w) -> (h',w'), the scatter form of nninputs.cpp:529-575.
+// `reverse` = false for inputs, true for outputs (the flips swap roles under transposition only for inputs).
+__device__ __forceinline__ void symMap(int sym, bool reverse, int H, int W, int h, int w, int& h2, int& w2) {
+  bool transpose = (sym & 4) != 0 && H == W;
+  bool flipX = (sym & 2) != 0;
+  bool flipY = (sym & 1) != 0;
+  if(transpose && !reverse) { bool t = flipX; flipX = flipY; flipY = t; }
+  if(!transpose) {
+    h2 = flipY ? H - 1 - h : h;
+    w2 = flipX ? W - 1 - w : w;
+  }
+  else {
+    h2 = flipY ? H - 1 - w : w;
+    w2 = flipX ? W - 1 - h : h;
+  }
+}
+
+#define KB_DISPATCH_DT(dt, EXPR)                                   \
+  switch(dt) {                                                     \
+    case DT_F32: { using T = float; EXPR; break; }                 \
+    case DT_F16: { using T = __half; EXPR; break; }                \
+    case DT_BF16: { using T = __nv_bfloat16; EXPR; break; }        \
+    default: return cudaErrorInvalidValue;                         \
+  }
+
+// ---------------------------------------------------------------------------------------------
+// Input packing
+
+template <typename T>
+__global__ void packInputKernel(
+  const float* __restrict__ spatial, const int32_t* __restrict__ symmetry, int inC, T* __restrict__ dst, int dstStride,
+  float* __restrict__ mask, float* __restrict__ maskSum, Geom g) {
+  const int n = blockIdx.x;
+  const int sym = symmetry ? symmetry[n] : 0;
+  float localSum = 0.0f;
+  const float* src = spatial + (size_t)n * g.S * inC;
+  // one thread per (point, channel); channel fastest so reads are contiguous
+  for(int idx = threadIdx.x; idx < g.S * inC; idx += blockDim.x) {
+    int p = idx / inC, c = idx - p * inC;
+    int h = p / g.X, w = p - h * g.X;
+    int h2, w2;
+    symMap(sym, false, g.Y, g.X, h, w, h2, w2);
+    size_t row = (size_t)n * g.PB + (size_t)h2 * g.RW + w2;
+    float v = src[idx];
+    dst[row * dstStride + c] = fromF<T>(v);
+    if(c == 0) { mask[row] = v; localSum += v; }
+  }
+  // padding rows of the mask stay 0 from allocation time; block-reduce the mask sum
+  __shared__ float red[32];
+  for(int o = 16; o > 0; o >>= 1) localSum += __shfl_down_sync(0xffffffffu, localSum, o);
+  if((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = localSum;
+  __syncthreads();
+  if(threadIdx.x < 32) {
+    float v = (threadIdx.x < (blockDim.x + 31) / 32) ? red[threadIdx.x] : 0.0f;
+    for(int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+    if(threadIdx.x == 0) maskSum[n] = v;
+  }
+}
+
+cudaError_t launchPackInput(
+  cudaStream_t st, int dt, const float* spatial, const int32_t* symmetry, int inC, void* dst, int dstStride,
+  float* mask, float* maskSum, Geom g) {
+  KB_DISPATCH_DT(dt, (packInputKernel<T><<<g.n, 256, 0, st>>>(spatial, symmetry, inC, (T*)dst, dstStride, mask, maskSum, g)));
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Generic convolution (CUDA cores).  Block tile 64 rows x 64 output channels, 256 threads, each
+// thread 4 rows x 4 channels; K loop over taps and chunks of 16 input channels staged in shared memory.
+
+constexpr int SC_BM = 64, SC_BN = 64, SC_BK = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(256) convSimtKernel(
+  const T* __restrict__ in, int inStride, int inC, const T* __restrict__ w, int outC, int kY, int kX, Geom g, Epilogue ep) {
+  __shared__ float sA[SC_BK][SC_BM + 4];
+  __shared__ float sB[SC_BK][SC_BN + 4];
+  const int tid = threadIdx.x;
+  const int tx = tid & 15, ty = tid >> 4;
+  const int m0 = blockIdx.x * SC_BM, n0 = blockIdx.y * SC_BN;
+  const int padY = kY / 2, padX = kX / 2;
+
+  // The A-tile element this thread stages: row lr (0..63), 4 consecutive k's starting at lk.
+  const int lr = tid >> 2, lk = (tid & 3) * 4;
+  const int lm = m0 + lr;
+  const int lb = lm / g.PB, lrem = lm - lb * g.PB;
+  const int ly = lrem / g.RW, lx = lrem - ly * g.RW;
+  const bool lvalid = lm < g.rows && ly < g.Y && lx < g.X;
+  // The B-tile element this thread stages: k row bk (0..15), 4 consecutive channels from bn.
+  const int bk = tid >> 4, bn = (tid & 15) * 4;
+
+  float acc[4][4];
+#pragma unroll
+  for(int i = 0; i < 4; i++)
+#pragma unroll
+    for(int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+
+  for(int dy = 0; dy < kY; dy++) {
+    for(int dx = 0; dx < kX; dx++) {
+      const int iy = ly + dy - padY, ix = lx + dx - padX;
+      const bool inb = lvalid && iy >= 0 && iy < g.Y && ix >= 0 && ix < g.X;
+      const T* arow = in + ((size_t)lb * g.PB + (size_t)iy * g.RW + ix) * inStride;
+      const T* wtap = w + (size_t)(dy * kX + dx) * inC * outC;
+      for(int k0 = 0; k0 < inC; k0 += SC_BK) {
+#pragma unroll
+        for(int q = 0; q < 4; q++) {
+          int k = k0 + lk + q;
+          sA[lk + q][lr] = (inb && k < inC) ? toF<T>(arow[k]) : 0.0f;
+        }
+#pragma unroll
+        for(int q = 0; q < 4; q++) {
+          int k = k0 + bk, c = n0 + bn + q;
+          sB[bk][bn + q] = (k < inC && c < outC) ? toF<T>(wtap[(size_t)k * outC + c]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for(int k = 0; k < SC_BK; k++) {
+          float a[4], b[4];
+#pragma unroll
+          for(int i = 0; i < 4; i++) a[i] = sA[k][ty * 4 + i];
+#pragma unroll
+          for(int j = 0; j < 4; j++) b[j] = sB[k][tx * 4 + j];
+#pragma unroll
+          for(int i = 0; i < 4; i++)
+#pragma unroll
+            for(int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+      }
+    }
+  }
+
+  // Epilogue
+#pragma unroll
+  for(int i = 0; i < 4; i++) {
+    const int m = m0 + ty * 4 + i;
+    if(m >= g.rowsPad) continue;
+    const int b = min(m / g.PB, g.n - 1);
+    const float mk = ep.mask ? ep.mask[m] : 1.0f;
+#pragma unroll
+    for(int j = 0; j < 4; j++) {
+      const int c = n0 + tx * 4 + j;
+      if(c >= outC) continue;
+      float v = acc[i][j];
+      if(ep.biasNC) v += ep.biasNC[(size_t)b * outC + c];
+      if(ep.residual) v += toF<T>(((const T*)ep.residual)[(size_t)m * ep.resStride + c]);
+      if(ep.outRaw && c >= ep.rawC0 && c < ep.rawC1) ((T*)ep.outRaw)[(size_t)m * ep.rawStride + (c - ep.rawC0)] = fromF<T>(v);
+      if(ep.outAct && c >= ep.actC0 && c < ep.actC1) {
+        const int ca = c - ep.actC0;
+        float a = (mk == 1.0f) ? applyActF(v * ep.scale[ca] + ep.bias[ca], ep.act) : 0.0f;
+        ((T*)ep.outAct)[(size_t)m * ep.actStride + ca] = fromF<T>(a);
+      }
+    }
+  }
+}
+
+cudaError_t launchConvSimt(
+  cudaStream_t st, int dt, const void* in, int inStride, int inC, const void* w, int outC, int kY, int kX,
+  Geom g, const Epilogue& ep) {
+  dim3 grid(g.rowsPad / SC_BM, (outC + SC_BN - 1) / SC_BN);
+  KB_DISPATCH_DT(dt, (convSimtKernel<T><<<grid, 256, 0, st>>>((const T*)in, inStride, inC, (const T*)w, outC, kY, kX, g, ep)));
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Small matmul: one block per row
+
+__global__ void matMulSmallKernel(
+  const float* __restrict__ in, int inC, const float* __restrict__ w, int outC, const float* __restrict__ bias, int act,
+  float* __restrict__ out) {
+  extern __shared__ float sIn[];
+  const int r = blockIdx.x;
+  for(int i = threadIdx.x; i < inC; i += blockDim.x) sIn[i] = in[(size_t)r * inC + i];
+  __syncthreads();
+  for(int oc = threadIdx.x; oc < outC; oc += blockDim.x) {
+    float s = 0.0f;
+    for(int ic = 0; ic < inC; ic++) s = fmaf(sIn[ic], w[(size_t)ic * outC + oc], s);
+    if(bias) s += bias[oc];
+    out[(size_t)r * outC + oc] = applyActF(s, act);
+  }
+}
+
+cudaError_t launchMatMulSmall(
+  cudaStream_t st, const float* in, int inC, const float* w, int outC, const float* bias, int act, float* out, int rows) {
+  matMulSmallKernel<<<rows, 128, inC * sizeof(float), st>>>(in, inC, w, outC, bias, act, out);
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Masked global pooling.  grid (n, ceil(C/32)), block (32 channels, 8 point groups).
+
+template <typename T>
+__global__ void gpoolKernel(
+  const T* __restrict__ in, int inStride, int c0, int C, const float* __restrict__ mask, const float* __restrict__ maskSum,
+  float* __restrict__ out, int valueHead, Geom g) {
+  const int n = blockIdx.x;
+  const int c = blockIdx.y * 32 + threadIdx.x;
+  float s = 0.0f, mx = -1.0f;
+  if(c < C) {
+    for(int p = threadIdx.y; p < g.S; p += blockDim.y) {
+      int y = p / g.X, x = p - y * g.X;
+      size_t row = (size_t)n * g.PB + (size_t)y * g.RW + x;
+      float v = toF<T>(in[row * inStride + c0 + c]);
+      s += v;
+      mx = fmaxf(mx, v + (mask[row] - 1.0f));
+    }
+  }
+  __shared__ float sSum[8][33], sMax[8][33];
+  sSum[threadIdx.y][threadIdx.x] = s;
+  sMax[threadIdx.y][threadIdx.x] = mx;
+  __syncthreads();
+  if(threadIdx.y == 0 && c < C) {
+    for(int k = 1; k < blockDim.y; k++) { s += sSum[k][threadIdx.x]; mx = fmaxf(mx, sMax[k][threadIdx.x]); }
+    float div = maskSum[n];
+    float sq = sqrtf(div);
+    float mean = s / div;
+    float* o = out + (size_t)n * 3 * C;
+    o[c] = mean;
+    o[C + c] = mean * (sq - 14.0f) * 0.1f;
+    o[2 * C + c] = valueHead ? mean * ((sq - 14.0f) * (sq - 14.0f) * 0.01f - 0.1f) : mx;
+  }
+}
+
+cudaError_t launchGPool(
+  cudaStream_t st, int dt, const void* in, int inStride, int c0, int C, const float* mask, const float* maskSum,
+  float* out, int valueHead, Geom g) {
+  dim3 grid(g.n, (C + 31) / 32), block(32, 8);
+  KB_DISPATCH_DT(dt, (gpoolKernel<T><<<grid, block, 0, st>>>((const T*)in, inStride, c0, C, mask, maskSum, out, valueHead, g)));
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Elementwise passes
+
+template <typename TI, typename TO>
+__global__ void biasBnActKernel(
+  const TI* __restrict__ in, int inStride, const float* __restrict__ biasNC, const float* __restrict__ scale,
+  const float* __restrict__ bias, int act, const float* __restrict__ mask, TO* __restrict__ out, int outStride, int C, Geom g) {
+  const size_t total = (size_t)g.rowsPad * C;
+  for(size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    size_t m = idx / C;
+    int c = (int)(idx - m * C);
+    float r = 0.0f;
+    if(m < (size_t)g.rows && mask[m] == 1.0f) {
+      float v = toF<TI>(in[m * inStride + c]);
+      if(biasNC) v += biasNC[(m / g.PB) * C + c];
+      r = applyActF(v * scale[c] + bias[c], act);
+    }
+    out[m * outStride + c] = fromF<TO>(r);
+  }
+}
+
+static int ewGrid(size_t total) {
+  size_t b = (total + 255) / 256;
+  return (int)(b > 148 * 16 ? 148 * 16 : (b < 1 ? 1 : b));
+}
+
+cudaError_t launchBiasBnAct(
+  cudaStream_t st, int dt, const void* in, int inStride, const float* biasNC, const float* scale, const float* bias,
+  int act, const float* mask, void* out, int outStride, int C, Geom g) {
+  int grid = ewGrid((size_t)g.rowsPad * C);
+  KB_DISPATCH_DT(dt, (biasBnActKernel<T, T><<<grid, 256, 0, st>>>((const T*)in, inStride, biasNC, scale, bias, act, mask, (T*)out, outStride, C, g)));
+  return cudaGetLastError();
+}
+
+cudaError_t launchBnAct(
+  cudaStream_t st, int dtIn, const void* in, int inStride, const float* scale, const float* bias, int act,
+  const float* mask, int dtOut, void* out, int outStride, int C, Geom g) {
+  int grid = ewGrid((size_t)g.rowsPad * C);
+  if(dtIn != dtOut && dtIn != DT_F32) return cudaErrorInvalidValue;
+  if(dtIn == dtOut) {
+    KB_DISPATCH_DT(dtIn, (biasBnActKernel<T, T><<<grid, 256, 0, st>>>((const T*)in, inStride, nullptr, scale, bias, act, mask, (T*)out, outStride, C, g)));
+  }
+  else {
+    KB_DISPATCH_DT(dtOut, (biasBnActKernel<float, T><<<grid, 256, 0, st>>>((const float*)in, inStride, nullptr, scale, bias, act, mask, (T*)out, outStride, C, g)));
+  }
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Head outputs: one thread per board point.
+
+template <typename T>
+__global__ void headFinalKernel(
+  const T* __restrict__ pAct, int pStride, int P1, const float* __restrict__ w2, int policyC, const T* __restrict__ vAct,
+  int vStride, int v0, int V1, const float* __restrict__ wOwn, const int32_t* __restrict__ symmetry,
+  float* __restrict__ policy, float* __restrict__ ownership, Geom g) {
+  extern __shared__ float sW[];  // w2 [P1][policyC] then wOwn [V1]
+  for(int i = threadIdx.x; i < P1 * policyC; i += blockDim.x) sW[i] = w2[i];
+  for(int i = threadIdx.x; i < V1; i += blockDim.x) sW[P1 * policyC + i] = wOwn[i];
+  __syncthreads();
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if(idx >= g.n * g.S) return;
+  const int n = idx / g.S, p = idx - n * g.S;
+  const int h = p / g.X, w = p - h * g.X;
+  const size_t row = (size_t)n * g.PB + (size_t)h * g.RW + w;
+  int h2, w2p;
+  symMap(symmetry ? symmetry[n] : 0, true, g.Y, g.X, h, w, h2, w2p);
+  const size_t outPos = (size_t)n * g.S + (size_t)h2 * g.X + w2p;
+  if(policy) {
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const T* pr = pAct + row * pStride;
+    for(int c = 0; c < P1; c++) {
+      float v = toF<T>(pr[c]);
+      for(int k = 0; k < policyC && k < 4; k++) acc[k] = fmaf(v, sW[c * policyC + k], acc[k]);
+    }
+    for(int k = 0; k < policyC && k < 4; k++) policy[outPos * policyC + k] = acc[k];
+  }
+  if(ownership) {
+    float o = 0.0f;
+    const T* vr = vAct + row * vStride + v0;
+    const float* wo = sW + P1 * policyC;
+    for(int c = 0; c < V1; c++) o = fmaf(toF<T>(vr[c]), wo[c], o);
+    ownership[outPos] = o;
+  }
+}
+
+cudaError_t launchHeadFinal(
+  cudaStream_t st, int dt, const void* pAct, int pStride, int P1, const float* w2, int policyC, const void* vAct,
+  int vStride, int v0, int V1, const float* wOwn, const int32_t* symmetry, float* policy, float* ownership, Geom g) {
+  if(policyC > 4) return cudaErrorInvalidValue;
+  int total = g.n * g.S;
+  size_t smem = ((size_t)P1 * policyC + V1) * sizeof(float);
+  KB_DISPATCH_DT(dt, (headFinalKernel<T><<<(total + 127) / 128, 128, smem, st>>>(
+    (const T*)pAct, pStride, P1, w2, policyC, (const T*)vAct, vStride, v0, V1, wOwn, symmetry, policy, ownership, g)));
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Layout conversion for single-layer tests
+
+template <typename T>
+__global__ void toPaddedKernel(const float* __restrict__ src, int C, T* __restrict__ dst, int dstStride, Geom g) {
+  const size_t total = (size_t)g.n * g.S * C;
+  for(size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    size_t p = idx / C;
+    int c = (int)(idx - p * C);
+    int n = (int)(p / g.S), q = (int)(p - (size_t)n * g.S);
+    int y = q / g.X, x = q - y * g.X;
+    dst[((size_t)n * g.PB + (size_t)y * g.RW + x) * dstStride + c] = fromF<T>(src[idx]);
+  }
+}
+template <typename T>
+__global__ void fromPaddedKernel(const T* __restrict__ src, int srcStride, int C, float* __restrict__ dst, Geom g) {
+  const size_t total = (size_t)g.n * g.S * C;
+  for(size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    size_t p = idx / C;
+    int c = (int)(idx - p * C);
+    int n = (int)(p / g.S), q = (int)(p - (size_t)n * g.S);
+    int y = q / g.X, x = q - y * g.X;
+    dst[idx] = toF<T>(src[((size_t)n * g.PB + (size_t)y * g.RW + x) * srcStride + c]);
+  }
+}
+__global__ void maskToPaddedKernel(const float* __restrict__ src, float* __restrict__ mask, float* __restrict__ maskSum, Geom g) {
+  const int n = blockIdx.x;
+  float s = 0.0f;
+  for(int p = threadIdx.x; p < g.S; p += blockDim.x) {
+    int y = p / g.X, x = p - y * g.X;
+    float v = src[(size_t)n * g.S + p];
+    mask[(size_t)n * g.PB + (size_t)y * g.RW + x] = v;
+    s += v;
+  }
+  __shared__ float red[32];
+  for(int o = 16; o > 0; o >>= 1) s += __shfl_down_sync(0xffffffffu, s, o);
+  if((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if(threadIdx.x < 32) {
+    float v = (threadIdx.x < (blockDim.x + 31) / 32) ? red[threadIdx.x] : 0.0f;
+    for(int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+    if(threadIdx.x == 0) maskSum[n] = v;
+  }
+}
+
+cudaError_t launchToPadded(cudaStream_t st, int dt, const float* src, int C, void* dst, int dstStride, Geom g) {
+  int grid = ewGrid((size_t)g.n * g.S * C);
+  KB_DISPATCH_DT(dt, (toPaddedKernel<T><<<grid, 256, 0, st>>>(src, C, (T*)dst, dstStride, g)));
+  return cudaGetLastError();
+}
+cudaError_t launchFromPadded(cudaStream_t st, int dt, const void* src, int srcStride, int C, float* dst, Geom g) {
+  int grid = ewGrid((size_t)g.n * g.S * C);
+  KB_DISPATCH_DT(dt, (fromPaddedKernel<T><<<grid, 256, 0, st>>>((const T*)src, srcStride, C, dst, g)));
+  return cudaGetLastError();
+}
+cudaError_t launchMaskToPadded(cudaStream_t st, const float* src, float* mask, float* maskSum, Geom g) {
+  maskToPaddedKernel<<<g.n, 128, 0, st>>>(src, mask, maskSum, g);
+  return cudaGetLastError();
+}
+
+}  // namespace kb

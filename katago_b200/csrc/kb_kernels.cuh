@@ -1,0 +1,118 @@
+// Device-side building blocks shared by the engine: activation layout, epilogue description,
+// and the launchers of every kernel.  All launchers enqueue on the given stream and return
+// the CUDA error of the launch.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+
+namespace kb {
+
+enum DType { DT_F32 = 0, DT_F16 = 1, DT_BF16 = 2 };
+inline size_t dtypeSize(int dt) { return dt == DT_F32 ? 4 : 2; }
+
+// Activation layout ("padded rows").  A batch of boards is one matrix of rows x channels; the row of
+// point (n,y,x) is n*PB + y*RW + x with RW = X+1 and PB = (Y+1)*RW.  Column X of every line and line Y of
+// every board are padding that always holds zeros in tensors that feed a convolution, so the 8 neighbours
+// of a point are at fixed row offsets (dy*RW + dx) and a 3x3 convolution is nine row-shifted GEMMs.
+// rowsPad = rows rounded up to a multiple of 128 (the MMA tile height).
+struct Geom {
+  int X, Y, RW, PB, S;
+  int n;        // boards in this batch
+  int rows;     // n * PB
+  int rowsPad;  // rows rounded up to 128
+};
+
+inline Geom makeGeom(int X, int Y, int n) {
+  Geom g;
+  g.X = X; g.Y = Y; g.RW = X + 1; g.PB = (Y + 1) * (X + 1); g.S = X * Y; g.n = n;
+  g.rows = n * g.PB;
+  g.rowsPad = (g.rows + 127) / 128 * 128;
+  return g;
+}
+
+// What a convolution does with each accumulator v[row][c] (c in [0,outC)):
+//   v += biasNC[n][c]            (per-board bias: global-feature bias, gpool bias)   if biasNC
+//   v += residual[row][c]                                                            if residual
+//   outRaw[row][c - rawC0] = v                     for c in [rawC0, rawC1)           if outRaw
+//   outAct[row][c - actC0] = mask[row]==1 ? act(v*scale[c-actC0] + bias[c-actC0]) : 0
+//                                                  for c in [actC0, actC1)           if outAct
+// The second form is the NEXT layer's batch norm + activation + board mask (eigenbackend.cpp:739-763)
+// applied while the accumulator is still on chip.
+struct Epilogue {
+  const float* biasNC = nullptr;
+  const void* residual = nullptr;
+  int resStride = 0;
+  void* outRaw = nullptr;
+  int rawStride = 0, rawC0 = 0, rawC1 = 0;
+  void* outAct = nullptr;
+  int actStride = 0, actC0 = 0, actC1 = 0;
+  const float* scale = nullptr;
+  const float* bias = nullptr;
+  int act = 0;
+  const float* mask = nullptr;
+};
+
+// --- SIMT kernels (any dtype) ---------------------------------------------------------------------
+
+// Packs NNEvaluator-style inputs into the padded-rows layout, applying the per-row board symmetry
+// (nninputs.cpp:529-597) and producing mask (= input channel 0, eigenbackend.cpp:2169) and maskSum.
+// spatial: [n][Y][X][inC] fp32.  dst: [rowsPad][dstStride] (channels >= inC are left zero).
+cudaError_t launchPackInput(
+  cudaStream_t st, int dt, const float* spatial, const int32_t* symmetry, int inC, void* dst, int dstStride,
+  float* mask, float* maskSum, Geom g);
+
+// Generic convolution on CUDA cores: any odd kernel size, any channel counts, fp32 accumulate.
+// in: [rowsPad][inStride]; w: [kY*kX][inC][outC] in the activation dtype.
+cudaError_t launchConvSimt(
+  cudaStream_t st, int dt, const void* in, int inStride, int inC, const void* w, int outC, int kY, int kX,
+  Geom g, const Epilogue& ep);
+
+// out[r][oc] = act(sum_ic in[r][ic]*w[ic][oc] + bias[oc]); fp32, small row counts (heads, gpool bias).
+cudaError_t launchMatMulSmall(
+  cudaStream_t st, const float* in, int inC, const float* w, int outC, const float* bias, int act, float* out, int rows);
+
+// Masked global pooling (eigenbackend.cpp:152-197).  in: [rowsPad][inStride] (channels c0..c0+C), already
+// activated and masked.  out: [n][3*C] fp32.  valueHead selects the third statistic.
+cudaError_t launchGPool(
+  cudaStream_t st, int dt, const void* in, int inStride, int c0, int C, const float* mask, const float* maskSum,
+  float* out, int valueHead, Geom g);
+
+// out[row][c] = mask ? act((in[row][c] + biasNC[n][c]) * scale[c] + bias[c]) : 0   (addNCBiasInplace + BN)
+cudaError_t launchBiasBnAct(
+  cudaStream_t st, int dt, const void* in, int inStride, const float* biasNC, const float* scale, const float* bias,
+  int act, const float* mask, void* out, int outStride, int C, Geom g);
+
+// Stand-alone batch norm + activation + mask (first layer of a block whose input was not produced by one
+// of our convolutions, and the single-layer test entry points).
+cudaError_t launchBnAct(
+  cudaStream_t st, int dtIn, const void* in, int inStride, const float* scale, const float* bias, int act,
+  const float* mask, int dtOut, void* out, int outStride, int C, Geom g);
+
+// Final 1x1 convolutions of the heads: policy = p2Conv(pAct), ownership = ownConv(vAct), written to the
+// caller-facing fp32 arrays with the inverse board symmetry.  pAct: [rowsPad][pStride] (P1 channels),
+// vAct: [rowsPad][vStride] channels v0..v0+V1.  w2: [P1][policyC] fp32, wOwn: [V1] fp32.
+cudaError_t launchHeadFinal(
+  cudaStream_t st, int dt, const void* pAct, int pStride, int P1, const float* w2, int policyC, const void* vAct,
+  int vStride, int v0, int V1, const float* wOwn, const int32_t* symmetry, float* policy, float* ownership, Geom g);
+
+// Layout conversion for the single-layer entry points: [n][Y][X][C] fp32 <-> padded rows of dtype dt.
+cudaError_t launchToPadded(cudaStream_t st, int dt, const float* src, int C, void* dst, int dstStride, Geom g);
+cudaError_t launchFromPadded(cudaStream_t st, int dt, const void* src, int srcStride, int C, float* dst, Geom g);
+// mask [n][Y][X] fp32 -> padded mask + maskSum
+cudaError_t launchMaskToPadded(cudaStream_t st, const float* src, float* mask, float* maskSum, Geom g);
+
+// --- Tensor-core convolution (fp16 / bf16, sm_100a tcgen05) ------------------------------------------
+
+struct ConvTcPlan;  // opaque: tensor maps + tile configuration for one convolution
+// True if the tensor-core kernel can run this convolution shape.
+bool convTcEligible(int dt, int inC, int outC, int kY, int kX);
+// in: [rowsPadMax][inStride] activations, w: [kY*kX][outC][inC] in dtype dt (K-major per tap).
+ConvTcPlan* convTcCreate(
+  int dt, const void* in, int inStride, int inC, const void* w, int outC, int kY, int kX, int X, int Y, int rowsPadMax);
+void convTcDestroy(ConvTcPlan* p);
+cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epilogue& ep, int* statusWord);
+
+}  // namespace kb

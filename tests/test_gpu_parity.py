@@ -1,0 +1,208 @@
+"""Parity of the CUDA path against the CPU oracle and the committed golden vectors.  Everything goes
+through the C ABI (katago_b200.capi -> libkatab200.so).  Tolerances: fp32 max-abs <= 1e-4 on value / score /
+ownership / policy probability; reduced precision p99 winrate <= 0.5 %, score <= 0.1 points, policy KL <= 1e-3."""
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+from katago_b200 import capi
+from katago_b200 import modelfile as mf
+from tests.golden.make_golden import CASES
+from tests.helpers import parity_metrics, symmetrise_inputs, unsymmetrise_outputs
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+KATAGO_B200 = os.path.join(ROOT, "oracle", "_ref", "katago_b200")
+
+
+def _assert_fp32_close(got, ref, mask):
+    m = parity_metrics(got, ref, mask)
+    for k in ("winrate", "policy_max", "ownership"):
+        assert m[k].max() <= 1e-4, (k, m[k].max())
+    for k in ("value", "scoreValue", "policyPass"):
+        assert np.abs(got[k] - ref[k]).max() <= 1e-4 * max(1.0, np.abs(ref[k]).max()), k
+    assert np.abs(got["policy"] - ref["policy"]).max() <= 1e-4 * max(1.0, np.abs(ref["policy"]).max())
+
+
+def _assert_reduced_close(got, ref, mask):
+    m = parity_metrics(got, ref, mask)
+    assert np.percentile(m["winrate"], 99) <= 0.005, m["winrate"]
+    assert np.percentile(m["score"], 99) <= 0.1, m["score"]
+    assert np.percentile(m["lead"], 99) <= 0.1, m["lead"]
+    assert np.percentile(m["policy_kl"], 99) <= 1e-3, m["policy_kl"]
+
+
+# --- single layers (the reference's testEvaluate* entry points) --------------------------------
+
+@pytest.mark.parametrize("k,ic,oc", [(1, 2, 3), (3, 5, 7), (5, 4, 4), (3, 22, 96), (1, 96, 32), (3, 64, 64)])
+def test_conv_layer_fp32(k, ic, oc, oracle):
+    g = mf._Gen(100 + k + ic)
+    rng = np.random.default_rng(ic * 7 + oc)
+    conv = g.conv(k, ic, oc)
+    blob = mf.layer_blob(conv)
+    for (n, ylen, xlen) in [(1, 19, 19), (3, 9, 13), (2, 3, 4)]:
+        x = rng.standard_normal((n, ylen, xlen, ic)).astype(np.float32)
+        ref = oracle.eval_layer(blob, x, None, oc)
+        out = capi.eval_layer(blob, x, None, oc, precision=capi.PRECISION_FP32)
+        assert np.abs(out - ref).max() <= 1e-4 * max(1.0, np.abs(ref).max())
+
+
+@pytest.mark.parametrize("prec,tol", [(capi.PRECISION_FP16, 0.03), (capi.PRECISION_BF16, 0.2)])
+@pytest.mark.parametrize("k,ic,oc", [(1, 384, 192), (3, 192, 192), (3, 128, 192), (1, 192, 384), (3, 22, 384), (3, 256, 256), (1, 64, 48)])
+def test_conv_layer_tensor_core(prec, tol, k, ic, oc, oracle):
+    """Shapes of the b18/b28 trunks; the tolerance is the reference's fp16 layer tolerance 0.03*max(|x|,|y|,3)
+    (cpp/tests/testnn.cpp:8-15), widened for bf16's 8 mantissa bits."""
+    g = mf._Gen(200 + k + ic)
+    rng = np.random.default_rng(ic + oc)
+    conv = g.conv(k, ic, oc)
+    blob = mf.layer_blob(conv)
+    for n in (1, 5):
+        x = rng.standard_normal((n, 19, 19, ic)).astype(np.float32)
+        ref = oracle.eval_layer(blob, x, None, oc)
+        out = capi.eval_layer(blob, x, None, oc, precision=prec)
+        assert np.all(np.abs(out - ref) <= tol * np.maximum(np.maximum(np.abs(out), np.abs(ref)), 3.0))
+
+
+@pytest.mark.parametrize("prec,tol", [(capi.PRECISION_FP32, 1e-4), (capi.PRECISION_FP16, 0.03)])
+def test_blocks_and_norm_with_masks(prec, tol, oracle):
+    g = mf._Gen(31)
+    rng = np.random.default_rng(9)
+    mask = np.zeros((4, 19, 19), np.float32)
+    mask[0] = 1; mask[1, :13, :13] = 1; mask[2, :9, :9] = 1; mask[3, :10, :14] = 1
+    floor = 1.0 if prec == capi.PRECISION_FP32 else 3.0
+    for C, layer in [(64, mf._gen_ordinary(g, 64, 64, mf.ACT_RELU)), (192, mf._gen_ordinary(g, 192, 192, mf.ACT_MISH)),
+                     (96, mf._gen_gpool(g, 96, 64, 32, mf.ACT_RELU)), (192, mf._gen_gpool(g, 192, 128, 64, mf.ACT_MISH)), (64, g.bn(64))]:
+        x = rng.standard_normal((4, 19, 19, C)).astype(np.float32) * mask[..., None]
+        blob = mf.layer_blob(layer)
+        ref = oracle.eval_layer(blob, x, mask, C)
+        out = capi.eval_layer(blob, x, mask, C, precision=prec)
+        assert np.all(np.abs(out - ref) <= tol * np.maximum(np.maximum(np.abs(out), np.abs(ref)), floor)), layer["kind"]
+
+
+# --- whole networks ----------------------------------------------------------------------------
+
+def _run_case(name, prec, oracle, syms=None):
+    factory, n, sizes, seed = CASES[name]
+    golden = dict(np.load(os.path.join(ROOT, "tests", "golden", f"{name}.npz")))
+    model = capi.Model(mf.to_blob(factory()))
+    h = capi.Handle(model, n, precision=prec)
+    sp, gl = mf.random_positions(n, seed=seed, board_sizes=sizes)
+    mask = sp[..., 0].reshape(n, -1)
+    if syms is None:
+        got = h.forward(sp, gl)
+        ref = golden
+    else:
+        # the library symmetrises inputs and un-symmetrises outputs on the device; the oracle sees explicitly
+        # symmetrised inputs and numpy undoes the symmetry on its outputs
+        got = h.forward(sp, gl, syms)
+        om = oracle.OracleModel(mf.to_blob(factory()))
+        ref = unsymmetrise_outputs(om.forward(symmetrise_inputs(sp, syms), gl), syms)
+    h.close()
+    return got, ref, mask
+
+
+def test_b6c96_fp32_matches_golden(oracle):
+    got, ref, mask = _run_case("b6c96", capi.PRECISION_FP32, oracle)
+    _assert_fp32_close(got, ref, mask)
+
+
+def test_b6c96_fp32_all_symmetries(oracle):
+    got, ref, mask = _run_case("b6c96", capi.PRECISION_FP32, oracle, syms=np.arange(8, dtype=np.int32))
+    _assert_fp32_close(got, ref, mask)
+
+
+@pytest.mark.parametrize("name", ["b18c384nbt_3blocks", "b28c512nbt_3blocks"])
+def test_nbt_fp32_matches_golden(name, oracle):
+    got, ref, mask = _run_case(name, capi.PRECISION_FP32, oracle)
+    _assert_fp32_close(got, ref, mask)
+
+
+@pytest.mark.parametrize("name,prec", [("b18c384nbt_3blocks", capi.PRECISION_FP16), ("b28c512nbt_3blocks", capi.PRECISION_BF16)])
+def test_nbt_reduced_precision_matches_golden(name, prec, oracle):
+    got, ref, mask = _run_case(name, prec, oracle)
+    _assert_reduced_close(got, ref, mask)
+
+
+def test_full_b18c384nbt_fp16_mixed_boards_vs_oracle(oracle):
+    """BASELINE configs[1] and [4] at a batch the oracle finishes in seconds: full 18-block net, boards of
+    9/13/19 in ratio 1:1:2, random symmetries."""
+    n = 16
+    model_tree = mf.make_b18c384nbt()
+    blob = mf.to_blob(model_tree)
+    sizes = [9, 13, 19, 19] * (n // 4)
+    sp, gl = mf.random_positions(n, seed=2004, board_sizes=sizes)
+    syms = (np.arange(n) * 3 % 8).astype(np.int32)
+    h = capi.Handle(capi.Model(blob), n, precision=capi.PRECISION_FP16)
+    got = h.forward(sp, gl, syms)
+    h.close()
+    ref = unsymmetrise_outputs(oracle.OracleModel(blob).forward(symmetrise_inputs(sp, syms), gl), syms)
+    _assert_reduced_close(got, ref, sp[..., 0].reshape(n, -1))
+
+
+def test_batch_size_independence_and_any_n():
+    """getOutput may be called with any 1 <= n <= maxBatch (nninterface.h:102-123); results of a row must not
+    depend on the batch it travels in (the reference's runnnbatchingtest property)."""
+    model = capi.Model(mf.to_blob(mf.make_b18c384nbt(num_blocks=2)))
+    h = capi.Handle(model, 37, precision=capi.PRECISION_FP16)
+    sp, gl = mf.random_positions(37, seed=77, board_sizes=[19, 13, 9, 19, 7] * 7 + [19, 19])
+    full = h.forward(sp, gl)
+    for n in (1, 3, 7, 32):
+        part = h.forward(sp[:n], gl[:n])
+        for k in full:
+            assert np.array_equal(part[k], full[k][:n]), (n, k)
+    h.close()
+
+
+def test_large_batch_properties():
+    """BASELINE configs[1] size (batch 256): size-independent properties instead of an oracle run --
+    duplicated positions give identical rows, and a symmetry applied to the input permutes policy/ownership."""
+    n = 256
+    model = capi.Model(mf.to_blob(mf.make_b18c384nbt(num_blocks=4)))
+    h = capi.Handle(model, n, precision=capi.PRECISION_FP16)
+    sp, gl = mf.random_positions(n, seed=5)
+    sp[128:] = sp[:128]; gl[128:] = gl[:128]
+    out = h.forward(sp, gl)
+    for k in out:
+        assert np.array_equal(out[k][:128], out[k][128:]), k
+    syms = np.full(n, 5, np.int32)
+    out_s = h.forward(symmetrise_inputs(sp[:8], np.zeros(8, np.int32)), gl[:8], syms[:8])
+    # evaluating the symmetrised position and undoing the symmetry changes only the rounding path
+    assert np.abs(out_s["value"] - out["value"][:8]).max() < 0.25
+    h.close()
+
+
+def test_requests_outside_limits_fail_cleanly():
+    model = capi.Model(mf.to_blob(mf.make_b6c96()))
+    h = capi.Handle(model, 4, precision=capi.PRECISION_FP32)
+    sp, gl = mf.random_positions(5, seed=1)
+    with pytest.raises(capi.KBError):
+        h.forward(sp, gl)  # n > maxBatch
+    with pytest.raises(capi.KBError):
+        h.forward(sp[:2], gl[:2], np.array([0, 9], np.int32))  # bad symmetry index
+    out = h.forward(sp[:4], gl[:4])  # the handle stays usable
+    assert np.all(np.isfinite(out["value"]))
+    h.close()
+    with pytest.raises(capi.KBError):
+        capi.Handle(model, 4, precision=capi.PRECISION_FP32, device=99)  # gpuIdx out of range -> host error
+
+
+# --- the reference's own programs on the B200 backend ---------------------------------------------
+
+needs_bin = pytest.mark.skipif(not os.path.exists(KATAGO_B200), reason="oracle/_ref/katago_b200 not built")
+
+
+@needs_bin
+def test_reference_layer_tests_on_b200_backend():
+    r = subprocess.run([KATAGO_B200, "runnnlayertests"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
+    assert "Test failed" not in r.stdout, r.stdout[-3000:]
+    assert "Tested 28 configurations" in r.stdout, r.stdout[-500:]
+
+
+@needs_bin
+def test_reference_tiny_net_test_on_b200_backend(tmp_path):
+    r = subprocess.run([KATAGO_B200, "runtinynntests", str(tmp_path), "1.0"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
+    assert "Tiny net sanity check complete" in r.stdout + r.stderr

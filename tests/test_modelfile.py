@@ -1,0 +1,76 @@
+"""Host logic: model-file reader/writer, generator and blob serialiser (no GPU)."""
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+from katago_b200 import modelfile as mf
+
+REF_MODELS = "/root/reference/cpp/tests/models"
+REF_TOOL = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref", "modelfile_to_blob")
+
+
+def test_writer_reader_roundtrip_bit_exact():
+    for model in (mf.make_b6c96(), mf.make_b18c384nbt(num_blocks=2), mf.make_transformer(layers=1, d=64, heads=2, head_dim=32, ffn=96)):
+        data = mf.model_file_bytes(model)
+        again = mf.parse_model_bytes(data, True)
+        assert mf.to_blob(again) == mf.to_blob(model)
+
+
+def test_generator_shapes_match_named_configs():
+    m = mf.make_b18c384nbt()
+    kinds = [b["blocks"][0]["kind"] for b in m["trunk"]["blocks"]]
+    assert len(kinds) == 18 and kinds.count("gpool_block") == 5 and kinds[17] == "ordinary_block"
+    assert m["trunk"]["trunkC"] == 384 and m["trunk"]["midC"] == 192 and m["trunk"]["gpoolC"] == 64
+    m = mf.make_b28c512nbt()
+    kinds = [b["blocks"][0]["kind"] for b in m["trunk"]["blocks"]]
+    assert len(kinds) == 28 and kinds.count("gpool_block") == 9
+    m = mf.make_b6c96()
+    assert [b["kind"] for b in m["trunk"]["blocks"]].count("gpool_block") == 1
+
+
+def test_generator_is_deterministic():
+    assert mf.to_blob(mf.make_b6c96(seed=5)) == mf.to_blob(mf.make_b6c96(seed=5))
+    assert mf.to_blob(mf.make_b6c96(seed=5)) != mf.to_blob(mf.make_b6c96(seed=6))
+
+
+def test_reader_rejects_bad_input():
+    data = mf.model_file_bytes(mf.make_b6c96())
+    with pytest.raises(ValueError):
+        mf.parse_model_bytes(data[: len(data) // 2], True)  # truncated
+    with pytest.raises(ValueError):
+        mf.parse_model_bytes(data, False)  # binary blocks read as text
+    bad = bytearray(data)
+    at = bad.find(b"@BIN@") + 5
+    bad[at : at + 4] = np.array([np.nan], "<f4").tobytes()
+    with pytest.raises(ValueError):
+        mf.parse_model_bytes(bytes(bad), True)  # non-finite weight (desc.cpp:21-26)
+
+
+def test_random_positions_scheme():
+    sp, gl = mf.random_positions(64, seed=2000, board_sizes=[19, 13, 9, 19] * 16)
+    assert sp.shape == (64, 19, 19, 22) and gl.shape == (64, 19)
+    assert set(np.unique(sp)) <= {0.0, 1.0}
+    assert sp[1, 13:, :, :].sum() == 0 and sp[1, :, 13:, :].sum() == 0 and sp[1, :13, :13, 0].min() == 1
+    stones = sp[0, :, :, 1] + sp[0, :, :, 2]
+    assert stones.max() <= 1.0 and 0.25 < stones.mean() < 0.55
+    assert np.all(np.abs(gl[:, 5]) <= 0.5)
+
+
+@pytest.mark.skipif(not (os.path.isdir(REF_MODELS) and os.path.exists(REF_TOOL)), reason="needs the reference checkout and oracle/_ref")
+@pytest.mark.parametrize("name", [
+    "g170-b6c96-s175395328-d26788732.bin.gz", "g103-b6c96-s103408384-d26419149.txt.gz",
+    "b7c96h3tfrs-test5-cnorm.bin.gz", "b7c96h6kv3qk32v16tflrs-fson-bnh.bin.gz"])
+def test_python_reader_agrees_with_reference_loader(name, oracle, tmp_path):
+    """Blob from this package's reader vs blob from the reference's own ModelDesc loader, compared through the
+    oracle (the loader rescales some channels, desc.cpp:2631, so weights differ by exactly equivalent factors)."""
+    out = tmp_path / "ref.blob"
+    subprocess.run([REF_TOOL, os.path.join(REF_MODELS, name), str(out)], check=True, stdout=subprocess.DEVNULL)
+    blob_ref = out.read_bytes()
+    blob_py = mf.to_blob(mf.load_model_file(os.path.join(REF_MODELS, name)))
+    a, b = oracle.OracleModel(blob_ref), oracle.OracleModel(blob_py)
+    sp, gl = mf.random_positions(2, seed=5, num_spatial=a.in_c, num_global=a.in_global_c, board_sizes=[19, 11])
+    oa, ob = a.forward(sp, gl), b.forward(sp, gl)
+    for k in oa:
+        assert np.abs(oa[k] - ob[k]).max() <= 1e-4 * max(1.0, np.abs(oa[k]).max()), k

@@ -1,17 +1,21 @@
 // Tensor-core convolution for sm_100a: 1x1 and 3x3 convolutions as implicit GEMM on tcgen05
-// with the accumulator in tensor memory (TMEM), operands staged into shared memory by TMA,
+// with the accumulators in tensor memory (TMEM), operands staged into shared memory by TMA,
 // and the next layer's norm + activation + mask (and the residual add) fused into the epilogue.
 //
 // GEMM view.  D[row][oc] = sum over taps t and input channels ic of A[row + shift(t)][ic] * W[t][oc][ic],
 // where rows are the padded-rows layout of kb_kernels.cuh: because every board line and every
-// board carry one line/column of zeros, shift(t) = dy*RW + dx is a constant row offset, so the
-// A tile of a tap is a plain 2-D TMA box [128 rows][64 channels] at row m0+shift(t) (rows before
-// the tensor start or past its end are filled with zeros by TMA).  K is walked tap by tap in
-// chunks of 64 channels (one 128-byte swizzle atom of fp16/bf16).
+// board carry one line/column of zeros, shift(t) = dy*RW + dx is a constant row offset.
 //
-// CTA = 192 threads: warp 0 issues TMA loads, warp 1 owns TMEM and issues the MMAs, warps 2..5
-// run the epilogue (one TMEM lane quarter each).  A ring of `stages` shared-memory slots is
-// handed back and forth with mbarriers (full: TMA -> MMA, empty: tcgen05.commit -> TMA).
+// A operand ("halo tile").  For one tile of 128 output rows and one chunk of 64 input channels, ONE TMA
+// box of 128 + 2*halo rows is loaded (rows before the tensor start or past its end are zero-filled by
+// TMA).  The nine taps of a 3x3 convolution read the same shared-memory tile through nine shared-memory
+// matrix descriptors whose start address is moved by shift(t) rows; activations therefore cross the
+// L2 -> SM path once per tile instead of nine times.  The weight tile of each (tap, chunk) streams
+// through a ring of slots.
+//
+// Persistent CTAs (one per SM), 320 threads: warp 0 issues TMA loads, warp 1 owns TMEM and issues the
+// MMAs, warps 2..9 run the epilogue (two warps per TMEM lane quarter, alternating 16-column groups).
+// Two accumulators live in TMEM, so the epilogue of tile i overlaps the main loop of tile i+1.
 // Every wait is bounded: on time-out the kernel records a code in the status word and all roles
 // leave through the common exit, which still frees TMEM.
 #include "kb_kernels.cuh"
@@ -118,7 +122,10 @@ __device__ __forceinline__ void tmemLd32(uint32_t taddr, uint32_t (&r)[32]) {
 __device__ __forceinline__ void tmemLdWait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows 128 B apart, 8-row groups
-// 1024 B apart (stride byte offset), descriptor version 1 (Blackwell).
+// 1024 B apart (stride byte offset), descriptor version 1 (Blackwell).  The swizzle is a function of the
+// absolute shared-memory address bits, so a start address moved by whole rows (any multiple of 128 B) or by
+// 32-byte K steps inside the atom addresses the data exactly where TMA put it; the base-offset field stays 0
+// (measured: results match the CUDA-core kernel bit for bit in that configuration only).
 __device__ __forceinline__ uint64_t makeSmemDesc(uint32_t saddr) {
   uint64_t d = 0;
   d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);  // start address, 16-byte units
@@ -168,6 +175,18 @@ template <> struct Pack2<__nv_bfloat16> {
   static __device__ __forceinline__ float2 unpack(uint32_t u) { return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u)); }
 };
 
+
+// 32 lanes x 16 consecutive 32-bit columns -> 16 registers per thread (thread t reads lane base+t).
+__device__ __forceinline__ void tmemLd16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+    "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+      "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+    : "r"(taddr)
+    : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // Kernel
 
@@ -175,45 +194,134 @@ struct ConvTcArgs {
   Geom g;
   Epilogue ep;
   int inC, outC, kY, kX;
-  int BN;        // output channels per CTA (multiple of 16, <= 256)
-  int stages;    // shared-memory ring depth
-  int kChunks;   // inC / 64
+  int BN;          // output channels per tile (multiple of 16, <= 256)
+  int kChunks;     // inC / 64
+  int haloPad;     // rows loaded above the tile (multiple of 8, >= largest upward shift); 0 for 1x1
+  int aRows;       // rows of the A halo tile (TMA box height)
+  int aSlotBytes;  // aRows * 128
+  int bSlotBytes;  // BN * 128
+  int numA, numB;  // ring depths
   uint32_t idesc;
   uint32_t tmemCols;
-  int* status;   // device status word: 0 = ok
-  int debug;     // experiment switch (KB_TC_DEBUG), 0 in production
+  int* status;     // device status word: 0 = ok
 };
 
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;
-constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;  // 16 KiB
+constexpr int TC_THREADS = 320;
+constexpr int TC_EPI_WARPS = 8;
 
 enum { TC_ERR_PRODUCER_TIMEOUT = 101, TC_ERR_MMA_TIMEOUT = 102, TC_ERR_EPILOGUE_TIMEOUT = 103 };
 
+// One group of 16 output channels of one row: bias, residual, raw store, norm+activation store.
+template <typename T, int ACT>
+__device__ __forceinline__ void epilogue16(
+  const uint32_t (&r)[16], const Epilogue& ep, int m, int c, float mk, const float* biasRow, const float* sScale, const float* sBias) {
+  float v[16];
+#pragma unroll
+  for(int j = 0; j < 16; j++) v[j] = __uint_as_float(r[j]);
+  if(biasRow) {
+    const float4* bp = reinterpret_cast<const float4*>(biasRow + c);
+#pragma unroll
+    for(int j = 0; j < 4; j++) {
+      float4 b4 = bp[j];
+      v[4 * j] += b4.x; v[4 * j + 1] += b4.y; v[4 * j + 2] += b4.z; v[4 * j + 3] += b4.w;
+    }
+  }
+  if(ep.residual) {
+    const uint4* rp = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(ep.residual) + (size_t)m * ep.resStride + c);
+    uint4 r0 = rp[0], r1 = rp[1];
+    const uint32_t ru[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+    for(int j = 0; j < 8; j++) {
+      float2 f = Pack2<T>::unpack(ru[j]);
+      v[2 * j] += f.x;
+      v[2 * j + 1] += f.y;
+    }
+  }
+  if(ep.outRaw && c >= ep.rawC0 && c < ep.rawC1) {
+    uint32_t pk[8];
+#pragma unroll
+    for(int j = 0; j < 8; j++) pk[j] = Pack2<T>::pack(v[2 * j], v[2 * j + 1]);
+    uint4* op = reinterpret_cast<uint4*>(reinterpret_cast<T*>(ep.outRaw) + (size_t)m * ep.rawStride + (c - ep.rawC0));
+    op[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    op[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+  }
+  if(ep.outAct && c >= ep.actC0 && c < ep.actC1) {
+    const int ca = c - ep.actC0;
+    uint32_t pk[8];
+    if(mk == 1.0f) {
+      const float4* sp = reinterpret_cast<const float4*>(sScale + ca);
+      const float4* bp = reinterpret_cast<const float4*>(sBias + ca);
+      float o[16];
+#pragma unroll
+      for(int j = 0; j < 4; j++) {
+        const float4 s4 = sp[j], b4 = bp[j];
+        o[4 * j] = fastAct(fmaf(v[4 * j], s4.x, b4.x), ACT);
+        o[4 * j + 1] = fastAct(fmaf(v[4 * j + 1], s4.y, b4.y), ACT);
+        o[4 * j + 2] = fastAct(fmaf(v[4 * j + 2], s4.z, b4.z), ACT);
+        o[4 * j + 3] = fastAct(fmaf(v[4 * j + 3], s4.w, b4.w), ACT);
+      }
+#pragma unroll
+      for(int j = 0; j < 8; j++) pk[j] = Pack2<T>::pack(o[2 * j], o[2 * j + 1]);
+    }
+    else {
+#pragma unroll
+      for(int j = 0; j < 8; j++) pk[j] = 0u;
+    }
+    uint4* op = reinterpret_cast<uint4*>(reinterpret_cast<T*>(ep.outAct) + (size_t)m * ep.actStride + ca);
+    op[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    op[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+  }
+}
+
+// All 16-column groups of one tile that belong to this warp (groups alternate between the two warps of a quarter).
+template <typename T, int ACT>
+__device__ __forceinline__ void epilogueTile(
+  const ConvTcArgs& a, uint32_t tmemAcc, int q, int half, int m, int n0, const float* sScale, const float* sBias) {
+  const Epilogue& ep = a.ep;
+  const float mk = ep.mask ? ep.mask[m] : 1.0f;
+  const int b = min(m / a.g.PB, a.g.n - 1);
+  const float* biasRow = ep.biasNC ? ep.biasNC + (size_t)b * a.outC : nullptr;
+  const int groups = a.BN / 16;
+  for(int gi = half; gi < groups; gi += 2) {
+    uint32_t r[16];
+    tmemLd16(tmemAcc + ((uint32_t)(q * 32) << 16) + (uint32_t)(gi * 16), r);
+    tmemLdWait();
+    epilogue16<T, ACT>(r, ep, m, n0 + gi * 16, mk, biasRow, sScale, sBias);
+  }
+}
+
 template <typename T>
-__global__ void __launch_bounds__(192) convTcKernel(
+__global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
   const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const ConvTcArgs a) {
   extern __shared__ uint8_t smemRaw[];
   // 1024-byte alignment for the 128-byte swizzle pattern
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~(uintptr_t)1023);
-  const int bBytes = a.BN * 128;
-  const int stageBytes = TC_A_BYTES + bBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)a.stages * stageBytes);
-  // bars[0..stages) full, [stages..2*stages) empty, [2*stages] accumulator ready
-  uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 2 * a.stages + 1);
+  uint8_t* smemA = smem;
+  uint8_t* smemB = smemA + (size_t)a.numA * a.aSlotBytes;
+  float* sScale = reinterpret_cast<float*>(smemB + (size_t)a.numB * a.bSlotBytes);
+  float* sBias = sScale + 512;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sBias + 512);
+  // barrier layout: fullA[numA] emptyA[numA] fullB[numB] emptyB[numB] accFull[2] accEmpty[2]
+  uint64_t* fullA = bars;
+  uint64_t* emptyA = fullA + a.numA;
+  uint64_t* fullB = emptyA + a.numA;
+  uint64_t* emptyB = fullB + a.numB;
+  uint64_t* accFull = emptyB + a.numB;
+  uint64_t* accEmpty = accFull + 2;
+  uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(accEmpty + 2);
   volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * TC_BM;
-  const int n0 = blockIdx.y * a.BN;
-  const int numK = a.kY * a.kX * a.kChunks;
+  const int numNTiles = a.outC / a.BN;
+  const int numTiles = (a.g.rowsPad / TC_BM) * numNTiles;
+  const int taps = a.kY * a.kX;
 
   if(threadIdx.x == 0) {
-    for(int s = 0; s < a.stages; s++) {
-      mbarInit(smemU32(&bars[s]), 1);
-      mbarInit(smemU32(&bars[a.stages + s]), 1);
-    }
-    mbarInit(smemU32(&bars[2 * a.stages]), 1);
+    for(int s = 0; s < a.numA; s++) { mbarInit(smemU32(&fullA[s]), 1); mbarInit(smemU32(&emptyA[s]), 1); }
+    for(int s = 0; s < a.numB; s++) { mbarInit(smemU32(&fullB[s]), 1); mbarInit(smemU32(&emptyB[s]), 1); }
+    for(int s = 0; s < 2; s++) { mbarInit(smemU32(&accFull[s]), 1); mbarInit(smemU32(&accEmpty[s]), TC_EPI_WARPS); }
     *abortFlag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -221,6 +329,11 @@ __global__ void __launch_bounds__(192) convTcKernel(
   if(warp == 1) {
     tmemAlloc(smemU32(tmemSlot), a.tmemCols);
     tmemRelinquish();
+  }
+  // next layer's norm parameters: read once per CTA
+  if(a.ep.outAct) {
+    const int nAct = a.ep.actC1 - a.ep.actC0;
+    for(int i = threadIdx.x; i < nAct; i += blockDim.x) { sScale[i] = a.ep.scale[i]; sBias[i] = a.ep.bias[i]; }
   }
   tcFenceBefore();
   __syncthreads();
@@ -230,123 +343,96 @@ __global__ void __launch_bounds__(192) convTcKernel(
   if(warp == 0) {
     // ---------------- TMA producer ----------------
     if(lane == 0) {
-      for(int it = 0; it < numK; it++) {
-        const int s = it % a.stages;
-        const uint32_t ph = (uint32_t)(it / a.stages) & 1u;
-        if(!mbarWait(smemU32(&bars[a.stages + s]), ph ^ 1u, abortFlag)) {
-          if(!*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, TC_ERR_PRODUCER_TIMEOUT); }
-          break;
+      uint32_t ia = 0, ib = 0;
+      bool ok = true;
+      for(int t = blockIdx.x; t < numTiles && ok; t += gridDim.x) {
+        const int m0 = (t / numNTiles) * TC_BM, n0 = (t % numNTiles) * a.BN;
+        for(int kc = 0; kc < a.kChunks && ok; kc++) {
+          const uint32_t sa = ia % a.numA;
+          if(!mbarWait(smemU32(&emptyA[sa]), ((ia / a.numA) & 1u) ^ 1u, abortFlag)) { ok = false; break; }
+          mbarExpectTx(smemU32(&fullA[sa]), (uint32_t)a.aSlotBytes);
+          tmaLoad2d(smemU32(smemA + (size_t)sa * a.aSlotBytes), &tmA, kc * TC_BK, m0 - a.haloPad, smemU32(&fullA[sa]));
+          ia++;
+          for(int tap = 0; tap < taps; tap++) {
+            const uint32_t sb = ib % a.numB;
+            if(!mbarWait(smemU32(&emptyB[sb]), ((ib / a.numB) & 1u) ^ 1u, abortFlag)) { ok = false; break; }
+            mbarExpectTx(smemU32(&fullB[sb]), (uint32_t)a.bSlotBytes);
+            tmaLoad2d(smemU32(smemB + (size_t)sb * a.bSlotBytes), &tmB, kc * TC_BK, tap * a.outC + n0, smemU32(&fullB[sb]));
+            ib++;
+          }
         }
-        const int tap = it / a.kChunks, kc = it - tap * a.kChunks;
-        const int dy = tap / a.kX - a.kY / 2, dx = tap % a.kX - a.kX / 2;
-        const uint32_t full = smemU32(&bars[s]);
-        mbarExpectTx(full, (uint32_t)stageBytes);
-        uint8_t* sA = smem + (size_t)s * stageBytes;
-        tmaLoad2d(smemU32(sA), &tmA, kc * TC_BK, m0 + dy * a.g.RW + dx, full);
-        tmaLoad2d(smemU32(sA + TC_A_BYTES), &tmB, kc * TC_BK, tap * a.outC + n0, full);
       }
+      if(!ok && !*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, TC_ERR_PRODUCER_TIMEOUT); }
     }
   }
   else if(warp == 1) {
     // ---------------- MMA issuer ----------------
     if(lane == 0) {
+      uint32_t ia = 0, ib = 0, it = 0;
       bool ok = true;
-      for(int it = 0; it < numK; it++) {
-        const int s = it % a.stages;
-        const uint32_t ph = (uint32_t)(it / a.stages) & 1u;
-        if(!mbarWait(smemU32(&bars[s]), ph, abortFlag)) {
-          if(!*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, TC_ERR_MMA_TIMEOUT); }
-          ok = false;
-          break;
-        }
+      for(int t = blockIdx.x; t < numTiles && ok; t += gridDim.x, it++) {
+        const uint32_t buf = it & 1u;
+        // wait until the epilogue has drained this accumulator (two tiles ago)
+        if(!mbarWait(smemU32(&accEmpty[buf]), ((it >> 1) & 1u) ^ 1u, abortFlag)) { ok = false; break; }
         tcFenceAfter();
-        const uint32_t sA = smemU32(smem + (size_t)s * stageBytes);
-        const uint32_t sB = sA + TC_A_BYTES;
+        const uint32_t dTmem = tmemBase + buf * (uint32_t)a.BN;
+        uint32_t first = 1;
+        for(int kc = 0; kc < a.kChunks && ok; kc++) {
+          const uint32_t sa = ia % a.numA;
+          if(!mbarWait(smemU32(&fullA[sa]), (ia / a.numA) & 1u, abortFlag)) { ok = false; break; }
+          const uint32_t aBase = smemU32(smemA + (size_t)sa * a.aSlotBytes);
+          for(int tap = 0; tap < taps; tap++) {
+            const uint32_t sb = ib % a.numB;
+            if(!mbarWait(smemU32(&fullB[sb]), (ib / a.numB) & 1u, abortFlag)) { ok = false; break; }
+            tcFenceAfter();
+            const int dy = tap / a.kX - a.kY / 2, dx = tap % a.kX - a.kX / 2;
+            const uint32_t aStart = aBase + (uint32_t)(a.haloPad + dy * a.g.RW + dx) * 128u;
+            const uint32_t bStart = smemU32(smemB + (size_t)sb * a.bSlotBytes);
 #pragma unroll
-        for(int k = 0; k < TC_BK / 16; k++) {
-          // advancing K by 16 elements = 32 bytes inside the 128-byte swizzle atom
-          umma(tmemBase, makeSmemDesc(sA + k * 32), makeSmemDesc(sB + k * 32), a.idesc, (it > 0 || k > 0) ? 1u : 0u);
+            for(int k = 0; k < TC_BK / 16; k++) {
+              // advancing K by 16 elements = 32 bytes inside the 128-byte swizzle atom
+              umma(dTmem, makeSmemDesc(aStart + k * 32), makeSmemDesc(bStart + k * 32), a.idesc, first ? 0u : 1u);
+              first = 0;
+            }
+            ummaCommit(smemU32(&emptyB[sb]));  // frees the weight slot once these MMAs have read it
+            ib++;
+          }
+          ummaCommit(smemU32(&emptyA[sa]));
+          ia++;
         }
-        ummaCommit(smemU32(&bars[a.stages + s]));  // frees the slot once these MMAs have read it
+        if(ok) ummaCommit(smemU32(&accFull[buf]));
       }
-      if(ok) ummaCommit(smemU32(&bars[2 * a.stages]));
+      if(!ok && !*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, TC_ERR_MMA_TIMEOUT); }
     }
   }
   else {
-    // ---------------- Epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----------------
+    // ---------------- Epilogue: warps 2..9; TMEM lane quarter = warp % 4 ----------------
     const int q = warp & 3;
-    const int m = m0 + q * 32 + lane;
-    bool ok = mbarWait(smemU32(&bars[2 * a.stages]), 0u, abortFlag);
-    ok = __all_sync(0xffffffffu, ok);
-    if(!ok) {
-      if(lane == 0 && !*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, TC_ERR_EPILOGUE_TIMEOUT); }
-    }
-    else {
-      tcFenceAfter();
-      const Epilogue& ep = a.ep;
-      const float mk = ep.mask ? ep.mask[m] : 1.0f;
-      const int b = min(m / a.g.PB, a.g.n - 1);
-      const float* biasRow = ep.biasNC ? ep.biasNC + (size_t)b * a.outC : nullptr;
-      for(int cb = 0; cb < a.BN; cb += 32) {
-        uint32_t r[32];
-        tmemLd32(tmemBase + ((uint32_t)(q * 32) << 16) + (uint32_t)cb, r);
-        tmemLdWait();
-        const int cw = min(32, a.BN - cb);  // BN is a multiple of 16: 32 or 16 valid columns
-#pragma unroll
-        for(int half = 0; half < 2; half++) {
-          if(half * 16 >= cw) break;
-          const int c = n0 + cb + half * 16;  // first global output channel of this group of 16
-          float v[16];
-#pragma unroll
-          for(int j = 0; j < 16; j++) v[j] = __uint_as_float(r[half * 16 + j]);
-          if(biasRow) {
-#pragma unroll
-            for(int j = 0; j < 16; j++) v[j] += biasRow[c + j];
-          }
-          if(ep.residual) {
-            const uint4* rp = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(ep.residual) + (size_t)m * ep.resStride + c);
-            uint4 r0 = rp[0], r1 = rp[1];
-            const uint32_t ru[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
-#pragma unroll
-            for(int j = 0; j < 8; j++) {
-              float2 f = Pack2<T>::unpack(ru[j]);
-              v[2 * j] += f.x;
-              v[2 * j + 1] += f.y;
-            }
-          }
-          if(ep.outRaw && c >= ep.rawC0 && c < ep.rawC1) {
-            uint32_t pk[8];
-#pragma unroll
-            for(int j = 0; j < 8; j++) pk[j] = Pack2<T>::pack(v[2 * j], v[2 * j + 1]);
-            uint4* op = reinterpret_cast<uint4*>(reinterpret_cast<T*>(ep.outRaw) + (size_t)m * ep.rawStride + (c - ep.rawC0));
-            op[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            op[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-          }
-          if(ep.outAct && c >= ep.actC0 && c < ep.actC1) {
-            const int ca = c - ep.actC0;
-            uint32_t pk[8];
-            if(mk == 1.0f) {
-              float o[16];
-#pragma unroll
-              for(int j = 0; j < 16; j++) {
-                float sc = (a.debug == 2) ? 1.25f : ep.scale[ca + j];
-                float bi = (a.debug == 2) ? 0.1f : ep.bias[ca + j];
-                float t = fmaf(v[j], sc, bi);
-                o[j] = (a.debug == 1) ? t : fastAct(t, ep.act);
-              }
-#pragma unroll
-              for(int j = 0; j < 8; j++) pk[j] = Pack2<T>::pack(o[2 * j], o[2 * j + 1]);
-            }
-            else {
-#pragma unroll
-              for(int j = 0; j < 8; j++) pk[j] = 0u;
-            }
-            uint4* op = reinterpret_cast<uint4*>(reinterpret_cast<T*>(ep.outAct) + (size_t)m * ep.actStride + ca);
-            op[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            op[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-          }
-        }
+    const int half = (warp - 2) >> 2;
+    uint32_t it = 0;
+    for(int t = blockIdx.x; t < numTiles; t += gridDim.x, it++) {
+      const uint32_t buf = it & 1u;
+      const int m0 = (t / numNTiles) * TC_BM, n0 = (t % numNTiles) * a.BN;
+      bool ok = mbarWait(smemU32(&accFull[buf]), (it >> 1) & 1u, abortFlag);
+      ok = __all_sync(0xffffffffu, ok);
+      if(!ok) {
+        if(lane == 0 && !*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, TC_ERR_EPILOGUE_TIMEOUT); }
+        break;
       }
+      tcFenceAfter();
+      const uint32_t acc = tmemBase + buf * (uint32_t)a.BN;
+      const int m = m0 + q * 32 + lane;
+      switch(a.ep.act) {
+        case KB_ACT_RELU: epilogueTile<T, KB_ACT_RELU>(a, acc, q, half, m, n0, sScale, sBias); break;
+        case KB_ACT_MISH: epilogueTile<T, KB_ACT_MISH>(a, acc, q, half, m, n0, sScale, sBias); break;
+        case KB_ACT_SILU: epilogueTile<T, KB_ACT_SILU>(a, acc, q, half, m, n0, sScale, sBias); break;
+        case KB_ACT_MISH_SCALE8: epilogueTile<T, KB_ACT_MISH_SCALE8>(a, acc, q, half, m, n0, sScale, sBias); break;
+        default: epilogueTile<T, KB_ACT_IDENTITY>(a, acc, q, half, m, n0, sScale, sBias); break;
+      }
+      // all TMEM reads of this warp are complete (tcgen05.wait::ld inside): hand the accumulator back
+      tcFenceBefore();
+      __syncwarp();
+      if(lane == 0) mbarArrive(smemU32(&accEmpty[buf]));
     }
   }
 
@@ -388,9 +474,10 @@ static EncodeTiledFn getEncodeTiled() {
 struct ConvTcPlan {
   CUtensorMap tmA, tmB;
   int dt, inC, outC, kY, kX, X, Y;
-  int BN, stages, kChunks;
+  int BN, kChunks, haloPad, aRows, aSlotBytes, bSlotBytes, numA, numB;
   uint32_t idesc, tmemCols;
   size_t smemBytes;
+  int numSMs;
 };
 
 static int pickBN(int outC) {
@@ -403,7 +490,7 @@ static int pickBN(int outC) {
 bool convTcEligible(int dt, int inC, int outC, int kY, int kX) {
   if(dt != DT_F16 && dt != DT_BF16) return false;
   if(!((kY == 1 && kX == 1) || (kY == 3 && kX == 3))) return false;
-  if(inC % TC_BK != 0 || outC % 16 != 0) return false;
+  if(inC % TC_BK != 0 || outC % 16 != 0 || outC > 512) return false;
   return pickBN(outC) >= 16;
 }
 
@@ -429,28 +516,33 @@ ConvTcPlan* convTcCreate(
   p->dt = dt; p->inC = inC; p->outC = outC; p->kY = kY; p->kX = kX; p->X = X; p->Y = Y;
   p->BN = pickBN(outC);
   p->kChunks = inC / TC_BK;
-  const int stageBytes = TC_A_BYTES + p->BN * 128;
-  // Two CTAs share an SM (each <= ~110 KiB of shared memory, <= 256 TMEM columns): while one runs its epilogue the
-  // other keeps the tensor pipe busy.
-  int stages = (108 * 1024) / stageBytes;
-  if(stages < 2) stages = 2;
-  if(const char* e = getenv("KB_TC_STAGES")) { int v = atoi(e); if(v >= 2 && v <= 12) stages = v; }
-  const int numK = kY * kX * p->kChunks;
-  if(stages > numK) stages = numK;
-  if(stages > 8) stages = 8;
-  if(stages < 1) stages = 1;
-  p->stages = stages;
-  p->smemBytes = (size_t)stages * stageBytes + (2 * stages + 1) * 8 + 16 + 1024;
+  const int maxShift = (kY == 3) ? (X + 1) + 1 : 0;  // RW + 1 rows up or down
+  p->haloPad = (maxShift + 7) / 8 * 8;
+  p->aRows = (p->haloPad + TC_BM + maxShift + 7) / 8 * 8;
+  if(p->aRows > 256) { delete p; return nullptr; }
+  p->aSlotBytes = p->aRows * 128;
+  p->bSlotBytes = p->BN * 128;
+  p->numA = 2;
+  const int fixedBytes = 2 * 512 * 4 + 64 * 8 + 64 + 1024;
+  int numB = (225 * 1024 - fixedBytes - p->numA * p->aSlotBytes) / p->bSlotBytes;
+  if(const char* e = getenv("KB_TC_NUMB")) { int v = atoi(e); if(v >= 1 && v <= 16) numB = v < numB ? v : numB; }
+  if(numB > 12) numB = 12;
+  if(numB < 2) { delete p; return nullptr; }
+  p->numB = numB;
+  p->smemBytes = (size_t)p->numA * p->aSlotBytes + (size_t)p->numB * p->bSlotBytes + fixedBytes;
   p->tmemCols = 32;
-  while((int)p->tmemCols < p->BN) p->tmemCols *= 2;
+  while((int)p->tmemCols < 2 * p->BN) p->tmemCols *= 2;
   const uint32_t fmt = dt == DT_F16 ? 0u : 1u;
   // instruction descriptor: D=f32, A/B format, both K-major, N>>3 at bit 17, M>>4 at bit 24
   p->idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(p->BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-  bool ok = encode2d(&p->tmA, dt, in, (uint64_t)inC, (uint64_t)rowsPadMax, (uint64_t)inStride * 2, TC_BK, TC_BM) &&
+  bool ok = encode2d(&p->tmA, dt, in, (uint64_t)inC, (uint64_t)rowsPadMax, (uint64_t)inStride * 2, TC_BK, (uint32_t)p->aRows) &&
             encode2d(&p->tmB, dt, w, (uint64_t)inC, (uint64_t)kY * kX * outC, (uint64_t)inC * 2, TC_BK, (uint32_t)p->BN);
   if(!ok) { delete p; return nullptr; }
   cudaError_t e1 = cudaFuncSetAttribute(convTcKernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
   cudaError_t e2 = cudaFuncSetAttribute(convTcKernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  int dev = 0, sms = 148;
+  if(cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  p->numSMs = sms;
   if(e1 != cudaSuccess || e2 != cudaSuccess) { delete p; return nullptr; }
   return p;
 }
@@ -460,19 +552,21 @@ void convTcDestroy(ConvTcPlan* p) { delete p; }
 cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epilogue& ep, int* statusWord) {
   // vector accesses in the epilogue need 16-byte aligned rows and 16-channel aligned ranges
   if(ep.outRaw && ((ep.rawStride % 8) || (ep.rawC0 % 16) || (ep.rawC1 % 16))) return cudaErrorInvalidValue;
-  if(ep.outAct && ((ep.actStride % 8) || (ep.actC0 % 16) || (ep.actC1 % 16))) return cudaErrorInvalidValue;
+  if(ep.outAct && ((ep.actStride % 8) || (ep.actC0 % 16) || (ep.actC1 % 16) || (ep.actC1 - ep.actC0) > 512)) return cudaErrorInvalidValue;
   if(ep.residual && (ep.resStride % 8)) return cudaErrorInvalidValue;
   ConvTcArgs a;
   a.g = g; a.ep = ep;
   a.inC = p->inC; a.outC = p->outC; a.kY = p->kY; a.kX = p->kX;
-  a.BN = p->BN; a.stages = p->stages; a.kChunks = p->kChunks; a.idesc = p->idesc; a.tmemCols = p->tmemCols;
+  a.BN = p->BN; a.kChunks = p->kChunks; a.haloPad = p->haloPad; a.aRows = p->aRows;
+  a.aSlotBytes = p->aSlotBytes; a.bSlotBytes = p->bSlotBytes; a.numA = p->numA; a.numB = p->numB;
+  a.idesc = p->idesc; a.tmemCols = p->tmemCols;
   a.status = statusWord;
-  { const char* e = getenv("KB_TC_DEBUG"); a.debug = e ? atoi(e) : 0; }
-  dim3 grid(g.rowsPad / TC_BM, p->outC / p->BN);
+  const int numTiles = (g.rowsPad / TC_BM) * (p->outC / p->BN);
+  const int grid = numTiles < p->numSMs ? numTiles : p->numSMs;
   if(p->dt == DT_F16)
-    convTcKernel<__half><<<grid, 192, p->smemBytes, st>>>(p->tmA, p->tmB, a);
+    convTcKernel<__half><<<grid, TC_THREADS, p->smemBytes, st>>>(p->tmA, p->tmB, a);
   else
-    convTcKernel<__nv_bfloat16><<<grid, 192, p->smemBytes, st>>>(p->tmA, p->tmB, a);
+    convTcKernel<__nv_bfloat16><<<grid, TC_THREADS, p->smemBytes, st>>>(p->tmA, p->tmB, a);
   return cudaGetLastError();
 }
 

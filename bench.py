@@ -196,13 +196,12 @@ def run_b200(args, rank, world, local, pg):
 
     # ---- device-resident throughput ----
     h.upload(pin_sp.array, pin_gl.array)
-    h.time_forward_steps(BATCH, max(args.warmup, 3), flush)
     sampler = ClockSampler(device)
+    sampler.start()  # started before the warm-up: nvidia-smi needs ~0.1 s to deliver its first sample
+    h.time_forward_steps(BATCH, max(args.warmup, 3), flush)
     _barrier_sync(pg)
-    sampler.start()
     ms_each = h.time_forward_steps(BATCH, args.steps, flush)
     _barrier_sync(pg)
-    clocks = sampler.stop()
     ms_total = _max_over_ranks(pg, sum(ms_each))
     value = world * BATCH * args.steps / (ms_total * 1e-3)
 
@@ -215,6 +214,7 @@ def run_b200(args, rank, world, local, pg):
         h.forward(pin_sp.array, pin_gl.array, pin_sym.array, out=out_arrays)
     _barrier_sync(pg)
     e2e_s = _max_over_ranks(pg, time.perf_counter() - t0)
+    clocks = sampler.stop()
     e2e = world * BATCH * args.steps / e2e_s
     h2d = pin_sp.nbytes + pin_gl.nbytes + pin_sym.nbytes
     d2h = sum(v.nbytes for v in outs.values())

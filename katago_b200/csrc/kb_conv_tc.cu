@@ -80,6 +80,15 @@ __device__ __forceinline__ void tmaLoad2d(uint32_t dst, const CUtensorMap* tmap,
     : "memory");
 }
 
+// shared -> global tile store (asynchronous, tracked by the issuing thread's bulk groups)
+__device__ __forceinline__ void tmaStore2d(const CUtensorMap* tmap, uint32_t src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap), "r"(src), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void bulkCommit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulkWaitRead0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulkWaitAll() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fenceProxyAsync() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 __device__ __forceinline__ void tmemAlloc(uint32_t dstSmem, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dstSmem), "r"(cols) : "memory");
 }
@@ -99,6 +108,18 @@ __device__ __forceinline__ void umma(uint32_t dTmem, uint64_t descA, uint64_t de
     "setp.ne.b32 p, %4, 0;\n\t"
     "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
     ::"r"(dTmem), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
+    : "memory");
+}
+// Same, with the two shared-memory descriptors given as their low words (start address + leading offset) and the
+// high word both share (stride offset, version, swizzle mode); keeps the issuing thread's instruction count low.
+__device__ __forceinline__ void ummaLoHi(uint32_t dTmem, uint32_t aLo, uint32_t bLo, uint32_t descHi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+    "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+    "mov.b64 da, {%1, %3};\n\t"
+    "mov.b64 db, {%2, %3};\n\t"
+    "setp.ne.b32 p, %5, 0;\n\t"
+    "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+    ::"r"(dTmem), "r"(aLo), "r"(bLo), "r"(descHi), "r"(idesc), "r"(accumulate)
     : "memory");
 }
 // mbarrier arrives once all MMAs issued so far by this thread have completed.
@@ -203,6 +224,7 @@ struct ConvTcArgs {
   int numA, numB;  // ring depths
   uint32_t idesc;
   uint32_t tmemCols;
+  int tmaEpi;      // 1: outputs and residual travel through shared memory and TMA (64-channel aligned ranges)
   int* status;     // device status word: 0 = ok
 };
 
@@ -213,10 +235,13 @@ constexpr int TC_EPI_WARPS = 8;
 
 enum { TC_ERR_PRODUCER_TIMEOUT = 101, TC_ERR_MMA_TIMEOUT = 102, TC_ERR_EPILOGUE_TIMEOUT = 103 };
 
-// One group of 16 output channels of one row: bias, residual, raw store, norm+activation store.
+constexpr int TC_MAX_GROUPS = 8;  // 16-column groups per warp and tile: BN/32 <= 8
+
+// One group of 16 output channels of one row: bias, residual (already in registers), raw store, norm+activation store.
 template <typename T, int ACT>
 __device__ __forceinline__ void epilogue16(
-  const uint32_t (&r)[16], const Epilogue& ep, int m, int c, float mk, const float* biasRow, const float* sScale, const float* sBias) {
+  const uint32_t (&r)[16], const Epilogue& ep, bool hasRes, const uint4& res0, const uint4& res1, int m, int c, float mk,
+  const float* biasRow, const float* sScale, const float* sBias) {
   float v[16];
 #pragma unroll
   for(int j = 0; j < 16; j++) v[j] = __uint_as_float(r[j]);
@@ -228,10 +253,8 @@ __device__ __forceinline__ void epilogue16(
       v[4 * j] += b4.x; v[4 * j + 1] += b4.y; v[4 * j + 2] += b4.z; v[4 * j + 3] += b4.w;
     }
   }
-  if(ep.residual) {
-    const uint4* rp = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(ep.residual) + (size_t)m * ep.resStride + c);
-    uint4 r0 = rp[0], r1 = rp[1];
-    const uint32_t ru[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+  if(hasRes) {
+    const uint32_t ru[8] = {res0.x, res0.y, res0.z, res0.w, res1.x, res1.y, res1.z, res1.w};
 #pragma unroll
     for(int j = 0; j < 8; j++) {
       float2 f = Pack2<T>::unpack(ru[j]);
@@ -276,31 +299,156 @@ __device__ __forceinline__ void epilogue16(
 }
 
 // All 16-column groups of one tile that belong to this warp (groups alternate between the two warps of a quarter).
+// res[] holds this row's residual values for those groups, fetched before the accumulator was ready.
 template <typename T, int ACT>
 __device__ __forceinline__ void epilogueTile(
-  const ConvTcArgs& a, uint32_t tmemAcc, int q, int half, int m, int n0, const float* sScale, const float* sBias) {
+  const ConvTcArgs& a, uint32_t tmemAcc, int q, int half, int m, int n0, float mk, const uint4 (&res)[2 * TC_MAX_GROUPS],
+  const float* sScale, const float* sBias) {
   const Epilogue& ep = a.ep;
-  const float mk = ep.mask ? ep.mask[m] : 1.0f;
   const int b = min(m / a.g.PB, a.g.n - 1);
   const float* biasRow = ep.biasNC ? ep.biasNC + (size_t)b * a.outC : nullptr;
   const int groups = a.BN / 16;
-  for(int gi = half; gi < groups; gi += 2) {
-    uint32_t r[16];
-    tmemLd16(tmemAcc + ((uint32_t)(q * 32) << 16) + (uint32_t)(gi * 16), r);
-    tmemLdWait();
-    epilogue16<T, ACT>(r, ep, m, n0 + gi * 16, mk, biasRow, sScale, sBias);
+  const bool hasRes = ep.residual != nullptr;
+#pragma unroll
+  for(int j = 0; j < TC_MAX_GROUPS; j++) {
+    const int gi = half + 2 * j;
+    if(gi < groups) {
+      uint32_t r[16];
+      tmemLd16(tmemAcc + ((uint32_t)(q * 32) << 16) + (uint32_t)(gi * 16), r);
+      tmemLdWait();
+      epilogue16<T, ACT>(r, ep, hasRes, res[2 * j], res[2 * j + 1], m, n0 + gi * 16, mk, biasRow, sScale, sBias);
+    }
   }
+}
+
+constexpr int TC_EPI_BLOCK_BYTES = TC_BM * 128;  // one staging block: 128 rows x 64 channels, 128-byte swizzled
+constexpr int TC_MAX_RES_BLOCKS = 3;
+
+struct EpiTma {
+  uint8_t* sR;          // residual / raw staging blocks, one per 64-channel block of the tile
+  uint8_t* sO;          // two blocks for the activated output
+  uint64_t* resFull;    // residual block landed (TMA)
+  uint64_t* epiBar;     // all 256 epilogue threads arrived
+  uint32_t epiPhase;
+  uint32_t oCount;
+};
+
+// Epilogue of one tile with shared-memory staging.  Each thread owns one row and, per 64-channel block, the
+// 32 channels of its half (64 contiguous bytes of the swizzled staging row).  The residual block was fetched by
+// TMA; the updated residual stream overwrites it in place and goes back out by TMA; the activated tensor is
+// staged in a second buffer.  Global memory therefore only sees whole 128-byte rows written by the TMA engine.
+template <typename T, int ACT>
+__device__ __forceinline__ bool epilogueTileTma(
+  const ConvTcArgs& a, const CUtensorMap* tmRaw, const CUtensorMap* tmAct, uint32_t tmemAcc, int q, int half, int lane, bool isE,
+  int m0, int n0, float mk, const float* biasRow, EpiTma& es, uint32_t tileParity, volatile int* abortFlag,
+  const float* sScale, const float* sBias) {
+  const Epilogue& ep = a.ep;
+  const bool hasRes = ep.residual != nullptr;
+  const int row = q * 32 + lane;
+  const int blocks = a.BN / 64;
+  for(int cb = 0; cb < blocks; cb++) {
+    uint32_t r[32];
+    tmemLd32(tmemAcc + ((uint32_t)(q * 32) << 16) + (uint32_t)(cb * 64 + half * 32), r);
+    if(hasRes) {
+      if(!mbarWait(smemU32(&es.resFull[cb]), tileParity, abortFlag)) return false;
+    }
+    tmemLdWait();
+    const int c = n0 + cb * 64 + half * 32;  // first output channel of this thread's 32
+    float v[32];
+#pragma unroll
+    for(int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+    if(biasRow) {
+      const float4* bp = reinterpret_cast<const float4*>(biasRow + c);
+#pragma unroll
+      for(int j = 0; j < 8; j++) {
+        float4 b4 = bp[j];
+        v[4 * j] += b4.x; v[4 * j + 1] += b4.y; v[4 * j + 2] += b4.z; v[4 * j + 3] += b4.w;
+      }
+    }
+    uint8_t* rRow = es.sR + (size_t)cb * TC_EPI_BLOCK_BYTES + row * 128;
+    const int sw = row & 7;
+    if(hasRes) {
+#pragma unroll
+      for(int jj = 0; jj < 4; jj++) {
+        const uint4 x = *reinterpret_cast<const uint4*>(rRow + (((half * 4 + jj) ^ sw) << 4));
+        const uint32_t xu[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+        for(int k = 0; k < 4; k++) {
+          float2 f = Pack2<T>::unpack(xu[k]);
+          v[8 * jj + 2 * k] += f.x;
+          v[8 * jj + 2 * k + 1] += f.y;
+        }
+      }
+    }
+    const bool doRaw = ep.outRaw && c >= ep.rawC0 && c < ep.rawC1;
+    const bool doAct = ep.outAct && c >= ep.actC0 && c < ep.actC1;
+    if(doRaw) {
+#pragma unroll
+      for(int jj = 0; jj < 4; jj++) {
+        uint4 o;
+        o.x = Pack2<T>::pack(v[8 * jj], v[8 * jj + 1]); o.y = Pack2<T>::pack(v[8 * jj + 2], v[8 * jj + 3]);
+        o.z = Pack2<T>::pack(v[8 * jj + 4], v[8 * jj + 5]); o.w = Pack2<T>::pack(v[8 * jj + 6], v[8 * jj + 7]);
+        *reinterpret_cast<uint4*>(rRow + (((half * 4 + jj) ^ sw) << 4)) = o;
+      }
+    }
+    uint8_t* oBlock = es.sO + (size_t)(es.oCount & 1u) * TC_EPI_BLOCK_BYTES;
+    if(doAct) {
+      uint8_t* oRow = oBlock + row * 128;
+      const int ca = c - ep.actC0;
+      if(mk == 1.0f) {
+        const float4* sp = reinterpret_cast<const float4*>(sScale + ca);
+        const float4* bp = reinterpret_cast<const float4*>(sBias + ca);
+#pragma unroll
+        for(int jj = 0; jj < 4; jj++) {
+          float o8[8];
+#pragma unroll
+          for(int k = 0; k < 2; k++) {
+            const float4 s4 = sp[2 * jj + k], b4 = bp[2 * jj + k];
+            o8[4 * k] = fastAct(fmaf(v[8 * jj + 4 * k], s4.x, b4.x), ACT);
+            o8[4 * k + 1] = fastAct(fmaf(v[8 * jj + 4 * k + 1], s4.y, b4.y), ACT);
+            o8[4 * k + 2] = fastAct(fmaf(v[8 * jj + 4 * k + 2], s4.z, b4.z), ACT);
+            o8[4 * k + 3] = fastAct(fmaf(v[8 * jj + 4 * k + 3], s4.w, b4.w), ACT);
+          }
+          uint4 o;
+          o.x = Pack2<T>::pack(o8[0], o8[1]); o.y = Pack2<T>::pack(o8[2], o8[3]);
+          o.z = Pack2<T>::pack(o8[4], o8[5]); o.w = Pack2<T>::pack(o8[6], o8[7]);
+          *reinterpret_cast<uint4*>(oRow + (((half * 4 + jj) ^ sw) << 4)) = o;
+        }
+      }
+      else {
+#pragma unroll
+        for(int jj = 0; jj < 4; jj++) *reinterpret_cast<uint4*>(oRow + (((half * 4 + jj) ^ sw) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    // make the generic-proxy writes visible to the TMA engine, then meet the other epilogue threads
+    fenceProxyAsync();
+    if(isE) bulkWaitRead0();  // every earlier store has finished reading its staging block
+    mbarArrive(smemU32(es.epiBar));
+    if(!mbarWait(smemU32(es.epiBar), es.epiPhase, abortFlag)) return false;
+    es.epiPhase ^= 1u;
+    if(isE) {
+      if(doRaw) tmaStore2d(tmRaw, smemU32(es.sR + (size_t)cb * TC_EPI_BLOCK_BYTES), n0 + cb * 64 - ep.rawC0, m0);
+      if(doAct) tmaStore2d(tmAct, smemU32(oBlock), n0 + cb * 64 - ep.actC0, m0);
+      bulkCommit();
+    }
+    if(doAct) es.oCount++;
+  }
+  return true;
 }
 
 template <typename T>
 __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
-  const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const ConvTcArgs a) {
+  const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmRes,
+  const __grid_constant__ CUtensorMap tmRaw, const __grid_constant__ CUtensorMap tmAct, const ConvTcArgs a) {
   extern __shared__ uint8_t smemRaw[];
   // 1024-byte alignment for the 128-byte swizzle pattern
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~(uintptr_t)1023);
   uint8_t* smemA = smem;
   uint8_t* smemB = smemA + (size_t)a.numA * a.aSlotBytes;
-  float* sScale = reinterpret_cast<float*>(smemB + (size_t)a.numB * a.bSlotBytes);
+  uint8_t* smemR = smemB + (size_t)a.numB * a.bSlotBytes;  // epilogue staging (TMA epilogue only)
+  const int epiBlocks = a.tmaEpi ? (a.BN / 64 + 2) : 0;
+  uint8_t* smemO = smemR + (size_t)(a.BN / 64) * TC_EPI_BLOCK_BYTES;
+  float* sScale = reinterpret_cast<float*>(smemR + (size_t)epiBlocks * TC_EPI_BLOCK_BYTES);
   float* sBias = sScale + 512;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sBias + 512);
   // barrier layout: fullA[numA] emptyA[numA] fullB[numB] emptyB[numB] accFull[2] accEmpty[2]
@@ -310,7 +458,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
   uint64_t* emptyB = fullB + a.numB;
   uint64_t* accFull = emptyB + a.numB;
   uint64_t* accEmpty = accFull + 2;
-  uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(accEmpty + 2);
+  uint64_t* resFull = accEmpty + 2;   // [TC_MAX_RES_BLOCKS]
+  uint64_t* epiBar = resFull + TC_MAX_RES_BLOCKS;
+  uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(epiBar + 1);
   volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -322,6 +472,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
     for(int s = 0; s < a.numA; s++) { mbarInit(smemU32(&fullA[s]), 1); mbarInit(smemU32(&emptyA[s]), 1); }
     for(int s = 0; s < a.numB; s++) { mbarInit(smemU32(&fullB[s]), 1); mbarInit(smemU32(&emptyB[s]), 1); }
     for(int s = 0; s < 2; s++) { mbarInit(smemU32(&accFull[s]), 1); mbarInit(smemU32(&accEmpty[s]), TC_EPI_WARPS); }
+    for(int s = 0; s < TC_MAX_RES_BLOCKS; s++) mbarInit(smemU32(&resFull[s]), 1);
+    mbarInit(smemU32(epiBar), TC_EPI_WARPS * 32);
     *abortFlag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -343,22 +495,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
   if(warp == 0) {
     // ---------------- TMA producer ----------------
     if(lane == 0) {
-      uint32_t ia = 0, ib = 0;
+      uint32_t sa = 0, phA = 0, sb = 0, phB = 0;
       bool ok = true;
       for(int t = blockIdx.x; t < numTiles && ok; t += gridDim.x) {
         const int m0 = (t / numNTiles) * TC_BM, n0 = (t % numNTiles) * a.BN;
         for(int kc = 0; kc < a.kChunks && ok; kc++) {
-          const uint32_t sa = ia % a.numA;
-          if(!mbarWait(smemU32(&emptyA[sa]), ((ia / a.numA) & 1u) ^ 1u, abortFlag)) { ok = false; break; }
+          if(!mbarWait(smemU32(&emptyA[sa]), phA ^ 1u, abortFlag)) { ok = false; break; }
           mbarExpectTx(smemU32(&fullA[sa]), (uint32_t)a.aSlotBytes);
           tmaLoad2d(smemU32(smemA + (size_t)sa * a.aSlotBytes), &tmA, kc * TC_BK, m0 - a.haloPad, smemU32(&fullA[sa]));
-          ia++;
+          if(++sa == (uint32_t)a.numA) { sa = 0; phA ^= 1u; }
           for(int tap = 0; tap < taps; tap++) {
-            const uint32_t sb = ib % a.numB;
-            if(!mbarWait(smemU32(&emptyB[sb]), ((ib / a.numB) & 1u) ^ 1u, abortFlag)) { ok = false; break; }
+            if(!mbarWait(smemU32(&emptyB[sb]), phB ^ 1u, abortFlag)) { ok = false; break; }
             mbarExpectTx(smemU32(&fullB[sb]), (uint32_t)a.bSlotBytes);
             tmaLoad2d(smemU32(smemB + (size_t)sb * a.bSlotBytes), &tmB, kc * TC_BK, tap * a.outC + n0, smemU32(&fullB[sb]));
-            ib++;
+            if(++sb == (uint32_t)a.numB) { sb = 0; phB ^= 1u; }
           }
         }
       }
@@ -367,8 +517,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
   }
   else if(warp == 1) {
     // ---------------- MMA issuer ----------------
+    // One thread issues every MMA; its instruction stream is the critical path of the main loop, so the
+    // descriptors are kept as 32-bit low words that only need an add per MMA, ring positions wrap by compare,
+    // and the tap offsets are computed once.
     if(lane == 0) {
-      uint32_t ia = 0, ib = 0, it = 0;
+      const uint32_t descHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);  // stride offset | version | SWIZZLE_128B
+      const uint32_t aLoBase = ((smemU32(smemA) & 0x3FFFFu) >> 4) | (1u << 16);
+      const uint32_t bLoBase = ((smemU32(smemB) & 0x3FFFFu) >> 4) | (1u << 16);
+      const uint32_t aSlot16 = (uint32_t)a.aSlotBytes >> 4, bSlot16 = (uint32_t)a.bSlotBytes >> 4;
+      // row offset of each tap inside the halo tile, in 16-byte units (one row = 128 B = 8 units)
+      uint32_t tapOff[9];
+#pragma unroll
+      for(int tap = 0; tap < 9; tap++) {
+        const int dy = tap / 3 - 1, dx = tap % 3 - 1;
+        tapOff[tap] = (taps == 9) ? (uint32_t)(a.haloPad + dy * a.g.RW + dx) * 8u : 0u;
+      }
+      uint32_t sa = 0, phA = 0, sb = 0, phB = 0, it = 0;
       bool ok = true;
       for(int t = blockIdx.x; t < numTiles && ok; t += gridDim.x, it++) {
         const uint32_t buf = it & 1u;
@@ -376,29 +540,40 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
         if(!mbarWait(smemU32(&accEmpty[buf]), ((it >> 1) & 1u) ^ 1u, abortFlag)) { ok = false; break; }
         tcFenceAfter();
         const uint32_t dTmem = tmemBase + buf * (uint32_t)a.BN;
-        uint32_t first = 1;
+        uint32_t accumulate = 0;
         for(int kc = 0; kc < a.kChunks && ok; kc++) {
-          const uint32_t sa = ia % a.numA;
-          if(!mbarWait(smemU32(&fullA[sa]), (ia / a.numA) & 1u, abortFlag)) { ok = false; break; }
-          const uint32_t aBase = smemU32(smemA + (size_t)sa * a.aSlotBytes);
-          for(int tap = 0; tap < taps; tap++) {
-            const uint32_t sb = ib % a.numB;
-            if(!mbarWait(smemU32(&fullB[sb]), (ib / a.numB) & 1u, abortFlag)) { ok = false; break; }
+          if(!mbarWait(smemU32(&fullA[sa]), phA, abortFlag)) { ok = false; break; }
+          const uint32_t aLo = aLoBase + sa * aSlot16;
+          if(taps == 9) {
+#pragma unroll
+            for(int tap = 0; tap < 9; tap++) {
+              if(!mbarWait(smemU32(&fullB[sb]), phB, abortFlag)) { ok = false; break; }
+              tcFenceAfter();
+              const uint32_t aT = aLo + tapOff[tap], bT = bLoBase + sb * bSlot16;
+#pragma unroll
+              for(int k = 0; k < TC_BK / 16; k++) {
+                // advancing K by 16 elements = 32 bytes = 2 units inside the 128-byte swizzle atom
+                ummaLoHi(dTmem, aT + 2 * k, bT + 2 * k, descHi, a.idesc, accumulate);
+                accumulate = 1;
+              }
+              ummaCommit(smemU32(&emptyB[sb]));  // frees the weight slot once these MMAs have read it
+              if(++sb == (uint32_t)a.numB) { sb = 0; phB ^= 1u; }
+            }
+          }
+          else {
+            if(!mbarWait(smemU32(&fullB[sb]), phB, abortFlag)) { ok = false; break; }
             tcFenceAfter();
-            const int dy = tap / a.kX - a.kY / 2, dx = tap % a.kX - a.kX / 2;
-            const uint32_t aStart = aBase + (uint32_t)(a.haloPad + dy * a.g.RW + dx) * 128u;
-            const uint32_t bStart = smemU32(smemB + (size_t)sb * a.bSlotBytes);
+            const uint32_t bT = bLoBase + sb * bSlot16;
 #pragma unroll
             for(int k = 0; k < TC_BK / 16; k++) {
-              // advancing K by 16 elements = 32 bytes inside the 128-byte swizzle atom
-              umma(dTmem, makeSmemDesc(aStart + k * 32), makeSmemDesc(bStart + k * 32), a.idesc, first ? 0u : 1u);
-              first = 0;
+              ummaLoHi(dTmem, aLo + 2 * k, bT + 2 * k, descHi, a.idesc, accumulate);
+              accumulate = 1;
             }
-            ummaCommit(smemU32(&emptyB[sb]));  // frees the weight slot once these MMAs have read it
-            ib++;
+            ummaCommit(smemU32(&emptyB[sb]));
+            if(++sb == (uint32_t)a.numB) { sb = 0; phB ^= 1u; }
           }
           ummaCommit(smemU32(&emptyA[sa]));
-          ia++;
+          if(++sa == (uint32_t)a.numA) { sa = 0; phA ^= 1u; }
         }
         if(ok) ummaCommit(smemU32(&accFull[buf]));
       }
@@ -409,10 +584,41 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
     // ---------------- Epilogue: warps 2..9; TMEM lane quarter = warp % 4 ----------------
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
+    const bool isE = (warp == 2 && lane == 0);  // the thread that issues this CTA's epilogue TMA traffic
+    EpiTma es;
+    es.sR = smemR; es.sO = smemO; es.resFull = resFull; es.epiBar = epiBar; es.epiPhase = 0; es.oCount = 0;
     uint32_t it = 0;
     for(int t = blockIdx.x; t < numTiles; t += gridDim.x, it++) {
       const uint32_t buf = it & 1u;
       const int m0 = (t / numNTiles) * TC_BM, n0 = (t % numNTiles) * a.BN;
+      // Nothing below depends on the accumulator yet: fetch mask and residual while the MMAs still run.
+      const int m = m0 + q * 32 + lane;
+      const float mk = a.ep.mask ? a.ep.mask[m] : 1.0f;
+      const int bIdx = min(m / a.g.PB, a.g.n - 1);
+      const float* biasRow = a.ep.biasNC ? a.ep.biasNC + (size_t)bIdx * a.outC : nullptr;
+      uint4 res[2 * TC_MAX_GROUPS];
+      if(a.tmaEpi) {
+        if(a.ep.residual && isE) {
+          bulkWaitRead0();  // stores of the previous tile have finished reading the staging blocks
+          for(int cb = 0; cb < a.BN / 64; cb++) {
+            mbarExpectTx(smemU32(&resFull[cb]), (uint32_t)TC_EPI_BLOCK_BYTES);
+            tmaLoad2d(smemU32(smemR + (size_t)cb * TC_EPI_BLOCK_BYTES), &tmRes, n0 + cb * 64, m0, smemU32(&resFull[cb]));
+          }
+        }
+      }
+      else if(a.ep.residual) {
+        const T* rrow = reinterpret_cast<const T*>(a.ep.residual) + (size_t)m * a.ep.resStride + n0;
+        const int groups = a.BN / 16;
+#pragma unroll
+        for(int j = 0; j < TC_MAX_GROUPS; j++) {
+          const int gi = half + 2 * j;
+          if(gi < groups) {
+            const uint4* rp = reinterpret_cast<const uint4*>(rrow + gi * 16);
+            res[2 * j] = rp[0];
+            res[2 * j + 1] = rp[1];
+          }
+        }
+      }
       bool ok = mbarWait(smemU32(&accFull[buf]), (it >> 1) & 1u, abortFlag);
       ok = __all_sync(0xffffffffu, ok);
       if(!ok) {
@@ -421,19 +627,33 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
       }
       tcFenceAfter();
       const uint32_t acc = tmemBase + buf * (uint32_t)a.BN;
-      const int m = m0 + q * 32 + lane;
-      switch(a.ep.act) {
-        case KB_ACT_RELU: epilogueTile<T, KB_ACT_RELU>(a, acc, q, half, m, n0, sScale, sBias); break;
-        case KB_ACT_MISH: epilogueTile<T, KB_ACT_MISH>(a, acc, q, half, m, n0, sScale, sBias); break;
-        case KB_ACT_SILU: epilogueTile<T, KB_ACT_SILU>(a, acc, q, half, m, n0, sScale, sBias); break;
-        case KB_ACT_MISH_SCALE8: epilogueTile<T, KB_ACT_MISH_SCALE8>(a, acc, q, half, m, n0, sScale, sBias); break;
-        default: epilogueTile<T, KB_ACT_IDENTITY>(a, acc, q, half, m, n0, sScale, sBias); break;
+      if(a.tmaEpi) {
+        bool ok2;
+        switch(a.ep.act) {
+          case KB_ACT_RELU: ok2 = epilogueTileTma<T, KB_ACT_RELU>(a, &tmRaw, &tmAct, acc, q, half, lane, isE, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias); break;
+          case KB_ACT_MISH: ok2 = epilogueTileTma<T, KB_ACT_MISH>(a, &tmRaw, &tmAct, acc, q, half, lane, isE, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias); break;
+          case KB_ACT_SILU: ok2 = epilogueTileTma<T, KB_ACT_SILU>(a, &tmRaw, &tmAct, acc, q, half, lane, isE, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias); break;
+          case KB_ACT_MISH_SCALE8: ok2 = epilogueTileTma<T, KB_ACT_MISH_SCALE8>(a, &tmRaw, &tmAct, acc, q, half, lane, isE, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias); break;
+          default: ok2 = epilogueTileTma<T, KB_ACT_IDENTITY>(a, &tmRaw, &tmAct, acc, q, half, lane, isE, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias); break;
+        }
+        if(!ok2) {
+          if(!*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, TC_ERR_EPILOGUE_TIMEOUT); }
+          break;
+        }
+      }
+      else switch(a.ep.act) {
+        case KB_ACT_RELU: epilogueTile<T, KB_ACT_RELU>(a, acc, q, half, m, n0, mk, res, sScale, sBias); break;
+        case KB_ACT_MISH: epilogueTile<T, KB_ACT_MISH>(a, acc, q, half, m, n0, mk, res, sScale, sBias); break;
+        case KB_ACT_SILU: epilogueTile<T, KB_ACT_SILU>(a, acc, q, half, m, n0, mk, res, sScale, sBias); break;
+        case KB_ACT_MISH_SCALE8: epilogueTile<T, KB_ACT_MISH_SCALE8>(a, acc, q, half, m, n0, mk, res, sScale, sBias); break;
+        default: epilogueTile<T, KB_ACT_IDENTITY>(a, acc, q, half, m, n0, mk, res, sScale, sBias); break;
       }
       // all TMEM reads of this warp are complete (tcgen05.wait::ld inside): hand the accumulator back
       tcFenceBefore();
       __syncwarp();
       if(lane == 0) mbarArrive(smemU32(&accEmpty[buf]));
     }
+    if(isE) bulkWaitAll();  // outstanding tile stores must complete before the CTA's shared memory goes away
   }
 
   // ---------------- common exit ----------------
@@ -478,6 +698,9 @@ struct ConvTcPlan {
   uint32_t idesc, tmemCols;
   size_t smemBytes;
   int numSMs;
+  int rowsPadMax;
+  int tmaEpi;
+  CUtensorMap tmRes, tmRaw, tmAct;
 };
 
 static int pickBN(int outC) {
@@ -508,12 +731,26 @@ static bool encode2d(CUtensorMap* tm, int dt, const void* base, uint64_t inner, 
   return r == CUDA_SUCCESS;
 }
 
+constexpr int TC_FIXED_SMEM = 2 * 512 * 4 + 64 * 8 + 64 + 1024;  // norm parameters, barriers, TMEM slot, alignment slack
+
+// Splits the shared memory between the weight ring and (optionally) the epilogue staging blocks.
+static bool sizeRings(ConvTcPlan* p, int epiBlocks) {
+  int numB = (225 * 1024 - TC_FIXED_SMEM - p->numA * p->aSlotBytes - epiBlocks * TC_EPI_BLOCK_BYTES) / p->bSlotBytes;
+  if(const char* e = getenv("KB_TC_NUMB")) { int v = atoi(e); if(v >= 1 && v <= 16) numB = v < numB ? v : numB; }
+  if(numB > 12) numB = 12;
+  if(numB < 2) return false;
+  p->numB = numB;
+  p->smemBytes = (size_t)p->numA * p->aSlotBytes + (size_t)p->numB * p->bSlotBytes + (size_t)epiBlocks * TC_EPI_BLOCK_BYTES + TC_FIXED_SMEM;
+  return true;
+}
+
 ConvTcPlan* convTcCreate(
   int dt, const void* in, int inStride, int inC, const void* w, int outC, int kY, int kX, int X, int Y, int rowsPadMax) {
   if(!convTcEligible(dt, inC, outC, kY, kX)) return nullptr;
   if((inStride % 8) != 0 || (reinterpret_cast<uintptr_t>(in) & 15) != 0 || (reinterpret_cast<uintptr_t>(w) & 15) != 0) return nullptr;
   ConvTcPlan* p = new ConvTcPlan();
   p->dt = dt; p->inC = inC; p->outC = outC; p->kY = kY; p->kX = kX; p->X = X; p->Y = Y;
+  p->rowsPadMax = rowsPadMax; p->tmaEpi = 0;
   p->BN = pickBN(outC);
   p->kChunks = inC / TC_BK;
   const int maxShift = (kY == 3) ? (X + 1) + 1 : 0;  // RW + 1 rows up or down
@@ -523,13 +760,7 @@ ConvTcPlan* convTcCreate(
   p->aSlotBytes = p->aRows * 128;
   p->bSlotBytes = p->BN * 128;
   p->numA = 2;
-  const int fixedBytes = 2 * 512 * 4 + 64 * 8 + 64 + 1024;
-  int numB = (225 * 1024 - fixedBytes - p->numA * p->aSlotBytes) / p->bSlotBytes;
-  if(const char* e = getenv("KB_TC_NUMB")) { int v = atoi(e); if(v >= 1 && v <= 16) numB = v < numB ? v : numB; }
-  if(numB > 12) numB = 12;
-  if(numB < 2) { delete p; return nullptr; }
-  p->numB = numB;
-  p->smemBytes = (size_t)p->numA * p->aSlotBytes + (size_t)p->numB * p->bSlotBytes + fixedBytes;
+  if(!sizeRings(p, 0)) { delete p; return nullptr; }
   p->tmemCols = 32;
   while((int)p->tmemCols < 2 * p->BN) p->tmemCols *= 2;
   const uint32_t fmt = dt == DT_F16 ? 0u : 1u;
@@ -549,6 +780,29 @@ ConvTcPlan* convTcCreate(
 
 void convTcDestroy(ConvTcPlan* p) { delete p; }
 
+// Decides how this convolution's outputs leave the SM.  When every output range (and the tile width) is a
+// multiple of 64 channels the residual is fetched and the outputs are written by TMA through swizzled
+// shared-memory blocks; otherwise the epilogue threads access global memory directly.
+bool convTcSetEpilogue(ConvTcPlan* p, const Epilogue& ep) {
+  p->tmaEpi = 0;
+  const bool force = getenv("KB_TC_NO_TMA_EPI") != nullptr && atoi(getenv("KB_TC_NO_TMA_EPI")) != 0;
+  auto aligned64 = [](int c0, int c1) { return (c0 % 64) == 0 && (c1 % 64) == 0 && c1 > c0; };
+  bool ok = !force && (p->BN % 64) == 0 && p->BN / 64 <= TC_MAX_RES_BLOCKS;
+  if(ep.outRaw) ok = ok && aligned64(ep.rawC0, ep.rawC1) && (ep.rawStride % 8) == 0 && (reinterpret_cast<uintptr_t>(ep.outRaw) & 15) == 0;
+  if(ep.outAct) ok = ok && aligned64(ep.actC0, ep.actC1) && (ep.actStride % 8) == 0 && (reinterpret_cast<uintptr_t>(ep.outAct) & 15) == 0;
+  if(ep.residual) ok = ok && (ep.resStride % 8) == 0 && ep.resStride >= p->outC && (reinterpret_cast<uintptr_t>(ep.residual) & 15) == 0;
+  if(!ok || (!ep.outRaw && !ep.outAct)) return sizeRings(p, 0);
+  if(!sizeRings(p, p->BN / 64 + 2)) return sizeRings(p, 0);
+  const uint64_t rows = (uint64_t)p->rowsPadMax;
+  bool enc = true;
+  if(ep.residual) enc = enc && encode2d(&p->tmRes, p->dt, ep.residual, (uint64_t)p->outC, rows, (uint64_t)ep.resStride * 2, 64, TC_BM);
+  if(ep.outRaw) enc = enc && encode2d(&p->tmRaw, p->dt, ep.outRaw, (uint64_t)(ep.rawC1 - ep.rawC0), rows, (uint64_t)ep.rawStride * 2, 64, TC_BM);
+  if(ep.outAct) enc = enc && encode2d(&p->tmAct, p->dt, ep.outAct, (uint64_t)(ep.actC1 - ep.actC0), rows, (uint64_t)ep.actStride * 2, 64, TC_BM);
+  if(!enc) return sizeRings(p, 0);
+  p->tmaEpi = 1;
+  return true;
+}
+
 cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epilogue& ep, int* statusWord) {
   // vector accesses in the epilogue need 16-byte aligned rows and 16-channel aligned ranges
   if(ep.outRaw && ((ep.rawStride % 8) || (ep.rawC0 % 16) || (ep.rawC1 % 16))) return cudaErrorInvalidValue;
@@ -561,12 +815,13 @@ cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epi
   a.aSlotBytes = p->aSlotBytes; a.bSlotBytes = p->bSlotBytes; a.numA = p->numA; a.numB = p->numB;
   a.idesc = p->idesc; a.tmemCols = p->tmemCols;
   a.status = statusWord;
+  a.tmaEpi = p->tmaEpi;
   const int numTiles = (g.rowsPad / TC_BM) * (p->outC / p->BN);
   const int grid = numTiles < p->numSMs ? numTiles : p->numSMs;
   if(p->dt == DT_F16)
-    convTcKernel<__half><<<grid, TC_THREADS, p->smemBytes, st>>>(p->tmA, p->tmB, a);
+    convTcKernel<__half><<<grid, TC_THREADS, p->smemBytes, st>>>(p->tmA, p->tmB, p->tmRes, p->tmRaw, p->tmAct, a);
   else
-    convTcKernel<__nv_bfloat16><<<grid, TC_THREADS, p->smemBytes, st>>>(p->tmA, p->tmB, a);
+    convTcKernel<__nv_bfloat16><<<grid, TC_THREADS, p->smemBytes, st>>>(p->tmA, p->tmB, p->tmRes, p->tmRaw, p->tmAct, a);
   return cudaGetLastError();
 }
 

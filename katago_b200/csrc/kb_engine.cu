@@ -160,6 +160,7 @@ void Engine::addConvOp(const ConvDev& c, Epilogue ep, const std::string& tag) {
   const int dt = dt_;
   int* status = statusWord_;
   if(c.tc) {
+    if(!convTcSetEpilogue(c.plan, ep)) throw std::runtime_error("tensor-core convolution: shared memory budget exceeded");
     const ConvTcPlan* plan = c.plan;
     addOp(name, flops, bytes, [plan, ep, status](cudaStream_t st, const Geom& g) { return launchConvTc(st, plan, g, ep, status); });
   }

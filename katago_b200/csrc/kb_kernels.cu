@@ -293,6 +293,33 @@ __global__ void biasBnActKernel(
   }
 }
 
+// 8 channels (16 bytes) per thread; rows and channel count are multiples of 8 elements.
+template <typename T>
+__global__ void biasBnActVec8Kernel(
+  const T* __restrict__ in, int inStride, const float* __restrict__ biasNC, const float* __restrict__ scale,
+  const float* __restrict__ bias, int act, const float* __restrict__ mask, T* __restrict__ out, int outStride, int C, Geom g) {
+  const int vecPerRow = C / 8;
+  const size_t total = (size_t)g.rowsPad * vecPerRow;
+  for(size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t m = idx / vecPerRow;
+    const int c = (int)(idx - m * vecPerRow) * 8;
+    uint4 o = make_uint4(0u, 0u, 0u, 0u);
+    if(m < (size_t)g.rows && mask[m] == 1.0f) {
+      const uint4 x = *reinterpret_cast<const uint4*>(in + m * inStride + c);
+      const T* xe = reinterpret_cast<const T*>(&x);
+      T* oe = reinterpret_cast<T*>(&o);
+      const float* bnc = biasNC ? biasNC + (m / g.PB) * C + c : nullptr;
+#pragma unroll
+      for(int j = 0; j < 8; j++) {
+        float v = toF<T>(xe[j]);
+        if(bnc) v += bnc[j];
+        oe[j] = fromF<T>(applyActF(v * scale[c + j] + bias[c + j], act));
+      }
+    }
+    *reinterpret_cast<uint4*>(out + m * outStride + c) = o;
+  }
+}
+
 static int ewGrid(size_t total) {
   size_t b = (total + 255) / 256;
   return (int)(b > 148 * 16 ? 148 * 16 : (b < 1 ? 1 : b));
@@ -301,6 +328,16 @@ static int ewGrid(size_t total) {
 cudaError_t launchBiasBnAct(
   cudaStream_t st, int dt, const void* in, int inStride, const float* biasNC, const float* scale, const float* bias,
   int act, const float* mask, void* out, int outStride, int C, Geom g) {
+  const bool vec = dt != DT_F32 && (C % 8) == 0 && (inStride % 8) == 0 && (outStride % 8) == 0 &&
+                   (reinterpret_cast<uintptr_t>(in) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+  if(vec) {
+    int grid = ewGrid((size_t)g.rowsPad * (C / 8));
+    if(dt == DT_F16)
+      biasBnActVec8Kernel<__half><<<grid, 256, 0, st>>>((const __half*)in, inStride, biasNC, scale, bias, act, mask, (__half*)out, outStride, C, g);
+    else
+      biasBnActVec8Kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)in, inStride, biasNC, scale, bias, act, mask, (__nv_bfloat16*)out, outStride, C, g);
+    return cudaGetLastError();
+  }
   int grid = ewGrid((size_t)g.rowsPad * C);
   KB_DISPATCH_DT(dt, (biasBnActKernel<T, T><<<grid, 256, 0, st>>>((const T*)in, inStride, biasNC, scale, bias, act, mask, (T*)out, outStride, C, g)));
   return cudaGetLastError();

@@ -113,6 +113,8 @@ bool convTcEligible(int dt, int inC, int outC, int kY, int kX);
 ConvTcPlan* convTcCreate(
   int dt, const void* in, int inStride, int inC, const void* w, int outC, int kY, int kX, int X, int Y, int rowsPadMax);
 void convTcDestroy(ConvTcPlan* p);
+// Binds the epilogue (output/residual tensors) to the plan; must be called once before the first launch.
+bool convTcSetEpilogue(ConvTcPlan* p, const Epilogue& ep);
 cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epilogue& ep, int* statusWord);
 
 }  // namespace kb

@@ -121,6 +121,31 @@ int kb_eval_layer(
   const void* blob, size_t nbytes, int device, int precision, int n, int nnXLen, int nnYLen,
   const float* in, const float* mask, float* out);
 
+/* Convolution without any allocation.  (No counterpart in the reference: its backends allocate freely.)
+ *
+ * For callers that may not allocate device memory themselves or through this library: plug-ins living inside a
+ * host application's memory pool, or latency-critical loops that cannot afford the locks and the implicit
+ * synchronisation of cudaMalloc/cudaFree.  The caller passes DEVICE pointers it already owns; the working
+ * memory the convolution needs (padded copies of input and output, re-ordered weights) is a fixed 2.4 MiB array
+ * inside the library's device image, present on every GPU that loads the library until the process exits.
+ *
+ *   dIn      [n][nnYLen][nnXLen][inC] fp32 NHWC     dWeights [outC][inC][kY][kX] fp32 (ConvLayerDesc order, desc.h:23)
+ *   dOut     [n][nnYLen][nnXLen][outC] fp32 NHWC    stream   a cudaStream_t (NULL = default stream)
+ * Computes the same zero-padded stride-1 cross-correlation as kb_eval_layer does for a CONV record in fp32.
+ * The kernels are enqueued on `stream`; the call returns without waiting for them.
+ *
+ * Limits (exceeding one is an error, nothing is launched): n*(nnYLen+1)*(nnXLen+1) rounded up to 128 <= 4096 rows
+ * (10 boards of 19x19), inC <= 64, outC <= 64, kernel at most 5x5 and odd.
+ * The first call on each device looks up the array's device address (with that device current); make that
+ * call before starting any stream capture.  All calls share the one array and it keeps the previous call's
+ * contents: two calls whose kernels overlap on the GPU (different streams, different threads) race on it.
+ * The call itself performs no cudaMalloc, cudaFree or other allocating routine. */
+int kb_conv_noalloc(
+  const float* dIn, const float* dWeights, float* dOut, int n, int nnXLen, int nnYLen, int inC, int outC, int kY, int kX,
+  void* stream);
+/* Message of the last kb_conv_noalloc failure on the calling thread. */
+const char* kb_conv_noalloc_last_error(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -19,7 +19,7 @@ EXPORTED_SYMBOLS = [
     "kb_model_info", "kb_handle_create", "kb_handle_destroy", "kb_handle_precision", "kb_forward_host",
     "kb_upload_inputs", "kb_forward_resident", "kb_download_outputs", "kb_time_forward_resident", "kb_time_forward_steps",
     "kb_profile_enable", "kb_profile_reset", "kb_profile_read", "kb_launches_per_forward", "kb_debug_read_trunk",
-    "kb_eval_layer", "kb_host_alloc", "kb_host_free",
+    "kb_eval_layer", "kb_host_alloc", "kb_host_free", "kb_conv_noalloc", "kb_conv_noalloc_last_error",
 ]
 
 
@@ -71,6 +71,8 @@ def lib():
         L.kb_eval_layer.argtypes = [vp, sz, ci, ci, ci, ci, ci, vp, vp, vp]
         L.kb_host_alloc.argtypes = [sz, ctypes.POINTER(vp)]
         L.kb_host_free.argtypes = [vp]
+        L.kb_conv_noalloc.argtypes = [vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, vp]
+        L.kb_conv_noalloc_last_error.restype = ctypes.c_char_p
         _lib = L
     return _lib
 
@@ -217,6 +219,14 @@ class Handle:
         out = np.empty((n, self.nn_x * self.nn_y, self.model.trunk_c), np.float32)
         _check(lib().kb_debug_read_trunk(self.h, n, _ptr(out)), "kb_debug_read_trunk")
         return out
+
+
+def conv_noalloc(d_in: int, d_weights: int, d_out: int, n: int, nn_x: int, nn_y: int, in_c: int, out_c: int, ky: int, kx: int,
+                 stream: int = 0) -> None:
+    """kb_conv_noalloc with raw device addresses (ints).  Enqueues on `stream`; the caller synchronises."""
+    status = lib().kb_conv_noalloc(d_in, d_weights, d_out, n, nn_x, nn_y, in_c, out_c, ky, kx, stream or None)
+    if status != 0:
+        raise KBError(f"kb_conv_noalloc failed ({status}): {lib().kb_conv_noalloc_last_error().decode()}")
 
 
 def eval_layer(blob: bytes, x: np.ndarray, mask, out_c: int, precision: int = PRECISION_FP32, device: int = -1) -> np.ndarray:

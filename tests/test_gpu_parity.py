@@ -206,3 +206,28 @@ def test_reference_tiny_net_test_on_b200_backend(tmp_path):
     r = subprocess.run([KATAGO_B200, "runtinynntests", str(tmp_path), "1.0"], capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
     assert "Tiny net sanity check complete" in r.stdout + r.stderr
+
+
+def _gpuerror_cases():
+    idx = os.path.join(ROOT, "oracle", "_ref", "gpuerror", "index.json")
+    if not os.path.exists(idx):
+        return []
+    import json
+    return json.load(open(idx))
+
+
+@needs_bin
+@pytest.mark.parametrize("case", _gpuerror_cases(), ids=lambda c: c["name"])
+def test_reference_testgpuerror_against_oracle_reference_file(case):
+    """The reference's cross-backend harness (cpp/command/gputest.cpp) on the B200 backend, fp16 "current config"
+    and its fp32 twin, against the values the same harness wrote when linked with the CPU oracle
+    (oracle/make_gpuerror_refs.py).  The program exits non-zero when any of its thresholds
+    (cpp/tests/testnnevalcanary.cpp:727-749) is exceeded."""
+    d = os.path.join(ROOT, "oracle", "_ref", "gpuerror")
+    cmd = [KATAGO_B200, "testgpuerror", "-model", os.path.join(d, case["model"]), "-config", os.path.join(d, "gpuerror.cfg"),
+           "-boardsize", case["boardsize"], "-quick", "-reference-file", os.path.join(d, case["reference"]),
+           "-override-config", case["overrides"]]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0, out[-4000:]
+    assert "current cfg error vs reference winrateError" in out

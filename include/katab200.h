@@ -102,7 +102,7 @@ int kb_profile_reset(kb_handle* h);
 int kb_profile_read(kb_handle* h, kb_profile_entry* entries, int cap, int* count);
 
 /* Number of kernel launches one forward pass of batch n issues (for the harness's launch count). */
-int kb_launches_per_forward(const kb_handle* h, int* launches);
+int kb_launches_per_forward(const kb_handle* h, int n, int* launches);
 
 /* Trunk output after the final norm+activation, [n][nnYLen*nnXLen][trunkC] fp32 (debugging aid;
  * mirrors the reference's DEBUG_INTERMEDIATE_VALUES dumps, cudabackend.cpp:46). */

@@ -66,7 +66,7 @@ def lib():
         L.kb_profile_enable.argtypes = [vp, ci]
         L.kb_profile_reset.argtypes = [vp]
         L.kb_profile_read.argtypes = [vp, ctypes.POINTER(ProfileEntry), ci, ctypes.POINTER(ci)]
-        L.kb_launches_per_forward.argtypes = [vp, ctypes.POINTER(ci)]
+        L.kb_launches_per_forward.argtypes = [vp, ci, ctypes.POINTER(ci)]
         L.kb_debug_read_trunk.argtypes = [vp, ci, vp]
         L.kb_eval_layer.argtypes = [vp, sz, ci, ci, ci, ci, ci, vp, vp, vp]
         L.kb_host_alloc.argtypes = [sz, ctypes.POINTER(vp)]
@@ -210,9 +210,9 @@ class Handle:
         return [dict(name=arr[i].name.decode(), launches=arr[i].launches, ms=arr[i].ms, flops=arr[i].flops, bytes=arr[i].bytes)
                 for i in range(cnt.value)]
 
-    def launches_per_forward(self) -> int:
+    def launches_per_forward(self, n=None) -> int:
         k = ctypes.c_int(0)
-        _check(lib().kb_launches_per_forward(self.h, ctypes.byref(k)), "kb_launches_per_forward")
+        _check(lib().kb_launches_per_forward(self.h, self.max_batch if n is None else n, ctypes.byref(k)), "kb_launches_per_forward")
         return k.value
 
     def read_trunk(self, n) -> np.ndarray:

@@ -144,8 +144,8 @@ int kb_profile_read(kb_handle* h, kb_profile_entry* entries, int cap, int* count
     *count = k;
   });
 }
-int kb_launches_per_forward(const kb_handle* h, int* launches) {
-  return guarded([&]() { need(h, "handle"); need(launches, "launches"); *launches = h->e->launchesPerForward(); });
+int kb_launches_per_forward(const kb_handle* h, int n, int* launches) {
+  return guarded([&]() { need(h, "handle"); need(launches, "launches"); *launches = h->e->launchesPerForward(n); });
 }
 int kb_debug_read_trunk(kb_handle* h, int n, float* trunkOut) {
   return guarded([&]() { need(h, "handle"); h->e->readTrunk(n, trunkOut); });

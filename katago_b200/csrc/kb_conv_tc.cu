@@ -86,6 +86,7 @@ __device__ __forceinline__ void tmaStore2d(const CUtensorMap* tmap, uint32_t src
 }
 __device__ __forceinline__ void bulkCommit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulkWaitRead0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulkWaitRead1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void bulkWaitAll() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fenceProxyAsync() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -222,8 +223,10 @@ struct ConvTcArgs {
   int aSlotBytes;  // aRows * 128
   int bSlotBytes;  // BN * 128
   int numA, numB;  // ring depths
+  int residentB;   // 1x1 only: all weight tiles of this CTA's channel tile stay in shared memory for the whole kernel
   uint32_t idesc;
   uint32_t tmemCols;
+  int epiWarpBytes; // shared memory of one epilogue warp's staging units (TMA epilogue)
   int tmaEpi;      // 1: outputs and residual travel through shared memory and TMA (64-channel aligned ranges)
   int* status;     // device status word: 0 = ok
 };
@@ -321,56 +324,56 @@ __device__ __forceinline__ void epilogueTile(
   }
 }
 
-constexpr int TC_EPI_BLOCK_BYTES = TC_BM * 128;  // one staging block: 128 rows x 64 channels, 128-byte swizzled
-constexpr int TC_MAX_RES_BLOCKS = 3;
+constexpr int TC_UNIT_BYTES = 32 * 64;        // one staging unit: 32 rows x 32 channels (64 B rows, 64-byte swizzle)
+constexpr int TC_MAX_UNITS_PER_WARP = 4;      // BN <= 256 -> 8 units of 32 channels, split over the two warps of a quarter
 
-struct EpiTma {
-  uint8_t* sR;          // residual / raw staging blocks, one per 64-channel block of the tile
-  uint8_t* sO;          // two blocks for the activated output
-  uint64_t* resFull;    // residual block landed (TMA)
-  uint64_t* epiBar;     // all 256 epilogue threads arrived
-  uint32_t epiPhase;
+struct EpiWarp {
+  uint8_t* sR;          // this warp's residual / raw staging units
+  uint8_t* sO;          // this warp's two units for the activated output
+  uint64_t* resFull;    // [TC_MAX_UNITS_PER_WARP] residual unit landed (TMA)
   uint32_t oCount;
 };
 
-// Epilogue of one tile with shared-memory staging.  Each thread owns one row and, per 64-channel block, the
-// 32 channels of its half (64 contiguous bytes of the swizzled staging row).  The residual block was fetched by
-// TMA; the updated residual stream overwrites it in place and goes back out by TMA; the activated tensor is
-// staged in a second buffer.  Global memory therefore only sees whole 128-byte rows written by the TMA engine.
+// Epilogue of one tile for one warp, staged through shared memory.  A warp owns 32 rows (its TMEM lane quarter) and
+// every second 32-channel unit of the tile; each thread owns one row of a unit (64 contiguous bytes).  The residual
+// unit was fetched by TMA; the updated residual stream overwrites it in place and goes back out by TMA; the
+// activated tensor is staged in one of two more units.  All synchronisation is inside the warp, and global memory
+// only sees whole 64-byte row segments written by the TMA engine.
 template <typename T, int ACT>
 __device__ __forceinline__ bool epilogueTileTma(
-  const ConvTcArgs& a, const CUtensorMap* tmRaw, const CUtensorMap* tmAct, uint32_t tmemAcc, int q, int half, int lane, bool isE,
-  int m0, int n0, float mk, const float* biasRow, EpiTma& es, uint32_t tileParity, volatile int* abortFlag,
+  const ConvTcArgs& a, const CUtensorMap* tmRaw, const CUtensorMap* tmAct, uint32_t tmemAcc, int q, int half, int lane,
+  int m0, int n0, float mk, const float* biasRow, EpiWarp& es, uint32_t tileParity, volatile int* abortFlag,
   const float* sScale, const float* sBias) {
   const Epilogue& ep = a.ep;
   const bool hasRes = ep.residual != nullptr;
-  const int row = q * 32 + lane;
-  const int blocks = a.BN / 64;
-  for(int cb = 0; cb < blocks; cb++) {
+  const int units = a.BN / 32;
+  const int sw = (lane >> 1) & 3;  // 64-byte swizzle: 16-byte chunk index XOR bits 1..2 of the row
+  int j = 0;
+  for(int u = half; u < units; u += 2, j++) {
     uint32_t r[32];
-    tmemLd32(tmemAcc + ((uint32_t)(q * 32) << 16) + (uint32_t)(cb * 64 + half * 32), r);
+    tmemLd32(tmemAcc + ((uint32_t)(q * 32) << 16) + (uint32_t)(u * 32), r);
     if(hasRes) {
-      if(!mbarWait(smemU32(&es.resFull[cb]), tileParity, abortFlag)) return false;
+      bool landed = mbarWait(smemU32(&es.resFull[j]), tileParity, abortFlag);
+      if(!__all_sync(0xffffffffu, landed)) return false;
     }
     tmemLdWait();
-    const int c = n0 + cb * 64 + half * 32;  // first output channel of this thread's 32
+    const int c = n0 + u * 32;  // first output channel of this unit
     float v[32];
 #pragma unroll
-    for(int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+    for(int k = 0; k < 32; k++) v[k] = __uint_as_float(r[k]);
     if(biasRow) {
       const float4* bp = reinterpret_cast<const float4*>(biasRow + c);
 #pragma unroll
-      for(int j = 0; j < 8; j++) {
-        float4 b4 = bp[j];
-        v[4 * j] += b4.x; v[4 * j + 1] += b4.y; v[4 * j + 2] += b4.z; v[4 * j + 3] += b4.w;
+      for(int k = 0; k < 8; k++) {
+        float4 b4 = bp[k];
+        v[4 * k] += b4.x; v[4 * k + 1] += b4.y; v[4 * k + 2] += b4.z; v[4 * k + 3] += b4.w;
       }
     }
-    uint8_t* rRow = es.sR + (size_t)cb * TC_EPI_BLOCK_BYTES + row * 128;
-    const int sw = row & 7;
+    uint8_t* rRow = es.sR + (size_t)j * TC_UNIT_BYTES + lane * 64;
     if(hasRes) {
 #pragma unroll
       for(int jj = 0; jj < 4; jj++) {
-        const uint4 x = *reinterpret_cast<const uint4*>(rRow + (((half * 4 + jj) ^ sw) << 4));
+        const uint4 x = *reinterpret_cast<const uint4*>(rRow + ((jj ^ sw) << 4));
         const uint32_t xu[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
         for(int k = 0; k < 4; k++) {
@@ -388,12 +391,12 @@ __device__ __forceinline__ bool epilogueTileTma(
         uint4 o;
         o.x = Pack2<T>::pack(v[8 * jj], v[8 * jj + 1]); o.y = Pack2<T>::pack(v[8 * jj + 2], v[8 * jj + 3]);
         o.z = Pack2<T>::pack(v[8 * jj + 4], v[8 * jj + 5]); o.w = Pack2<T>::pack(v[8 * jj + 6], v[8 * jj + 7]);
-        *reinterpret_cast<uint4*>(rRow + (((half * 4 + jj) ^ sw) << 4)) = o;
+        *reinterpret_cast<uint4*>(rRow + ((jj ^ sw) << 4)) = o;
       }
     }
-    uint8_t* oBlock = es.sO + (size_t)(es.oCount & 1u) * TC_EPI_BLOCK_BYTES;
+    uint8_t* oUnit = es.sO + (size_t)(es.oCount & 1u) * TC_UNIT_BYTES;
     if(doAct) {
-      uint8_t* oRow = oBlock + row * 128;
+      uint8_t* oRow = oUnit + lane * 64;
       const int ca = c - ep.actC0;
       if(mk == 1.0f) {
         const float4* sp = reinterpret_cast<const float4*>(sScale + ca);
@@ -412,25 +415,24 @@ __device__ __forceinline__ bool epilogueTileTma(
           uint4 o;
           o.x = Pack2<T>::pack(o8[0], o8[1]); o.y = Pack2<T>::pack(o8[2], o8[3]);
           o.z = Pack2<T>::pack(o8[4], o8[5]); o.w = Pack2<T>::pack(o8[6], o8[7]);
-          *reinterpret_cast<uint4*>(oRow + (((half * 4 + jj) ^ sw) << 4)) = o;
+          *reinterpret_cast<uint4*>(oRow + ((jj ^ sw) << 4)) = o;
         }
       }
       else {
 #pragma unroll
-        for(int jj = 0; jj < 4; jj++) *reinterpret_cast<uint4*>(oRow + (((half * 4 + jj) ^ sw) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+        for(int jj = 0; jj < 4; jj++) *reinterpret_cast<uint4*>(oRow + ((jj ^ sw) << 4)) = make_uint4(0u, 0u, 0u, 0u);
       }
     }
-    // make the generic-proxy writes visible to the TMA engine, then meet the other epilogue threads
+    // make the generic-proxy writes visible to the TMA engine, then let lane 0 send the unit out
     fenceProxyAsync();
-    if(isE) bulkWaitRead0();  // every earlier store has finished reading its staging block
-    mbarArrive(smemU32(es.epiBar));
-    if(!mbarWait(smemU32(es.epiBar), es.epiPhase, abortFlag)) return false;
-    es.epiPhase ^= 1u;
-    if(isE) {
-      if(doRaw) tmaStore2d(tmRaw, smemU32(es.sR + (size_t)cb * TC_EPI_BLOCK_BYTES), n0 + cb * 64 - ep.rawC0, m0);
-      if(doAct) tmaStore2d(tmAct, smemU32(oBlock), n0 + cb * 64 - ep.actC0, m0);
+    __syncwarp();
+    if(lane == 0) {
+      if(doRaw) tmaStore2d(tmRaw, smemU32(es.sR + (size_t)j * TC_UNIT_BYTES), c - ep.rawC0, m0 + q * 32);
+      if(doAct) tmaStore2d(tmAct, smemU32(oUnit), c - ep.actC0, m0 + q * 32);
       bulkCommit();
+      bulkWaitRead1();  // the store issued one unit ago has finished reading: its output unit may be rewritten
     }
+    __syncwarp();
     if(doAct) es.oCount++;
   }
   return true;
@@ -446,9 +448,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
   uint8_t* smemA = smem;
   uint8_t* smemB = smemA + (size_t)a.numA * a.aSlotBytes;
   uint8_t* smemR = smemB + (size_t)a.numB * a.bSlotBytes;  // epilogue staging (TMA epilogue only)
-  const int epiBlocks = a.tmaEpi ? (a.BN / 64 + 2) : 0;
-  uint8_t* smemO = smemR + (size_t)(a.BN / 64) * TC_EPI_BLOCK_BYTES;
-  float* sScale = reinterpret_cast<float*>(smemR + (size_t)epiBlocks * TC_EPI_BLOCK_BYTES);
+  float* sScale = reinterpret_cast<float*>(smemR + (a.tmaEpi ? (size_t)TC_EPI_WARPS * a.epiWarpBytes : 0));
   float* sBias = sScale + 512;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sBias + 512);
   // barrier layout: fullA[numA] emptyA[numA] fullB[numB] emptyB[numB] accFull[2] accEmpty[2]
@@ -458,9 +458,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
   uint64_t* emptyB = fullB + a.numB;
   uint64_t* accFull = emptyB + a.numB;
   uint64_t* accEmpty = accFull + 2;
-  uint64_t* resFull = accEmpty + 2;   // [TC_MAX_RES_BLOCKS]
-  uint64_t* epiBar = resFull + TC_MAX_RES_BLOCKS;
-  uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(epiBar + 1);
+  uint64_t* resFull = accEmpty + 2;   // [TC_EPI_WARPS][TC_MAX_UNITS_PER_WARP]
+  uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(resFull + TC_EPI_WARPS * TC_MAX_UNITS_PER_WARP);
   volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -472,8 +471,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
     for(int s = 0; s < a.numA; s++) { mbarInit(smemU32(&fullA[s]), 1); mbarInit(smemU32(&emptyA[s]), 1); }
     for(int s = 0; s < a.numB; s++) { mbarInit(smemU32(&fullB[s]), 1); mbarInit(smemU32(&emptyB[s]), 1); }
     for(int s = 0; s < 2; s++) { mbarInit(smemU32(&accFull[s]), 1); mbarInit(smemU32(&accEmpty[s]), TC_EPI_WARPS); }
-    for(int s = 0; s < TC_MAX_RES_BLOCKS; s++) mbarInit(smemU32(&resFull[s]), 1);
-    mbarInit(smemU32(epiBar), TC_EPI_WARPS * 32);
+    for(int s = 0; s < TC_EPI_WARPS * TC_MAX_UNITS_PER_WARP; s++) mbarInit(smemU32(&resFull[s]), 1);
     *abortFlag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -497,6 +495,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
     if(lane == 0) {
       uint32_t sa = 0, phA = 0, sb = 0, phB = 0;
       bool ok = true;
+      if(a.residentB) {
+        // the grid is a multiple of the number of channel tiles, so this CTA always works on the same one
+        const int n0 = (blockIdx.x % numNTiles) * a.BN;
+        for(int kc = 0; kc < a.kChunks; kc++) {
+          mbarExpectTx(smemU32(&fullB[kc]), (uint32_t)a.bSlotBytes);
+          tmaLoad2d(smemU32(smemB + (size_t)kc * a.bSlotBytes), &tmB, kc * TC_BK, n0, smemU32(&fullB[kc]));
+        }
+      }
       for(int t = blockIdx.x; t < numTiles && ok; t += gridDim.x) {
         const int m0 = (t / numNTiles) * TC_BM, n0 = (t % numNTiles) * a.BN;
         for(int kc = 0; kc < a.kChunks && ok; kc++) {
@@ -504,6 +510,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
           mbarExpectTx(smemU32(&fullA[sa]), (uint32_t)a.aSlotBytes);
           tmaLoad2d(smemU32(smemA + (size_t)sa * a.aSlotBytes), &tmA, kc * TC_BK, m0 - a.haloPad, smemU32(&fullA[sa]));
           if(++sa == (uint32_t)a.numA) { sa = 0; phA ^= 1u; }
+          if(a.residentB) continue;
           for(int tap = 0; tap < taps; tap++) {
             if(!mbarWait(smemU32(&emptyB[sb]), phB ^ 1u, abortFlag)) { ok = false; break; }
             mbarExpectTx(smemU32(&fullB[sb]), (uint32_t)a.bSlotBytes);
@@ -560,6 +567,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
               if(++sb == (uint32_t)a.numB) { sb = 0; phB ^= 1u; }
             }
           }
+          else if(a.residentB) {
+            // weights were loaded once; the barrier of chunk kc completed its only phase during the first tile
+            if(!mbarWait(smemU32(&fullB[kc]), 0u, abortFlag)) { ok = false; break; }
+            tcFenceAfter();
+            const uint32_t bT = bLoBase + (uint32_t)kc * bSlot16;
+#pragma unroll
+            for(int k = 0; k < TC_BK / 16; k++) {
+              ummaLoHi(dTmem, aLo + 2 * k, bT + 2 * k, descHi, a.idesc, accumulate);
+              accumulate = 1;
+            }
+          }
           else {
             if(!mbarWait(smemU32(&fullB[sb]), phB, abortFlag)) { ok = false; break; }
             tcFenceAfter();
@@ -584,9 +602,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
     // ---------------- Epilogue: warps 2..9; TMEM lane quarter = warp % 4 ----------------
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
-    const bool isE = (warp == 2 && lane == 0);  // the thread that issues this CTA's epilogue TMA traffic
-    EpiTma es;
-    es.sR = smemR; es.sO = smemO; es.resFull = resFull; es.epiBar = epiBar; es.epiPhase = 0; es.oCount = 0;
+    EpiWarp es;
+    es.sR = smemR + (size_t)(warp - 2) * a.epiWarpBytes;
+    es.sO = es.sR + (size_t)(a.epiWarpBytes - 2 * TC_UNIT_BYTES);
+    es.resFull = resFull + (warp - 2) * TC_MAX_UNITS_PER_WARP;
+    es.oCount = 0;
     uint32_t it = 0;
     for(int t = blockIdx.x; t < numTiles; t += gridDim.x, it++) {
       const uint32_t buf = it & 1u;
@@ -598,13 +618,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
       const float* biasRow = a.ep.biasNC ? a.ep.biasNC + (size_t)bIdx * a.outC : nullptr;
       uint4 res[2 * TC_MAX_GROUPS];
       if(a.tmaEpi) {
-        if(a.ep.residual && isE) {
-          bulkWaitRead0();  // stores of the previous tile have finished reading the staging blocks
-          for(int cb = 0; cb < a.BN / 64; cb++) {
-            mbarExpectTx(smemU32(&resFull[cb]), (uint32_t)TC_EPI_BLOCK_BYTES);
-            tmaLoad2d(smemU32(smemR + (size_t)cb * TC_EPI_BLOCK_BYTES), &tmRes, n0 + cb * 64, m0, smemU32(&resFull[cb]));
+        if(a.ep.residual && lane == 0) {
+          bulkWaitRead0();  // this warp's stores of the previous tile have finished reading its staging units
+          int j = 0;
+          for(int u = half; u < a.BN / 32; u += 2, j++) {
+            mbarExpectTx(smemU32(&es.resFull[j]), (uint32_t)TC_UNIT_BYTES);
+            tmaLoad2d(smemU32(es.sR + (size_t)j * TC_UNIT_BYTES), &tmRes, n0 + u * 32, m0 + q * 32, smemU32(&es.resFull[j]));
           }
         }
+        __syncwarp();
       }
       else if(a.ep.residual) {
         const T* rrow = reinterpret_cast<const T*>(a.ep.residual) + (size_t)m * a.ep.resStride + n0;
@@ -630,14 +652,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
       if(a.tmaEpi) {
         bool ok2;
         switch(a.ep.act) {
-          case KB_ACT_RELU: ok2 = epilogueTileTma<T, KB_ACT_RELU>(a, &tmRaw, &tmAct, acc, q, half, lane, isE, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias); break;
-          case KB_ACT_MISH: ok2 = epilogueTileTma<T, KB_ACT_MISH>(a, &tmRaw, &tmAct, acc, q, half, lane, isE, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias); break;
-          case KB_ACT_SILU: ok2 = epilogueTileTma<T, KB_ACT_SILU>(a, &tmRaw, &tmAct, acc, q, half, lane, isE, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias); break;
-          case KB_ACT_MISH_SCALE8: ok2 = epilogueTileTma<T, KB_ACT_MISH_SCALE8>(a, &tmRaw, &tmAct, acc, q, half, lane, isE, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias); break;
-          default: ok2 = epilogueTileTma<T, KB_ACT_IDENTITY>(a, &tmRaw, &tmAct, acc, q, half, lane, isE, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias); break;
+          case KB_ACT_RELU: ok2 = epilogueTileTma<T, KB_ACT_RELU>(a, &tmRaw, &tmAct, acc, q, half, lane, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias); break;
+          case KB_ACT_MISH: ok2 = epilogueTileTma<T, KB_ACT_MISH>(a, &tmRaw, &tmAct, acc, q, half, lane, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias); break;
+          case KB_ACT_SILU: ok2 = epilogueTileTma<T, KB_ACT_SILU>(a, &tmRaw, &tmAct, acc, q, half, lane, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias); break;
+          case KB_ACT_MISH_SCALE8: ok2 = epilogueTileTma<T, KB_ACT_MISH_SCALE8>(a, &tmRaw, &tmAct, acc, q, half, lane, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias); break;
+          default: ok2 = epilogueTileTma<T, KB_ACT_IDENTITY>(a, &tmRaw, &tmAct, acc, q, half, lane, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias); break;
         }
         if(!ok2) {
-          if(!*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, TC_ERR_EPILOGUE_TIMEOUT); }
+          if(lane == 0 && !*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, TC_ERR_EPILOGUE_TIMEOUT); }
           break;
         }
       }
@@ -653,7 +675,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
       __syncwarp();
       if(lane == 0) mbarArrive(smemU32(&accEmpty[buf]));
     }
-    if(isE) bulkWaitAll();  // outstanding tile stores must complete before the CTA's shared memory goes away
+    if(lane == 0) bulkWaitAll();  // outstanding tile stores must complete before the CTA's shared memory goes away
   }
 
   // ---------------- common exit ----------------
@@ -694,12 +716,12 @@ static EncodeTiledFn getEncodeTiled() {
 struct ConvTcPlan {
   CUtensorMap tmA, tmB;
   int dt, inC, outC, kY, kX, X, Y;
-  int BN, kChunks, haloPad, aRows, aSlotBytes, bSlotBytes, numA, numB;
+  int BN, kChunks, haloPad, aRows, aSlotBytes, bSlotBytes, numA, numB, residentB;
   uint32_t idesc, tmemCols;
   size_t smemBytes;
   int numSMs;
   int rowsPadMax;
-  int tmaEpi;
+  int tmaEpi, epiWarpBytes;
   CUtensorMap tmRes, tmRaw, tmAct;
 };
 
@@ -717,7 +739,9 @@ bool convTcEligible(int dt, int inC, int outC, int kY, int kX) {
   return pickBN(outC) >= 16;
 }
 
-static bool encode2d(CUtensorMap* tm, int dt, const void* base, uint64_t inner, uint64_t outer, uint64_t strideBytes, uint32_t boxInner, uint32_t boxOuter) {
+static bool encode2d(
+  CUtensorMap* tm, int dt, const void* base, uint64_t inner, uint64_t outer, uint64_t strideBytes, uint32_t boxInner, uint32_t boxOuter,
+  CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn fn = getEncodeTiled();
   if(!fn) return false;
   cuuint64_t dims[2] = {inner, outer};
@@ -726,21 +750,45 @@ static bool encode2d(CUtensorMap* tm, int dt, const void* base, uint64_t inner, 
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(
     tm, dt == DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
-    strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+    strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 
-constexpr int TC_FIXED_SMEM = 2 * 512 * 4 + 64 * 8 + 64 + 1024;  // norm parameters, barriers, TMEM slot, alignment slack
+constexpr int TC_FIXED_SMEM = 2 * 512 * 4 + 96 * 8 + 64 + 1024;  // norm parameters, barriers, TMEM slot, alignment slack
 
 // Splits the shared memory between the weight ring and (optionally) the epilogue staging blocks.
-static bool sizeRings(ConvTcPlan* p, int epiBlocks) {
-  int numB = (225 * 1024 - TC_FIXED_SMEM - p->numA * p->aSlotBytes - epiBlocks * TC_EPI_BLOCK_BYTES) / p->bSlotBytes;
-  if(const char* e = getenv("KB_TC_NUMB")) { int v = atoi(e); if(v >= 1 && v <= 16) numB = v < numB ? v : numB; }
-  if(numB > 12) numB = 12;
-  if(numB < 2) return false;
-  p->numB = numB;
-  p->smemBytes = (size_t)p->numA * p->aSlotBytes + (size_t)p->numB * p->bSlotBytes + (size_t)epiBlocks * TC_EPI_BLOCK_BYTES + TC_FIXED_SMEM;
+static bool sizeRings(ConvTcPlan* p, int epiBytes) {
+  const int budget = 227 * 1024 - TC_FIXED_SMEM - epiBytes;
+  p->residentB = 0;
+  if(p->kY == 1 && p->kX == 1) {
+    // 1x1: little math per byte, so the kernel is bound by how many bytes of activations are in flight.  If all
+    // weight tiles of one channel tile fit next to at least three activation slots they stay resident and only
+    // activations stream; otherwise activation and weight slots are paired.
+    const int allB = p->kChunks * p->bSlotBytes;
+    if(allB + 3 * p->aSlotBytes <= budget && p->kChunks <= 12) {
+      p->residentB = 1;
+      p->numB = p->kChunks;
+      int numA = (budget - allB) / p->aSlotBytes;
+      p->numA = numA > 8 ? 8 : numA;
+    }
+    else {
+      int n = budget / (p->aSlotBytes + p->bSlotBytes);
+      if(n > 8) n = 8;
+      if(n < 2) return false;
+      p->numA = n;
+      p->numB = n;
+    }
+  }
+  else {
+    p->numA = 2;
+    int numB = (budget - p->numA * p->aSlotBytes) / p->bSlotBytes;
+    if(const char* e = getenv("KB_TC_NUMB")) { int v = atoi(e); if(v >= 1 && v <= 16) numB = v < numB ? v : numB; }
+    if(numB > 12) numB = 12;
+    if(numB < 2) return false;
+    p->numB = numB;
+  }
+  p->smemBytes = (size_t)p->numA * p->aSlotBytes + (size_t)p->numB * p->bSlotBytes + (size_t)epiBytes + TC_FIXED_SMEM;
   return true;
 }
 
@@ -759,7 +807,6 @@ ConvTcPlan* convTcCreate(
   if(p->aRows > 256) { delete p; return nullptr; }
   p->aSlotBytes = p->aRows * 128;
   p->bSlotBytes = p->BN * 128;
-  p->numA = 2;
   if(!sizeRings(p, 0)) { delete p; return nullptr; }
   p->tmemCols = 32;
   while((int)p->tmemCols < 2 * p->BN) p->tmemCols *= 2;
@@ -781,23 +828,25 @@ ConvTcPlan* convTcCreate(
 void convTcDestroy(ConvTcPlan* p) { delete p; }
 
 // Decides how this convolution's outputs leave the SM.  When every output range (and the tile width) is a
-// multiple of 64 channels the residual is fetched and the outputs are written by TMA through swizzled
-// shared-memory blocks; otherwise the epilogue threads access global memory directly.
+// multiple of 32 channels the residual is fetched and the outputs are written by TMA through swizzled
+// shared-memory units; otherwise the epilogue threads access global memory directly.
 bool convTcSetEpilogue(ConvTcPlan* p, const Epilogue& ep) {
   p->tmaEpi = 0;
   const bool force = getenv("KB_TC_NO_TMA_EPI") != nullptr && atoi(getenv("KB_TC_NO_TMA_EPI")) != 0;
-  auto aligned64 = [](int c0, int c1) { return (c0 % 64) == 0 && (c1 % 64) == 0 && c1 > c0; };
-  bool ok = !force && (p->BN % 64) == 0 && p->BN / 64 <= TC_MAX_RES_BLOCKS;
-  if(ep.outRaw) ok = ok && aligned64(ep.rawC0, ep.rawC1) && (ep.rawStride % 8) == 0 && (reinterpret_cast<uintptr_t>(ep.outRaw) & 15) == 0;
-  if(ep.outAct) ok = ok && aligned64(ep.actC0, ep.actC1) && (ep.actStride % 8) == 0 && (reinterpret_cast<uintptr_t>(ep.outAct) & 15) == 0;
+  auto aligned32 = [](int c0, int c1) { return (c0 % 32) == 0 && (c1 % 32) == 0 && c1 > c0; };
+  bool ok = !force && (p->BN % 32) == 0 && p->BN / 32 <= 2 * TC_MAX_UNITS_PER_WARP;
+  if(ep.outRaw) ok = ok && aligned32(ep.rawC0, ep.rawC1) && (ep.rawStride % 8) == 0 && (reinterpret_cast<uintptr_t>(ep.outRaw) & 15) == 0;
+  if(ep.outAct) ok = ok && aligned32(ep.actC0, ep.actC1) && (ep.actStride % 8) == 0 && (reinterpret_cast<uintptr_t>(ep.outAct) & 15) == 0;
   if(ep.residual) ok = ok && (ep.resStride % 8) == 0 && ep.resStride >= p->outC && (reinterpret_cast<uintptr_t>(ep.residual) & 15) == 0;
   if(!ok || (!ep.outRaw && !ep.outAct)) return sizeRings(p, 0);
-  if(!sizeRings(p, p->BN / 64 + 2)) return sizeRings(p, 0);
+  p->epiWarpBytes = ((p->BN / 32 + 1) / 2 + 2) * TC_UNIT_BYTES;  // residual/raw units of this warp + two activated-output units
+  if(!sizeRings(p, TC_EPI_WARPS * p->epiWarpBytes)) return sizeRings(p, 0);
   const uint64_t rows = (uint64_t)p->rowsPadMax;
+  const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_64B;
   bool enc = true;
-  if(ep.residual) enc = enc && encode2d(&p->tmRes, p->dt, ep.residual, (uint64_t)p->outC, rows, (uint64_t)ep.resStride * 2, 64, TC_BM);
-  if(ep.outRaw) enc = enc && encode2d(&p->tmRaw, p->dt, ep.outRaw, (uint64_t)(ep.rawC1 - ep.rawC0), rows, (uint64_t)ep.rawStride * 2, 64, TC_BM);
-  if(ep.outAct) enc = enc && encode2d(&p->tmAct, p->dt, ep.outAct, (uint64_t)(ep.actC1 - ep.actC0), rows, (uint64_t)ep.actStride * 2, 64, TC_BM);
+  if(ep.residual) enc = enc && encode2d(&p->tmRes, p->dt, ep.residual, (uint64_t)p->outC, rows, (uint64_t)ep.resStride * 2, 32, 32, sw);
+  if(ep.outRaw) enc = enc && encode2d(&p->tmRaw, p->dt, ep.outRaw, (uint64_t)(ep.rawC1 - ep.rawC0), rows, (uint64_t)ep.rawStride * 2, 32, 32, sw);
+  if(ep.outAct) enc = enc && encode2d(&p->tmAct, p->dt, ep.outAct, (uint64_t)(ep.actC1 - ep.actC0), rows, (uint64_t)ep.actStride * 2, 32, 32, sw);
   if(!enc) return sizeRings(p, 0);
   p->tmaEpi = 1;
   return true;
@@ -812,12 +861,18 @@ cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epi
   a.g = g; a.ep = ep;
   a.inC = p->inC; a.outC = p->outC; a.kY = p->kY; a.kX = p->kX;
   a.BN = p->BN; a.kChunks = p->kChunks; a.haloPad = p->haloPad; a.aRows = p->aRows;
-  a.aSlotBytes = p->aSlotBytes; a.bSlotBytes = p->bSlotBytes; a.numA = p->numA; a.numB = p->numB;
+  a.aSlotBytes = p->aSlotBytes; a.bSlotBytes = p->bSlotBytes; a.numA = p->numA; a.numB = p->numB; a.residentB = p->residentB;
   a.idesc = p->idesc; a.tmemCols = p->tmemCols;
   a.status = statusWord;
   a.tmaEpi = p->tmaEpi;
+  a.epiWarpBytes = p->epiWarpBytes;
   const int numTiles = (g.rowsPad / TC_BM) * (p->outC / p->BN);
-  const int grid = numTiles < p->numSMs ? numTiles : p->numSMs;
+  int grid = numTiles < p->numSMs ? numTiles : p->numSMs;
+  if(p->residentB) {
+    const int nt = p->outC / p->BN;
+    grid = grid / nt * nt;  // each CTA keeps one channel tile
+    if(grid < nt) grid = nt;
+  }
   if(p->dt == DT_F16)
     convTcKernel<__half><<<grid, TC_THREADS, p->smemBytes, st>>>(p->tmA, p->tmB, p->tmRes, p->tmRaw, p->tmAct, a);
   else

@@ -46,7 +46,10 @@ class Engine {
   Engine& operator=(const Engine&) = delete;
 
   int precision() const { return dt_; }
-  int launchesPerForward() const { return (int)ops_.size(); }
+  int launchesPerForward(int n) const {
+    const int chunk = chunkBoards_ > 0 ? chunkBoards_ : n;
+    return (int)ops_.size() * ((n + chunk - 1) / chunk);
+  }
 
   void uploadInputs(int n, const float* spatial, const float* global, const int32_t* symmetry);
   void forwardResident(int n);
@@ -97,6 +100,8 @@ class Engine {
 
   int device_ = 0, dt_ = DT_F32, X_ = 19, Y_ = 19, maxBatch_ = 1, rowsPadMax_ = 0;
   bool forceSimt_ = false;
+  int chunkBoards_ = 0;   // boards per pass through the launch list (0 = whole batch)
+  int boardOffset_ = 0;   // first board of the chunk being launched
   cudaStream_t stream_ = nullptr;
   std::vector<void*> allocations_;
   std::map<std::string, DevBuf> scratch_;

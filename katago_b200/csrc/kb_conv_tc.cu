@@ -257,6 +257,10 @@ __device__ __forceinline__ void epilogue16(
     }
   }
   if(hasRes) {
+    if(ep.resMask) {
+#pragma unroll
+      for(int j = 0; j < 16; j++) v[j] *= mk;
+    }
     const uint32_t ru[8] = {res0.x, res0.y, res0.z, res0.w, res1.x, res1.y, res1.z, res1.w};
 #pragma unroll
     for(int j = 0; j < 8; j++) {
@@ -371,6 +375,10 @@ __device__ __forceinline__ bool epilogueTileTma(
     }
     uint8_t* rRow = es.sR + (size_t)j * TC_UNIT_BYTES + lane * 64;
     if(hasRes) {
+      if(ep.resMask) {
+#pragma unroll
+        for(int k = 0; k < 32; k++) v[k] *= mk;
+      }
 #pragma unroll
       for(int jj = 0; jj < 4; jj++) {
         const uint4 x = *reinterpret_cast<const uint4*>(rRow + ((jj ^ sw) << 4));
@@ -735,7 +743,7 @@ static int pickBN(int outC) {
 bool convTcEligible(int dt, int inC, int outC, int kY, int kX) {
   if(dt != DT_F16 && dt != DT_BF16) return false;
   if(!((kY == 1 && kX == 1) || (kY == 3 && kX == 3))) return false;
-  if(inC % TC_BK != 0 || outC % 16 != 0 || outC > 512) return false;
+  if(inC % TC_BK != 0 || outC % 16 != 0) return false;
   return pickBN(outC) >= 16;
 }
 

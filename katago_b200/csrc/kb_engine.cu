@@ -173,14 +173,76 @@ void Engine::addConvOp(const ConvDev& c, Epilogue ep, const std::string& tag) {
   }
 }
 
+// A matmul (or several sharing their input, concatenated along the output channels) as a 1x1 convolution:
+// MatMulW weights are [ic][oc], ConvW weights [oc][ic].
+static ConvW matmulsAsConv(const std::vector<const MatMulW*>& parts) {
+  ConvW c;
+  c.kY = 1; c.kX = 1; c.inC = parts[0]->inC; c.outC = 0;
+  for(const MatMulW* m : parts) {
+    if(m->inC != c.inC) throw std::runtime_error("internal: merged matmuls differ in input width");
+    c.outC += m->outC;
+  }
+  c.w.resize((size_t)c.inC * c.outC);
+  int oc0 = 0;
+  for(const MatMulW* m : parts) {
+    for(int ic = 0; ic < m->inC; ic++)
+      for(int oc = 0; oc < m->outC; oc++) c.w[(size_t)(oc0 + oc) * c.inC + ic] = m->w[(size_t)ic * m->outC + oc];
+    oc0 += m->outC;
+  }
+  return c;
+}
+
+// cos/sin tables of the rotary embedding, [tableHeads][pairs][S] (desc.cpp:1212-1275 computeRopeCosSin).
+static void ropeTables(const BlockW& b, int X, int Y, std::vector<float>& cosT, std::vector<float>& sinT, int& tableHeads) {
+  const int S = X * Y, pairs = b.qDim / 2;
+  if(b.learnableRope) {
+    tableHeads = b.kvHeads;
+    cosT.assign((size_t)b.kvHeads * pairs * S, 0.0f); sinT.assign((size_t)b.kvHeads * pairs * S, 0.0f);
+    for(int h = 0; h < b.kvHeads; h++)
+      for(int p = 0; p < pairs; p++) {
+        const float fx = b.ropeFreqs[(h * pairs + p) * 2 + 0], fy = b.ropeFreqs[(h * pairs + p) * 2 + 1];
+        for(int y = 0; y < Y; y++)
+          for(int x = 0; x < X; x++) {
+            const float angle = (float)x * fx + (float)y * fy;
+            const size_t idx = ((size_t)h * pairs + p) * S + y * X + x;
+            cosT[idx] = cosf(angle); sinT[idx] = sinf(angle);
+          }
+      }
+  }
+  else {
+    tableHeads = 1;
+    const int pairsPerDim = pairs / 2, dimHalf = b.qDim / 2;
+    cosT.assign((size_t)pairs * S, 0.0f); sinT.assign((size_t)pairs * S, 0.0f);
+    for(int p = 0; p < pairs; p++)
+      for(int y = 0; y < Y; y++)
+        for(int x = 0; x < X; x++) {
+          float angle;
+          if(p < pairsPerDim) angle = (float)y * (1.0f / powf(b.ropeTheta, (float)(2 * p) / (float)dimHalf));
+          else angle = (float)x * (1.0f / powf(b.ropeTheta, (float)(2 * (p - pairsPerDim)) / (float)dimHalf));
+          const size_t idx = (size_t)p * S + y * X + x;
+          cosT[idx] = cosf(angle); sinT[idx] = sinf(angle);
+        }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Block graph -> launches
 
-void Engine::emitStack(const std::vector<BlockW>& blocks, int C, void* raw, void* act, const BNW* tail, int depth) {
+void Engine::emitStack(const std::vector<BlockW>& blocks, int C, void* raw, void* act, const BNW* tail, int depth, bool actValid) {
   for(size_t i = 0; i < blocks.size(); i++) {
     const BNW* next = tail;
     if(i + 1 < blocks.size()) next = isConvBlock(blocks[i + 1]) ? &blocks[i + 1].preBN : nullptr;
+    if(isConvBlock(blocks[i]) && !actValid) {
+      // the producer of `raw` could not apply this block's norm (first block after a layer of another kind)
+      BNDev pb = makeBN({&blocks[i].preBN});
+      const int dt = dt_;
+      float* mask = mask_;
+      addOp("norm+act", 0.0, 2.0 * X_ * Y_ * C * dtypeSize(dt_), [=](cudaStream_t st, const Geom& g) {
+        return launchBnAct(st, dt, raw, C, pb.scale, pb.bias, pb.act, mask, dt, act, C, C, g);
+      });
+    }
     emitBlock(blocks[i], C, raw, act, next, depth);
+    actValid = next != nullptr;
   }
 }
 
@@ -264,18 +326,89 @@ void Engine::emitBlock(const BlockW& b, int C, void* raw, void* act, const BNW* 
     ConvDev c1 = makeConv({&b.conv1}, act, C, C);
     Epilogue e1;
     e1.outRaw = midRaw; e1.rawStride = mid; e1.rawC0 = 0; e1.rawC1 = mid;
-    if(!isConvBlock(b.inner[0])) throw std::runtime_error("transformer blocks are not supported by this build yet");
-    BNDev ib = makeBN({&b.inner[0].preBN});
-    e1.outAct = midAct; e1.actStride = mid; e1.actC0 = 0; e1.actC1 = mid; e1.scale = ib.scale; e1.bias = ib.bias; e1.act = ib.act;
+    const bool innerConv = isConvBlock(b.inner[0]);
+    if(innerConv) {
+      BNDev ib = makeBN({&b.inner[0].preBN});
+      e1.outAct = midAct; e1.actStride = mid; e1.actC0 = 0; e1.actC1 = mid; e1.scale = ib.scale; e1.bias = ib.bias; e1.act = ib.act;
+    }
     addConvOp(c1, e1, "");
-    emitStack(b.inner, mid, midRaw, midAct, &b.midBN, depth + 1);
+    emitStack(b.inner, mid, midRaw, midAct, &b.midBN, depth + 1, innerConv);
     ConvDev c2 = makeConv({&b.conv2}, midAct, mid, mid);
     Epilogue e2;
     finishEp(e2);
     addConvOp(c2, e2, "+res");
   }
+  else if(b.kind == BLOCK_ATTN) {
+    // eigenbackend.cpp:1307-1588: x += (Wo * attention(rope(Wq h), rope(Wk h), Wv h)) * mask, h = rmsnorm(x)
+    const int dt = dt_;
+    float* mask = mask_;
+    const double S = (double)X_ * Y_;
+    const int H = b.heads, Hkv = b.kvHeads, dq = b.qDim, dv = b.vDim;
+    const int qC = H * dq, kC = Hkv * dq, vC = Hkv * dv, qkvC = qC + kC + vC, oC = H * dv;
+    void* normed = scratch("tfNorm" + d + "_c" + std::to_string(C), (size_t)rowsPadMax_ * C * es);
+    void* qkv = scratch("tfQKV" + d + "_c" + std::to_string(qkvC), (size_t)rowsPadMax_ * qkvC * es);
+    void* attn = scratch("tfAttn" + d + "_c" + std::to_string(oC), (size_t)rowsPadMax_ * oC * es);
+    float* gamma = uploadF32(b.preLN.weight);
+    const float eps = b.preLN.eps;
+    addOp("rmsnorm", 0.0, 2.0 * S * C * es, [=](cudaStream_t st, const Geom& g) {
+      return launchRmsNorm(st, dt, raw, C, gamma, nullptr, eps, 0, mask, normed, C, C, g);
+    });
+    ConvW qkvW = matmulsAsConv({&b.q, &b.k, &b.v});
+    ConvDev cq = makeConv({&qkvW}, normed, C, C);
+    Epilogue eq;
+    eq.outRaw = qkv; eq.rawStride = qkvC; eq.rawC0 = 0; eq.rawC1 = qkvC;
+    addConvOp(cq, eq, "qkv");
+    if(b.useRope) {
+      std::vector<float> cosT, sinT;
+      int tableHeads = 1;
+      ropeTables(b, X_, Y_, cosT, sinT, tableHeads);
+      float* dCos = uploadF32(cosT);
+      float* dSin = uploadF32(sinT);
+      addOp("rope", 0.0, 2.0 * S * (qC + kC) * es, [=](cudaStream_t st, const Geom& g) {
+        cudaError_t e = launchRope(st, dt, qkv, qkvC, 0, H, dq, dCos, dSin, tableHeads, g);
+        if(e != cudaSuccess) return e;
+        return launchRope(st, dt, qkv, qkvC, qC, Hkv, dq, dCos, dSin, tableHeads, g);
+      });
+    }
+    addOp("attention", 2.0 * S * S * (dq + dv) * H, S * (qkvC + oC) * es, [=](cudaStream_t st, const Geom& g) {
+      return launchAttention(st, dt, qkv, qkvC, 0, qC, qC + kC, H, Hkv, dq, dv, mask, attn, oC, g);
+    });
+    ConvW outW = matmulsAsConv({&b.out});
+    ConvDev co = makeConv({&outW}, attn, oC, oC);
+    Epilogue eo;
+    finishEp(eo);
+    eo.resMask = 1;
+    addConvOp(co, eo, "attn out +res");
+  }
+  else if(b.kind == BLOCK_FFN) {
+    // eigenbackend.cpp:1592-1707: x += (W2 (silu(W1 h) * (Wg h))) * mask, h = rmsnorm(x)
+    const int dt = dt_;
+    float* mask = mask_;
+    const double S = (double)X_ * Y_;
+    const int F = b.ffnC;
+    void* normed = scratch("tfNorm" + d + "_c" + std::to_string(C), (size_t)rowsPadMax_ * C * es);
+    void* up = scratch("tfUp" + d + "_c" + std::to_string(2 * F), (size_t)rowsPadMax_ * 2 * F * es);
+    void* hid = scratch("tfHid" + d + "_c" + std::to_string(F), (size_t)rowsPadMax_ * F * es);
+    float* gamma = uploadF32(b.preLN.weight);
+    const float eps = b.preLN.eps;
+    addOp("rmsnorm", 0.0, 2.0 * S * C * es, [=](cudaStream_t st, const Geom& g) {
+      return launchRmsNorm(st, dt, raw, C, gamma, nullptr, eps, 0, mask, normed, C, C, g);
+    });
+    ConvW upW = matmulsAsConv({&b.linear1, &b.gate});
+    ConvDev cu = makeConv({&upW}, normed, C, C);
+    Epilogue eu;
+    eu.outRaw = up; eu.rawStride = 2 * F; eu.rawC0 = 0; eu.rawC1 = 2 * F;
+    addConvOp(cu, eu, "ffn up|gate");
+    addOp("swiglu", 0.0, 3.0 * S * F * es, [=](cudaStream_t st, const Geom& g) { return launchSwiGLU(st, dt, up, 2 * F, hid, F, F, g); });
+    ConvW downW = matmulsAsConv({&b.linear2});
+    ConvDev cd = makeConv({&downW}, hid, F, F);
+    Epilogue ed;
+    finishEp(ed);
+    ed.resMask = 1;
+    addConvOp(cd, ed, "ffn down +res");
+  }
   else {
-    throw std::runtime_error("transformer blocks are not supported by this build yet");
+    throw std::runtime_error("unknown block kind");
   }
 }
 
@@ -406,7 +539,6 @@ Engine::Engine(const Model& m, int device, int maxBatch, int X, int Y, int preci
   if(maxBatch < 1 || maxBatch > 65536) throw std::runtime_error("maxBatch out of range");
   if(X < 2 || Y < 2 || X > 50 || Y > 50) throw std::runtime_error("board size out of range");
   if(precision != DT_F32 && precision != DT_F16 && precision != DT_BF16) throw std::runtime_error("unknown precision");
-  if(m.normKind != 0) throw std::runtime_error("RMSNorm trunk tips are not supported by this build yet");
   device_ = pickDevice(device);
   dt_ = precision; X_ = X; Y_ = Y; maxBatch_ = maxBatch;
   forceSimt_ = getenv("KB_FORCE_SIMT") != nullptr && atoi(getenv("KB_FORCE_SIMT")) != 0;
@@ -462,12 +594,27 @@ Engine::Engine(const Model& m, int device, int maxBatch, int X, int Y, int preci
     Epilogue e;
     e.biasNC = gbias;
     e.outRaw = trunkRaw; e.rawStride = m.trunkC; e.rawC0 = 0; e.rawC1 = m.trunkC;
-    if(!isConvBlock(m.blocks[0])) throw std::runtime_error("transformer blocks are not supported by this build yet");
-    BNDev b0 = makeBN({&m.blocks[0].preBN});
-    e.outAct = trunkAct_; e.actStride = m.trunkC; e.actC0 = 0; e.actC1 = m.trunkC; e.scale = b0.scale; e.bias = b0.bias; e.act = b0.act;
+    if(isConvBlock(m.blocks[0])) {
+      BNDev b0 = makeBN({&m.blocks[0].preBN});
+      e.outAct = trunkAct_; e.actStride = m.trunkC; e.actC0 = 0; e.actC1 = m.trunkC; e.scale = b0.scale; e.bias = b0.bias; e.act = b0.act;
+    }
     addConvOp(c0, e, "initial");
   }
-  emitStack(m.blocks, m.trunkC, trunkRaw, trunkAct_, &m.tipBN, 0);
+  emitStack(m.blocks, m.trunkC, trunkRaw, trunkAct_, m.normKind == 0 ? &m.tipBN : nullptr, 0, isConvBlock(m.blocks[0]));
+  if(m.normKind != 0) {
+    // RMSNorm trunk tip (eigenbackend.cpp:923-1022); only SiLU is applied as its activation, as in the reference
+    float* gamma = uploadF32(m.tipRMS.gamma);
+    float* beta = uploadF32(m.tipRMS.beta);
+    const float eps = m.tipRMS.eps;
+    const int silu = m.tipRMS.act == KB_ACT_SILU ? 1 : 0, spatial = m.tipRMS.spatial, C = m.trunkC, dt = dt_;
+    float* boardScale = static_cast<float*>(alloc((size_t)maxBatch * sizeof(float)));
+    void* tact = trunkAct_;
+    float* mask = mask_;
+    addOp("rmsnorm", 0.0, 2.0 * S * C * es, [=](cudaStream_t st, const Geom& g) {
+      if(spatial) return launchSpatialRmsNorm(st, dt, trunkRaw, C, gamma, beta, eps, silu, mask, tact, C, C, boardScale, g);
+      return launchRmsNorm(st, dt, trunkRaw, C, gamma, beta, eps, silu, mask, tact, C, C, g);
+    });
+  }
   emitHeads(m, trunkAct_);
   cudaCheck(cudaStreamSynchronize(stream_), "engine setup");
 }
@@ -705,19 +852,21 @@ Engine::Engine(const void* layerBlob, size_t nbytes, int device, int n, int X, i
   else {
     BlockW bw;
     parseBlock(rd, bw);
-    if(!isConvBlock(bw)) throw std::runtime_error("transformer blocks are not supported by this build yet");
     const int C = bw.channels();
     layerInC_ = C; layerOutC_ = C;
     void* raw = alloc((size_t)rowsPadMax_ * C * es);
     void* act = alloc((size_t)rowsPadMax_ * C * es);
     layerIn_ = static_cast<float*>(alloc((size_t)n * S * C * sizeof(float)));
     layerOut_ = static_cast<float*>(alloc((size_t)n * S * C * sizeof(float)));
-    BNDev pb = makeBN({&bw.preBN});
+    BNDev pb;
+    if(isConvBlock(bw)) pb = makeBN({&bw.preBN});
     float* lin = layerIn_; float* lout = layerOut_; float* mask = mask_;
     addOp("to padded", 0, 0, [=](cudaStream_t st, const Geom& gg) { return launchToPadded(st, dt, lin, C, raw, C, gg); });
-    addOp("norm+act", 0, 0, [=](cudaStream_t st, const Geom& gg) {
-      return launchBnAct(st, dt, raw, C, pb.scale, pb.bias, pb.act, mask, dt, act, C, C, gg);
-    });
+    if(isConvBlock(bw)) {
+      addOp("norm+act", 0, 0, [=](cudaStream_t st, const Geom& gg) {
+        return launchBnAct(st, dt, raw, C, pb.scale, pb.bias, pb.act, mask, dt, act, C, C, gg);
+      });
+    }
     emitBlock(bw, C, raw, act, nullptr, 0);
     addOp("from padded", 0, 0, [=](cudaStream_t st, const Geom& gg) { return launchFromPadded(st, dt, raw, C, C, lout, gg); });
     layerNeedsMask_ = true;

@@ -93,7 +93,7 @@ class Engine {
   // Emits the launches of a block stack.  On entry `raw` holds the residual stream ([rows][C]) and, if the
   // first block wants it, `act` holds preBN+activation of it.  On exit `raw` is updated and `act` holds
   // tail-norm(raw) if `tail` is given.
-  void emitStack(const std::vector<BlockW>& blocks, int C, void* raw, void* act, const BNW* tail, int depth);
+  void emitStack(const std::vector<BlockW>& blocks, int C, void* raw, void* act, const BNW* tail, int depth, bool actValid);
   void emitBlock(const BlockW& b, int C, void* raw, void* act, const BNW* next, int depth);
   void emitHeads(const Model& m, const void* trunkAct);
   void runOps(int n);

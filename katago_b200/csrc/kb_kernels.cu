@@ -186,7 +186,7 @@ __global__ void __launch_bounds__(256) convSimtKernel(
       if(c >= outC) continue;
       float v = acc[i][j];
       if(ep.biasNC) v += ep.biasNC[(size_t)b * outC + c];
-      if(ep.residual) v += toF<T>(((const T*)ep.residual)[(size_t)m * ep.resStride + c]);
+      if(ep.residual) v = (ep.resMask ? v * mk : v) + toF<T>(((const T*)ep.residual)[(size_t)m * ep.resStride + c]);
       if(ep.outRaw && c >= ep.rawC0 && c < ep.rawC1) ((T*)ep.outRaw)[(size_t)m * ep.rawStride + (c - ep.rawC0)] = fromF<T>(v);
       if(ep.outAct && c >= ep.actC0 && c < ep.actC1) {
         const int ca = c - ep.actC0;

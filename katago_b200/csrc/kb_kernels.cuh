@@ -35,7 +35,8 @@ inline Geom makeGeom(int X, int Y, int n) {
 
 // What a convolution does with each accumulator v[row][c] (c in [0,outC)):
 //   v += biasNC[n][c]            (per-board bias: global-feature bias, gpool bias)   if biasNC
-//   v += residual[row][c]                                                            if residual
+//   v += residual[row][c]   (resMask: v = v*mask[row] + residual[row][c], the transformer blocks' masked residual add,
+//                            eigenbackend.cpp:1573-1582)                              if residual
 //   outRaw[row][c - rawC0] = v                     for c in [rawC0, rawC1)           if outRaw
 //   outAct[row][c - actC0] = mask[row]==1 ? act(v*scale[c-actC0] + bias[c-actC0]) : 0
 //                                                  for c in [actC0, actC1)           if outAct
@@ -45,6 +46,7 @@ struct Epilogue {
   const float* biasNC = nullptr;
   const void* residual = nullptr;
   int resStride = 0;
+  int resMask = 0;
   void* outRaw = nullptr;
   int rawStride = 0, rawC0 = 0, rawC1 = 0;
   void* outAct = nullptr;
@@ -116,5 +118,39 @@ void convTcDestroy(ConvTcPlan* p);
 // Binds the epilogue (output/residual tensors) to the plan; must be called once before the first launch.
 bool convTcSetEpilogue(ConvTcPlan* p, const Epilogue& ep);
 cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epilogue& ep, int* statusWord);
+
+}  // namespace kb
+
+namespace kb {
+
+// --- Transformer pieces (CUDA cores; the projections themselves run through the convolution path as 1x1) ---------
+
+// Per-position RMS norm over channels (eigenbackend.cpp:867-1022): out = x * rsqrt(mean_c(x^2) + eps) * gamma[c] (+ beta[c]),
+// optional SiLU, masked rows -> 0.  beta may be NULL.  in/out: [rowsPad][stride] of dtype dt.
+cudaError_t launchRmsNorm(
+  cudaStream_t st, int dt, const void* in, int inStride, const float* gamma, const float* beta, float eps, int silu,
+  const float* mask, void* out, int outStride, int C, Geom g);
+
+// Spatial RMS norm (eigenbackend.cpp:979-1020): one scale per board over all on-board points and channels.
+// scratch: [n] floats.
+cudaError_t launchSpatialRmsNorm(
+  cudaStream_t st, int dt, const void* in, int inStride, const float* gamma, const float* beta, float eps, int silu,
+  const float* mask, void* out, int outStride, int C, float* scratch, Geom g);
+
+// Rotary embedding on interleaved channel pairs (eigenbackend.cpp:1415-1451), in place on `heads` heads of `dim`
+// channels starting at column c0 of buf.  cosT/sinT: [tableHeads][dim/2][S]; head h uses table h*tableHeads/heads.
+cudaError_t launchRope(
+  cudaStream_t st, int dt, void* buf, int stride, int c0, int heads, int dim, const float* cosT, const float* sinT,
+  int tableHeads, Geom g);
+
+// Masked softmax attention over the board points of each board (eigenbackend.cpp:1455-1560).  qkv: [rowsPad][stride]
+// with Q at column qOff (heads*dq), K at kOff (kvHeads*dq), V at vOff (kvHeads*dv).  out: [rowsPad][outStride]
+// (heads*dv); rows of masked or padding points are written as zeros.
+cudaError_t launchAttention(
+  cudaStream_t st, int dt, const void* qkv, int stride, int qOff, int kOff, int vOff, int heads, int kvHeads, int dq, int dv,
+  const float* mask, void* out, int outStride, Geom g);
+
+// SwiGLU (eigenbackend.cpp:1660-1672): out[r][c] = silu(in[r][c]) * in[r][C + c].
+cudaError_t launchSwiGLU(cudaStream_t st, int dt, const void* in, int inStride, void* out, int outStride, int C, Geom g);
 
 }  // namespace kb

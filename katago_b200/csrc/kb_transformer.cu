@@ -1,0 +1,269 @@
+// CUDA-core kernels of the transformer trunk blocks: RMS norms, rotary embedding, masked attention over the
+// board points, SwiGLU.  The projections (Q/K/V, output, FFN) are 1x1 convolutions and use the convolution
+// kernels.  All of these are memory-bound except attention, which here is a straightforward shared-memory
+// implementation on CUDA cores (one block per board, head and 32-query slice).
+#include "kb_kernels.cuh"
+#include "../../include/kb_modelblob.h"
+
+namespace kb {
+
+template <typename T> __device__ __forceinline__ float tToF(T v);
+template <> __device__ __forceinline__ float tToF<float>(float v) { return v; }
+template <> __device__ __forceinline__ float tToF<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float tToF<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T fToT(float v);
+template <> __device__ __forceinline__ float fToT<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half fToT<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 fToT<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+#define KBT_DISPATCH_DT(dt, EXPR)                                  \
+  switch(dt) {                                                     \
+    case DT_F32: { using T = float; EXPR; break; }                 \
+    case DT_F16: { using T = __half; EXPR; break; }                \
+    case DT_BF16: { using T = __nv_bfloat16; EXPR; break; }        \
+    default: return cudaErrorInvalidValue;                         \
+  }
+
+__device__ __forceinline__ float warpSum(float v) {
+  for(int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warpMax(float v) {
+  for(int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// ---------------------------------------------------------------------------------------------
+// RMS norm: one warp per row
+
+template <typename T>
+__global__ void rmsNormKernel(
+  const T* __restrict__ in, int inStride, const float* __restrict__ gamma, const float* __restrict__ beta, float eps, int silu,
+  const float* __restrict__ mask, const float* __restrict__ boardScale, T* __restrict__ out, int outStride, int C, Geom g) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if(row >= g.rowsPad) return;
+  T* o = out + (size_t)row * outStride;
+  if(row >= g.rows || mask[row] == 0.0f) {
+    for(int c = lane; c < C; c += 32) o[c] = fToT<T>(0.0f);
+    return;
+  }
+  const T* x = in + (size_t)row * inStride;
+  float rms;
+  if(boardScale) rms = boardScale[row / g.PB];
+  else {
+    float ss = 0.0f;
+    for(int c = lane; c < C; c += 32) { float v = tToF<T>(x[c]); ss += v * v; }
+    ss = warpSum(ss);
+    rms = 1.0f / sqrtf(ss / (float)C + eps);
+  }
+  for(int c = lane; c < C; c += 32) {
+    float v = tToF<T>(x[c]) * rms * gamma[c];
+    if(beta) v += beta[c];
+    if(silu) v = v / (1.0f + expf(-v));
+    o[c] = fToT<T>(v);
+  }
+}
+
+cudaError_t launchRmsNorm(
+  cudaStream_t st, int dt, const void* in, int inStride, const float* gamma, const float* beta, float eps, int silu,
+  const float* mask, void* out, int outStride, int C, Geom g) {
+  const int warps = 8;
+  KBT_DISPATCH_DT(dt, (rmsNormKernel<T><<<(g.rowsPad + warps - 1) / warps, warps * 32, 0, st>>>(
+    (const T*)in, inStride, gamma, beta, eps, silu, mask, nullptr, (T*)out, outStride, C, g)));
+  return cudaGetLastError();
+}
+
+// per-board 1/rms over all on-board points and channels: one block per board
+template <typename T>
+__global__ void boardRmsKernel(const T* __restrict__ in, int inStride, const float* __restrict__ mask, float eps, float* __restrict__ outScale, int C, Geom g) {
+  const int n = blockIdx.x;
+  float ss = 0.0f, cnt = 0.0f;
+  for(int p = threadIdx.x >> 5; p < g.S; p += (blockDim.x >> 5)) {
+    const int y = p / g.X, x = p - y * g.X;
+    const size_t row = (size_t)n * g.PB + (size_t)y * g.RW + x;
+    if(mask[row] == 0.0f) continue;
+    const T* xr = in + row * inStride;
+    for(int c = threadIdx.x & 31; c < C; c += 32) { float v = tToF<T>(xr[c]); ss += v * v; }
+    if((threadIdx.x & 31) == 0) cnt += 1.0f;
+  }
+  __shared__ float sS[32], sC[32];
+  ss = warpSum(ss); cnt = warpSum(cnt);
+  if((threadIdx.x & 31) == 0) { sS[threadIdx.x >> 5] = ss; sC[threadIdx.x >> 5] = cnt; }
+  __syncthreads();
+  if(threadIdx.x < 32) {
+    float a = threadIdx.x < (blockDim.x >> 5) ? sS[threadIdx.x] : 0.0f;
+    float b = threadIdx.x < (blockDim.x >> 5) ? sC[threadIdx.x] : 0.0f;
+    a = warpSum(a); b = warpSum(b);
+    if(threadIdx.x == 0) outScale[n] = 1.0f / sqrtf(a / (b * (float)C) + eps);
+  }
+}
+
+cudaError_t launchSpatialRmsNorm(
+  cudaStream_t st, int dt, const void* in, int inStride, const float* gamma, const float* beta, float eps, int silu,
+  const float* mask, void* out, int outStride, int C, float* scratch, Geom g) {
+  const int warps = 8;
+  KBT_DISPATCH_DT(dt, (boardRmsKernel<T><<<g.n, 256, 0, st>>>((const T*)in, inStride, mask, eps, scratch, C, g)));
+  cudaError_t e = cudaGetLastError();
+  if(e != cudaSuccess) return e;
+  KBT_DISPATCH_DT(dt, (rmsNormKernel<T><<<(g.rowsPad + warps - 1) / warps, warps * 32, 0, st>>>(
+    (const T*)in, inStride, gamma, beta, eps, silu, mask, scratch, (T*)out, outStride, C, g)));
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Rotary embedding
+
+template <typename T>
+__global__ void ropeKernel(
+  T* __restrict__ buf, int stride, int c0, int heads, int dim, const float* __restrict__ cosT, const float* __restrict__ sinT,
+  int tableHeads, Geom g) {
+  const int pairs = dim / 2;
+  const size_t total = (size_t)g.n * g.S * heads * pairs;
+  for(size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const int p = (int)(idx % pairs);
+    size_t r = idx / pairs;
+    const int h = (int)(r % heads);
+    r /= heads;
+    const int xy = (int)(r % g.S), n = (int)(r / g.S);
+    const int y = xy / g.X, x = xy - y * g.X;
+    T* e = buf + ((size_t)n * g.PB + (size_t)y * g.RW + x) * stride + c0 + h * dim + 2 * p;
+    const int th = h * tableHeads / heads;
+    const size_t t = ((size_t)th * pairs + p) * g.S + xy;
+    const float c = cosT[t], s = sinT[t];
+    const float x0 = tToF<T>(e[0]), x1 = tToF<T>(e[1]);
+    e[0] = fToT<T>(x0 * c - x1 * s);
+    e[1] = fToT<T>(x0 * s + x1 * c);
+  }
+}
+
+cudaError_t launchRope(
+  cudaStream_t st, int dt, void* buf, int stride, int c0, int heads, int dim, const float* cosT, const float* sinT,
+  int tableHeads, Geom g) {
+  const size_t total = (size_t)g.n * g.S * heads * (dim / 2);
+  int grid = (int)((total + 255) / 256);
+  if(grid > 148 * 16) grid = 148 * 16;
+  KBT_DISPATCH_DT(dt, (ropeKernel<T><<<grid, 256, 0, st>>>((T*)buf, stride, c0, heads, dim, cosT, sinT, tableHeads, g)));
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Attention.  grid (ceil(S/32), n*heads), 256 threads = 8 warps, each warp owns 4 of the block's 32 queries.
+// K and V of the (board, kv head) live in shared memory as fp32 with an odd row pitch; scores of the warp's
+// current query live in shared memory too.
+
+template <typename T>
+__global__ void __launch_bounds__(256) attentionKernel(
+  const T* __restrict__ qkv, int stride, int qOff, int kOff, int vOff, int heads, int kvHeads, int dq, int dv,
+  const float* __restrict__ mask, T* __restrict__ out, int outStride, Geom g) {
+  extern __shared__ float sm[];
+  const int S = g.S;
+  const int kp = dq + 1, vp = dv + 1;
+  float* sK = sm;                      // [S][kp]
+  float* sV = sK + (size_t)S * kp;     // [S][vp]
+  float* sMask = sV + (size_t)S * vp;  // [S]
+  float* sP = sMask + S;               // [8][S]
+  float* sQ = sP + 8 * S;              // [8][dq]
+  const int n = blockIdx.y / heads, h = blockIdx.y % heads;
+  const int kvh = h / (heads / kvHeads);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const size_t boardRow = (size_t)n * g.PB;
+  for(int idx = threadIdx.x; idx < S * dq; idx += blockDim.x) {
+    const int p = idx / dq, d = idx - p * dq;
+    const int y = p / g.X, x = p - y * g.X;
+    sK[p * kp + d] = tToF<T>(qkv[(boardRow + (size_t)y * g.RW + x) * stride + kOff + kvh * dq + d]);
+  }
+  for(int idx = threadIdx.x; idx < S * dv; idx += blockDim.x) {
+    const int p = idx / dv, d = idx - p * dv;
+    const int y = p / g.X, x = p - y * g.X;
+    sV[p * vp + d] = tToF<T>(qkv[(boardRow + (size_t)y * g.RW + x) * stride + vOff + kvh * dv + d]);
+  }
+  for(int p = threadIdx.x; p < S; p += blockDim.x) {
+    const int y = p / g.X, x = p - y * g.X;
+    sMask[p] = mask[boardRow + (size_t)y * g.RW + x];
+  }
+  __syncthreads();
+  const float scale = 1.0f / sqrtf((float)dq);
+  float* myP = sP + warp * S;
+  float* myQ = sQ + warp * dq;
+  for(int qi = blockIdx.x * 32 + warp; qi < min(S, blockIdx.x * 32 + 32); qi += 8) {
+    const int y = qi / g.X, x = qi - y * g.X;
+    const size_t row = boardRow + (size_t)y * g.RW + x;
+    T* o = out + row * outStride + h * dv;
+    if(sMask[qi] == 0.0f) {
+      for(int d = lane; d < dv; d += 32) o[d] = fToT<T>(0.0f);
+      continue;
+    }
+    for(int d = lane; d < dq; d += 32) myQ[d] = tToF<T>(qkv[row * stride + qOff + h * dq + d]);
+    __syncwarp();
+    float mx = -1e30f;
+    for(int k = lane; k < S; k += 32) {
+      float s = -1e30f;
+      if(sMask[k] != 0.0f) {
+        const float* kr = sK + k * kp;
+        float dot = 0.0f;
+        for(int d = 0; d < dq; d++) dot = fmaf(myQ[d], kr[d], dot);
+        s = dot * scale;
+      }
+      myP[k] = s;
+      mx = fmaxf(mx, s);
+    }
+    mx = warpMax(mx);
+    float sum = 0.0f;
+    for(int k = lane; k < S; k += 32) {
+      const float e = (sMask[k] != 0.0f) ? expf(myP[k] - mx) : 0.0f;
+      myP[k] = e;
+      sum += e;
+    }
+    sum = warpSum(sum);
+    __syncwarp();
+    const float inv = 1.0f / sum;
+    for(int d = lane; d < dv; d += 32) {
+      float acc = 0.0f;
+      for(int k = 0; k < S; k++) acc = fmaf(myP[k], sV[k * vp + d], acc);
+      o[d] = fToT<T>(acc * inv);
+    }
+    __syncwarp();
+  }
+}
+
+cudaError_t launchAttention(
+  cudaStream_t st, int dt, const void* qkv, int stride, int qOff, int kOff, int vOff, int heads, int kvHeads, int dq, int dv,
+  const float* mask, void* out, int outStride, Geom g) {
+  const size_t smem = ((size_t)g.S * (dq + 1) + (size_t)g.S * (dv + 1) + g.S + 8 * (size_t)g.S + 8 * (size_t)dq) * sizeof(float);
+  if(smem > 227 * 1024) return cudaErrorInvalidValue;
+  dim3 grid((g.S + 31) / 32, g.n * heads);
+  switch(dt) {
+    case DT_F32: cudaFuncSetAttribute(attentionKernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); break;
+    case DT_F16: cudaFuncSetAttribute(attentionKernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); break;
+    default: cudaFuncSetAttribute(attentionKernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); break;
+  }
+  KBT_DISPATCH_DT(dt, (attentionKernel<T><<<grid, 256, smem, st>>>(
+    (const T*)qkv, stride, qOff, kOff, vOff, heads, kvHeads, dq, dv, mask, (T*)out, outStride, g)));
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// SwiGLU
+
+template <typename T>
+__global__ void swigluKernel(const T* __restrict__ in, int inStride, T* __restrict__ out, int outStride, int C, Geom g) {
+  const size_t total = (size_t)g.rowsPad * C;
+  for(size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t m = idx / C;
+    const int c = (int)(idx - m * C);
+    const float a = tToF<T>(in[m * inStride + c]);
+    const float b = tToF<T>(in[m * inStride + C + c]);
+    out[m * outStride + c] = fToT<T>((a / (1.0f + expf(-a))) * b);
+  }
+}
+
+cudaError_t launchSwiGLU(cudaStream_t st, int dt, const void* in, int inStride, void* out, int outStride, int C, Geom g) {
+  size_t total = (size_t)g.rowsPad * C;
+  int grid = (int)((total + 255) / 256);
+  if(grid > 148 * 32) grid = 148 * 32;
+  KBT_DISPATCH_DT(dt, (swigluKernel<T><<<grid, 256, 0, st>>>((const T*)in, inStride, (T*)out, outStride, C, g)));
+  return cudaGetLastError();
+}
+
+}  // namespace kb

@@ -37,6 +37,9 @@ CASES = [
     ("b18x4_random_rect", "gen:b18x4", "rectangle", "requireMaxBoardSize=False, maxBatchSize=7"),
     ("g170_b6c96_13", "g170-b6c96-s175395328-d26788732.bin.gz", "13", "requireMaxBoardSize=False"),
     ("g170e_b10c128_19", "g170e-b10c128-s1141046784-d204142634.bin.gz", "19", "requireMaxBoardSize=True, maxBatchSize=19"),
+    ("b7c96h3tfrs_13", "b7c96h3tfrs-test5-cnorm.bin.gz", "13", "requireMaxBoardSize=False, maxBatchSize=5"),
+    ("b4c256h4nbttflrs_rect", "b4c256h4nbttflrs-fson-silu-rsnh.bin.gz", "rectangle", "requireMaxBoardSize=False, maxBatchSize=6"),
+    ("b7c96h6kv3_9", "b7c96h6kv3qk32v16tflrs-fson-bnh.bin.gz", "9", "requireMaxBoardSize=True, maxBatchSize=12"),
 ]
 
 

@@ -81,6 +81,64 @@ def test_blocks_and_norm_with_masks(prec, tol, oracle):
         assert np.all(np.abs(out - ref) <= tol * np.maximum(np.maximum(np.abs(out), np.abs(ref)), floor)), layer["kind"]
 
 
+def _attn_block(g, C, heads, kv, dq, dv, rope):
+    b = dict(kind="transformer_attention_block", name=g.name("attn"), heads=heads, kvHeads=kv, qDim=dq, vDim=dv,
+             useRope=0 if rope == "none" else 1, learnableRope=1 if rope == "learnable" else 0, preLN=g.trms(C),
+             q=g.matmul(C, heads * dq), k=g.matmul(C, kv * dq), v=g.matmul(C, kv * dv), out=g.matmul(heads * dv, C))
+    b["preLN"]["w"] = g.rng.uniform(0.5, 1.5, C).astype(np.float32)
+    if rope == "learnable":
+        b["ropeFreqs"] = g.rng.uniform(-1.0, 1.0, kv * (dq // 2) * 2).astype(np.float32)
+    elif rope == "fixed":
+        b["ropeTheta"] = np.float32(100.0)
+    return b
+
+
+@pytest.mark.parametrize("prec,tol", [(capi.PRECISION_FP32, 2e-4), (capi.PRECISION_FP16, 0.03)])
+def test_transformer_blocks_with_masks(prec, tol, oracle):
+    """Attention (plain, grouped-query, fixed and learnable RoPE) and SwiGLU FFN blocks on masked boards."""
+    g = mf._Gen(77)
+    rng = np.random.default_rng(5)
+    mask = np.zeros((3, 19, 19), np.float32)
+    mask[0] = 1; mask[1, :13, :13] = 1; mask[2, :9, :11] = 1
+    floor = 1.0 if prec == capi.PRECISION_FP32 else 3.0
+    layers = [
+        (64, _attn_block(g, 64, 2, 2, 32, 32, "learnable")),
+        (96, _attn_block(g, 96, 6, 3, 32, 16, "fixed")),
+        (384, _attn_block(g, 384, 6, 6, 64, 64, "learnable")),
+        (64, _attn_block(g, 64, 4, 4, 16, 16, "none")),
+        (384, dict(kind="transformer_ffn_block", name="ffn", C=384, ffnC=1024, swiglu=1, preLN=g.trms(384), linear1=g.matmul(384, 1024),
+                   gate=g.matmul(384, 1024), linear2=g.matmul(1024, 384))),
+        (96, dict(kind="transformer_ffn_block", name="ffn2", C=96, ffnC=160, swiglu=1, preLN=g.trms(96), linear1=g.matmul(96, 160),
+                  gate=g.matmul(96, 160), linear2=g.matmul(160, 96))),
+    ]
+    for C, layer in layers:
+        x = rng.standard_normal((3, 19, 19, C)).astype(np.float32) * mask[..., None]
+        blob = mf.layer_blob(layer)
+        ref = oracle.eval_layer(blob, x, mask, C)
+        out = capi.eval_layer(blob, x, mask, C, precision=prec)
+        assert np.all(np.abs(out - ref) <= tol * np.maximum(np.maximum(np.abs(out), np.abs(ref)), floor)), (layer["kind"], C, np.abs(out - ref).max())
+
+
+@pytest.mark.parametrize("prec", [capi.PRECISION_FP32, capi.PRECISION_FP16])
+def test_transformer_net_vs_oracle(prec, oracle):
+    """BASELINE configs[3] architecture (conv stem to d=384, pre-norm attention + SwiGLU layers of 6 heads x 64, FFN 1024,
+    RMSNorm+SiLU tip, standard heads) with 3 layers, and a small net with fixed RoPE; mixed board sizes and symmetries."""
+    for model_tree, n in [(mf.make_transformer(layers=3), 4), (mf.make_transformer(seed=9, layers=2, d=64, heads=2, head_dim=32, ffn=96, rope="fixed"), 5)]:
+        blob = mf.to_blob(model_tree)
+        sizes = ([19, 13, 9, 19, 11])[:n]
+        sp, gl = mf.random_positions(n, seed=2003, board_sizes=sizes)
+        syms = (np.arange(n) * 5 % 8).astype(np.int32)
+        h = capi.Handle(capi.Model(blob), n, precision=prec)
+        got = h.forward(sp, gl, syms)
+        h.close()
+        ref = unsymmetrise_outputs(oracle.OracleModel(blob).forward(symmetrise_inputs(sp, syms), gl), syms)
+        mask = sp[..., 0].reshape(n, -1)
+        if prec == capi.PRECISION_FP32:
+            _assert_fp32_close(got, ref, mask)
+        else:
+            _assert_reduced_close(got, ref, mask)
+
+
 # --- whole networks ----------------------------------------------------------------------------
 
 def _run_case(name, prec, oracle, syms=None):

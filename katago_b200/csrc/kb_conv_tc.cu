@@ -19,6 +19,7 @@
 // Every wait is bounded: on time-out the kernel records a code in the status word and all roles
 // leave through the common exit, which still frees TMEM.
 #include "kb_kernels.cuh"
+#include "kb_tc_ptx.cuh"
 #include "../../include/kb_modelblob.h"
 
 #include <cuda.h>
@@ -27,136 +28,6 @@
 #include <mutex>
 
 namespace kb {
-
-// ---------------------------------------------------------------------------------------------
-// PTX wrappers
-
-__device__ __forceinline__ uint32_t smemU32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbarInit(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbarExpectTx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbarArrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t mbarTryWait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-    "{\n\t.reg .pred p;\n\t"
-    "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-    "selp.u32 %0, 1, 0, p;\n\t}"
-    : "=r"(ok)
-    : "r"(bar), "r"(parity)
-    : "memory");
-  return ok;
-}
-__device__ __forceinline__ uint64_t globalTimerNs() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-
-// Bounded wait (about 2 s).  Returns false on time-out or if another role already gave up.
-__device__ __forceinline__ bool mbarWait(uint32_t bar, uint32_t parity, volatile int* abortFlag) {
-  if(mbarTryWait(bar, parity)) return true;
-  const uint64_t t0 = globalTimerNs();
-  uint32_t spins = 0;
-  while(true) {
-    if(mbarTryWait(bar, parity)) return true;
-    if((++spins & 63u) == 0u) {
-      if(*abortFlag) return false;
-      if(globalTimerNs() - t0 > 2000000000ull) return false;
-    }
-  }
-}
-
-__device__ __forceinline__ void tmaLoad2d(uint32_t dst, const CUtensorMap* tmap, int c0, int c1, uint32_t bar) {
-  asm volatile(
-    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-    ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1)
-    : "memory");
-}
-
-// shared -> global tile store (asynchronous, tracked by the issuing thread's bulk groups)
-__device__ __forceinline__ void tmaStore2d(const CUtensorMap* tmap, uint32_t src, int c0, int c1) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap), "r"(src), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void bulkCommit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulkWaitRead0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void bulkWaitRead1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
-__device__ __forceinline__ void bulkWaitAll() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void fenceProxyAsync() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-__device__ __forceinline__ void tmemAlloc(uint32_t dstSmem, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dstSmem), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tmemRelinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmemDealloc(uint32_t taddr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcFenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// D[tmem] (+)= A[smem] * B[smem], M=128, N from idesc, K=16 (fp16/bf16), fp32 accumulate.
-__device__ __forceinline__ void umma(uint32_t dTmem, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-    "{\n\t.reg .pred p;\n\t"
-    "setp.ne.b32 p, %4, 0;\n\t"
-    "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-    ::"r"(dTmem), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
-    : "memory");
-}
-// Same, with the two shared-memory descriptors given as their low words (start address + leading offset) and the
-// high word both share (stride offset, version, swizzle mode); keeps the issuing thread's instruction count low.
-__device__ __forceinline__ void ummaLoHi(uint32_t dTmem, uint32_t aLo, uint32_t bLo, uint32_t descHi, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-    "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
-    "mov.b64 da, {%1, %3};\n\t"
-    "mov.b64 db, {%2, %3};\n\t"
-    "setp.ne.b32 p, %5, 0;\n\t"
-    "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
-    ::"r"(dTmem), "r"(aLo), "r"(bLo), "r"(descHi), "r"(idesc), "r"(accumulate)
-    : "memory");
-}
-// mbarrier arrives once all MMAs issued so far by this thread have completed.
-__device__ __forceinline__ void ummaCommit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-// 32 lanes x 32 consecutive 32-bit columns -> 32 registers per thread (thread t reads lane base+t).
-__device__ __forceinline__ void tmemLd32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-      "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-      "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-      "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-    : "r"(taddr)
-    : "memory");
-}
-__device__ __forceinline__ void tmemLdWait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows 128 B apart, 8-row groups
-// 1024 B apart (stride byte offset), descriptor version 1 (Blackwell).  The swizzle is a function of the
-// absolute shared-memory address bits, so a start address moved by whole rows (any multiple of 128 B) or by
-// 32-byte K steps inside the atom addresses the data exactly where TMA put it; the base-offset field stays 0
-// (measured: results match the CUDA-core kernel bit for bit in that configuration only).
-__device__ __forceinline__ uint64_t makeSmemDesc(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);  // start address, 16-byte units
-  d |= (uint64_t)1 << 16;                    // leading byte offset (unused for swizzled K-major)
-  d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset
-  d |= (uint64_t)1 << 46;                    // version
-  d |= (uint64_t)2 << 61;                    // SWIZZLE_128B
-  return d;
-}
 
 // ---------------------------------------------------------------------------------------------
 // Fast activations for the reduced-precision epilogue

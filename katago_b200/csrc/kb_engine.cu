@@ -370,9 +370,21 @@ void Engine::emitBlock(const BlockW& b, int C, void* raw, void* act, const BNW* 
         return launchRope(st, dt, qkv, qkvC, qC, Hkv, dq, dCos, dSin, tableHeads, g);
       });
     }
-    addOp("attention", 2.0 * S * S * (dq + dv) * H, S * (qkvC + oC) * es, [=](cudaStream_t st, const Geom& g) {
-      return launchAttention(st, dt, qkv, qkvC, 0, qC, qC + kC, H, Hkv, dq, dv, mask, attn, oC, g);
-    });
+    const bool attnTc = !forceSimt_ && attentionTcEligible(dt_, dq, dv, X_, Y_, qkvC, 0, qC, qC + kC, oC);
+    if(attnTc) {
+      AttnTcPlan* ap = attentionTcCreate(dt_, qkv, qkvC, qkvC, rowsPadMax_);
+      if(!ap) throw std::runtime_error("failed to create the tensor-core attention plan (TMA descriptor encoding)");
+      attnPlans_.push_back(ap);
+      int* status = statusWord_;
+      addOp("attention tcgen05", 2.0 * S * S * (dq + dv) * H, S * (qkvC + oC) * es, [=](cudaStream_t st, const Geom& g) {
+        return launchAttentionTc(st, ap, 0, qC, qC + kC, H, Hkv, mask, attn, oC, g, status);
+      });
+    }
+    else {
+      addOp("attention simt", 2.0 * S * S * (dq + dv) * H, S * (qkvC + oC) * es, [=](cudaStream_t st, const Geom& g) {
+        return launchAttention(st, dt, qkv, qkvC, 0, qC, qC + kC, H, Hkv, dq, dv, mask, attn, oC, g);
+      });
+    }
     ConvW outW = matmulsAsConv({&b.out});
     ConvDev co = makeConv({&outW}, attn, oC, oC);
     Epilogue eo;
@@ -624,6 +636,7 @@ Engine::~Engine() {
   if(stream_) cudaStreamSynchronize(stream_);
   for(cudaEvent_t e : events_) cudaEventDestroy(e);
   for(ConvTcPlan* p : tcPlans_) convTcDestroy(p);
+  for(AttnTcPlan* p : attnPlans_) attentionTcDestroy(p);
   for(void* p : allocations_) cudaFree(p);
   if(statusHost_) cudaFreeHost(statusHost_);
   if(flushBuf_) cudaFree(flushBuf_);

@@ -106,6 +106,7 @@ class Engine {
   std::vector<void*> allocations_;
   std::map<std::string, DevBuf> scratch_;
   std::vector<ConvTcPlan*> tcPlans_;
+  std::vector<AttnTcPlan*> attnPlans_;
   std::vector<Op> ops_;
   std::vector<OpClass> classes_;
   bool profiling_ = false;

@@ -208,24 +208,40 @@ cudaError_t launchConvSimt(
 // ---------------------------------------------------------------------------------------------
 // Small matmul: one block per row
 
+constexpr int MM_ROWS = 4;
+
 __global__ void matMulSmallKernel(
   const float* __restrict__ in, int inC, const float* __restrict__ w, int outC, const float* __restrict__ bias, int act,
-  float* __restrict__ out) {
-  extern __shared__ float sIn[];
-  const int r = blockIdx.x;
-  for(int i = threadIdx.x; i < inC; i += blockDim.x) sIn[i] = in[(size_t)r * inC + i];
+  float* __restrict__ out, int rows) {
+  extern __shared__ float sIn[];  // [MM_ROWS][inC]
+  const int r0 = blockIdx.x * MM_ROWS;
+  const int nr = min(MM_ROWS, rows - r0);
+  for(int i = threadIdx.x; i < MM_ROWS * inC; i += blockDim.x) {
+    const int r = i / inC;
+    sIn[i] = r < nr ? in[(size_t)r0 * inC + i] : 0.0f;
+  }
   __syncthreads();
   for(int oc = threadIdx.x; oc < outC; oc += blockDim.x) {
-    float s = 0.0f;
-    for(int ic = 0; ic < inC; ic++) s = fmaf(sIn[ic], w[(size_t)ic * outC + oc], s);
-    if(bias) s += bias[oc];
-    out[(size_t)r * outC + oc] = applyActF(s, act);
+    float s[MM_ROWS];
+#pragma unroll
+    for(int r = 0; r < MM_ROWS; r++) s[r] = 0.0f;
+#pragma unroll 8
+    for(int ic = 0; ic < inC; ic++) {
+      const float wv = w[(size_t)ic * outC + oc];
+#pragma unroll
+      for(int r = 0; r < MM_ROWS; r++) s[r] = fmaf(sIn[r * inC + ic], wv, s[r]);
+    }
+    const float b = bias ? bias[oc] : 0.0f;
+#pragma unroll
+    for(int r = 0; r < MM_ROWS; r++)
+      if(r < nr) out[(size_t)(r0 + r) * outC + oc] = applyActF(s[r] + b, act);
   }
 }
 
 cudaError_t launchMatMulSmall(
   cudaStream_t st, const float* in, int inC, const float* w, int outC, const float* bias, int act, float* out, int rows) {
-  matMulSmallKernel<<<rows, 128, inC * sizeof(float), st>>>(in, inC, w, outC, bias, act, out);
+  const int threads = outC >= 128 ? 128 : (outC > 32 ? 64 : 32);
+  matMulSmallKernel<<<(rows + MM_ROWS - 1) / MM_ROWS, threads, MM_ROWS * inC * sizeof(float), st>>>(in, inC, w, outC, bias, act, out, rows);
   return cudaGetLastError();
 }
 
@@ -264,9 +280,62 @@ __global__ void gpoolKernel(
   }
 }
 
+// Vectorised variant: one block per board, each thread owns 8 adjacent channels (16 bytes) of every k-th point.
+template <typename T>
+__global__ void __launch_bounds__(256) gpoolVec8Kernel(
+  const T* __restrict__ in, int inStride, int c0, int C, const float* __restrict__ mask, const float* __restrict__ maskSum,
+  float* __restrict__ out, int valueHead, Geom g) {
+  extern __shared__ float sRed[];  // [groups][C] sums then [groups][C] maxima
+  const int n = blockIdx.x;
+  const int vecs = C / 8;
+  const int groups = blockDim.x / vecs;
+  const int cg = threadIdx.x % vecs, rg = threadIdx.x / vecs;
+  float s[8], mx[8];
+#pragma unroll
+  for(int j = 0; j < 8; j++) { s[j] = 0.0f; mx[j] = -1.0f; }
+  if(rg < groups) {
+    for(int p = rg; p < g.S; p += groups) {
+      const int y = p / g.X, x = p - y * g.X;
+      const size_t row = (size_t)n * g.PB + (size_t)y * g.RW + x;
+      const uint4 v4 = *reinterpret_cast<const uint4*>(in + row * inStride + c0 + cg * 8);
+      const T* ve = reinterpret_cast<const T*>(&v4);
+      const float mOff = mask[row] - 1.0f;
+#pragma unroll
+      for(int j = 0; j < 8; j++) {
+        const float v = toF<T>(ve[j]);
+        s[j] += v;
+        mx[j] = fmaxf(mx[j], v + mOff);
+      }
+    }
+#pragma unroll
+    for(int j = 0; j < 8; j++) { sRed[rg * C + cg * 8 + j] = s[j]; sRed[(groups + rg) * C + cg * 8 + j] = mx[j]; }
+  }
+  __syncthreads();
+  for(int c = threadIdx.x; c < C; c += blockDim.x) {
+    float ss = 0.0f, mm = -1.0f;
+    for(int k = 0; k < groups; k++) { ss += sRed[k * C + c]; mm = fmaxf(mm, sRed[(groups + k) * C + c]); }
+    const float div = maskSum[n];
+    const float sq = sqrtf(div);
+    const float mean = ss / div;
+    float* o = out + (size_t)n * 3 * C;
+    o[c] = mean;
+    o[C + c] = mean * (sq - 14.0f) * 0.1f;
+    o[2 * C + c] = valueHead ? mean * ((sq - 14.0f) * (sq - 14.0f) * 0.01f - 0.1f) : mm;
+  }
+}
+
 cudaError_t launchGPool(
   cudaStream_t st, int dt, const void* in, int inStride, int c0, int C, const float* mask, const float* maskSum,
   float* out, int valueHead, Geom g) {
+  if(dt != DT_F32 && (C % 8) == 0 && (c0 % 8) == 0 && (inStride % 8) == 0 && C / 8 <= 256 && (reinterpret_cast<uintptr_t>(in) & 15) == 0) {
+    const int groups = 256 / (C / 8);
+    const size_t smem = (size_t)2 * groups * C * sizeof(float);
+    if(dt == DT_F16)
+      gpoolVec8Kernel<__half><<<g.n, 256, smem, st>>>((const __half*)in, inStride, c0, C, mask, maskSum, out, valueHead, g);
+    else
+      gpoolVec8Kernel<__nv_bfloat16><<<g.n, 256, smem, st>>>((const __nv_bfloat16*)in, inStride, c0, C, mask, maskSum, out, valueHead, g);
+    return cudaGetLastError();
+  }
   dim3 grid(g.n, (C + 31) / 32), block(32, 8);
   KB_DISPATCH_DT(dt, (gpoolKernel<T><<<grid, block, 0, st>>>((const T*)in, inStride, c0, C, mask, maskSum, out, valueHead, g)));
   return cudaGetLastError();

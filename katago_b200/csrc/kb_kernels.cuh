@@ -153,4 +153,13 @@ cudaError_t launchAttention(
 // SwiGLU (eigenbackend.cpp:1660-1672): out[r][c] = silu(in[r][c]) * in[r][C + c].
 cudaError_t launchSwiGLU(cudaStream_t st, int dt, const void* in, int inStride, void* out, int outStride, int C, Geom g);
 
+// Tensor-core attention (fp16/bf16, head dimension 64, boards whose Y*(X+1) rows fit 384 keys).
+struct AttnTcPlan;
+bool attentionTcEligible(int dt, int dq, int dv, int X, int Y, int stride, int qOff, int kOff, int vOff, int outStride);
+AttnTcPlan* attentionTcCreate(int dt, const void* qkv, int stride, int totalCols, int rowsPadMax);
+void attentionTcDestroy(AttnTcPlan* p);
+cudaError_t launchAttentionTc(
+  cudaStream_t st, const AttnTcPlan* p, int qOff, int kOff, int vOff, int heads, int kvHeads, const float* mask, void* out,
+  int outStride, Geom g, int* statusWord);
+
 }  // namespace kb

@@ -137,9 +137,47 @@ __global__ void ropeKernel(
   }
 }
 
+// 8 channels (4 pairs) per thread
+template <typename T>
+__global__ void ropeVec8Kernel(
+  T* __restrict__ buf, int stride, int c0, int heads, int dim, const float* __restrict__ cosT, const float* __restrict__ sinT,
+  int tableHeads, Geom g) {
+  const int pairs = dim / 2, vecsPerHead = dim / 8;
+  const size_t total = (size_t)g.n * g.S * heads * vecsPerHead;
+  for(size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const int v = (int)(idx % vecsPerHead);
+    size_t r = idx / vecsPerHead;
+    const int h = (int)(r % heads);
+    r /= heads;
+    const int xy = (int)(r % g.S), n = (int)(r / g.S);
+    const int y = xy / g.X, x = xy - y * g.X;
+    T* e = buf + ((size_t)n * g.PB + (size_t)y * g.RW + x) * stride + c0 + h * dim + v * 8;
+    uint4 val = *reinterpret_cast<uint4*>(e);
+    T* ve = reinterpret_cast<T*>(&val);
+    const int th = h * tableHeads / heads;
+#pragma unroll
+    for(int j = 0; j < 4; j++) {
+      const size_t t = ((size_t)th * pairs + v * 4 + j) * g.S + xy;
+      const float c = cosT[t], s = sinT[t];
+      const float x0 = tToF<T>(ve[2 * j]), x1 = tToF<T>(ve[2 * j + 1]);
+      ve[2 * j] = fToT<T>(x0 * c - x1 * s);
+      ve[2 * j + 1] = fToT<T>(x0 * s + x1 * c);
+    }
+    *reinterpret_cast<uint4*>(e) = val;
+  }
+}
+
 cudaError_t launchRope(
   cudaStream_t st, int dt, void* buf, int stride, int c0, int heads, int dim, const float* cosT, const float* sinT,
   int tableHeads, Geom g) {
+  if(dt != DT_F32 && (dim % 8) == 0 && (stride % 8) == 0 && (c0 % 8) == 0 && (reinterpret_cast<uintptr_t>(buf) & 15) == 0) {
+    const size_t totalV = (size_t)g.n * g.S * heads * (dim / 8);
+    int gridV = (int)((totalV + 255) / 256);
+    if(gridV > 148 * 32) gridV = 148 * 32;
+    if(dt == DT_F16) ropeVec8Kernel<__half><<<gridV, 256, 0, st>>>((__half*)buf, stride, c0, heads, dim, cosT, sinT, tableHeads, g);
+    else ropeVec8Kernel<__nv_bfloat16><<<gridV, 256, 0, st>>>((__nv_bfloat16*)buf, stride, c0, heads, dim, cosT, sinT, tableHeads, g);
+    return cudaGetLastError();
+  }
   const size_t total = (size_t)g.n * g.S * heads * (dim / 2);
   int grid = (int)((total + 255) / 256);
   if(grid > 148 * 16) grid = 148 * 16;
@@ -258,7 +296,38 @@ __global__ void swigluKernel(const T* __restrict__ in, int inStride, T* __restri
   }
 }
 
+template <typename T>
+__global__ void swigluVec8Kernel(const T* __restrict__ in, int inStride, T* __restrict__ out, int outStride, int C, Geom g) {
+  const int vecs = C / 8;
+  const size_t total = (size_t)g.rowsPad * vecs;
+  for(size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t m = idx / vecs;
+    const int c = (int)(idx - m * vecs) * 8;
+    const uint4 av = *reinterpret_cast<const uint4*>(in + m * inStride + c);
+    const uint4 bv = *reinterpret_cast<const uint4*>(in + m * inStride + C + c);
+    const T* ae = reinterpret_cast<const T*>(&av);
+    const T* be = reinterpret_cast<const T*>(&bv);
+    uint4 ov;
+    T* oe = reinterpret_cast<T*>(&ov);
+#pragma unroll
+    for(int j = 0; j < 8; j++) {
+      const float x = tToF<T>(ae[j]);
+      oe[j] = fToT<T>(__fdividef(x, 1.0f + __expf(-x)) * tToF<T>(be[j]));
+    }
+    *reinterpret_cast<uint4*>(out + m * outStride + c) = ov;
+  }
+}
+
 cudaError_t launchSwiGLU(cudaStream_t st, int dt, const void* in, int inStride, void* out, int outStride, int C, Geom g) {
+  if(dt != DT_F32 && (C % 8) == 0 && (inStride % 8) == 0 && (outStride % 8) == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0 &&
+     (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    const size_t totalV = (size_t)g.rowsPad * (C / 8);
+    int gridV = (int)((totalV + 255) / 256);
+    if(gridV > 148 * 32) gridV = 148 * 32;
+    if(dt == DT_F16) swigluVec8Kernel<__half><<<gridV, 256, 0, st>>>((const __half*)in, inStride, (__half*)out, outStride, C, g);
+    else swigluVec8Kernel<__nv_bfloat16><<<gridV, 256, 0, st>>>((const __nv_bfloat16*)in, inStride, (__nv_bfloat16*)out, outStride, C, g);
+    return cudaGetLastError();
+  }
   size_t total = (size_t)g.rowsPad * C;
   int grid = (int)((total + 255) / 256);
   if(grid > 148 * 32) grid = 148 * 32;

@@ -32,23 +32,70 @@ namespace kb {
 // ---------------------------------------------------------------------------------------------
 // Fast activations for the reduced-precision epilogue
 
+__device__ __forceinline__ float ex2Approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcpApprox(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// mish(x) = x*tanh(softplus(x)) = x - 2x / (n^2 + 2n + 2) with n = e^x (exact identity).  Large x: n = inf, the
+// reciprocal is 0 and the result is x; very negative x: n = 0 and the result is 0.  No clamp is needed.
 __device__ __forceinline__ float fastMish(float x) {
-  // x*tanh(softplus(x)) = x * w/(w+2), w = e^x (e^x + 2); exact identity, evaluated with ex2/rcp approximations.
-  float e = __expf(fminf(x, 20.0f));
-  float w = e * (e + 2.0f);
-  return x * __fdividef(w, w + 2.0f);
+  const float n = ex2Approx(x * 1.4426950408889634f);
+  const float r = rcpApprox(fmaf(n, n + 2.0f, 2.0f));
+  return fmaf(-2.0f, x * r, x);
 }
 __device__ __forceinline__ float fastAct(float x, int act) {
   switch(act) {
     case KB_ACT_RELU: return fmaxf(x, 0.0f);
     case KB_ACT_MISH: return fastMish(x);
-    case KB_ACT_SILU: return __fdividef(x, 1.0f + __expf(-x));
+    case KB_ACT_SILU: return x * rcpApprox(1.0f + ex2Approx(x * -1.4426950408889634f));
     case KB_ACT_MISH_SCALE8: {
-      float e = __expf(fminf(8.0f * x, 20.0f));
-      float w = e * (e + 2.0f);
-      return x * __fdividef(w, w + 2.0f);
+      const float n = ex2Approx(x * (8.0f * 1.4426950408889634f));
+      const float r = rcpApprox(fmaf(n, n + 2.0f, 2.0f));
+      return fmaf(-2.0f, x * r, x);
     }
     default: return x;
+  }
+}
+
+// G values at once, stage by stage, so that G independent dependency chains are in flight per thread: the special
+// function unit has a long latency and an epilogue warp has only one other warp to share its scheduler with.
+template <int ACT, int G>
+__device__ __forceinline__ void actStaged(float (&x)[G]) {
+  if(ACT == KB_ACT_RELU) {
+#pragma unroll
+    for(int i = 0; i < G; i++) x[i] = fmaxf(x[i], 0.0f);
+  }
+  else if(ACT == KB_ACT_MISH || ACT == KB_ACT_MISH_SCALE8) {
+    const float kk = (ACT == KB_ACT_MISH ? 1.0f : 8.0f) * 1.4426950408889634f;
+    float n[G];
+#pragma unroll
+    for(int i = 0; i < G; i++) n[i] = x[i] * kk;
+#pragma unroll
+    for(int i = 0; i < G; i++) n[i] = ex2Approx(n[i]);
+#pragma unroll
+    for(int i = 0; i < G; i++) n[i] = fmaf(n[i], n[i] + 2.0f, 2.0f);
+#pragma unroll
+    for(int i = 0; i < G; i++) n[i] = rcpApprox(n[i]);
+#pragma unroll
+    for(int i = 0; i < G; i++) x[i] = fmaf(-2.0f, x[i] * n[i], x[i]);
+  }
+  else if(ACT == KB_ACT_SILU) {
+    float n[G];
+#pragma unroll
+    for(int i = 0; i < G; i++) n[i] = x[i] * -1.4426950408889634f;
+#pragma unroll
+    for(int i = 0; i < G; i++) n[i] = ex2Approx(n[i]);
+#pragma unroll
+    for(int i = 0; i < G; i++) n[i] = rcpApprox(1.0f + n[i]);
+#pragma unroll
+    for(int i = 0; i < G; i++) x[i] *= n[i];
   }
 }
 
@@ -218,7 +265,7 @@ template <typename T, int ACT>
 __device__ __forceinline__ bool epilogueTileTma(
   const ConvTcArgs& a, const CUtensorMap* tmRaw, const CUtensorMap* tmAct, uint32_t tmemAcc, int q, int half, int lane,
   int m0, int n0, float mk, const float* biasRow, EpiWarp& es, uint32_t tileParity, volatile int* abortFlag,
-  const float* sScale, const float* sBias) {
+  const float* sScale, const float* sBias, const CUtensorMap* tmRes, bool hasNext, int nextM0, int nextN0) {
   const Epilogue& ep = a.ep;
   const bool hasRes = ep.residual != nullptr;
   const int units = a.BN / 32;
@@ -277,29 +324,28 @@ __device__ __forceinline__ bool epilogueTileTma(
     if(doAct) {
       uint8_t* oRow = oUnit + lane * 64;
       const int ca = c - ep.actC0;
-      if(mk == 1.0f) {
-        const float4* sp = reinterpret_cast<const float4*>(sScale + ca);
-        const float4* bp = reinterpret_cast<const float4*>(sBias + ca);
+      const float4* sp = reinterpret_cast<const float4*>(sScale + ca);
+      const float4* bp = reinterpret_cast<const float4*>(sBias + ca);
+      const bool on = mk == 1.0f;
 #pragma unroll
-        for(int jj = 0; jj < 4; jj++) {
-          float o8[8];
+      for(int hh = 0; hh < 2; hh++) {
+        float x[16];
 #pragma unroll
-          for(int k = 0; k < 2; k++) {
-            const float4 s4 = sp[2 * jj + k], b4 = bp[2 * jj + k];
-            o8[4 * k] = fastAct(fmaf(v[8 * jj + 4 * k], s4.x, b4.x), ACT);
-            o8[4 * k + 1] = fastAct(fmaf(v[8 * jj + 4 * k + 1], s4.y, b4.y), ACT);
-            o8[4 * k + 2] = fastAct(fmaf(v[8 * jj + 4 * k + 2], s4.z, b4.z), ACT);
-            o8[4 * k + 3] = fastAct(fmaf(v[8 * jj + 4 * k + 3], s4.w, b4.w), ACT);
-          }
-          uint4 o;
-          o.x = Pack2<T>::pack(o8[0], o8[1]); o.y = Pack2<T>::pack(o8[2], o8[3]);
-          o.z = Pack2<T>::pack(o8[4], o8[5]); o.w = Pack2<T>::pack(o8[6], o8[7]);
-          *reinterpret_cast<uint4*>(oRow + ((jj ^ sw) << 4)) = o;
+        for(int k = 0; k < 4; k++) {
+          const float4 s4 = sp[4 * hh + k], b4 = bp[4 * hh + k];
+          x[4 * k] = fmaf(v[16 * hh + 4 * k], s4.x, b4.x);
+          x[4 * k + 1] = fmaf(v[16 * hh + 4 * k + 1], s4.y, b4.y);
+          x[4 * k + 2] = fmaf(v[16 * hh + 4 * k + 2], s4.z, b4.z);
+          x[4 * k + 3] = fmaf(v[16 * hh + 4 * k + 3], s4.w, b4.w);
         }
-      }
-      else {
+        actStaged<ACT, 16>(x);
 #pragma unroll
-        for(int jj = 0; jj < 4; jj++) *reinterpret_cast<uint4*>(oRow + ((jj ^ sw) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+        for(int jj = 0; jj < 2; jj++) {
+          uint4 o;
+          o.x = on ? Pack2<T>::pack(x[8 * jj], x[8 * jj + 1]) : 0u; o.y = on ? Pack2<T>::pack(x[8 * jj + 2], x[8 * jj + 3]) : 0u;
+          o.z = on ? Pack2<T>::pack(x[8 * jj + 4], x[8 * jj + 5]) : 0u; o.w = on ? Pack2<T>::pack(x[8 * jj + 6], x[8 * jj + 7]) : 0u;
+          *reinterpret_cast<uint4*>(oRow + (((2 * hh + jj) ^ sw) << 4)) = o;
+        }
       }
     }
     // make the generic-proxy writes visible to the TMA engine, then let lane 0 send the unit out
@@ -310,6 +356,11 @@ __device__ __forceinline__ bool epilogueTileTma(
       if(doAct) tmaStore2d(tmAct, smemU32(oUnit), c - ep.actC0, m0 + q * 32);
       bulkCommit();
       bulkWaitRead1();  // the store issued one unit ago has finished reading: its output unit may be rewritten
+      if(hasRes && hasNext && j > 0) {
+        // ... and so may the residual unit it was sent from: fetch the next tile's residual into it already
+        mbarExpectTx(smemU32(&es.resFull[j - 1]), (uint32_t)TC_UNIT_BYTES);
+        tmaLoad2d(smemU32(es.sR + (size_t)(j - 1) * TC_UNIT_BYTES), tmRes, nextN0 + (u - 2) * 32, nextM0 + q * 32, smemU32(&es.resFull[j - 1]));
+      }
     }
     __syncwarp();
     if(doAct) es.oCount++;
@@ -346,6 +397,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
   const int numTiles = (a.g.rowsPad / TC_BM) * numNTiles;
   const int taps = a.kY * a.kX;
 
+  gridDepLaunch();
   if(threadIdx.x == 0) {
     for(int s = 0; s < a.numA; s++) { mbarInit(smemU32(&fullA[s]), 1); mbarInit(smemU32(&emptyA[s]), 1); }
     for(int s = 0; s < a.numB; s++) { mbarInit(smemU32(&fullB[s]), 1); mbarInit(smemU32(&emptyB[s]), 1); }
@@ -359,7 +411,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
     tmemAlloc(smemU32(tmemSlot), a.tmemCols);
     tmemRelinquish();
   }
-  // next layer's norm parameters: read once per CTA
+  // next layer's norm parameters: read once per CTA (weights: not produced by the preceding kernels)
   if(a.ep.outAct) {
     const int nAct = a.ep.actC1 - a.ep.actC0;
     for(int i = threadIdx.x; i < nAct; i += blockDim.x) { sScale[i] = a.ep.scale[i]; sBias[i] = a.ep.bias[i]; }
@@ -382,6 +434,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
           tmaLoad2d(smemU32(smemB + (size_t)kc * a.bSlotBytes), &tmB, kc * TC_BK, n0, smemU32(&fullB[kc]));
         }
       }
+      // everything above touched only weights; the activations belong to the kernels before this one
+      gridDepWait();
       for(int t = blockIdx.x; t < numTiles && ok; t += gridDim.x) {
         const int m0 = (t / numNTiles) * TC_BM, n0 = (t % numNTiles) * a.BN;
         for(int kc = 0; kc < a.kChunks && ok; kc++) {
@@ -487,6 +541,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
     es.resFull = resFull + (warp - 2) * TC_MAX_UNITS_PER_WARP;
     es.oCount = 0;
     uint32_t it = 0;
+    gridDepWait();  // mask, per-board bias, residual and the output buffers belong to the kernels before this one
     for(int t = blockIdx.x; t < numTiles; t += gridDim.x, it++) {
       const uint32_t buf = it & 1u;
       const int m0 = (t / numNTiles) * TC_BM, n0 = (t % numNTiles) * a.BN;
@@ -498,9 +553,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
       uint4 res[2 * TC_MAX_GROUPS];
       if(a.tmaEpi) {
         if(a.ep.residual && lane == 0) {
+          // All units of the first tile; afterwards only the last one, the others were fetched while the previous
+          // tile's units drained.
           bulkWaitRead0();  // this warp's stores of the previous tile have finished reading its staging units
+          const int nU = (a.BN / 32 - half + 1) / 2;
           int j = 0;
           for(int u = half; u < a.BN / 32; u += 2, j++) {
+            if(it > 0 && j < nU - 1) continue;
             mbarExpectTx(smemU32(&es.resFull[j]), (uint32_t)TC_UNIT_BYTES);
             tmaLoad2d(smemU32(es.sR + (size_t)j * TC_UNIT_BYTES), &tmRes, n0 + u * 32, m0 + q * 32, smemU32(&es.resFull[j]));
           }
@@ -529,13 +588,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
       tcFenceAfter();
       const uint32_t acc = tmemBase + buf * (uint32_t)a.BN;
       if(a.tmaEpi) {
+        const int tn = t + gridDim.x;
+        const bool hasNext = tn < numTiles;
+        const int nextM0 = (tn / numNTiles) * TC_BM, nextN0 = (tn % numNTiles) * a.BN;
         bool ok2;
         switch(a.ep.act) {
-          case KB_ACT_RELU: ok2 = epilogueTileTma<T, KB_ACT_RELU>(a, &tmRaw, &tmAct, acc, q, half, lane, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias); break;
-          case KB_ACT_MISH: ok2 = epilogueTileTma<T, KB_ACT_MISH>(a, &tmRaw, &tmAct, acc, q, half, lane, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias); break;
-          case KB_ACT_SILU: ok2 = epilogueTileTma<T, KB_ACT_SILU>(a, &tmRaw, &tmAct, acc, q, half, lane, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias); break;
-          case KB_ACT_MISH_SCALE8: ok2 = epilogueTileTma<T, KB_ACT_MISH_SCALE8>(a, &tmRaw, &tmAct, acc, q, half, lane, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias); break;
-          default: ok2 = epilogueTileTma<T, KB_ACT_IDENTITY>(a, &tmRaw, &tmAct, acc, q, half, lane, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias); break;
+          case KB_ACT_RELU: ok2 = epilogueTileTma<T, KB_ACT_RELU>(a, &tmRaw, &tmAct, acc, q, half, lane, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias, &tmRes, hasNext, nextM0, nextN0); break;
+          case KB_ACT_MISH: ok2 = epilogueTileTma<T, KB_ACT_MISH>(a, &tmRaw, &tmAct, acc, q, half, lane, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias, &tmRes, hasNext, nextM0, nextN0); break;
+          case KB_ACT_SILU: ok2 = epilogueTileTma<T, KB_ACT_SILU>(a, &tmRaw, &tmAct, acc, q, half, lane, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias, &tmRes, hasNext, nextM0, nextN0); break;
+          case KB_ACT_MISH_SCALE8: ok2 = epilogueTileTma<T, KB_ACT_MISH_SCALE8>(a, &tmRaw, &tmAct, acc, q, half, lane, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias, &tmRes, hasNext, nextM0, nextN0); break;
+          default: ok2 = epilogueTileTma<T, KB_ACT_IDENTITY>(a, &tmRaw, &tmAct, acc, q, half, lane, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias, &tmRes, hasNext, nextM0, nextN0); break;
         }
         if(!ok2) {
           if(lane == 0 && !*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, TC_ERR_EPILOGUE_TIMEOUT); }
@@ -604,8 +666,29 @@ struct ConvTcPlan {
   CUtensorMap tmRes, tmRaw, tmAct;
 };
 
-static int pickBN(int outC) {
-  // largest multiple of 16 that divides outC and fits one MMA (N <= 256)
+// Tile table: output-channel tile width per convolution shape, chosen from measurements on B200 (batch 256, 19x19).
+// Shapes that are not listed take the largest multiple of 16 that divides outC and fits one MMA (N <= 256).
+struct TileRule { int k, inC, outC, BN; };
+static const TileRule TILE_TABLE[] = {
+  {0, 0, 0, 0},
+};
+
+static int pickBN(int k, int inC, int outC) {
+  // experiments: KB_TC_BN="k:inC:outC=BN,..." overrides the table
+  if(const char* e = getenv("KB_TC_BN")) {
+    const char* s = e;
+    while(*s) {
+      int kk = 0, ic = 0, oc = 0, bn = 0, used = 0;
+      if(sscanf(s, "%d:%d:%d=%d%n", &kk, &ic, &oc, &bn, &used) == 4) {
+        if(kk == k && ic == inC && oc == outC && bn >= 16 && bn <= 256 && bn % 16 == 0 && outC % bn == 0) return bn;
+        s += used;
+      }
+      while(*s && *s != ',') s++;
+      if(*s == ',') s++;
+    }
+  }
+  for(const TileRule& r : TILE_TABLE)
+    if(r.k == k && r.inC == inC && r.outC == outC && r.BN > 0 && outC % r.BN == 0) return r.BN;
   for(int bn = 256; bn >= 16; bn -= 16)
     if(outC % bn == 0) return bn;
   return 0;
@@ -615,7 +698,7 @@ bool convTcEligible(int dt, int inC, int outC, int kY, int kX) {
   if(dt != DT_F16 && dt != DT_BF16) return false;
   if(!((kY == 1 && kX == 1) || (kY == 3 && kX == 3))) return false;
   if(inC % TC_BK != 0 || outC % 16 != 0) return false;
-  return pickBN(outC) >= 16;
+  return pickBN(kY, inC, outC) >= 16;
 }
 
 static bool encode2d(
@@ -678,7 +761,7 @@ ConvTcPlan* convTcCreate(
   ConvTcPlan* p = new ConvTcPlan();
   p->dt = dt; p->inC = inC; p->outC = outC; p->kY = kY; p->kX = kX; p->X = X; p->Y = Y;
   p->rowsPadMax = rowsPadMax; p->tmaEpi = 0;
-  p->BN = pickBN(outC);
+  p->BN = pickBN(kY, inC, outC);
   p->kChunks = inC / TC_BK;
   const int maxShift = (kY == 3) ? (X + 1) + 1 : 0;  // RW + 1 rows up or down
   p->haloPad = (maxShift + 7) / 8 * 8;
@@ -752,11 +835,17 @@ cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epi
     grid = grid / nt * nt;  // each CTA keeps one channel tile
     if(grid < nt) grid = nt;
   }
-  if(p->dt == DT_F16)
-    convTcKernel<__half><<<grid, TC_THREADS, p->smemBytes, st>>>(p->tmA, p->tmB, p->tmRes, p->tmRaw, p->tmAct, a);
-  else
-    convTcKernel<__nv_bfloat16><<<grid, TC_THREADS, p->smemBytes, st>>>(p->tmA, p->tmB, p->tmRes, p->tmRaw, p->tmAct, a);
-  return cudaGetLastError();
+  // Programmatic dependent launch: the preamble (barriers, TMEM, resident weights) overlaps the tail of the kernel
+  // before this one in the stream; the kernel waits for that kernel before it touches any activation.
+  static const bool usePdl = getenv("KB_NO_PDL") == nullptr;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(TC_THREADS); cfg.dynamicSmemBytes = p->smemBytes; cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = usePdl ? 1 : 0;
+  if(p->dt == DT_F16) return cudaLaunchKernelEx(&cfg, convTcKernel<__half>, p->tmA, p->tmB, p->tmRes, p->tmRaw, p->tmAct, a);
+  return cudaLaunchKernelEx(&cfg, convTcKernel<__nv_bfloat16>, p->tmA, p->tmB, p->tmRes, p->tmRaw, p->tmAct, a);
 }
 
 }  // namespace kb

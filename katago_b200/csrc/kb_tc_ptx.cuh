@@ -53,6 +53,12 @@ __device__ __forceinline__ bool mbarWait(uint32_t bar, uint32_t parity, volatile
   }
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-stream-serialization attribute may start
+// while the kernel before it in the stream still runs; it must not touch memory that kernel produces (or still
+// reads) before gridDepWait() returns.  gridDepLaunch() lets the next such kernel begin its own preamble.
+__device__ __forceinline__ void gridDepWait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void gridDepLaunch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void tmaLoad2d(uint32_t dst, const CUtensorMap* tmap, int c0, int c1, uint32_t bar) {
   asm volatile(
     "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"

@@ -14,7 +14,7 @@
 // through a ring of slots.
 //
 // Persistent CTAs (one per SM), 320 threads: warp 0 issues TMA loads, warp 1 owns TMEM and issues the
-// MMAs, warps 2..9 run the epilogue (two warps per TMEM lane quarter, alternating 16-column groups).
+// MMAs, warps 2..13 run the epilogue (three warps per TMEM lane quarter, taking 32-channel units in turn).
 // Two accumulators live in TMEM, so the epilogue of tile i overlaps the main loop of tile i+1.
 // Every wait is bounded: on time-out the kernel records a code in the status word and all roles
 // leave through the common exit, which still frees TMEM.
@@ -26,6 +26,9 @@
 #include <cstdio>
 #include <cstdlib>
 #include <mutex>
+#include <vector>
+#include <algorithm>
+#include <utility>
 
 namespace kb {
 
@@ -147,16 +150,26 @@ struct ConvTcArgs {
   int epiWarpBytes; // shared memory of one epilogue warp's staging units (TMA epilogue)
   int tmaEpi;      // 1: outputs and residual travel through shared memory and TMA (64-channel aligned ranges)
   int* status;     // device status word: 0 = ok
+  int trace;       // timeline instrumentation requested (only in builds with KB_TC_TRACE)
 };
 
+// Optional timeline instrumentation (build with -DKB_TC_TRACE): CTA 0 of a launch whose shape matches the environment
+// variable KB_TC_TRACE="k:inC:outC:hasResidual" records SM cycle counts of its producer, MMA and first epilogue warp.
+#ifdef KB_TC_TRACE
+__device__ long long g_tcTrace[2048];
+#define TRACE(cond, slot) do { if((a.trace) && blockIdx.x == 0 && (cond)) g_tcTrace[(slot)] = clock64(); } while(0)
+#else
+#define TRACE(cond, slot) do { } while(0)
+#endif
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;
-constexpr int TC_THREADS = 320;
-constexpr int TC_EPI_WARPS = 8;
+constexpr int TC_EPI_CG = 2;                   // epilogue warps per TMEM lane quarter; each takes every third 32-channel unit
+constexpr int TC_EPI_WARPS = 4 * TC_EPI_CG;
+constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS;
 
 enum { TC_ERR_PRODUCER_TIMEOUT = 101, TC_ERR_MMA_TIMEOUT = 102, TC_ERR_EPILOGUE_TIMEOUT = 103 };
 
-constexpr int TC_MAX_GROUPS = 8;  // 16-column groups per warp and tile: BN/32 <= 8
+constexpr int TC_MAX_GROUPS = (16 + TC_EPI_CG - 1) / TC_EPI_CG;  // 16-column groups per warp and tile (BN <= 256)
 
 // One group of 16 output channels of one row: bias, residual (already in registers), raw store, norm+activation store.
 template <typename T, int ACT>
@@ -223,12 +236,12 @@ __device__ __forceinline__ void epilogue16(
   }
 }
 
-// All 16-column groups of one tile that belong to this warp (groups alternate between the two warps of a quarter).
-// res[] holds this row's residual values for those groups, fetched before the accumulator was ready.
+// All 16-column groups of one tile that belong to this warp (the warps of a quarter take the groups in turn).
+// This is the path for channel ranges that the TMA epilogue cannot express (head convolutions, odd widths); it reads the
+// residual and writes the outputs with plain vector accesses.
 template <typename T, int ACT>
 __device__ __forceinline__ void epilogueTile(
-  const ConvTcArgs& a, uint32_t tmemAcc, int q, int half, int m, int n0, float mk, const uint4 (&res)[2 * TC_MAX_GROUPS],
-  const float* sScale, const float* sBias) {
+  const ConvTcArgs& a, uint32_t tmemAcc, int q, int cg, int m, int n0, float mk, const float* sScale, const float* sBias) {
   const Epilogue& ep = a.ep;
   const int b = min(m / a.g.PB, a.g.n - 1);
   const float* biasRow = ep.biasNC ? ep.biasNC + (size_t)b * a.outC : nullptr;
@@ -236,49 +249,69 @@ __device__ __forceinline__ void epilogueTile(
   const bool hasRes = ep.residual != nullptr;
 #pragma unroll
   for(int j = 0; j < TC_MAX_GROUPS; j++) {
-    const int gi = half + 2 * j;
+    const int gi = cg + TC_EPI_CG * j;
     if(gi < groups) {
       uint32_t r[16];
       tmemLd16(tmemAcc + ((uint32_t)(q * 32) << 16) + (uint32_t)(gi * 16), r);
+      uint4 res0 = make_uint4(0u, 0u, 0u, 0u), res1 = res0;
+      if(hasRes) {
+        const uint4* rp = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(ep.residual) + (size_t)m * ep.resStride + n0 + gi * 16);
+        res0 = rp[0];
+        res1 = rp[1];
+      }
       tmemLdWait();
-      epilogue16<T, ACT>(r, ep, hasRes, res[2 * j], res[2 * j + 1], m, n0 + gi * 16, mk, biasRow, sScale, sBias);
+      epilogue16<T, ACT>(r, ep, hasRes, res0, res1, m, n0 + gi * 16, mk, biasRow, sScale, sBias);
     }
   }
 }
 
 constexpr int TC_UNIT_BYTES = 32 * 64;        // one staging unit: 32 rows x 32 channels (64 B rows, 64-byte swizzle)
-constexpr int TC_MAX_UNITS_PER_WARP = 4;      // BN <= 256 -> 8 units of 32 channels, split over the two warps of a quarter
+constexpr int TC_MAX_RING = (8 + TC_EPI_CG - 1) / TC_EPI_CG + 1;  // BN <= 256 -> 8 units over the warps of a quarter, plus one
 
 struct EpiWarp {
-  uint8_t* sR;          // this warp's residual / raw staging units
-  uint8_t* sO;          // this warp's two units for the activated output
-  uint64_t* resFull;    // [TC_MAX_UNITS_PER_WARP] residual unit landed (TMA)
-  uint32_t oCount;
+  uint8_t* sR;          // ring of `ring` units: the residual lands here, the raw output leaves from here
+  uint8_t* sO;          // one unit for the activated output
+  uint64_t* resFull;    // [ring] residual unit landed (TMA)
+  int nU;               // units of this warp per tile
+  int ring;             // nU + 1 with a residual (one tile of look-ahead), else 2
+  uint32_t seq;         // units processed so far, over all tiles
 };
 
+// Fetches the residual of this warp's unit j of the tile at (m0, n0) into its ring slot (lane 0 only).
+__device__ __forceinline__ void prefetchResidual(
+  const CUtensorMap* tmRes, const EpiWarp& es, uint32_t seq, int m0, int n0, int q, int cg, int j) {
+  const uint32_t b = seq % (uint32_t)es.ring;
+  mbarExpectTx(smemU32(&es.resFull[b]), (uint32_t)TC_UNIT_BYTES);
+  tmaLoad2d(smemU32(es.sR + (size_t)b * TC_UNIT_BYTES), tmRes, n0 + (cg + TC_EPI_CG * j) * 32, m0 + q * 32, smemU32(&es.resFull[b]));
+}
+
 // Epilogue of one tile for one warp, staged through shared memory.  A warp owns 32 rows (its TMEM lane quarter) and
-// every second 32-channel unit of the tile; each thread owns one row of a unit (64 contiguous bytes).  The residual
-// unit was fetched by TMA; the updated residual stream overwrites it in place and goes back out by TMA; the
-// activated tensor is staged in one of two more units.  All synchronisation is inside the warp, and global memory
-// only sees whole 64-byte row segments written by the TMA engine.
+// every third 32-channel unit of the tile; each thread owns one row of a unit (64 contiguous bytes).  The residual
+// unit was fetched by TMA one tile ahead; the updated residual stream overwrites it in place and goes back out by
+// TMA; the activated tensor is staged in one more unit.  A unit is computed entirely in registers first; only then
+// does the warp wait for the TMA engine to have read the previous unit's stores, so that wait is normally free.  All
+// synchronisation is inside the warp, and global memory only sees whole 64-byte row segments written by the TMA engine.
 template <typename T, int ACT>
 __device__ __forceinline__ bool epilogueTileTma(
-  const ConvTcArgs& a, const CUtensorMap* tmRaw, const CUtensorMap* tmAct, uint32_t tmemAcc, int q, int half, int lane,
-  int m0, int n0, float mk, const float* biasRow, EpiWarp& es, uint32_t tileParity, volatile int* abortFlag,
+  const ConvTcArgs& a, const CUtensorMap* tmRaw, const CUtensorMap* tmAct, uint32_t tmemAcc, int q, int cg, int lane,
+  int m0, int n0, float mk, const float* biasRow, EpiWarp& es, uint32_t tileIter, volatile int* abortFlag,
   const float* sScale, const float* sBias, const CUtensorMap* tmRes, bool hasNext, int nextM0, int nextN0) {
   const Epilogue& ep = a.ep;
   const bool hasRes = ep.residual != nullptr;
-  const int units = a.BN / 32;
   const int sw = (lane >> 1) & 3;  // 64-byte swizzle: 16-byte chunk index XOR bits 1..2 of the row
-  int j = 0;
-  for(int u = half; u < units; u += 2, j++) {
+  const bool on = mk == 1.0f;
+  for(int j = 0; j < es.nU; j++) {
+    const int u = cg + TC_EPI_CG * j;
+    const uint32_t slot = es.seq % (uint32_t)es.ring;
+    TRACE(threadIdx.x == 64, 1024 + (int)(tileIter & 31u) * 16 + j * 5);
     uint32_t r[32];
     tmemLd32(tmemAcc + ((uint32_t)(q * 32) << 16) + (uint32_t)(u * 32), r);
     if(hasRes) {
-      bool landed = mbarWait(smemU32(&es.resFull[j]), tileParity, abortFlag);
+      bool landed = mbarWait(smemU32(&es.resFull[slot]), (es.seq / (uint32_t)es.ring) & 1u, abortFlag);
       if(!__all_sync(0xffffffffu, landed)) return false;
     }
     tmemLdWait();
+    TRACE(threadIdx.x == 64, 1024 + (int)(tileIter & 31u) * 16 + j * 5 + 1);
     const int c = n0 + u * 32;  // first output channel of this unit
     float v[32];
 #pragma unroll
@@ -291,7 +324,7 @@ __device__ __forceinline__ bool epilogueTileTma(
         v[4 * k] += b4.x; v[4 * k + 1] += b4.y; v[4 * k + 2] += b4.z; v[4 * k + 3] += b4.w;
       }
     }
-    uint8_t* rRow = es.sR + (size_t)j * TC_UNIT_BYTES + lane * 64;
+    uint8_t* rRow = es.sR + (size_t)slot * TC_UNIT_BYTES + lane * 64;
     if(hasRes) {
       if(ep.resMask) {
 #pragma unroll
@@ -311,6 +344,8 @@ __device__ __forceinline__ bool epilogueTileTma(
     }
     const bool doRaw = ep.outRaw && c >= ep.rawC0 && c < ep.rawC1;
     const bool doAct = ep.outAct && c >= ep.actC0 && c < ep.actC1;
+    // The raw output can go to its staging unit at once: with a residual it replaces the residual just read, without
+    // one the two raw units alternate and the store from this one was waited for one unit ago.
     if(doRaw) {
 #pragma unroll
       for(int jj = 0; jj < 4; jj++) {
@@ -320,13 +355,11 @@ __device__ __forceinline__ bool epilogueTileTma(
         *reinterpret_cast<uint4*>(rRow + ((jj ^ sw) << 4)) = o;
       }
     }
-    uint8_t* oUnit = es.sO + (size_t)(es.oCount & 1u) * TC_UNIT_BYTES;
+    uint32_t actP[16];
     if(doAct) {
-      uint8_t* oRow = oUnit + lane * 64;
       const int ca = c - ep.actC0;
       const float4* sp = reinterpret_cast<const float4*>(sScale + ca);
       const float4* bp = reinterpret_cast<const float4*>(sBias + ca);
-      const bool on = mk == 1.0f;
 #pragma unroll
       for(int hh = 0; hh < 2; hh++) {
         float x[16];
@@ -340,35 +373,41 @@ __device__ __forceinline__ bool epilogueTileTma(
         }
         actStaged<ACT, 16>(x);
 #pragma unroll
-        for(int jj = 0; jj < 2; jj++) {
-          uint4 o;
-          o.x = on ? Pack2<T>::pack(x[8 * jj], x[8 * jj + 1]) : 0u; o.y = on ? Pack2<T>::pack(x[8 * jj + 2], x[8 * jj + 3]) : 0u;
-          o.z = on ? Pack2<T>::pack(x[8 * jj + 4], x[8 * jj + 5]) : 0u; o.w = on ? Pack2<T>::pack(x[8 * jj + 6], x[8 * jj + 7]) : 0u;
-          *reinterpret_cast<uint4*>(oRow + (((2 * hh + jj) ^ sw) << 4)) = o;
-        }
+        for(int k = 0; k < 8; k++) actP[8 * hh + k] = on ? Pack2<T>::pack(x[2 * k], x[2 * k + 1]) : 0u;
       }
+    }
+    TRACE(threadIdx.x == 64, 1024 + (int)(tileIter & 31u) * 16 + j * 5 + 2);
+    // The TMA engine must have read the previous unit's stores before their staging units are written again; that
+    // also frees the ring slot before this one for the residual of the same unit of the next tile.
+    if(lane == 0) {
+      bulkWaitRead0();
+      if(hasRes && hasNext && es.seq > 0) prefetchResidual(tmRes, es, es.seq + (uint32_t)es.nU, nextM0, nextN0, q, cg, j);
+    }
+    __syncwarp();
+    TRACE(threadIdx.x == 64, 1024 + (int)(tileIter & 31u) * 16 + j * 5 + 3);
+    if(doAct) {
+      uint8_t* oRow = es.sO + lane * 64;
+#pragma unroll
+      for(int jj = 0; jj < 4; jj++)
+        *reinterpret_cast<uint4*>(oRow + ((jj ^ sw) << 4)) = make_uint4(actP[4 * jj], actP[4 * jj + 1], actP[4 * jj + 2], actP[4 * jj + 3]);
     }
     // make the generic-proxy writes visible to the TMA engine, then let lane 0 send the unit out
     fenceProxyAsync();
     __syncwarp();
     if(lane == 0) {
-      if(doRaw) tmaStore2d(tmRaw, smemU32(es.sR + (size_t)j * TC_UNIT_BYTES), c - ep.rawC0, m0 + q * 32);
-      if(doAct) tmaStore2d(tmAct, smemU32(oUnit), c - ep.actC0, m0 + q * 32);
+      if(doRaw) tmaStore2d(tmRaw, smemU32(es.sR + (size_t)slot * TC_UNIT_BYTES), c - ep.rawC0, m0 + q * 32);
+      if(doAct) tmaStore2d(tmAct, smemU32(es.sO), c - ep.actC0, m0 + q * 32);
       bulkCommit();
-      bulkWaitRead1();  // the store issued one unit ago has finished reading: its output unit may be rewritten
-      if(hasRes && hasNext && j > 0) {
-        // ... and so may the residual unit it was sent from: fetch the next tile's residual into it already
-        mbarExpectTx(smemU32(&es.resFull[j - 1]), (uint32_t)TC_UNIT_BYTES);
-        tmaLoad2d(smemU32(es.sR + (size_t)(j - 1) * TC_UNIT_BYTES), tmRes, nextN0 + (u - 2) * 32, nextM0 + q * 32, smemU32(&es.resFull[j - 1]));
-      }
     }
-    __syncwarp();
-    if(doAct) es.oCount++;
+    TRACE(threadIdx.x == 64, 1024 + (int)(tileIter & 31u) * 16 + j * 5 + 4);
+    es.seq++;
   }
   return true;
 }
 
-template <typename T>
+// One instantiation per element type, activation and epilogue kind: the epilogue is long straight-line code, and a
+// kernel that carried every variant ran measurably slower (instruction cache).
+template <typename T, int ACT, bool TMA_EPI>
 __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
   const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmRes,
   const __grid_constant__ CUtensorMap tmRaw, const __grid_constant__ CUtensorMap tmAct, const ConvTcArgs a) {
@@ -378,7 +417,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
   uint8_t* smemA = smem;
   uint8_t* smemB = smemA + (size_t)a.numA * a.aSlotBytes;
   uint8_t* smemR = smemB + (size_t)a.numB * a.bSlotBytes;  // epilogue staging (TMA epilogue only)
-  float* sScale = reinterpret_cast<float*>(smemR + (a.tmaEpi ? (size_t)TC_EPI_WARPS * a.epiWarpBytes : 0));
+  float* sScale = reinterpret_cast<float*>(smemR + (TMA_EPI ? (size_t)TC_EPI_WARPS * a.epiWarpBytes : 0));
   float* sBias = sScale + 512;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sBias + 512);
   // barrier layout: fullA[numA] emptyA[numA] fullB[numB] emptyB[numB] accFull[2] accEmpty[2]
@@ -388,8 +427,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
   uint64_t* emptyB = fullB + a.numB;
   uint64_t* accFull = emptyB + a.numB;
   uint64_t* accEmpty = accFull + 2;
-  uint64_t* resFull = accEmpty + 2;   // [TC_EPI_WARPS][TC_MAX_UNITS_PER_WARP]
-  uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(resFull + TC_EPI_WARPS * TC_MAX_UNITS_PER_WARP);
+  uint64_t* resFull = accEmpty + 2;   // [TC_EPI_WARPS][TC_MAX_RING]
+  uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(resFull + TC_EPI_WARPS * TC_MAX_RING);
   volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -402,7 +441,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
     for(int s = 0; s < a.numA; s++) { mbarInit(smemU32(&fullA[s]), 1); mbarInit(smemU32(&emptyA[s]), 1); }
     for(int s = 0; s < a.numB; s++) { mbarInit(smemU32(&fullB[s]), 1); mbarInit(smemU32(&emptyB[s]), 1); }
     for(int s = 0; s < 2; s++) { mbarInit(smemU32(&accFull[s]), 1); mbarInit(smemU32(&accEmpty[s]), TC_EPI_WARPS); }
-    for(int s = 0; s < TC_EPI_WARPS * TC_MAX_UNITS_PER_WARP; s++) mbarInit(smemU32(&resFull[s]), 1);
+    for(int s = 0; s < TC_EPI_WARPS * TC_MAX_RING; s++) mbarInit(smemU32(&resFull[s]), 1);
     *abortFlag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -440,6 +479,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
         const int m0 = (t / numNTiles) * TC_BM, n0 = (t % numNTiles) * a.BN;
         for(int kc = 0; kc < a.kChunks && ok; kc++) {
           if(!mbarWait(smemU32(&emptyA[sa]), phA ^ 1u, abortFlag)) { ok = false; break; }
+          TRACE(true, ((t - blockIdx.x) / gridDim.x) * 16 + kc);
           mbarExpectTx(smemU32(&fullA[sa]), (uint32_t)a.aSlotBytes);
           tmaLoad2d(smemU32(smemA + (size_t)sa * a.aSlotBytes), &tmA, kc * TC_BK, m0 - a.haloPad, smemU32(&fullA[sa]));
           if(++sa == (uint32_t)a.numA) { sa = 0; phA ^= 1u; }
@@ -479,10 +519,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
         // wait until the epilogue has drained this accumulator (two tiles ago)
         if(!mbarWait(smemU32(&accEmpty[buf]), ((it >> 1) & 1u) ^ 1u, abortFlag)) { ok = false; break; }
         tcFenceAfter();
+        TRACE(true, 256 + it * 16);
         const uint32_t dTmem = tmemBase + buf * (uint32_t)a.BN;
         uint32_t accumulate = 0;
         for(int kc = 0; kc < a.kChunks && ok; kc++) {
           if(!mbarWait(smemU32(&fullA[sa]), phA, abortFlag)) { ok = false; break; }
+          TRACE(true, 256 + it * 16 + 1 + kc);
           const uint32_t aLo = aLoBase + sa * aSlot16;
           if(taps == 9) {
 #pragma unroll
@@ -527,93 +569,68 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
           if(++sa == (uint32_t)a.numA) { sa = 0; phA ^= 1u; }
         }
         if(ok) ummaCommit(smemU32(&accFull[buf]));
+        TRACE(true, 256 + it * 16 + 15);
       }
       if(!ok && !*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, TC_ERR_MMA_TIMEOUT); }
     }
   }
   else {
-    // ---------------- Epilogue: warps 2..9; TMEM lane quarter = warp % 4 ----------------
+    // ---------------- Epilogue: warps 2..; TMEM lane quarter = warp % 4 ----------------
     const int q = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int cg = (warp - 2) >> 2;  // which of the quarter's warps: takes units cg, cg + TC_EPI_CG, ...
     EpiWarp es;
     es.sR = smemR + (size_t)(warp - 2) * a.epiWarpBytes;
-    es.sO = es.sR + (size_t)(a.epiWarpBytes - 2 * TC_UNIT_BYTES);
-    es.resFull = resFull + (warp - 2) * TC_MAX_UNITS_PER_WARP;
-    es.oCount = 0;
+    es.sO = es.sR + (size_t)(a.epiWarpBytes - TC_UNIT_BYTES);
+    es.resFull = resFull + (warp - 2) * TC_MAX_RING;
+    es.nU = (a.BN / 32 - cg + TC_EPI_CG - 1) / TC_EPI_CG;
+    es.ring = a.ep.residual ? es.nU + 1 : 2;
+    es.seq = 0;
     uint32_t it = 0;
     gridDepWait();  // mask, per-board bias, residual and the output buffers belong to the kernels before this one
     for(int t = blockIdx.x; t < numTiles; t += gridDim.x, it++) {
       const uint32_t buf = it & 1u;
       const int m0 = (t / numNTiles) * TC_BM, n0 = (t % numNTiles) * a.BN;
       // Nothing below depends on the accumulator yet: fetch mask and residual while the MMAs still run.
+      TRACE(threadIdx.x == 64, 512 + it * 16);
       const int m = m0 + q * 32 + lane;
       const float mk = a.ep.mask ? a.ep.mask[m] : 1.0f;
       const int bIdx = min(m / a.g.PB, a.g.n - 1);
       const float* biasRow = a.ep.biasNC ? a.ep.biasNC + (size_t)bIdx * a.outC : nullptr;
-      uint4 res[2 * TC_MAX_GROUPS];
-      if(a.tmaEpi) {
-        if(a.ep.residual && lane == 0) {
-          // All units of the first tile; afterwards only the last one, the others were fetched while the previous
-          // tile's units drained.
-          bulkWaitRead0();  // this warp's stores of the previous tile have finished reading its staging units
-          const int nU = (a.BN / 32 - half + 1) / 2;
-          int j = 0;
-          for(int u = half; u < a.BN / 32; u += 2, j++) {
-            if(it > 0 && j < nU - 1) continue;
-            mbarExpectTx(smemU32(&es.resFull[j]), (uint32_t)TC_UNIT_BYTES);
-            tmaLoad2d(smemU32(es.sR + (size_t)j * TC_UNIT_BYTES), &tmRes, n0 + u * 32, m0 + q * 32, smemU32(&es.resFull[j]));
-          }
+      if(TMA_EPI) {
+        if(a.ep.residual && lane == 0 && it == 0 && es.nU > 0) {
+          // The ring holds one tile plus one unit: fill it now; afterwards every unit that drains fetches the same
+          // unit of the next tile.
+          for(int j = 0; j < es.nU; j++) prefetchResidual(&tmRes, es, (uint32_t)j, m0, n0, q, cg, j);
+          const int tn = t + gridDim.x;
+          if(tn < numTiles) prefetchResidual(&tmRes, es, (uint32_t)es.nU, (tn / numNTiles) * TC_BM, (tn % numNTiles) * a.BN, q, cg, 0);
         }
         __syncwarp();
       }
-      else if(a.ep.residual) {
-        const T* rrow = reinterpret_cast<const T*>(a.ep.residual) + (size_t)m * a.ep.resStride + n0;
-        const int groups = a.BN / 16;
-#pragma unroll
-        for(int j = 0; j < TC_MAX_GROUPS; j++) {
-          const int gi = half + 2 * j;
-          if(gi < groups) {
-            const uint4* rp = reinterpret_cast<const uint4*>(rrow + gi * 16);
-            res[2 * j] = rp[0];
-            res[2 * j + 1] = rp[1];
-          }
-        }
-      }
+      TRACE(threadIdx.x == 64, 512 + it * 16 + 1);
       bool ok = mbarWait(smemU32(&accFull[buf]), (it >> 1) & 1u, abortFlag);
       ok = __all_sync(0xffffffffu, ok);
+      TRACE(threadIdx.x == 64, 512 + it * 16 + 2);
       if(!ok) {
         if(lane == 0 && !*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, TC_ERR_EPILOGUE_TIMEOUT); }
         break;
       }
       tcFenceAfter();
       const uint32_t acc = tmemBase + buf * (uint32_t)a.BN;
-      if(a.tmaEpi) {
+      if(TMA_EPI) {
         const int tn = t + gridDim.x;
         const bool hasNext = tn < numTiles;
         const int nextM0 = (tn / numNTiles) * TC_BM, nextN0 = (tn % numNTiles) * a.BN;
-        bool ok2;
-        switch(a.ep.act) {
-          case KB_ACT_RELU: ok2 = epilogueTileTma<T, KB_ACT_RELU>(a, &tmRaw, &tmAct, acc, q, half, lane, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias, &tmRes, hasNext, nextM0, nextN0); break;
-          case KB_ACT_MISH: ok2 = epilogueTileTma<T, KB_ACT_MISH>(a, &tmRaw, &tmAct, acc, q, half, lane, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias, &tmRes, hasNext, nextM0, nextN0); break;
-          case KB_ACT_SILU: ok2 = epilogueTileTma<T, KB_ACT_SILU>(a, &tmRaw, &tmAct, acc, q, half, lane, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias, &tmRes, hasNext, nextM0, nextN0); break;
-          case KB_ACT_MISH_SCALE8: ok2 = epilogueTileTma<T, KB_ACT_MISH_SCALE8>(a, &tmRaw, &tmAct, acc, q, half, lane, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias, &tmRes, hasNext, nextM0, nextN0); break;
-          default: ok2 = epilogueTileTma<T, KB_ACT_IDENTITY>(a, &tmRaw, &tmAct, acc, q, half, lane, m0, n0, mk, biasRow, es, it & 1u, abortFlag, sScale, sBias, &tmRes, hasNext, nextM0, nextN0); break;
-        }
+        const bool ok2 = epilogueTileTma<T, ACT>(a, &tmRaw, &tmAct, acc, q, cg, lane, m0, n0, mk, biasRow, es, it, abortFlag, sScale, sBias, &tmRes, hasNext, nextM0, nextN0);
         if(!ok2) {
           if(lane == 0 && !*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, TC_ERR_EPILOGUE_TIMEOUT); }
           break;
         }
       }
-      else switch(a.ep.act) {
-        case KB_ACT_RELU: epilogueTile<T, KB_ACT_RELU>(a, acc, q, half, m, n0, mk, res, sScale, sBias); break;
-        case KB_ACT_MISH: epilogueTile<T, KB_ACT_MISH>(a, acc, q, half, m, n0, mk, res, sScale, sBias); break;
-        case KB_ACT_SILU: epilogueTile<T, KB_ACT_SILU>(a, acc, q, half, m, n0, mk, res, sScale, sBias); break;
-        case KB_ACT_MISH_SCALE8: epilogueTile<T, KB_ACT_MISH_SCALE8>(a, acc, q, half, m, n0, mk, res, sScale, sBias); break;
-        default: epilogueTile<T, KB_ACT_IDENTITY>(a, acc, q, half, m, n0, mk, res, sScale, sBias); break;
-      }
+      else epilogueTile<T, ACT>(a, acc, q, cg, m, n0, mk, sScale, sBias);
       // all TMEM reads of this warp are complete (tcgen05.wait::ld inside): hand the accumulator back
       tcFenceBefore();
       __syncwarp();
+      TRACE(threadIdx.x == 64, 512 + it * 16 + 3);
       if(lane == 0) mbarArrive(smemU32(&accEmpty[buf]));
     }
     if(lane == 0) bulkWaitAll();  // outstanding tile stores must complete before the CTA's shared memory goes away
@@ -652,6 +669,23 @@ static EncodeTiledFn getEncodeTiled() {
       fn = reinterpret_cast<EncodeTiledFn>(p);
   });
   return fn;
+}
+
+// Kernel variants by (element type, activation, epilogue kind).
+typedef void (*ConvTcKernelFn)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, ConvTcArgs);
+template <typename T, bool TMA_EPI>
+static ConvTcKernelFn kernelForAct(int act) {
+  switch(act) {
+    case KB_ACT_RELU: return convTcKernel<T, KB_ACT_RELU, TMA_EPI>;
+    case KB_ACT_MISH: return convTcKernel<T, KB_ACT_MISH, TMA_EPI>;
+    case KB_ACT_SILU: return convTcKernel<T, KB_ACT_SILU, TMA_EPI>;
+    case KB_ACT_MISH_SCALE8: return convTcKernel<T, KB_ACT_MISH_SCALE8, TMA_EPI>;
+    default: return convTcKernel<T, KB_ACT_IDENTITY, TMA_EPI>;
+  }
+}
+static ConvTcKernelFn kernelFor(int dt, int act, bool tmaEpi) {
+  if(dt == DT_F16) return tmaEpi ? kernelForAct<__half, true>(act) : kernelForAct<__half, false>(act);
+  return tmaEpi ? kernelForAct<__nv_bfloat16, true>(act) : kernelForAct<__nv_bfloat16, false>(act);
 }
 
 struct ConvTcPlan {
@@ -778,12 +812,9 @@ ConvTcPlan* convTcCreate(
   bool ok = encode2d(&p->tmA, dt, in, (uint64_t)inC, (uint64_t)rowsPadMax, (uint64_t)inStride * 2, TC_BK, (uint32_t)p->aRows) &&
             encode2d(&p->tmB, dt, w, (uint64_t)inC, (uint64_t)kY * kX * outC, (uint64_t)inC * 2, TC_BK, (uint32_t)p->BN);
   if(!ok) { delete p; return nullptr; }
-  cudaError_t e1 = cudaFuncSetAttribute(convTcKernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-  cudaError_t e2 = cudaFuncSetAttribute(convTcKernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
   int dev = 0, sms = 148;
   if(cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   p->numSMs = sms;
-  if(e1 != cudaSuccess || e2 != cudaSuccess) { delete p; return nullptr; }
   return p;
 }
 
@@ -796,12 +827,15 @@ bool convTcSetEpilogue(ConvTcPlan* p, const Epilogue& ep) {
   p->tmaEpi = 0;
   const bool force = getenv("KB_TC_NO_TMA_EPI") != nullptr && atoi(getenv("KB_TC_NO_TMA_EPI")) != 0;
   auto aligned32 = [](int c0, int c1) { return (c0 % 32) == 0 && (c1 % 32) == 0 && c1 > c0; };
-  bool ok = !force && (p->BN % 32) == 0 && p->BN / 32 <= 2 * TC_MAX_UNITS_PER_WARP;
+  bool ok = !force && (p->BN % 32) == 0 && p->BN <= 256;
   if(ep.outRaw) ok = ok && aligned32(ep.rawC0, ep.rawC1) && (ep.rawStride % 8) == 0 && (reinterpret_cast<uintptr_t>(ep.outRaw) & 15) == 0;
   if(ep.outAct) ok = ok && aligned32(ep.actC0, ep.actC1) && (ep.actStride % 8) == 0 && (reinterpret_cast<uintptr_t>(ep.outAct) & 15) == 0;
   if(ep.residual) ok = ok && (ep.resStride % 8) == 0 && ep.resStride >= p->outC && (reinterpret_cast<uintptr_t>(ep.residual) & 15) == 0;
   if(!ok || (!ep.outRaw && !ep.outAct)) return sizeRings(p, 0);
-  p->epiWarpBytes = ((p->BN / 32 + 1) / 2 + 2) * TC_UNIT_BYTES;  // residual/raw units of this warp + two activated-output units
+  // per warp: the residual/raw ring (one tile of this warp's units plus one with a residual, else two units) and one
+  // unit for the activated output
+  const int unitsPerWarp = (p->BN / 32 + TC_EPI_CG - 1) / TC_EPI_CG;
+  p->epiWarpBytes = ((ep.residual ? unitsPerWarp + 1 : 2) + 1) * TC_UNIT_BYTES;
   if(!sizeRings(p, TC_EPI_WARPS * p->epiWarpBytes)) return sizeRings(p, 0);
   const uint64_t rows = (uint64_t)p->rowsPadMax;
   const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_64B;
@@ -826,6 +860,13 @@ cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epi
   a.aSlotBytes = p->aSlotBytes; a.bSlotBytes = p->bSlotBytes; a.numA = p->numA; a.numB = p->numB; a.residentB = p->residentB;
   a.idesc = p->idesc; a.tmemCols = p->tmemCols;
   a.status = statusWord;
+  a.trace = 0;
+#ifdef KB_TC_TRACE
+  if(const char* e = getenv("KB_TC_TRACE")) {
+    int k = 0, ic = 0, oc = 0, r = 0;
+    if(sscanf(e, "%d:%d:%d:%d", &k, &ic, &oc, &r) == 4 && k == p->kY && ic == p->inC && oc == p->outC && r == (ep.residual ? 1 : 0)) a.trace = 1;
+  }
+#endif
   a.tmaEpi = p->tmaEpi;
   a.epiWarpBytes = p->epiWarpBytes;
   const int numTiles = (g.rowsPad / TC_BM) * (p->outC / p->BN);
@@ -844,8 +885,27 @@ cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epi
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr; cfg.numAttrs = usePdl ? 1 : 0;
-  if(p->dt == DT_F16) return cudaLaunchKernelEx(&cfg, convTcKernel<__half>, p->tmA, p->tmB, p->tmRes, p->tmRaw, p->tmAct, a);
-  return cudaLaunchKernelEx(&cfg, convTcKernel<__nv_bfloat16>, p->tmA, p->tmB, p->tmRes, p->tmRaw, p->tmAct, a);
+  // without an activated output the activation code is irrelevant: use the identity variant
+  ConvTcKernelFn fn = kernelFor(p->dt, ep.outAct ? ep.act : KB_ACT_IDENTITY, p->tmaEpi != 0);
+  {
+    // opt in to the large dynamic shared memory once per variant and device
+    static std::mutex mu;
+    static std::vector<std::pair<const void*, int>> done;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lock(mu);
+    const std::pair<const void*, int> key((const void*)fn, dev);
+    if(std::find(done.begin(), done.end(), key) == done.end()) {
+      cudaError_t e = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+      if(e != cudaSuccess) return e;
+      done.push_back(key);
+    }
+  }
+  return cudaLaunchKernelEx(&cfg, fn, p->tmA, p->tmB, p->tmRes, p->tmRaw, p->tmAct, a);
 }
 
 }  // namespace kb
+
+#ifdef KB_TC_TRACE
+extern "C" int kb_debug_trace(long long* out, int n) { return (int)cudaMemcpyFromSymbol(out, kb::g_tcTrace, sizeof(long long) * n); }
+#endif

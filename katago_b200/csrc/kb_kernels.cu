@@ -4,6 +4,7 @@
 // except the convolution; rows are channel-contiguous (NHWC), so adjacent threads read adjacent
 // channels.
 #include "kb_kernels.cuh"
+#include "kb_act.cuh"
 #include "../../include/kb_modelblob.h"
 
 namespace kb {
@@ -209,39 +210,58 @@ cudaError_t launchConvSimt(
 // Small matmul: one block per row
 
 constexpr int MM_ROWS = 4;
+constexpr int MM_KSPLIT = 4;  // the input channels are split over threadIdx.y so that each thread's dependent chain is short
 
 __global__ void matMulSmallKernel(
   const float* __restrict__ in, int inC, const float* __restrict__ w, int outC, const float* __restrict__ bias, int act,
   float* __restrict__ out, int rows) {
-  extern __shared__ float sIn[];  // [MM_ROWS][inC]
+  extern __shared__ float sIn[];  // [MM_ROWS][inC], then partial sums [MM_KSPLIT][MM_ROWS][blockDim.x]
+  float* sPart = sIn + MM_ROWS * inC;
   const int r0 = blockIdx.x * MM_ROWS;
   const int nr = min(MM_ROWS, rows - r0);
-  for(int i = threadIdx.x; i < MM_ROWS * inC; i += blockDim.x) {
+  const int tid = threadIdx.y * blockDim.x + threadIdx.x, nthreads = blockDim.x * blockDim.y;
+  for(int i = tid; i < MM_ROWS * inC; i += nthreads) {
     const int r = i / inC;
     sIn[i] = r < nr ? in[(size_t)r0 * inC + i] : 0.0f;
   }
   __syncthreads();
-  for(int oc = threadIdx.x; oc < outC; oc += blockDim.x) {
+  const int kPer = (inC + MM_KSPLIT - 1) / MM_KSPLIT;
+  const int k0 = threadIdx.y * kPer, k1 = min(inC, k0 + kPer);
+  for(int ocBase = 0; ocBase < outC; ocBase += blockDim.x) {
+    const int oc = ocBase + threadIdx.x;
     float s[MM_ROWS];
 #pragma unroll
     for(int r = 0; r < MM_ROWS; r++) s[r] = 0.0f;
+    if(oc < outC) {
 #pragma unroll 8
-    for(int ic = 0; ic < inC; ic++) {
-      const float wv = w[(size_t)ic * outC + oc];
+      for(int ic = k0; ic < k1; ic++) {
+        const float wv = w[(size_t)ic * outC + oc];
 #pragma unroll
-      for(int r = 0; r < MM_ROWS; r++) s[r] = fmaf(sIn[r * inC + ic], wv, s[r]);
+        for(int r = 0; r < MM_ROWS; r++) s[r] = fmaf(sIn[r * inC + ic], wv, s[r]);
+      }
     }
-    const float b = bias ? bias[oc] : 0.0f;
 #pragma unroll
-    for(int r = 0; r < MM_ROWS; r++)
-      if(r < nr) out[(size_t)(r0 + r) * outC + oc] = applyActF(s[r] + b, act);
+    for(int r = 0; r < MM_ROWS; r++) sPart[(threadIdx.y * MM_ROWS + r) * blockDim.x + threadIdx.x] = s[r];
+    __syncthreads();
+    if(threadIdx.y == 0 && oc < outC) {
+      const float b = bias ? bias[oc] : 0.0f;
+#pragma unroll
+      for(int r = 0; r < MM_ROWS; r++) {
+        float t = 0.0f;
+#pragma unroll
+        for(int k = 0; k < MM_KSPLIT; k++) t += sPart[(k * MM_ROWS + r) * blockDim.x + threadIdx.x];
+        if(r < nr) out[(size_t)(r0 + r) * outC + oc] = applyActF(t + b, act);
+      }
+    }
+    __syncthreads();
   }
 }
 
 cudaError_t launchMatMulSmall(
   cudaStream_t st, const float* in, int inC, const float* w, int outC, const float* bias, int act, float* out, int rows) {
   const int threads = outC >= 128 ? 128 : (outC > 32 ? 64 : 32);
-  matMulSmallKernel<<<(rows + MM_ROWS - 1) / MM_ROWS, threads, MM_ROWS * inC * sizeof(float), st>>>(in, inC, w, outC, bias, act, out, rows);
+  const size_t smem = (size_t)(MM_ROWS * inC + MM_KSPLIT * MM_ROWS * threads) * sizeof(float);
+  matMulSmallKernel<<<(rows + MM_ROWS - 1) / MM_ROWS, dim3(threads, MM_KSPLIT), smem, st>>>(in, inC, w, outC, bias, act, out, rows);
   return cudaGetLastError();
 }
 
@@ -377,13 +397,22 @@ __global__ void biasBnActVec8Kernel(
       const uint4 x = *reinterpret_cast<const uint4*>(in + m * inStride + c);
       const T* xe = reinterpret_cast<const T*>(&x);
       T* oe = reinterpret_cast<T*>(&o);
-      const float* bnc = biasNC ? biasNC + (m / g.PB) * C + c : nullptr;
+      float v[8];
 #pragma unroll
-      for(int j = 0; j < 8; j++) {
-        float v = toF<T>(xe[j]);
-        if(bnc) v += bnc[j];
-        oe[j] = fromF<T>(applyActF(v * scale[c + j] + bias[c + j], act));
+      for(int j = 0; j < 8; j++) v[j] = toF<T>(xe[j]);
+      if(biasNC) {
+        const float4* bn4 = reinterpret_cast<const float4*>(biasNC + (m / g.PB) * C + c);
+        const float4 b0 = bn4[0], b1 = bn4[1];
+        v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w; v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
       }
+      const float4* s4 = reinterpret_cast<const float4*>(scale + c);
+      const float4* b4 = reinterpret_cast<const float4*>(bias + c);
+      const float4 s0 = s4[0], s1 = s4[1], c0 = b4[0], c1 = b4[1];
+      const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+      const float bi[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+      // reduced-precision output: the fast activation's error is far below the rounding of the result
+#pragma unroll
+      for(int j = 0; j < 8; j++) oe[j] = fromF<T>(fastAct(fmaf(v[j], sc[j], bi[j]), act));
     }
     *reinterpret_cast<uint4*>(out + m * outStride + c) = o;
   }

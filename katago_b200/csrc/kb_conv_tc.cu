@@ -117,6 +117,7 @@ struct ConvTcArgs {
   uint32_t idesc;
   uint32_t tmemCols;
   int epiWarpBytes; // shared memory of one epilogue warp's staging units (TMA epilogue)
+  int resRing;     // TMA epilogue with a residual: slots of each warp's residual ring (look-ahead = resRing - 1 units)
   int tmaEpi;      // 1: outputs and residual travel through shared memory and TMA (64-channel aligned ranges)
   int* status;     // device status word: 0 = ok
   int trace;       // timeline instrumentation requested (only in builds with KB_TC_TRACE)
@@ -242,13 +243,18 @@ struct EpiWarp {
   uint8_t* sO;          // one unit for the activated output
   uint64_t* resFull;    // [ring] residual unit landed (TMA)
   int nU;               // units of this warp per tile
-  int ring;             // nU + 1 with a residual (one tile of look-ahead), else 2
+  int ring;             // slots of the residual/raw ring
   uint32_t seq;         // units processed so far, over all tiles
 };
 
-// Fetches the residual of this warp's unit j of the tile at (m0, n0) into its ring slot (lane 0 only).
+// Fetches the residual of this warp's unit number `seq` (counted over all of the CTA's tiles, nU per tile) into its
+// ring slot, if that tile exists (lane 0 only).
 __device__ __forceinline__ void prefetchResidual(
-  const CUtensorMap* tmRes, const EpiWarp& es, uint32_t seq, int m0, int n0, int q, int cg, int j) {
+  const CUtensorMap* tmRes, const ConvTcArgs& a, const EpiWarp& es, uint32_t seq, int numTiles, int numNTiles, int q, int cg) {
+  const int tile = (int)blockIdx.x + (int)(seq / (uint32_t)es.nU) * (int)gridDim.x;
+  if(tile >= numTiles) return;
+  const int j = (int)(seq % (uint32_t)es.nU);
+  const int m0 = (tile / numNTiles) * TC_BM, n0 = (tile % numNTiles) * a.BN;
   const uint32_t b = seq % (uint32_t)es.ring;
   mbarExpectTx(smemU32(&es.resFull[b]), (uint32_t)TC_UNIT_BYTES);
   tmaLoad2d(smemU32(es.sR + (size_t)b * TC_UNIT_BYTES), tmRes, n0 + (cg + TC_EPI_CG * j) * 32, m0 + q * 32, smemU32(&es.resFull[b]));
@@ -264,7 +270,7 @@ template <typename T, int ACT>
 __device__ __forceinline__ bool epilogueTileTma(
   const ConvTcArgs& a, const CUtensorMap* tmRaw, const CUtensorMap* tmAct, uint32_t tmemAcc, int q, int cg, int lane,
   int m0, int n0, float mk, const float* biasRow, EpiWarp& es, uint32_t tileIter, volatile int* abortFlag,
-  const float* sScale, const float* sBias, const CUtensorMap* tmRes, bool hasNext, int nextM0, int nextN0) {
+  const float* sScale, const float* sBias, const CUtensorMap* tmRes, int numTiles, int numNTiles) {
   const Epilogue& ep = a.ep;
   const bool hasRes = ep.residual != nullptr;
   const int sw = (lane >> 1) & 3;  // 64-byte swizzle: 16-byte chunk index XOR bits 1..2 of the row
@@ -350,7 +356,8 @@ __device__ __forceinline__ bool epilogueTileTma(
     // also frees the ring slot before this one for the residual of the same unit of the next tile.
     if(lane == 0) {
       bulkWaitRead0();
-      if(hasRes && hasNext && es.seq > 0) prefetchResidual(tmRes, es, es.seq + (uint32_t)es.nU, nextM0, nextN0, q, cg, j);
+      // the slot of the unit before this one is free now: it takes the unit ring-1 ahead of this one
+      if(hasRes && es.seq > 0) prefetchResidual(tmRes, a, es, es.seq + (uint32_t)es.ring - 1u, numTiles, numNTiles, q, cg);
     }
     __syncwarp();
     TRACE(threadIdx.x == 64, 1024 + (int)(tileIter & 31u) * 16 + j * 5 + 3);
@@ -552,7 +559,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
     es.sO = es.sR + (size_t)(a.epiWarpBytes - TC_UNIT_BYTES);
     es.resFull = resFull + (warp - 2) * TC_MAX_RING;
     es.nU = (a.BN / 32 - cg + TC_EPI_CG - 1) / TC_EPI_CG;
-    es.ring = a.ep.residual ? es.nU + 1 : 2;
+    es.ring = a.ep.residual ? a.resRing : 2;
     es.seq = 0;
     uint32_t it = 0;
     gridDepWait();  // mask, per-board bias, residual and the output buffers belong to the kernels before this one
@@ -567,11 +574,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
       const float* biasRow = a.ep.biasNC ? a.ep.biasNC + (size_t)bIdx * a.outC : nullptr;
       if(TMA_EPI) {
         if(a.ep.residual && lane == 0 && it == 0 && es.nU > 0) {
-          // The ring holds one tile plus one unit: fill it now; afterwards every unit that drains fetches the same
-          // unit of the next tile.
-          for(int j = 0; j < es.nU; j++) prefetchResidual(&tmRes, es, (uint32_t)j, m0, n0, q, cg, j);
-          const int tn = t + gridDim.x;
-          if(tn < numTiles) prefetchResidual(&tmRes, es, (uint32_t)es.nU, (tn / numNTiles) * TC_BM, (tn % numNTiles) * a.BN, q, cg, 0);
+          // fill the ring; afterwards every unit that drains fetches the unit ring-1 ahead of it
+          for(int k = 0; k < es.ring; k++) prefetchResidual(&tmRes, a, es, (uint32_t)k, numTiles, numNTiles, q, cg);
         }
         __syncwarp();
       }
@@ -586,10 +590,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
       tcFenceAfter();
       const uint32_t acc = tmemBase + buf * (uint32_t)a.BN;
       if(TMA_EPI) {
-        const int tn = t + gridDim.x;
-        const bool hasNext = tn < numTiles;
-        const int nextM0 = (tn / numNTiles) * TC_BM, nextN0 = (tn % numNTiles) * a.BN;
-        const bool ok2 = epilogueTileTma<T, ACT>(a, &tmRaw, &tmAct, acc, q, cg, lane, m0, n0, mk, biasRow, es, it, abortFlag, sScale, sBias, &tmRes, hasNext, nextM0, nextN0);
+        const bool ok2 = epilogueTileTma<T, ACT>(a, &tmRaw, &tmAct, acc, q, cg, lane, m0, n0, mk, biasRow, es, it, abortFlag, sScale, sBias, &tmRes, numTiles, numNTiles);
         if(!ok2) {
           if(lane == 0 && !*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, TC_ERR_EPILOGUE_TIMEOUT); }
           break;
@@ -665,7 +666,7 @@ struct ConvTcPlan {
   size_t smemBytes;
   int numSMs;
   int rowsPadMax;
-  int tmaEpi, epiWarpBytes;
+  int tmaEpi, epiWarpBytes, resRing;
   CUtensorMap tmRes, tmRaw, tmAct;
 };
 
@@ -803,8 +804,13 @@ bool convTcSetEpilogue(ConvTcPlan* p, const Epilogue& ep) {
   if(!ok || (!ep.outRaw && !ep.outAct)) return sizeRings(p, 0);
   // per warp: the residual/raw ring (one tile of this warp's units plus one with a residual, else two units) and one
   // unit for the activated output
+  // With a residual the ring holds it one whole tile ahead for 1x1 convolutions, whose epilogue is the critical path;
+  // a 3x3 convolution hides its epilogue behind the MMAs and does better with the shared memory spent on weight slots,
+  // so it looks only one unit ahead.  Without a residual two raw units alternate (none if there is no raw output).
   const int unitsPerWarp = (p->BN / 32 + TC_EPI_CG - 1) / TC_EPI_CG;
-  p->epiWarpBytes = ((ep.residual ? unitsPerWarp + 1 : 2) + 1) * TC_UNIT_BYTES;
+  p->resRing = (p->kY == 1) ? unitsPerWarp + 1 : 2;
+  const int rawUnits = ep.residual ? p->resRing : (ep.outRaw ? 2 : 0);
+  p->epiWarpBytes = (rawUnits + 1) * TC_UNIT_BYTES;
   if(!sizeRings(p, TC_EPI_WARPS * p->epiWarpBytes)) return sizeRings(p, 0);
   const uint64_t rows = (uint64_t)p->rowsPadMax;
   const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_64B;
@@ -838,6 +844,7 @@ cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epi
 #endif
   a.tmaEpi = p->tmaEpi;
   a.epiWarpBytes = p->epiWarpBytes;
+  a.resRing = p->resRing;
   const int numTiles = (g.rowsPad / TC_BM) * (p->outC / p->BN);
   int grid = numTiles < p->numSMs ? numTiles : p->numSMs;
   if(p->residentB) {

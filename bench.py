@@ -37,6 +37,25 @@ FLOPS_PER_EVAL = 18.87e9  # direct-convolution FLOPs of b18c384nbt on the 19x19 
 METRIC = "NN evals/sec, b18c384nbt fp16 batch 256 19x19"
 WORKLOAD = "b18c384nbt nested-bottleneck net (18 blocks, 384/192 channels, Mish), fp16 storage fp32 accumulate, 19x19, batch 256 per GPU"
 
+# The headline workload is "b18" (the configuration the metric is quoted on).  The others are the remaining
+# configurations of the parity suite, selectable for measurement only; the default line never changes.
+WORKLOADS = {
+    "b18": dict(builder="make_b18c384nbt", precision="fp16", batch=256, sizes=None, metric=METRIC, text=WORKLOAD,
+                dominant="conv3x3 192->192"),
+    "b28": dict(builder="make_b28c512nbt", precision="bf16", batch=512, sizes=None,
+                metric="NN evals/sec, b28c512nbt bf16 batch 512 19x19",
+                text="b28c512nbt nested-bottleneck net (28 blocks, 512/256 channels, Mish), bf16 storage fp32 accumulate, 19x19, batch 512 per GPU",
+                dominant="conv3x3 256->256"),
+    "transformer": dict(builder="make_transformer", precision="fp16", batch=128, sizes=None,
+                        metric="NN evals/sec, transformer trunk 12x(6x64, SwiGLU 1024) fp16 batch 128 19x19",
+                        text="3x3 stem to d=384, 12 pre-norm layers (6 heads x 64, learnable RoPE, SwiGLU 1024), fp16, 19x19, batch 128 per GPU",
+                        dominant="attention"),
+    "mixed": dict(builder="make_b18c384nbt", precision="fp16", batch=128, sizes=[9, 13, 19, 19],
+                  metric="NN evals/sec, b18c384nbt fp16 mixed 9/13/19 boards padded to 19x19, batch 128 per GPU",
+                  text="b18c384nbt, fp16, boards 9x9/13x13/19x19 in ratio 1:1:2 zero-padded to 19x19 with the on-board mask, batch 128 per GPU (1024 over 8)",
+                  dominant="conv3x3 192->192"),
+}
+
 
 def _peaks():
     try:
@@ -122,12 +141,14 @@ def _max_over_ranks(pg, x):
     return float(t.item())
 
 
-def cpu_oracle_rate(budget_s, positions_per_call, max_calls):
+def cpu_oracle_rate(budget_s, positions_per_call, max_calls, wl=None):
     """evals/s of the CPU port of the reference's Eigen backend on the same net and position scheme."""
     from katago_b200 import modelfile as mf
     from oracle import pyoracle as po
-    om = po.OracleModel(mf.to_blob(mf.make_b18c384nbt()))
-    sp, gl = mf.random_positions(positions_per_call, seed=2000)
+    wl = wl or WORKLOADS["b18"]
+    om = po.OracleModel(mf.to_blob(getattr(mf, wl["builder"])()))
+    sizes = (wl["sizes"] * positions_per_call)[:positions_per_call] if wl["sizes"] else None
+    sp, gl = mf.random_positions(positions_per_call, seed=2000, board_sizes=sizes)
     om.forward(sp[:1], gl[:1])  # touch the weights once
     done, t0 = 0, time.perf_counter()
     per_call = []
@@ -181,9 +202,13 @@ def run_b200(args, rank, world, local, pg):
     except Exception:
         pass
 
-    model = kb.Model(mf.to_blob(mf.make_b18c384nbt()))
-    h = kb.Handle(model, BATCH, precision=kb.PRECISION_FP16, device=device)
-    sp, gl = mf.random_positions(BATCH, seed=2000 + rank)
+    wl = WORKLOADS[args.workload]
+    BATCH = wl["batch"]
+    precision = dict(fp16=kb.PRECISION_FP16, bf16=kb.PRECISION_BF16)[wl["precision"]]
+    model = kb.Model(mf.to_blob(getattr(mf, wl["builder"])()))
+    h = kb.Handle(model, BATCH, precision=precision, device=device)
+    sizes = (wl["sizes"] * BATCH)[:BATCH] if wl["sizes"] else None
+    sp, gl = mf.random_positions(BATCH, seed=2000 + rank, board_sizes=sizes)
     S = 19 * 19
     # page-locked staging, as the backend's InputBuffers hold it
     pin_sp = capi.PinnedArray((BATCH, 19, 19, model.in_c)); pin_sp.array[...] = sp
@@ -233,33 +258,35 @@ def run_b200(args, rank, world, local, pg):
         return
     peaks = _peaks()
     total_ms = sum(p["ms"] for p in prof) or 1.0
-    dom = [p for p in prof if p["name"].startswith("conv3x3 192->192") and "tcgen05" in p["name"] and "reg|gpool" not in p["name"]]
+    dom = [p for p in prof if p["name"].startswith(wl["dominant"]) and "tcgen05" in p["name"] and "reg|gpool" not in p["name"]]
     dom_ms = sum(p["ms"] for p in dom); dom_launches = sum(p["launches"] for p in dom); dom_flops = sum(p["flops"] for p in dom)
     achieved = (dom_flops / (dom_ms * 1e-3) / 1e12) if dom_ms > 0 else 0.0
     traffic = None
-    try:
-        with open(os.path.join(ROOT, "profiles", "conv3x3_192_b18_n256_traffic.json")) as f:
-            traffic = json.load(f)["dram_bytes_per_launch"]
-    except Exception:
-        pass
+    if args.workload == "b18":
+        try:
+            with open(os.path.join(ROOT, "profiles", "conv3x3_192_b18_n256_traffic.json")) as f:
+                traffic = json.load(f)["dram_bytes_per_launch"]
+        except Exception:
+            pass
     all_conv_flops = sum(p["flops"] for p in prof)
-    cpu = cpu_oracle_rate(budget_s=12.0, positions_per_call=8, max_calls=8)
+    flops_per_eval = FLOPS_PER_EVAL if args.workload == "b18" else all_conv_flops / (args.steps * BATCH)
+    cpu = cpu_oracle_rate(budget_s=12.0, positions_per_call=8, max_calls=8, wl=wl)
     line = {
-        "metric": METRIC, "value": value, "unit": "evals/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "metric": wl["metric"], "value": value, "unit": "evals/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_total / args.steps, "p50_batch_latency_ms": statistics.median(ms_each), "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "batch_per_gpu": BATCH, "parallelism": f"replicas x{world}, no collective",
+        "vs_baseline": None, "dtype": {"fp16": "f16", "bf16": "bf16"}[wl["precision"]], "data": "synthetic",
+        "config": {"workload": wl["text"], "batch_per_gpu": BATCH, "parallelism": f"replicas x{world}, no collective",
                    "l2": "256 MiB memset between timed steps (L2 flush); per-step activations (~0.4 GB) also exceed the 126 MB L2",
                    "weights": "random init N(0,1/fan_in), BN scale U(0.5,1.5) bias N(0,0.1), seed 1001", "positions": "seeded synthetic, empty/black/white 0.6/0.2/0.2"},
         "clocks": clocks,
         "e2e": {"value": e2e, "unit": "evals/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s / args.steps * 1e3},
         "gpu_launches": launches * args.steps,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
-                     "traffic": traffic, "kernel": "convTcKernel<half> 3x3 192->192 (both epilogue variants)", "launches": dom_launches,
+                     "traffic": traffic, "kernel": ("convTcKernel<half> 3x3 192->192 (both epilogue variants)" if args.workload in ("b18", "mixed") else wl["dominant"] + " (tcgen05)"), "launches": dom_launches,
                      "avg_launch_ms": dom_ms / dom_launches if dom_launches else None, "share_of_step": dom_ms / total_ms,
                      "peak_source": f"MEASURED_PEAKS.json bf16_tflops_sustained ({peaks['src']}); burst {peaks['burst']}",
                      "whole_step_tflops": all_conv_flops / (total_ms * 1e-3) / 1e12,
-                     "whole_step_frac_of_peak": FLOPS_PER_EVAL * value / world / 1e12 / peaks["tflops"]},
+                     "whole_step_frac_of_peak": flops_per_eval * value / world / 1e12 / peaks["tflops"]},
         "cpu_baseline": {"value": cpu["value"], "unit": "evals/s", "cores": cpu["cores"], "kind": "port",
                          "sample": f"{cpu['calls']} calls of 8 positions of the same net and position scheme (oracle/kata_oracle.cpp, OpenMP, fp32)"},
         "kernels": [{"name": p["name"], "launches": p["launches"], "ms": round(p["ms"], 4), "share": round(p["ms"] / total_ms, 4)}
@@ -274,6 +301,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="b18", choices=sorted(WORKLOADS), help="b18 is the headline configuration; the others are for measurement of the remaining configurations")
     args = ap.parse_args()
     rank, world, local, pg = _dist()
     if args.impl == "reference":

@@ -113,6 +113,7 @@ struct ConvTcArgs {
   int aSlotBytes;  // aRows * 128
   int bSlotBytes;  // BN * 128
   int numA, numB;  // ring depths
+  int pair;        // 1: CTA pairs (cluster of 2, cta_group::2 MMAs over 256 rows); bSlotBytes then holds half a weight tile
   int residentB;   // 1x1 only: all weight tiles of this CTA's channel tile stay in shared memory for the whole kernel
   uint32_t idesc;
   uint32_t tmemCols;
@@ -249,12 +250,20 @@ struct EpiWarp {
 
 // Fetches the residual of this warp's unit number `seq` (counted over all of the CTA's tiles, nU per tile) into its
 // ring slot, if that tile exists (lane 0 only).
+// Which tiles a CTA works on: tile t covers rows (t / numNTiles) * rowsPerUnit + rowBase and channel tile t % numNTiles;
+// a CTA takes t = first, first + step, ...  (a CTA pair shares t; rowBase selects the half).
+struct TileMap {
+  int first, step, numTiles, numNTiles, rowsPerUnit, rowBase;
+  __device__ __forceinline__ int m0(int t) const { return (t / numNTiles) * rowsPerUnit + rowBase; }
+  __device__ __forceinline__ int nTile(int t) const { return t % numNTiles; }
+};
+
 __device__ __forceinline__ void prefetchResidual(
-  const CUtensorMap* tmRes, const ConvTcArgs& a, const EpiWarp& es, uint32_t seq, int numTiles, int numNTiles, int q, int cg) {
-  const int tile = (int)blockIdx.x + (int)(seq / (uint32_t)es.nU) * (int)gridDim.x;
-  if(tile >= numTiles) return;
+  const CUtensorMap* tmRes, const ConvTcArgs& a, const EpiWarp& es, uint32_t seq, const TileMap& tm, int q, int cg) {
+  const int tile = tm.first + (int)(seq / (uint32_t)es.nU) * tm.step;
+  if(tile >= tm.numTiles) return;
   const int j = (int)(seq % (uint32_t)es.nU);
-  const int m0 = (tile / numNTiles) * TC_BM, n0 = (tile % numNTiles) * a.BN;
+  const int m0 = tm.m0(tile), n0 = tm.nTile(tile) * a.BN;
   const uint32_t b = seq % (uint32_t)es.ring;
   mbarExpectTx(smemU32(&es.resFull[b]), (uint32_t)TC_UNIT_BYTES);
   tmaLoad2d(smemU32(es.sR + (size_t)b * TC_UNIT_BYTES), tmRes, n0 + (cg + TC_EPI_CG * j) * 32, m0 + q * 32, smemU32(&es.resFull[b]));
@@ -270,7 +279,7 @@ template <typename T, int ACT>
 __device__ __forceinline__ bool epilogueTileTma(
   const ConvTcArgs& a, const CUtensorMap* tmRaw, const CUtensorMap* tmAct, uint32_t tmemAcc, int q, int cg, int lane,
   int m0, int n0, float mk, const float* biasRow, EpiWarp& es, uint32_t tileIter, volatile int* abortFlag,
-  const float* sScale, const float* sBias, const CUtensorMap* tmRes, int numTiles, int numNTiles) {
+  const float* sScale, const float* sBias, const CUtensorMap* tmRes, const TileMap& tm) {
   const Epilogue& ep = a.ep;
   const bool hasRes = ep.residual != nullptr;
   const int sw = (lane >> 1) & 3;  // 64-byte swizzle: 16-byte chunk index XOR bits 1..2 of the row
@@ -357,7 +366,7 @@ __device__ __forceinline__ bool epilogueTileTma(
     if(lane == 0) {
       bulkWaitRead0();
       // the slot of the unit before this one is free now: it takes the unit ring-1 ahead of this one
-      if(hasRes && es.seq > 0) prefetchResidual(tmRes, a, es, es.seq + (uint32_t)es.ring - 1u, numTiles, numNTiles, q, cg);
+      if(hasRes && es.seq > 0) prefetchResidual(tmRes, a, es, es.seq + (uint32_t)es.ring - 1u, tm, q, cg);
     }
     __syncwarp();
     TRACE(threadIdx.x == 64, 1024 + (int)(tileIter & 31u) * 16 + j * 5 + 3);
@@ -383,7 +392,7 @@ __device__ __forceinline__ bool epilogueTileTma(
 
 // One instantiation per element type, activation and epilogue kind: the epilogue is long straight-line code, and a
 // kernel that carried every variant ran measurably slower (instruction cache).
-template <typename T, int ACT, bool TMA_EPI>
+template <typename T, int ACT, bool TMA_EPI, bool PAIR>
 __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
   const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmRes,
   const __grid_constant__ CUtensorMap tmRaw, const __grid_constant__ CUtensorMap tmAct, const ConvTcArgs a) {
@@ -409,22 +418,33 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int numNTiles = a.outC / a.BN;
-  const int numTiles = (a.g.rowsPad / TC_BM) * numNTiles;
   const int taps = a.kY * a.kX;
+  // CTA pair: both CTAs walk the same tile list; a tile is 256 rows, the even CTA (leader) takes the upper 128
+  const uint32_t rank = PAIR ? clusterCtaRank() : 0u;
+  const bool leader = rank == 0u;
+  TileMap tm;
+  tm.first = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  tm.step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  tm.numNTiles = numNTiles;
+  tm.rowsPerUnit = PAIR ? 2 * TC_BM : TC_BM;
+  tm.numTiles = (a.g.rowsPad / tm.rowsPerUnit) * numNTiles;
+  tm.rowBase = (int)rank * TC_BM;
+  const int numTiles = tm.numTiles;
 
   gridDepLaunch();
   if(threadIdx.x == 0) {
     for(int s = 0; s < a.numA; s++) { mbarInit(smemU32(&fullA[s]), 1); mbarInit(smemU32(&emptyA[s]), 1); }
     for(int s = 0; s < a.numB; s++) { mbarInit(smemU32(&fullB[s]), 1); mbarInit(smemU32(&emptyB[s]), 1); }
-    for(int s = 0; s < 2; s++) { mbarInit(smemU32(&accFull[s]), 1); mbarInit(smemU32(&accEmpty[s]), TC_EPI_WARPS); }
+    // the leader's accumulator-drained barrier collects the epilogue warps of both CTAs of a pair
+    for(int s = 0; s < 2; s++) { mbarInit(smemU32(&accFull[s]), 1); mbarInit(smemU32(&accEmpty[s]), PAIR ? 2 * TC_EPI_WARPS : TC_EPI_WARPS); }
     for(int s = 0; s < TC_EPI_WARPS * TC_MAX_RING; s++) mbarInit(smemU32(&resFull[s]), 1);
     *abortFlag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if(warp == 1) {
-    tmemAlloc(smemU32(tmemSlot), a.tmemCols);
-    tmemRelinquish();
+    if(PAIR) { tmemAllocPair(smemU32(tmemSlot), a.tmemCols); tmemRelinquishPair(); }
+    else { tmemAlloc(smemU32(tmemSlot), a.tmemCols); tmemRelinquish(); }
   }
   // next layer's norm parameters: read once per CTA (weights: not produced by the preceding kernels)
   if(a.ep.outAct) {
@@ -433,6 +453,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
   }
   tcFenceBefore();
   __syncthreads();
+  if(PAIR) clusterSync();  // the other CTA's barriers are initialised before anything here signals them
   tcFenceAfter();
   const uint32_t tmemBase = *tmemSlot;
 
@@ -441,29 +462,40 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
     if(lane == 0) {
       uint32_t sa = 0, phA = 0, sb = 0, phB = 0;
       bool ok = true;
+      // In a pair both CTAs load their own rows of A and their own half of each weight tile; every load signals the
+      // leader's barrier, on which the leader alone has announced the bytes of both CTAs.
+      const uint32_t aBytes = (PAIR ? 2u : 1u) * (uint32_t)a.aSlotBytes, bBytes = (PAIR ? 2u : 1u) * (uint32_t)a.bSlotBytes;
+      const int bRow0 = PAIR ? (int)rank * (a.BN / 2) : 0;
+      auto loadA = [&](uint32_t slot, int kc, int m0) {
+        const uint32_t bar = smemU32(&fullA[slot]), dst = smemU32(smemA + (size_t)slot * a.aSlotBytes);
+        if(leader) mbarExpectTx(bar, aBytes);
+        if(PAIR) tmaLoad2dPair(dst, &tmA, kc * TC_BK, m0 - a.haloPad, pairLeaderAddr(bar));
+        else tmaLoad2d(dst, &tmA, kc * TC_BK, m0 - a.haloPad, bar);
+      };
+      auto loadB = [&](uint32_t slot, int kc, int row) {
+        const uint32_t bar = smemU32(&fullB[slot]), dst = smemU32(smemB + (size_t)slot * a.bSlotBytes);
+        if(leader) mbarExpectTx(bar, bBytes);
+        if(PAIR) tmaLoad2dPair(dst, &tmB, kc * TC_BK, row + bRow0, pairLeaderAddr(bar));
+        else tmaLoad2d(dst, &tmB, kc * TC_BK, row, bar);
+      };
       if(a.residentB) {
-        // the grid is a multiple of the number of channel tiles, so this CTA always works on the same one
-        const int n0 = (blockIdx.x % numNTiles) * a.BN;
-        for(int kc = 0; kc < a.kChunks; kc++) {
-          mbarExpectTx(smemU32(&fullB[kc]), (uint32_t)a.bSlotBytes);
-          tmaLoad2d(smemU32(smemB + (size_t)kc * a.bSlotBytes), &tmB, kc * TC_BK, n0, smemU32(&fullB[kc]));
-        }
+        // the number of CTAs (pairs) is a multiple of the number of channel tiles, so this CTA always works on the same one
+        const int n0 = (tm.first % numNTiles) * a.BN;
+        for(int kc = 0; kc < a.kChunks; kc++) loadB((uint32_t)kc, kc, n0);
       }
       // everything above touched only weights; the activations belong to the kernels before this one
       gridDepWait();
-      for(int t = blockIdx.x; t < numTiles && ok; t += gridDim.x) {
-        const int m0 = (t / numNTiles) * TC_BM, n0 = (t % numNTiles) * a.BN;
+      for(int t = tm.first; t < numTiles && ok; t += tm.step) {
+        const int m0 = tm.m0(t), n0 = tm.nTile(t) * a.BN;
         for(int kc = 0; kc < a.kChunks && ok; kc++) {
           if(!mbarWait(smemU32(&emptyA[sa]), phA ^ 1u, abortFlag)) { ok = false; break; }
-          TRACE(true, ((t - blockIdx.x) / gridDim.x) * 16 + kc);
-          mbarExpectTx(smemU32(&fullA[sa]), (uint32_t)a.aSlotBytes);
-          tmaLoad2d(smemU32(smemA + (size_t)sa * a.aSlotBytes), &tmA, kc * TC_BK, m0 - a.haloPad, smemU32(&fullA[sa]));
+          TRACE(true, ((t - tm.first) / tm.step) * 16 + kc);
+          loadA(sa, kc, m0);
           if(++sa == (uint32_t)a.numA) { sa = 0; phA ^= 1u; }
           if(a.residentB) continue;
           for(int tap = 0; tap < taps; tap++) {
             if(!mbarWait(smemU32(&emptyB[sb]), phB ^ 1u, abortFlag)) { ok = false; break; }
-            mbarExpectTx(smemU32(&fullB[sb]), (uint32_t)a.bSlotBytes);
-            tmaLoad2d(smemU32(smemB + (size_t)sb * a.bSlotBytes), &tmB, kc * TC_BK, tap * a.outC + n0, smemU32(&fullB[sb]));
+            loadB(sb, kc, tap * a.outC + n0);
             if(++sb == (uint32_t)a.numB) { sb = 0; phB ^= 1u; }
           }
         }
@@ -476,7 +508,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
     // One thread issues every MMA; its instruction stream is the critical path of the main loop, so the
     // descriptors are kept as 32-bit low words that only need an add per MMA, ring positions wrap by compare,
     // and the tap offsets are computed once.
-    if(lane == 0) {
+    // In a pair only the leader issues; its MMAs read both CTAs' shared memory and write both CTAs' TMEM, and every
+    // completion is signalled to the same barrier of both CTAs.
+    if(lane == 0 && leader) {
+      auto mma = [&](uint32_t d, uint32_t aLo, uint32_t bLo, uint32_t descHi, uint32_t acc) {
+        if(PAIR) ummaLoHiPair(d, aLo, bLo, descHi, a.idesc, acc);
+        else ummaLoHi(d, aLo, bLo, descHi, a.idesc, acc);
+      };
+      auto commit = [&](uint64_t* bar) {
+        const uint32_t b = smemU32(bar);
+        if(PAIR) { ummaCommitPair(b); ummaCommitPair(clusterMapAddr(b, 1u)); }
+        else ummaCommit(b);
+      };
       const uint32_t descHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);  // stride offset | version | SWIZZLE_128B
       const uint32_t aLoBase = ((smemU32(smemA) & 0x3FFFFu) >> 4) | (1u << 16);
       const uint32_t bLoBase = ((smemU32(smemB) & 0x3FFFFu) >> 4) | (1u << 16);
@@ -490,7 +533,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
       }
       uint32_t sa = 0, phA = 0, sb = 0, phB = 0, it = 0;
       bool ok = true;
-      for(int t = blockIdx.x; t < numTiles && ok; t += gridDim.x, it++) {
+      for(int t = tm.first; t < numTiles && ok; t += tm.step, it++) {
         const uint32_t buf = it & 1u;
         // wait until the epilogue has drained this accumulator (two tiles ago)
         if(!mbarWait(smemU32(&accEmpty[buf]), ((it >> 1) & 1u) ^ 1u, abortFlag)) { ok = false; break; }
@@ -511,10 +554,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
 #pragma unroll
               for(int k = 0; k < TC_BK / 16; k++) {
                 // advancing K by 16 elements = 32 bytes = 2 units inside the 128-byte swizzle atom
-                ummaLoHi(dTmem, aT + 2 * k, bT + 2 * k, descHi, a.idesc, accumulate);
+                mma(dTmem, aT + 2 * k, bT + 2 * k, descHi, accumulate);
                 accumulate = 1;
               }
-              ummaCommit(smemU32(&emptyB[sb]));  // frees the weight slot once these MMAs have read it
+              commit(&emptyB[sb]);  // frees the weight slot once these MMAs have read it
               if(++sb == (uint32_t)a.numB) { sb = 0; phB ^= 1u; }
             }
           }
@@ -525,7 +568,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
             const uint32_t bT = bLoBase + (uint32_t)kc * bSlot16;
 #pragma unroll
             for(int k = 0; k < TC_BK / 16; k++) {
-              ummaLoHi(dTmem, aLo + 2 * k, bT + 2 * k, descHi, a.idesc, accumulate);
+              mma(dTmem, aLo + 2 * k, bT + 2 * k, descHi, accumulate);
               accumulate = 1;
             }
           }
@@ -535,16 +578,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
             const uint32_t bT = bLoBase + sb * bSlot16;
 #pragma unroll
             for(int k = 0; k < TC_BK / 16; k++) {
-              ummaLoHi(dTmem, aLo + 2 * k, bT + 2 * k, descHi, a.idesc, accumulate);
+              mma(dTmem, aLo + 2 * k, bT + 2 * k, descHi, accumulate);
               accumulate = 1;
             }
-            ummaCommit(smemU32(&emptyB[sb]));
+            commit(&emptyB[sb]);
             if(++sb == (uint32_t)a.numB) { sb = 0; phB ^= 1u; }
           }
-          ummaCommit(smemU32(&emptyA[sa]));
+          commit(&emptyA[sa]);
           if(++sa == (uint32_t)a.numA) { sa = 0; phA ^= 1u; }
         }
-        if(ok) ummaCommit(smemU32(&accFull[buf]));
+        if(ok) commit(&accFull[buf]);
         TRACE(true, 256 + it * 16 + 15);
       }
       if(!ok && !*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, TC_ERR_MMA_TIMEOUT); }
@@ -563,9 +606,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
     es.seq = 0;
     uint32_t it = 0;
     gridDepWait();  // mask, per-board bias, residual and the output buffers belong to the kernels before this one
-    for(int t = blockIdx.x; t < numTiles; t += gridDim.x, it++) {
+    for(int t = tm.first; t < numTiles; t += tm.step, it++) {
       const uint32_t buf = it & 1u;
-      const int m0 = (t / numNTiles) * TC_BM, n0 = (t % numNTiles) * a.BN;
+      const int m0 = tm.m0(t), n0 = tm.nTile(t) * a.BN;
       // Nothing below depends on the accumulator yet: fetch mask and residual while the MMAs still run.
       TRACE(threadIdx.x == 64, 512 + it * 16);
       const int m = m0 + q * 32 + lane;
@@ -575,7 +618,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
       if(TMA_EPI) {
         if(a.ep.residual && lane == 0 && it == 0 && es.nU > 0) {
           // fill the ring; afterwards every unit that drains fetches the unit ring-1 ahead of it
-          for(int k = 0; k < es.ring; k++) prefetchResidual(&tmRes, a, es, (uint32_t)k, numTiles, numNTiles, q, cg);
+          for(int k = 0; k < es.ring; k++) prefetchResidual(&tmRes, a, es, (uint32_t)k, tm, q, cg);
         }
         __syncwarp();
       }
@@ -590,7 +633,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
       tcFenceAfter();
       const uint32_t acc = tmemBase + buf * (uint32_t)a.BN;
       if(TMA_EPI) {
-        const bool ok2 = epilogueTileTma<T, ACT>(a, &tmRaw, &tmAct, acc, q, cg, lane, m0, n0, mk, biasRow, es, it, abortFlag, sScale, sBias, &tmRes, numTiles, numNTiles);
+        const bool ok2 = epilogueTileTma<T, ACT>(a, &tmRaw, &tmAct, acc, q, cg, lane, m0, n0, mk, biasRow, es, it, abortFlag, sScale, sBias, &tmRes, tm);
         if(!ok2) {
           if(lane == 0 && !*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, TC_ERR_EPILOGUE_TIMEOUT); }
           break;
@@ -601,7 +644,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
       tcFenceBefore();
       __syncwarp();
       TRACE(threadIdx.x == 64, 512 + it * 16 + 3);
-      if(lane == 0) mbarArrive(smemU32(&accEmpty[buf]));
+      if(lane == 0) {
+        if(PAIR) mbarArriveCluster(pairLeaderAddr(smemU32(&accEmpty[buf])));
+        else mbarArrive(smemU32(&accEmpty[buf]));
+      }
     }
     if(lane == 0) bulkWaitAll();  // outstanding tile stores must complete before the CTA's shared memory goes away
   }
@@ -615,9 +661,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
     while(globalTimerNs() - t0 < 2000000ull) { __nanosleep(1000); }
   }
   __syncthreads();
+  // a pair leaves together: the leader's MMAs and commits touch the other CTA's shared memory, and the other CTA's
+  // epilogue signals the leader's barriers
+  if(PAIR) clusterSync();
   if(warp == 1) {
     tcFenceAfter();
-    tmemDealloc(tmemBase, a.tmemCols);
+    if(PAIR) tmemDeallocPair(tmemBase, a.tmemCols);
+    else tmemDealloc(tmemBase, a.tmemCols);
   }
 }
 
@@ -643,25 +693,30 @@ static EncodeTiledFn getEncodeTiled() {
 
 // Kernel variants by (element type, activation, epilogue kind).
 typedef void (*ConvTcKernelFn)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, ConvTcArgs);
-template <typename T, bool TMA_EPI>
+template <typename T, bool TMA_EPI, bool PAIR>
 static ConvTcKernelFn kernelForAct(int act) {
   switch(act) {
-    case KB_ACT_RELU: return convTcKernel<T, KB_ACT_RELU, TMA_EPI>;
-    case KB_ACT_MISH: return convTcKernel<T, KB_ACT_MISH, TMA_EPI>;
-    case KB_ACT_SILU: return convTcKernel<T, KB_ACT_SILU, TMA_EPI>;
-    case KB_ACT_MISH_SCALE8: return convTcKernel<T, KB_ACT_MISH_SCALE8, TMA_EPI>;
-    default: return convTcKernel<T, KB_ACT_IDENTITY, TMA_EPI>;
+    case KB_ACT_RELU: return convTcKernel<T, KB_ACT_RELU, TMA_EPI, PAIR>;
+    case KB_ACT_MISH: return convTcKernel<T, KB_ACT_MISH, TMA_EPI, PAIR>;
+    case KB_ACT_SILU: return convTcKernel<T, KB_ACT_SILU, TMA_EPI, PAIR>;
+    case KB_ACT_MISH_SCALE8: return convTcKernel<T, KB_ACT_MISH_SCALE8, TMA_EPI, PAIR>;
+    default: return convTcKernel<T, KB_ACT_IDENTITY, TMA_EPI, PAIR>;
   }
 }
-static ConvTcKernelFn kernelFor(int dt, int act, bool tmaEpi) {
-  if(dt == DT_F16) return tmaEpi ? kernelForAct<__half, true>(act) : kernelForAct<__half, false>(act);
-  return tmaEpi ? kernelForAct<__nv_bfloat16, true>(act) : kernelForAct<__nv_bfloat16, false>(act);
+template <typename T>
+static ConvTcKernelFn kernelForT(int act, bool tmaEpi, bool pair) {
+  if(pair) return tmaEpi ? kernelForAct<T, true, true>(act) : kernelForAct<T, false, true>(act);
+  return tmaEpi ? kernelForAct<T, true, false>(act) : kernelForAct<T, false, false>(act);
+}
+static ConvTcKernelFn kernelFor(int dt, int act, bool tmaEpi, bool pair) {
+  return dt == DT_F16 ? kernelForT<__half>(act, tmaEpi, pair) : kernelForT<__nv_bfloat16>(act, tmaEpi, pair);
 }
 
 struct ConvTcPlan {
   CUtensorMap tmA, tmB;
   int dt, inC, outC, kY, kX, X, Y;
   int BN, kChunks, haloPad, aRows, aSlotBytes, bSlotBytes, numA, numB, residentB;
+  int pair;  // CTA pairs: 256-row tiles, half a weight tile per CTA
   uint32_t idesc, tmemCols;
   size_t smemBytes;
   int numSMs;
@@ -771,16 +826,24 @@ ConvTcPlan* convTcCreate(
   p->haloPad = (maxShift + 7) / 8 * 8;
   p->aRows = (p->haloPad + TC_BM + maxShift + 7) / 8 * 8;
   if(p->aRows > 256) { delete p; return nullptr; }
+  // CTA pairs halve the weight bytes each SM stages and reads per MMA.  Measured on B200: a gain only for the widest
+  // tiles (3x3 256->256, batch 512: 3 % faster, the SM clock under the power cap 3.5 % higher); the 192-wide tiles and
+  // all 1x1 convolutions run 5-10 % slower in pairs (a 256-row MMA takes 143 cycles against 127 for 128 rows, and the
+  // two CTAs move in lockstep).  KB_TC_PAIR=0/1 forces the choice for experiments.  Pairs need an even row-tile count,
+  // which the padded-rows layout guarantees.
+  bool wantPair = kY == 3 && p->BN == 256;
+  if(const char* e = getenv("KB_TC_PAIR")) wantPair = atoi(e) != 0;
+  p->pair = (wantPair && (rowsPadMax % (2 * TC_BM)) == 0 && (p->BN % 16) == 0) ? 1 : 0;
   p->aSlotBytes = p->aRows * 128;
-  p->bSlotBytes = p->BN * 128;
+  p->bSlotBytes = (p->pair ? p->BN / 2 : p->BN) * 128;
   if(!sizeRings(p, 0)) { delete p; return nullptr; }
   p->tmemCols = 32;
   while((int)p->tmemCols < 2 * p->BN) p->tmemCols *= 2;
   const uint32_t fmt = dt == DT_F16 ? 0u : 1u;
   // instruction descriptor: D=f32, A/B format, both K-major, N>>3 at bit 17, M>>4 at bit 24
-  p->idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(p->BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+  p->idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(p->BN >> 3) << 17) | ((uint32_t)((p->pair ? 2 * TC_BM : TC_BM) >> 4) << 24);
   bool ok = encode2d(&p->tmA, dt, in, (uint64_t)inC, (uint64_t)rowsPadMax, (uint64_t)inStride * 2, TC_BK, (uint32_t)p->aRows) &&
-            encode2d(&p->tmB, dt, w, (uint64_t)inC, (uint64_t)kY * kX * outC, (uint64_t)inC * 2, TC_BK, (uint32_t)p->BN);
+            encode2d(&p->tmB, dt, w, (uint64_t)inC, (uint64_t)kY * kX * outC, (uint64_t)inC * 2, TC_BK, (uint32_t)(p->pair ? p->BN / 2 : p->BN));
   if(!ok) { delete p; return nullptr; }
   int dev = 0, sms = 148;
   if(cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -833,6 +896,7 @@ cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epi
   a.inC = p->inC; a.outC = p->outC; a.kY = p->kY; a.kX = p->kX;
   a.BN = p->BN; a.kChunks = p->kChunks; a.haloPad = p->haloPad; a.aRows = p->aRows;
   a.aSlotBytes = p->aSlotBytes; a.bSlotBytes = p->bSlotBytes; a.numA = p->numA; a.numB = p->numB; a.residentB = p->residentB;
+  a.pair = p->pair;
   a.idesc = p->idesc; a.tmemCols = p->tmemCols;
   a.status = statusWord;
   a.trace = 0;
@@ -845,24 +909,38 @@ cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epi
   a.tmaEpi = p->tmaEpi;
   a.epiWarpBytes = p->epiWarpBytes;
   a.resRing = p->resRing;
-  const int numTiles = (g.rowsPad / TC_BM) * (p->outC / p->BN);
-  int grid = numTiles < p->numSMs ? numTiles : p->numSMs;
+  // work units: tiles of 128 rows for single CTAs, of 256 rows for CTA pairs
+  if(p->pair && (g.rowsPad % (2 * TC_BM)) != 0) return cudaErrorInvalidValue;
+  const int unitRows = p->pair ? 2 * TC_BM : TC_BM;
+  const int maxUnits = p->pair ? p->numSMs / 2 : p->numSMs;
+  const int numTiles = (g.rowsPad / unitRows) * (p->outC / p->BN);
+  int units = numTiles < maxUnits ? numTiles : maxUnits;
   if(p->residentB) {
     const int nt = p->outC / p->BN;
-    grid = grid / nt * nt;  // each CTA keeps one channel tile
-    if(grid < nt) grid = nt;
+    units = units / nt * nt;  // each CTA (pair) keeps one channel tile
+    if(units < nt) units = nt;
   }
+  const int grid = p->pair ? 2 * units : units;
   // Programmatic dependent launch: the preamble (barriers, TMEM, resident weights) overlaps the tail of the kernel
   // before this one in the stream; the kernel waits for that kernel before it touches any activation.
   static const bool usePdl = getenv("KB_NO_PDL") == nullptr;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid); cfg.blockDim = dim3(TC_THREADS); cfg.dynamicSmemBytes = p->smemBytes; cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr; cfg.numAttrs = usePdl ? 1 : 0;
+  cudaLaunchAttribute attr[2];
+  int numAttrs = 0;
+  if(p->pair) {
+    attr[numAttrs].id = cudaLaunchAttributeClusterDimension;
+    attr[numAttrs].val.clusterDim.x = 2; attr[numAttrs].val.clusterDim.y = 1; attr[numAttrs].val.clusterDim.z = 1;
+    numAttrs++;
+  }
+  if(usePdl) {
+    attr[numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[numAttrs].val.programmaticStreamSerializationAllowed = 1;
+    numAttrs++;
+  }
+  cfg.attrs = attr; cfg.numAttrs = numAttrs;
   // without an activated output the activation code is irrelevant: use the identity variant
-  ConvTcKernelFn fn = kernelFor(p->dt, ep.outAct ? ep.act : KB_ACT_IDENTITY, p->tmaEpi != 0);
+  ConvTcKernelFn fn = kernelFor(p->dt, ep.outAct ? ep.act : KB_ACT_IDENTITY, p->tmaEpi != 0, p->pair != 0);
   {
     // opt in to the large dynamic shared memory once per variant and device
     static std::mutex mu;

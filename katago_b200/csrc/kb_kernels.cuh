@@ -17,19 +17,19 @@ inline size_t dtypeSize(int dt) { return dt == DT_F32 ? 4 : 2; }
 // point (n,y,x) is n*PB + y*RW + x with RW = X+1 and PB = (Y+1)*RW.  Column X of every line and line Y of
 // every board are padding that always holds zeros in tensors that feed a convolution, so the 8 neighbours
 // of a point are at fixed row offsets (dy*RW + dx) and a 3x3 convolution is nine row-shifted GEMMs.
-// rowsPad = rows rounded up to a multiple of 128 (the MMA tile height).
+// rowsPad = rows rounded up to a multiple of 256 (two MMA tiles of 128 rows: a CTA pair works on both).
 struct Geom {
   int X, Y, RW, PB, S;
   int n;        // boards in this batch
   int rows;     // n * PB
-  int rowsPad;  // rows rounded up to 128
+  int rowsPad;  // rows rounded up to 256
 };
 
 inline Geom makeGeom(int X, int Y, int n) {
   Geom g;
   g.X = X; g.Y = Y; g.RW = X + 1; g.PB = (Y + 1) * (X + 1); g.S = X * Y; g.n = n;
   g.rows = n * g.PB;
-  g.rowsPad = (g.rows + 127) / 128 * 128;
+  g.rowsPad = (g.rows + 255) / 256 * 256;
   return g;
 }
 

@@ -15,7 +15,7 @@
 
 namespace {
 
-constexpr int NA_MAX_ROWS = 4096;      // padded rows: n*(Y+1)*(X+1) rounded up to 128
+constexpr int NA_MAX_ROWS = 4096;      // padded rows: n*(Y+1)*(X+1) rounded up to 256
 constexpr int NA_MAX_CHANNELS = 64;    // input and output channels
 constexpr int NA_MAX_TAPS = 25;        // up to 5x5
 constexpr size_t NA_IN_FLOATS = (size_t)NA_MAX_ROWS * NA_MAX_CHANNELS;

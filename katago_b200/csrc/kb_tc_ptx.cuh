@@ -114,6 +114,65 @@ __device__ __forceinline__ void ummaCommit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// ---------------------------------------------------------------------------------------------
+// CTA pairs (cluster of two CTAs on neighbouring SMs; cta_group::2).  One MMA instruction, issued by the even CTA,
+// computes 256 rows: each CTA supplies its own 128 rows of A and half of the B tile from its own shared memory (at
+// the same offsets) and receives its 128 rows of the result in its own TMEM.  Loads of both CTAs signal the even
+// CTA's barrier; none of them uses multicast.
+
+__device__ __forceinline__ uint32_t clusterCtaRank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void clusterSync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of the same shared-memory location in the even CTA of the pair (the cluster window places CTA rank r at
+// bit 24 of the shared::cluster address).
+__device__ __forceinline__ uint32_t pairLeaderAddr(uint32_t saddr) { return saddr & 0xFEFFFFFFu; }
+// Address of the same location in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t clusterMapAddr(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbarArriveCluster(uint32_t clusterAddr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(clusterAddr) : "memory");
+}
+// Tile load into this CTA's shared memory whose completion is signalled on a barrier that may live in the pair's
+// other CTA (bar is a shared::cluster address).
+__device__ __forceinline__ void tmaLoad2dPair(uint32_t dst, const CUtensorMap* tmap, int c0, int c1, uint32_t bar) {
+  asm volatile(
+    "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+    ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1)
+    : "memory");
+}
+__device__ __forceinline__ void tmemAllocPair(uint32_t dstSmem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dstSmem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmemRelinquishPair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmemDeallocPair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void ummaLoHiPair(uint32_t dTmem, uint32_t aLo, uint32_t bLo, uint32_t descHi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+    "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+    "mov.b64 da, {%1, %3};\n\t"
+    "mov.b64 db, {%2, %3};\n\t"
+    "setp.ne.b32 p, %5, 0;\n\t"
+    "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p;\n\t}"
+    ::"r"(dTmem), "r"(aLo), "r"(bLo), "r"(descHi), "r"(idesc), "r"(accumulate)
+    : "memory");
+}
+// The barrier (a shared::cluster address, in either CTA of the pair) receives one arrival once all MMAs issued so far
+// by this thread have completed in both CTAs.
+__device__ __forceinline__ void ummaCommitPair(uint32_t clusterBar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(clusterBar) : "memory");
+}
+
 // 32 lanes x 32 consecutive 32-bit columns -> 32 registers per thread (thread t reads lane base+t).
 __device__ __forceinline__ void tmemLd32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(

@@ -118,7 +118,7 @@ __device__ __forceinline__ void ummaCommit(uint32_t bar) {
 // CTA pairs (cluster of two CTAs on neighbouring SMs; cta_group::2).  One MMA instruction, issued by the even CTA,
 // computes 256 rows: each CTA supplies its own 128 rows of A and half of the B tile from its own shared memory (at
 // the same offsets) and receives its 128 rows of the result in its own TMEM.  Loads of both CTAs signal the even
-// CTA's barrier; none of them uses multicast.
+// CTA's barrier; every load has a single destination.
 
 __device__ __forceinline__ uint32_t clusterCtaRank() {
   uint32_t r;

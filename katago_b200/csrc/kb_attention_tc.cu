@@ -1,18 +1,21 @@
 // Attention over the points of one board on sm_100a tensor cores (tcgen05), for head dimension 64.
 //
-// One CTA = one (board, head); it loads K and V once and walks the board's 128-query tiles.  The tokens of a board are its padded rows (row = y*RW + x,
-// kb_kernels.cuh): contiguous in memory, so Q, K and V tiles are plain 2-D TMA boxes of the QKV matrix; padding
-// rows and off-board points are excluded as keys by the board mask and produce zero output as queries
-// (eigenbackend.cpp:1505-1536).  All keys of a board (<= 384 rows) are processed in one pass:
+// One CTA = one (board, head); it loads K and V once and walks the board's 128-query tiles.  The tokens of a board are
+// its padded rows (row = y*RW + x, kb_kernels.cuh): contiguous in memory, so Q, K and V tiles are plain 2-D TMA boxes
+// of the QKV matrix; padding rows and off-board points are excluded as keys by an additive bias of -1e30 and produce
+// zero output as queries (eigenbackend.cpp:1505-1536).  All keys of a board (<= 384 rows) are processed in one pass:
+//   rope           (optional) Q and K are rotated in place in shared memory by all 256 threads
 //   S = Q K^T      12 MMAs 128x128x16 into 384 TMEM columns (fp32)
-//   softmax        one thread per query row reads its row of S from TMEM twice (max, then exp and sum),
-//                  writes P in the activation dtype into shared memory in the K-major swizzled operand layout
+//   softmax        two warps per query-row quarter, each over half of the keys: a pass for the maximum and a pass for
+//                  exp and sum straight out of TMEM (the next 32-key chunk is in flight while one is processed);
+//                  P is written in the activation dtype into shared memory in the K-major swizzled operand layout
 //   O = P V        24 MMAs 128x64x16; V is used as it lies in memory (dv contiguous = MN-major B operand)
 //   out = O / sum  read from TMEM, written with 16-byte stores
-// Waits are bounded as in the convolution kernel; on a time-out the status word is set and the CTA runs
-// through its remaining barriers without touching data.
+// The next Q tile is fetched behind the softmax.  Waits are bounded as in the convolution kernel; on a time-out the
+// status word is set and the CTA runs through its remaining barriers without touching data.
 #include "kb_kernels.cuh"
 #include "kb_tc_ptx.cuh"
+#include "kb_act.cuh"
 
 #include <mutex>
 
@@ -25,6 +28,14 @@ constexpr int AT_TILE_BYTES = 128 * 128;  // 128 rows x 64 elements x 2 bytes
 
 enum { AT_ERR_TIMEOUT = 201 };
 
+// Optional timeline instrumentation (build with -DKB_TC_TRACE): thread 0 of CTA 0 records SM cycle counts.
+#ifdef KB_TC_TRACE
+__device__ long long g_atTrace[64];
+#define AT_TRACE(slot) do { if(blockIdx.x == 0 && threadIdx.x == 0) g_atTrace[(slot)] = clock64(); } while(0)
+#else
+#define AT_TRACE(slot) do { } while(0)
+#endif
+
 struct AttnTcArgs {
   Geom g;
   int heads, kvHeads;
@@ -35,6 +46,9 @@ struct AttnTcArgs {
   int outStride;
   uint32_t idescS, idescO;
   float scaleLog2e;       // 1/sqrt(dq) * log2(e)
+  const float* ropeCos;   // rotary tables [tableHeads][AT_D/2][S], or NULL: Q and K are used as stored
+  const float* ropeSin;
+  int tableHeads;
   int* status;
 };
 
@@ -45,6 +59,52 @@ template <> struct AtPack<__half> {
 template <> struct AtPack<__nv_bfloat16> {
   static __device__ __forceinline__ uint32_t pack(float a, float b) { __nv_bfloat162 h = __floats2bfloat162_rn(a, b); return *reinterpret_cast<uint32_t*>(&h); }
 };
+
+template <typename T> struct AtUnpack;
+template <> struct AtUnpack<__half> {
+  static __device__ __forceinline__ float2 unpack(uint32_t u) { return __half22float2(*reinterpret_cast<__half2*>(&u)); }
+};
+template <> struct AtUnpack<__nv_bfloat16> {
+  static __device__ __forceinline__ float2 unpack(uint32_t u) { return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u)); }
+};
+
+// Rotary embedding (eigenbackend.cpp:1415-1451) applied in place to one 128-row x 64-channel tile that TMA put into
+// shared memory with the 128-byte swizzle: channel pair (2p, 2p+1) of the row at board position xy is rotated by the
+// angle whose cosine and sine are table[(tableHead * 32 + p) * S + xy].  Rows that are not board points are left
+// alone (they are masked out of the softmax, and their outputs are written as zeros).  Lanes take consecutive rows,
+// so the table reads coalesce and the 16-byte shared-memory accesses of a quarter warp fall into distinct banks.
+static_assert(AT_THREADS == 256, "ropeTileInPlace maps 256 threads onto 128 rows x 2 chunk phases");
+template <typename T>
+__device__ __forceinline__ void ropeTileInPlace(
+  uint8_t* tile, int firstRow, int tableHead, const float* __restrict__ cosT, const float* __restrict__ sinT, const Geom& g, int tid) {
+  // 256 threads: thread -> one row and every second 16-byte chunk of it (4 chunks = 16 channel pairs); all 32 table
+  // values are requested before any is used, so a tile costs one memory latency
+  const int row = tid & 127, c0 = tid >> 7;
+  const int br = firstRow + row;  // row inside the board's padded block
+  const int y = br / g.RW, x = br - y * g.RW;
+  if(y >= g.Y || x >= g.X) return;
+  const int xy = y * g.X + x;
+  float cs[16], sn[16];
+#pragma unroll
+  for(int kk = 0; kk < 4; kk++) {
+    const size_t t0 = ((size_t)tableHead * (AT_D / 2) + (c0 + 2 * kk) * 4) * g.S + xy;
+#pragma unroll
+    for(int k = 0; k < 4; k++) { cs[4 * kk + k] = __ldg(cosT + t0 + (size_t)k * g.S); sn[4 * kk + k] = __ldg(sinT + t0 + (size_t)k * g.S); }
+  }
+#pragma unroll
+  for(int kk = 0; kk < 4; kk++) {
+    const int chunk = c0 + 2 * kk;
+    uint4* p = reinterpret_cast<uint4*>(tile + row * 128 + ((chunk ^ (row & 7)) << 4));
+    const uint4 val = *p;
+    uint32_t w[4] = {val.x, val.y, val.z, val.w};
+#pragma unroll
+    for(int k = 0; k < 4; k++) {
+      const float2 v = AtUnpack<T>::unpack(w[k]);
+      w[k] = AtPack<T>::pack(v.x * cs[4 * kk + k] - v.y * sn[4 * kk + k], v.x * sn[4 * kk + k] + v.y * cs[4 * kk + k]);
+    }
+    *p = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
 
 // MN-major B operand (V): 64 contiguous elements (128 B) per key row, 128-byte swizzle; the K dimension (keys)
 // advances by rows, 8-row groups 1024 B apart.
@@ -66,10 +126,10 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_
   uint8_t* sK = sQ + AT_TILE_BYTES;           // 3 x 16 KiB (128 keys each)
   uint8_t* sV = sK + 3 * AT_TILE_BYTES;       // 3 x 16 KiB
   uint8_t* sP = sV + 3 * AT_TILE_BYTES;       // 6 x 16 KiB (64 keys each), K-major operand layout
-  float* sMask = reinterpret_cast<float*>(sP + 6 * AT_TILE_BYTES);  // [AT_SK]
-  float* sRed = sMask + AT_SK;                                      // [2][128] partial row maxima, then partial row sums
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sRed + 256);         // kv, q, mma1, mma2
-  uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 4);
+  float* sKb = reinterpret_cast<float*>(sP + 6 * AT_TILE_BYTES);  // [AT_SK] additive key bias: 0 on the board, -1e30 elsewhere
+  float* sRed = sKb + AT_SK;                                      // [2][128] partial row maxima, then partial row sums
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sRed + 256);         // k (all tiles), q, mma1, mma2, v
+  uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 5);
   volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -82,13 +142,13 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_
   const int numQTiles = (a.keysValid + 127) / 128;
 
   if(tid == 0) {
-    for(int i = 0; i < 4; i++) mbarInit(smemU32(&bars[i]), 1);
+    for(int i = 0; i < 5; i++) mbarInit(smemU32(&bars[i]), 1);
     *abortFlag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if(warp == 0) { tmemAlloc(smemU32(tmemSlot), 512); tmemRelinquish(); }
-  for(int j = tid; j < AT_SK; j += AT_THREADS) sMask[j] = (j < a.keysValid) ? a.mask[boardRow + j] : 0.0f;
+  for(int j = tid; j < AT_SK; j += AT_THREADS) sKb[j] = (j < a.keysValid && a.mask[boardRow + j] != 0.0f) ? 0.0f : -1e30f;
   tcFenceBefore();
   __syncthreads();
   tcFenceAfter();
@@ -97,20 +157,38 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_
 
   if(tid == 0) {
     // K and V of this (board, kv head) are loaded once and serve every query tile; the first Q tile rides along
-    mbarExpectTx(smemU32(&bars[0]), 6u * AT_TILE_BYTES);
-    for(int j = 0; j < 3; j++) {
-      tmaLoad2d(smemU32(sK + j * AT_TILE_BYTES), &tmQKV, a.kOff + kvh * AT_D, boardRow + j * 128, smemU32(&bars[0]));
-      tmaLoad2d(smemU32(sV + j * AT_TILE_BYTES), &tmQKV, a.vOff + kvh * AT_D, boardRow + j * 128, smemU32(&bars[0]));
-    }
+    // K and Q first (S = Q K^T needs only them), V on a barrier of its own: it is not needed before O = P V
+    mbarExpectTx(smemU32(&bars[0]), 3u * AT_TILE_BYTES);
+    for(int j = 0; j < 3; j++) tmaLoad2d(smemU32(sK + j * AT_TILE_BYTES), &tmQKV, a.kOff + kvh * AT_D, boardRow + j * 128, smemU32(&bars[0]));
     mbarExpectTx(smemU32(&bars[1]), (uint32_t)AT_TILE_BYTES);
     tmaLoad2d(smemU32(sQ), &tmQKV, a.qOff + h * AT_D, boardRow, smemU32(&bars[1]));
+    mbarExpectTx(smemU32(&bars[4]), 3u * AT_TILE_BYTES);
+    for(int j = 0; j < 3; j++) tmaLoad2d(smemU32(sV + j * AT_TILE_BYTES), &tmQKV, a.vOff + kvh * AT_D, boardRow + j * 128, smemU32(&bars[4]));
   }
 
+  AT_TRACE(0);
   for(int qt = 0; qt < numQTiles; qt++) {
+    AT_TRACE(1 + qt * 8);
     const uint32_t ph = (uint32_t)qt & 1u;
     const int q0 = qt * 128;
+    bool landed = true;
+    if(a.ropeCos) {
+      // every thread waits for the tiles, rotates its share of K (first tile only) and Q in shared memory, and the
+      // rotated operands are made visible to the tensor core before the MMAs are issued
+      landed = (qt > 0 || mbarWait(smemU32(&bars[0]), 0u, abortFlag)) && mbarWait(smemU32(&bars[1]), ph, abortFlag);
+      if(landed) {
+        if(qt == 0) {
+          const int thK = kvh * a.tableHeads / a.kvHeads;
+          for(int j = 0; j < 3; j++) ropeTileInPlace<T>(sK + j * AT_TILE_BYTES, j * 128, thK, a.ropeCos, a.ropeSin, a.g, tid);
+        }
+        ropeTileInPlace<T>(sQ, q0, h * a.tableHeads / a.heads, a.ropeCos, a.ropeSin, a.g, tid);
+      }
+      fenceProxyAsync();
+      __syncthreads();
+    }
+    AT_TRACE(2 + qt * 8);
     if(tid == 0) {
-      bool ok = (qt > 0 || mbarWait(smemU32(&bars[0]), 0u, abortFlag)) && mbarWait(smemU32(&bars[1]), ph, abortFlag);
+      bool ok = landed && (qt > 0 || mbarWait(smemU32(&bars[0]), 0u, abortFlag)) && mbarWait(smemU32(&bars[1]), ph, abortFlag);
       if(ok) {
         tcFenceAfter();
         for(int j = 0; j < 3; j++) {
@@ -131,19 +209,36 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_
       mbarExpectTx(smemU32(&bars[1]), (uint32_t)AT_TILE_BYTES);
       tmaLoad2d(smemU32(sQ), &tmQKV, a.qOff + h * AT_D, boardRow + q0 + 128, smemU32(&bars[1]));
     }
-    const int cBegin = half * (AT_SK / 2), cEnd = cBegin + AT_SK / 2;
+    AT_TRACE(3 + qt * 8);
+    // Scores leave TMEM in chunks of 32 keys; the load of the next chunk is in flight while this one is processed.
+    // Keys off the board carry a bias of -1e30, so they lose every maximum and their exponential is 0.
+    constexpr int NCH = AT_SK / 2 / 32;
+    const int cBegin = half * (AT_SK / 2);
+    const uint32_t tS = tmemS + ((uint32_t)(quarter * 32) << 16) + (uint32_t)cBegin;
+    const float4* kb4 = reinterpret_cast<const float4*>(sKb + cBegin);
     float mx = -1e30f;
     if(ok) {
       tcFenceAfter();
-      for(int c = cBegin; c < cEnd; c += 32) {
-        uint32_t r[32];
-        tmemLd32(tmemS + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, r);
-        tmemLdWait();
+      uint32_t r[2][32];
+      float m4[4] = {-1e30f, -1e30f, -1e30f, -1e30f};
+      tmemLd32(tS, r[0]);
+      tmemLdWaitFor(r[0]);
 #pragma unroll
-        for(int j = 0; j < 32; j++)
-          if(sMask[c + j] != 0.0f) mx = fmaxf(mx, __uint_as_float(r[j]));
+      for(int i = 0; i < NCH; i++) {
+        if(i + 1 < NCH) tmemLd32(tS + (uint32_t)((i + 1) * 32), r[(i + 1) & 1]);
+#pragma unroll
+        for(int j = 0; j < 8; j++) {
+          const float4 b = kb4[i * 8 + j];
+          m4[0] = fmaxf(m4[0], __uint_as_float(r[i & 1][4 * j]) + b.x);
+          m4[1] = fmaxf(m4[1], __uint_as_float(r[i & 1][4 * j + 1]) + b.y);
+          m4[2] = fmaxf(m4[2], __uint_as_float(r[i & 1][4 * j + 2]) + b.z);
+          m4[3] = fmaxf(m4[3], __uint_as_float(r[i & 1][4 * j + 3]) + b.w);
+        }
+        if(i + 1 < NCH) tmemLdWaitFor(r[(i + 1) & 1]);
       }
+      mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
     }
+    AT_TRACE(4 + qt * 8);
     sRed[half * 128 + row] = mx;
     __syncthreads();
     mx = fmaxf(sRed[row], sRed[128 + row]);
@@ -151,34 +246,46 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_
     float sum = 0.0f;
     if(ok) {
       const int sw = row & 7;
-      for(int c = cBegin; c < cEnd; c += 32) {
-        uint32_t r[32];
-        tmemLd32(tmemS + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, r);
-        tmemLdWait();
-        float p[32];
+      const float mxs = mx * a.scaleLog2e;
+      uint32_t r[2][32];
+      float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      tmemLd32(tS, r[0]);
+      tmemLdWaitFor(r[0]);
 #pragma unroll
-        for(int j = 0; j < 32; j++) {
-          p[j] = (sMask[c + j] != 0.0f) ? exp2f((__uint_as_float(r[j]) - mx) * a.scaleLog2e) : 0.0f;
-          sum += p[j];
-        }
+      for(int i = 0; i < NCH; i++) {
+        if(i + 1 < NCH) tmemLd32(tS + (uint32_t)((i + 1) * 32), r[(i + 1) & 1]);
+        const int c = cBegin + i * 32;
         // P chunk of 64 keys = one 128-byte swizzled row per query; this 32-key group is its half (c/32)&1
         uint8_t* pRow = sP + (size_t)(c / 64) * AT_TILE_BYTES + row * 128;
         const int halfSel = (c / 32) & 1;
 #pragma unroll
         for(int jj = 0; jj < 4; jj++) {
+          float p[8];
+#pragma unroll
+          for(int k = 0; k < 2; k++) {
+            const float4 b = kb4[i * 8 + 2 * jj + k];
+            p[4 * k] = ex2Approx(fmaf(__uint_as_float(r[i & 1][8 * jj + 4 * k]), a.scaleLog2e, b.x - mxs));
+            p[4 * k + 1] = ex2Approx(fmaf(__uint_as_float(r[i & 1][8 * jj + 4 * k + 1]), a.scaleLog2e, b.y - mxs));
+            p[4 * k + 2] = ex2Approx(fmaf(__uint_as_float(r[i & 1][8 * jj + 4 * k + 2]), a.scaleLog2e, b.z - mxs));
+            p[4 * k + 3] = ex2Approx(fmaf(__uint_as_float(r[i & 1][8 * jj + 4 * k + 3]), a.scaleLog2e, b.w - mxs));
+            s4[0] += p[4 * k]; s4[1] += p[4 * k + 1]; s4[2] += p[4 * k + 2]; s4[3] += p[4 * k + 3];
+          }
           uint4 o;
-          o.x = AtPack<T>::pack(p[8 * jj], p[8 * jj + 1]); o.y = AtPack<T>::pack(p[8 * jj + 2], p[8 * jj + 3]);
-          o.z = AtPack<T>::pack(p[8 * jj + 4], p[8 * jj + 5]); o.w = AtPack<T>::pack(p[8 * jj + 6], p[8 * jj + 7]);
+          o.x = AtPack<T>::pack(p[0], p[1]); o.y = AtPack<T>::pack(p[2], p[3]);
+          o.z = AtPack<T>::pack(p[4], p[5]); o.w = AtPack<T>::pack(p[6], p[7]);
           *reinterpret_cast<uint4*>(pRow + (((halfSel * 4 + jj) ^ sw) << 4)) = o;
         }
+        if(i + 1 < NCH) tmemLdWaitFor(r[(i + 1) & 1]);
       }
+      sum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
     }
+    AT_TRACE(5 + qt * 8);
     sRed[half * 128 + row] = sum;
     fenceProxyAsync();
     tcFenceBefore();
     __syncthreads();
     const float rowSum = sRed[row] + sRed[128 + row];
-    if(tid == 0 && !*abortFlag) {
+    if(tid == 0 && !*abortFlag && (qt > 0 || mbarWait(smemU32(&bars[4]), 0u, abortFlag))) {
       tcFenceAfter();
       uint32_t acc = 0;
       for(int kc = 0; kc < AT_SK / 64; kc++) {
@@ -192,7 +299,9 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_
       }
       ummaCommit(smemU32(&bars[3]));
     }
+    AT_TRACE(6 + qt * 8);
     ok = !*abortFlag && mbarWait(smemU32(&bars[3]), ph, abortFlag);
+    AT_TRACE(7 + qt * 8);
     if(!ok && !*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, AT_ERR_TIMEOUT); }
     if(ok) {
       tcFenceAfter();
@@ -213,6 +322,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_
         }
       }
     }
+    AT_TRACE(8 + qt * 8);
     // every warp has finished reading S and O of this tile before the next tile's MMAs overwrite them
     tcFenceBefore();
     __syncthreads();
@@ -261,7 +371,7 @@ AttnTcPlan* attentionTcCreate(int dt, const void* qkv, int stride, int totalCols
     &p->tmQKV, dt == DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(qkv), dims, strides,
     box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if(r != CUDA_SUCCESS) { delete p; return nullptr; }
-  p->smemBytes = 13 * (size_t)AT_TILE_BYTES + (AT_SK + 256) * sizeof(float) + 4 * 8 + 16 + 1024;
+  p->smemBytes = 13 * (size_t)AT_TILE_BYTES + (AT_SK + 256) * sizeof(float) + 5 * 8 + 16 + 1024;
   cudaError_t e1 = cudaFuncSetAttribute(attentionTcKernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p->smemBytes);
   cudaError_t e2 = cudaFuncSetAttribute(attentionTcKernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p->smemBytes);
   if(e1 != cudaSuccess || e2 != cudaSuccess) { delete p; return nullptr; }
@@ -272,7 +382,7 @@ void attentionTcDestroy(AttnTcPlan* p) { delete p; }
 
 cudaError_t launchAttentionTc(
   cudaStream_t st, const AttnTcPlan* p, int qOff, int kOff, int vOff, int heads, int kvHeads, const float* mask, void* out,
-  int outStride, Geom g, int* statusWord) {
+  int outStride, Geom g, int* statusWord, const float* ropeCos, const float* ropeSin, int tableHeads) {
   AttnTcArgs a;
   a.g = g; a.heads = heads; a.kvHeads = kvHeads; a.qOff = qOff; a.kOff = kOff; a.vOff = vOff;
   a.keysValid = g.Y * g.RW;
@@ -282,6 +392,7 @@ cudaError_t launchAttentionTc(
   a.idescO = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((uint32_t)(AT_D >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
   a.scaleLog2e = 1.4426950408889634f / sqrtf((float)AT_D);
   a.status = statusWord;
+  a.ropeCos = ropeCos; a.ropeSin = ropeSin; a.tableHeads = tableHeads;
   dim3 grid(g.n * heads);
   if(p->dt == DT_F16) attentionTcKernel<__half><<<grid, AT_THREADS, p->smemBytes, st>>>(p->tmQKV, a);
   else attentionTcKernel<__nv_bfloat16><<<grid, AT_THREADS, p->smemBytes, st>>>(p->tmQKV, a);
@@ -289,3 +400,7 @@ cudaError_t launchAttentionTc(
 }
 
 }  // namespace kb
+
+#ifdef KB_TC_TRACE
+extern "C" int kb_debug_attention_trace(long long* out, int n) { return (int)cudaMemcpyFromSymbol(out, kb::g_atTrace, sizeof(long long) * n); }
+#endif

@@ -279,7 +279,7 @@ template <typename T, int ACT>
 __device__ __forceinline__ bool epilogueTileTma(
   const ConvTcArgs& a, const CUtensorMap* tmRaw, const CUtensorMap* tmAct, uint32_t tmemAcc, int q, int cg, int lane,
   int m0, int n0, float mk, const float* biasRow, EpiWarp& es, uint32_t tileIter, volatile int* abortFlag,
-  const float* sScale, const float* sBias, const CUtensorMap* tmRes, const TileMap& tm) {
+  const float* sScale, const float* sBias, const CUtensorMap* tmRes, const TileMap& tm, float rowScale, float& rowSumsq) {
   const Epilogue& ep = a.ep;
   const bool hasRes = ep.residual != nullptr;
   const int sw = (lane >> 1) & 3;  // 64-byte swizzle: 16-byte chunk index XOR bits 1..2 of the row
@@ -300,6 +300,10 @@ __device__ __forceinline__ bool epilogueTileTma(
     float v[32];
 #pragma unroll
     for(int k = 0; k < 32; k++) v[k] = __uint_as_float(r[k]);
+    if(ep.rowSumsq) {
+#pragma unroll
+      for(int k = 0; k < 32; k++) v[k] *= rowScale;
+    }
     if(biasRow) {
       const float4* bp = reinterpret_cast<const float4*>(biasRow + c);
 #pragma unroll
@@ -331,6 +335,12 @@ __device__ __forceinline__ bool epilogueTileTma(
     // The raw output can go to its staging unit at once: with a residual it replaces the residual just read, without
     // one the two raw units alternate and the store from this one was waited for one unit ago.
     if(doRaw) {
+      if(ep.sumsqOut) {
+        float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for(int k = 0; k < 32; k++) s4[k & 3] = fmaf(v[k], v[k], s4[k & 3]);
+        rowSumsq += (s4[0] + s4[1]) + (s4[2] + s4[3]);
+      }
 #pragma unroll
       for(int jj = 0; jj < 4; jj++) {
         uint4 o;
@@ -340,7 +350,21 @@ __device__ __forceinline__ bool epilogueTileTma(
       }
     }
     uint32_t actP[16];
-    if(doAct) {
+    if(ACT == KB_ACT_SWIGLU_PAIRS) {
+      // columns 0..15 of the unit are "up" channels, 16..31 their "gate" channels: h = silu(up) * gate
+      if(doAct) {
+        float n[16];
+#pragma unroll
+        for(int k = 0; k < 16; k++) n[k] = ex2Approx(v[k] * -1.4426950408889634f);
+#pragma unroll
+        for(int k = 0; k < 16; k++) n[k] = rcpApprox(1.0f + n[k]);
+#pragma unroll
+        for(int k = 0; k < 16; k++) n[k] = v[k] * n[k] * v[16 + k];
+#pragma unroll
+        for(int k = 0; k < 8; k++) actP[k] = Pack2<T>::pack(n[2 * k], n[2 * k + 1]);
+      }
+    }
+    else if(doAct) {
       const int ca = c - ep.actC0;
       const float4* sp = reinterpret_cast<const float4*>(sScale + ca);
       const float4* bp = reinterpret_cast<const float4*>(sBias + ca);
@@ -370,7 +394,13 @@ __device__ __forceinline__ bool epilogueTileTma(
     }
     __syncwarp();
     TRACE(threadIdx.x == 64, 1024 + (int)(tileIter & 31u) * 16 + j * 5 + 3);
-    if(doAct) {
+    if(doAct && ACT == KB_ACT_SWIGLU_PAIRS) {
+      // 32 rows x 16 channels, 32-byte rows, no swizzle
+      uint8_t* oRow = es.sO + lane * 32;
+      *reinterpret_cast<uint4*>(oRow) = make_uint4(actP[0], actP[1], actP[2], actP[3]);
+      *reinterpret_cast<uint4*>(oRow + 16) = make_uint4(actP[4], actP[5], actP[6], actP[7]);
+    }
+    else if(doAct) {
       uint8_t* oRow = es.sO + lane * 64;
 #pragma unroll
       for(int jj = 0; jj < 4; jj++)
@@ -381,7 +411,7 @@ __device__ __forceinline__ bool epilogueTileTma(
     __syncwarp();
     if(lane == 0) {
       if(doRaw) tmaStore2d(tmRaw, smemU32(es.sR + (size_t)slot * TC_UNIT_BYTES), c - ep.rawC0, m0 + q * 32);
-      if(doAct) tmaStore2d(tmAct, smemU32(es.sO), c - ep.actC0, m0 + q * 32);
+      if(doAct) tmaStore2d(tmAct, smemU32(es.sO), ACT == KB_ACT_SWIGLU_PAIRS ? (c - ep.actC0) / 2 : c - ep.actC0, m0 + q * 32);
       bulkCommit();
     }
     TRACE(threadIdx.x == 64, 1024 + (int)(tileIter & 31u) * 16 + j * 5 + 4);
@@ -447,7 +477,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
     else { tmemAlloc(smemU32(tmemSlot), a.tmemCols); tmemRelinquish(); }
   }
   // next layer's norm parameters: read once per CTA (weights: not produced by the preceding kernels)
-  if(a.ep.outAct) {
+  if(a.ep.outAct && a.ep.scale) {
     const int nAct = a.ep.actC1 - a.ep.actC0;
     for(int i = threadIdx.x; i < nAct; i += blockDim.x) { sScale[i] = a.ep.scale[i]; sBias[i] = a.ep.bias[i]; }
   }
@@ -633,7 +663,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
       tcFenceAfter();
       const uint32_t acc = tmemBase + buf * (uint32_t)a.BN;
       if(TMA_EPI) {
-        const bool ok2 = epilogueTileTma<T, ACT>(a, &tmRaw, &tmAct, acc, q, cg, lane, m0, n0, mk, biasRow, es, it, abortFlag, sScale, sBias, &tmRes, tm);
+        const float rowScale = a.ep.rowSumsq ? (mk == 1.0f ? rsqrtf(fmaf(a.ep.rowSumsq[m], a.ep.rowInvC, a.ep.rowEps)) : 0.0f) : 1.0f;
+        float rowSumsq = 0.0f;
+        const bool ok2 = epilogueTileTma<T, ACT>(a, &tmRaw, &tmAct, acc, q, cg, lane, m0, n0, mk, biasRow, es, it, abortFlag, sScale, sBias, &tmRes, tm, rowScale, rowSumsq);
+        if(a.ep.sumsqOut && es.nU > 0) atomicAdd(a.ep.sumsqOut + m, rowSumsq);
+        if(a.ep.sumsqClear && cg == 0 && n0 == 0) a.ep.sumsqClear[m] = 0.0f;
         if(!ok2) {
           if(lane == 0 && !*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, TC_ERR_EPILOGUE_TIMEOUT); }
           break;
@@ -700,6 +734,7 @@ static ConvTcKernelFn kernelForAct(int act) {
     case KB_ACT_MISH: return convTcKernel<T, KB_ACT_MISH, TMA_EPI, PAIR>;
     case KB_ACT_SILU: return convTcKernel<T, KB_ACT_SILU, TMA_EPI, PAIR>;
     case KB_ACT_MISH_SCALE8: return convTcKernel<T, KB_ACT_MISH_SCALE8, TMA_EPI, PAIR>;
+    case KB_ACT_SWIGLU_PAIRS: return convTcKernel<T, KB_ACT_SWIGLU_PAIRS, TMA_EPI, PAIR>;
     default: return convTcKernel<T, KB_ACT_IDENTITY, TMA_EPI, PAIR>;
   }
 }
@@ -758,6 +793,16 @@ bool convTcEligible(int dt, int inC, int outC, int kY, int kX) {
   if(!((kY == 1 && kX == 1) || (kY == 3 && kX == 3))) return false;
   if(inC % TC_BK != 0 || outC % 16 != 0) return false;
   return pickBN(kY, inC, outC) >= 16;
+}
+
+bool convTcRowNormEligible(int dt, int inC, int outC) {
+  if(!convTcEligible(dt, inC, outC, 1, 1) || (outC % 32) != 0) return false;
+  return (pickBN(1, inC, outC) % 32) == 0;
+}
+
+bool convTcSwigluEligible(int dt, int inC, int F) {
+  if(!convTcEligible(dt, inC, 2 * F, 1, 1) || (F % 16) != 0) return false;
+  return (pickBN(1, inC, 2 * F) % 32) == 0;  // whole 32-column units, each holding 16 up and 16 gate channels
 }
 
 static bool encode2d(
@@ -864,7 +909,8 @@ bool convTcSetEpilogue(ConvTcPlan* p, const Epilogue& ep) {
   if(ep.outRaw) ok = ok && aligned32(ep.rawC0, ep.rawC1) && (ep.rawStride % 8) == 0 && (reinterpret_cast<uintptr_t>(ep.outRaw) & 15) == 0;
   if(ep.outAct) ok = ok && aligned32(ep.actC0, ep.actC1) && (ep.actStride % 8) == 0 && (reinterpret_cast<uintptr_t>(ep.outAct) & 15) == 0;
   if(ep.residual) ok = ok && (ep.resStride % 8) == 0 && ep.resStride >= p->outC && (reinterpret_cast<uintptr_t>(ep.residual) & 15) == 0;
-  if(!ok || (!ep.outRaw && !ep.outAct)) return sizeRings(p, 0);
+  const bool needsStaged = ep.act == KB_ACT_SWIGLU_PAIRS || ep.sumsqOut || ep.rowSumsq;
+  if(!ok || (!ep.outRaw && !ep.outAct)) return needsStaged ? false : sizeRings(p, 0);
   // per warp: the residual/raw ring (one tile of this warp's units plus one with a residual, else two units) and one
   // unit for the activated output
   // With a residual the ring holds it one whole tile ahead for 1x1 convolutions, whose epilogue is the critical path;
@@ -874,14 +920,16 @@ bool convTcSetEpilogue(ConvTcPlan* p, const Epilogue& ep) {
   p->resRing = (p->kY == 1) ? unitsPerWarp + 1 : 2;
   const int rawUnits = ep.residual ? p->resRing : (ep.outRaw ? 2 : 0);
   p->epiWarpBytes = (rawUnits + 1) * TC_UNIT_BYTES;
-  if(!sizeRings(p, TC_EPI_WARPS * p->epiWarpBytes)) return sizeRings(p, 0);
+  if(!sizeRings(p, TC_EPI_WARPS * p->epiWarpBytes)) return needsStaged ? false : sizeRings(p, 0);
   const uint64_t rows = (uint64_t)p->rowsPadMax;
   const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_64B;
   bool enc = true;
   if(ep.residual) enc = enc && encode2d(&p->tmRes, p->dt, ep.residual, (uint64_t)p->outC, rows, (uint64_t)ep.resStride * 2, 32, 32, sw);
   if(ep.outRaw) enc = enc && encode2d(&p->tmRaw, p->dt, ep.outRaw, (uint64_t)(ep.rawC1 - ep.rawC0), rows, (uint64_t)ep.rawStride * 2, 32, 32, sw);
-  if(ep.outAct) enc = enc && encode2d(&p->tmAct, p->dt, ep.outAct, (uint64_t)(ep.actC1 - ep.actC0), rows, (uint64_t)ep.actStride * 2, 32, 32, sw);
-  if(!enc) return sizeRings(p, 0);
+  if(ep.outAct && ep.act == KB_ACT_SWIGLU_PAIRS)
+    enc = enc && encode2d(&p->tmAct, p->dt, ep.outAct, (uint64_t)(ep.actC1 - ep.actC0) / 2, rows, (uint64_t)ep.actStride * 2, 16, 32, CU_TENSOR_MAP_SWIZZLE_NONE);
+  else if(ep.outAct) enc = enc && encode2d(&p->tmAct, p->dt, ep.outAct, (uint64_t)(ep.actC1 - ep.actC0), rows, (uint64_t)ep.actStride * 2, 32, 32, sw);
+  if(!enc) return needsStaged ? false : sizeRings(p, 0);
   p->tmaEpi = 1;
   return true;
 }
@@ -889,7 +937,7 @@ bool convTcSetEpilogue(ConvTcPlan* p, const Epilogue& ep) {
 cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epilogue& ep, int* statusWord) {
   // vector accesses in the epilogue need 16-byte aligned rows and 16-channel aligned ranges
   if(ep.outRaw && ((ep.rawStride % 8) || (ep.rawC0 % 16) || (ep.rawC1 % 16))) return cudaErrorInvalidValue;
-  if(ep.outAct && ((ep.actStride % 8) || (ep.actC0 % 16) || (ep.actC1 % 16) || (ep.actC1 - ep.actC0) > 512)) return cudaErrorInvalidValue;
+  if(ep.outAct && ((ep.actStride % 8) || (ep.actC0 % 16) || (ep.actC1 % 16) || ((ep.actC1 - ep.actC0) > 512 && ep.act != KB_ACT_SWIGLU_PAIRS))) return cudaErrorInvalidValue;
   if(ep.residual && (ep.resStride % 8)) return cudaErrorInvalidValue;
   ConvTcArgs a;
   a.g = g; a.ep = ep;

@@ -155,7 +155,7 @@ void Engine::addConvOp(const ConvDev& c, Epilogue ep, const std::string& tag) {
   double bytes = S * c.inCReal * es;
   if(ep.residual) bytes += S * c.outC * es;
   if(ep.outRaw) bytes += S * (ep.rawC1 - ep.rawC0) * es;
-  if(ep.outAct) bytes += S * (ep.actC1 - ep.actC0) * es;
+  if(ep.outAct) bytes += S * (ep.actC1 - ep.actC0) * es / (ep.act == KB_ACT_SWIGLU_PAIRS ? 2 : 1);
   std::string name = "conv" + std::to_string(c.kY) + "x" + std::to_string(c.kX) + " " + std::to_string(c.inCReal) + "->" +
                      std::to_string(c.outC) + (c.tc ? " tcgen05" : " simt") + (tag.empty() ? "" : " " + tag);
   const int dt = dt_;
@@ -188,6 +188,30 @@ static ConvW matmulsAsConv(const std::vector<const MatMulW*>& parts) {
     for(int ic = 0; ic < m->inC; ic++)
       for(int oc = 0; oc < m->outC; oc++) c.w[(size_t)(oc0 + oc) * c.inC + ic] = m->w[(size_t)ic * m->outC + oc];
     oc0 += m->outC;
+  }
+  return c;
+}
+
+// conv(rmsnorm(x)) = rowScale * conv'(x) with the norm's gain folded into the weights: w'[oc][ic] = w[oc][ic] * gamma[ic].
+static void foldGain(ConvW& c, const std::vector<float>& gamma) {
+  if((int)gamma.size() != c.inC || c.kY != 1 || c.kX != 1) throw std::runtime_error("internal: cannot fold a norm gain into this convolution");
+  for(int oc = 0; oc < c.outC; oc++)
+    for(int ic = 0; ic < c.inC; ic++) c.w[(size_t)oc * c.inC + ic] *= gamma[ic];
+}
+
+// The merged FFN up|gate projection with its output channels interleaved in groups of 16 (16 up, their 16 gate), the
+// order the tensor-core convolution's SwiGLU epilogue expects.
+static ConvW upGateInterleaved(const MatMulW& up, const MatMulW& gate) {
+  if(up.inC != gate.inC || up.outC != gate.outC || (up.outC % 16) != 0) throw std::runtime_error("internal: up/gate shapes cannot be interleaved");
+  ConvW c;
+  c.kY = 1; c.kX = 1; c.inC = up.inC; c.outC = 2 * up.outC;
+  c.w.resize((size_t)c.inC * c.outC);
+  for(int f = 0; f < up.outC; f++) {
+    const int rowUp = (f / 16) * 32 + (f % 16), rowGate = rowUp + 16;
+    for(int ic = 0; ic < up.inC; ic++) {
+      c.w[(size_t)rowUp * c.inC + ic] = up.w[(size_t)ic * up.outC + f];
+      c.w[(size_t)rowGate * c.inC + ic] = gate.w[(size_t)ic * gate.outC + f];
+    }
   }
   return c;
 }
@@ -228,6 +252,16 @@ static void ropeTables(const BlockW& b, int X, int Y, std::vector<float>& cosT, 
 // ---------------------------------------------------------------------------------------------
 // Block graph -> launches
 
+// Called for a convolution whose raw output becomes the residual stream of a pre-norm transformer stack.
+void Engine::produceRowSums(Epilogue& ep, int inC, int outC) {
+  rowSumsCur_ = -1;
+  if(!rowNormFold_ || !convTcRowNormEligible(dt_, inC, outC)) return;
+  ep.sumsqOut = rowSums_[rowSumsNext_];
+  ep.sumsqClear = rowSums_[rowSumsNext_ ^ 1];
+  rowSumsCur_ = rowSumsNext_;
+  rowSumsNext_ ^= 1;
+}
+
 void Engine::emitStack(const std::vector<BlockW>& blocks, int C, void* raw, void* act, const BNW* tail, int depth, bool actValid) {
   for(size_t i = 0; i < blocks.size(); i++) {
     const BNW* next = tail;
@@ -241,7 +275,9 @@ void Engine::emitStack(const std::vector<BlockW>& blocks, int C, void* raw, void
         return launchBnAct(st, dt, raw, C, pb.scale, pb.bias, pb.act, mask, dt, act, C, C, g);
       });
     }
+    if(isConvBlock(blocks[i])) rowSumsCur_ = -1;  // its convolutions change the stream without recording row sums
     emitBlock(blocks[i], C, raw, act, next, depth);
+    if(isConvBlock(blocks[i])) rowSumsCur_ = -1;
     actValid = next != nullptr;
   }
 }
@@ -350,34 +386,48 @@ void Engine::emitBlock(const BlockW& b, int C, void* raw, void* act, const BNW* 
     void* attn = scratch("tfAttn" + d + "_c" + std::to_string(oC), (size_t)rowsPadMax_ * oC * es);
     float* gamma = uploadF32(b.preLN.weight);
     const float eps = b.preLN.eps;
-    addOp("rmsnorm", 0.0, 2.0 * S * C * es, [=](cudaStream_t st, const Geom& g) {
-      return launchRmsNorm(st, dt, raw, C, gamma, nullptr, eps, 0, mask, normed, C, C, g);
-    });
     ConvW qkvW = matmulsAsConv({&b.q, &b.k, &b.v});
-    ConvDev cq = makeConv({&qkvW}, normed, C, C);
     Epilogue eq;
     eq.outRaw = qkv; eq.rawStride = qkvC; eq.rawC0 = 0; eq.rawC1 = qkvC;
-    addConvOp(cq, eq, "qkv");
-    if(b.useRope) {
-      std::vector<float> cosT, sinT;
-      int tableHeads = 1;
-      ropeTables(b, X_, Y_, cosT, sinT, tableHeads);
-      float* dCos = uploadF32(cosT);
-      float* dSin = uploadF32(sinT);
-      addOp("rope", 0.0, 2.0 * S * (qC + kC) * es, [=](cudaStream_t st, const Geom& g) {
-        cudaError_t e = launchRope(st, dt, qkv, qkvC, 0, H, dq, dCos, dSin, tableHeads, g);
-        if(e != cudaSuccess) return e;
-        return launchRope(st, dt, qkv, qkvC, qC, Hkv, dq, dCos, dSin, tableHeads, g);
+    if(rowSumsCur_ >= 0 && convTcRowNormEligible(dt_, C, qkvC)) {
+      // the norm is folded into the projection: it reads the stream itself and scales its rows
+      foldGain(qkvW, b.preLN.weight);
+      ConvDev cq = makeConv({&qkvW}, raw, C, C);
+      eq.rowSumsq = rowSums_[rowSumsCur_]; eq.rowInvC = 1.0f / (float)C; eq.rowEps = eps;
+      addConvOp(cq, eq, "norm+qkv");
+    }
+    else {
+      addOp("rmsnorm", 0.0, 2.0 * S * C * es, [=](cudaStream_t st, const Geom& g) {
+        return launchRmsNorm(st, dt, raw, C, gamma, nullptr, eps, 0, mask, normed, C, C, g);
       });
+      ConvDev cq = makeConv({&qkvW}, normed, C, C);
+      addConvOp(cq, eq, "qkv");
     }
     const bool attnTc = !forceSimt_ && attentionTcEligible(dt_, dq, dv, X_, Y_, qkvC, 0, qC, qC + kC, oC);
+    float* dCos = nullptr;
+    float* dSin = nullptr;
+    int tableHeads = 1;
+    if(b.useRope) {
+      std::vector<float> cosT, sinT;
+      ropeTables(b, X_, Y_, cosT, sinT, tableHeads);
+      dCos = uploadF32(cosT);
+      dSin = uploadF32(sinT);
+      // the tensor-core attention kernel rotates Q and K itself, in shared memory
+      if(!attnTc) {
+        addOp("rope", 0.0, 2.0 * S * (qC + kC) * es, [=](cudaStream_t st, const Geom& g) {
+          cudaError_t e = launchRope(st, dt, qkv, qkvC, 0, H, dq, dCos, dSin, tableHeads, g);
+          if(e != cudaSuccess) return e;
+          return launchRope(st, dt, qkv, qkvC, qC, Hkv, dq, dCos, dSin, tableHeads, g);
+        });
+      }
+    }
     if(attnTc) {
       AttnTcPlan* ap = attentionTcCreate(dt_, qkv, qkvC, qkvC, rowsPadMax_);
       if(!ap) throw std::runtime_error("failed to create the tensor-core attention plan (TMA descriptor encoding)");
       attnPlans_.push_back(ap);
       int* status = statusWord_;
-      addOp("attention tcgen05", 2.0 * S * S * (dq + dv) * H, S * (qkvC + oC) * es, [=](cudaStream_t st, const Geom& g) {
-        return launchAttentionTc(st, ap, 0, qC, qC + kC, H, Hkv, mask, attn, oC, g, status);
+      addOp(b.useRope ? "attention tcgen05 +rope" : "attention tcgen05", 2.0 * S * S * (dq + dv) * H, S * (qkvC + oC) * es, [=](cudaStream_t st, const Geom& g) {
+        return launchAttentionTc(st, ap, 0, qC, qC + kC, H, Hkv, mask, attn, oC, g, status, dCos, dSin, tableHeads);
       });
     }
     else {
@@ -390,6 +440,7 @@ void Engine::emitBlock(const BlockW& b, int C, void* raw, void* act, const BNW* 
     Epilogue eo;
     finishEp(eo);
     eo.resMask = 1;
+    produceRowSums(eo, oC, C);
     addConvOp(co, eo, "attn out +res");
   }
   else if(b.kind == BLOCK_FFN) {
@@ -399,24 +450,41 @@ void Engine::emitBlock(const BlockW& b, int C, void* raw, void* act, const BNW* 
     const double S = (double)X_ * Y_;
     const int F = b.ffnC;
     void* normed = scratch("tfNorm" + d + "_c" + std::to_string(C), (size_t)rowsPadMax_ * C * es);
-    void* up = scratch("tfUp" + d + "_c" + std::to_string(2 * F), (size_t)rowsPadMax_ * 2 * F * es);
+    const bool needUp = forceSimt_ || !convTcSwigluEligible(dt_, C, F);
+    void* up = needUp ? scratch("tfUp" + d + "_c" + std::to_string(2 * F), (size_t)rowsPadMax_ * 2 * F * es) : nullptr;
     void* hid = scratch("tfHid" + d + "_c" + std::to_string(F), (size_t)rowsPadMax_ * F * es);
     float* gamma = uploadF32(b.preLN.weight);
     const float eps = b.preLN.eps;
-    addOp("rmsnorm", 0.0, 2.0 * S * C * es, [=](cudaStream_t st, const Geom& g) {
-      return launchRmsNorm(st, dt, raw, C, gamma, nullptr, eps, 0, mask, normed, C, C, g);
-    });
-    ConvW upW = matmulsAsConv({&b.linear1, &b.gate});
-    ConvDev cu = makeConv({&upW}, normed, C, C);
+    const bool fuseSwiglu = !forceSimt_ && convTcSwigluEligible(dt_, C, F);
+    const bool foldNorm = rowSumsCur_ >= 0 && convTcRowNormEligible(dt_, C, 2 * F);
+    const void* ffnIn = foldNorm ? raw : normed;
+    if(!foldNorm) {
+      addOp("rmsnorm", 0.0, 2.0 * S * C * es, [=](cudaStream_t st, const Geom& g) {
+        return launchRmsNorm(st, dt, raw, C, gamma, nullptr, eps, 0, mask, normed, C, C, g);
+      });
+    }
+    ConvW upW = fuseSwiglu ? upGateInterleaved(b.linear1, b.gate) : matmulsAsConv({&b.linear1, &b.gate});
+    if(foldNorm) foldGain(upW, b.preLN.weight);
+    ConvDev cu = makeConv({&upW}, ffnIn, C, C);
     Epilogue eu;
-    eu.outRaw = up; eu.rawStride = 2 * F; eu.rawC0 = 0; eu.rawC1 = 2 * F;
-    addConvOp(cu, eu, "ffn up|gate");
-    addOp("swiglu", 0.0, 3.0 * S * F * es, [=](cudaStream_t st, const Geom& g) { return launchSwiGLU(st, dt, up, 2 * F, hid, F, F, g); });
+    if(foldNorm) { eu.rowSumsq = rowSums_[rowSumsCur_]; eu.rowInvC = 1.0f / (float)C; eu.rowEps = eps; }
+    if(fuseSwiglu) {
+      // one kernel: the projection's epilogue writes silu(up) * gate; the 2F-wide intermediate never reaches memory
+      if(!cu.tc) throw std::runtime_error("internal: fused SwiGLU projection is not on the tensor-core path");
+      eu.outAct = hid; eu.actStride = F; eu.actC0 = 0; eu.actC1 = 2 * F; eu.act = KB_ACT_SWIGLU_PAIRS;
+      addConvOp(cu, eu, foldNorm ? "norm+ffn up|gate+swiglu" : "ffn up|gate+swiglu");
+    }
+    else {
+      eu.outRaw = up; eu.rawStride = 2 * F; eu.rawC0 = 0; eu.rawC1 = 2 * F;
+      addConvOp(cu, eu, foldNorm ? "norm+ffn up|gate" : "ffn up|gate");
+      addOp("swiglu", 0.0, 3.0 * S * F * es, [=](cudaStream_t st, const Geom& g) { return launchSwiGLU(st, dt, up, 2 * F, hid, F, F, g); });
+    }
     ConvW downW = matmulsAsConv({&b.linear2});
     ConvDev cd = makeConv({&downW}, hid, F, F);
     Epilogue ed;
     finishEp(ed);
     ed.resMask = 1;
+    produceRowSums(ed, F, C);
     addConvOp(cd, ed, "ffn down +res");
   }
   else {
@@ -584,6 +652,18 @@ Engine::Engine(const Model& m, int device, int maxBatch, int X, int Y, int preci
   dScore_ = static_cast<float*>(alloc((size_t)maxBatch * m.scoreValueC * sizeof(float)));
   dOwnership_ = static_cast<float*>(alloc((size_t)maxBatch * S * sizeof(float)));
 
+  // pre-norm transformer stacks on the tensor-core path: their norms are folded into the convolutions around them
+  rowNormFold_ = !forceSimt_ && dt_ != DT_F32 && !isConvBlock(m.blocks[0]) && getenv("KB_NO_NORM_FOLD") == nullptr;
+  if(rowNormFold_) {
+    for(int i = 0; i < 2; i++) rowSums_[i] = static_cast<float*>(alloc((size_t)rowsPadMax_ * sizeof(float)));
+    float* s0 = rowSums_[0];
+    float* s1 = rowSums_[1];
+    const size_t nb = (size_t)rowsPadMax_ * sizeof(float);
+    addOp("clear row sums", 0.0, 0.0, [=](cudaStream_t st, const Geom&) {
+      cudaError_t e = cudaMemsetAsync(s0, 0, nb, st);
+      return e != cudaSuccess ? e : cudaMemsetAsync(s1, 0, nb, st);
+    });
+  }
   // input packing (symmetry, mask, maskSum)
   {
     const int dt = dt_, inC = inC_, inCdev = inCdev_;
@@ -609,6 +689,14 @@ Engine::Engine(const Model& m, int device, int maxBatch, int X, int Y, int preci
     if(isConvBlock(m.blocks[0])) {
       BNDev b0 = makeBN({&m.blocks[0].preBN});
       e.outAct = trunkAct_; e.actStride = m.trunkC; e.actC0 = 0; e.actC1 = m.trunkC; e.scale = b0.scale; e.bias = b0.bias; e.act = b0.act;
+    }
+    else if(c0.tc && c0.kY == 3) {
+      // the stem feeds a pre-norm transformer block: record the row sums of the stream it creates
+      rowSumsCur_ = -1;
+      if(rowNormFold_ && (m.trunkC % 32) == 0) {
+        e.sumsqOut = rowSums_[rowSumsNext_]; e.sumsqClear = rowSums_[rowSumsNext_ ^ 1];
+        rowSumsCur_ = rowSumsNext_; rowSumsNext_ ^= 1;
+      }
     }
     addConvOp(c0, e, "initial");
   }

@@ -78,6 +78,14 @@ class Engine {
     const void* in = nullptr;
     int inStride = 0;
   };
+  // RMS norms of pre-norm transformer blocks folded into the convolutions around them: two row-sum-of-squares
+  // buffers that the producers of the residual stream fill alternately; rowSumsCur_ = the one describing the current
+  // stream, or -1.
+  float* rowSums_[2] = {nullptr, nullptr};
+  int rowSumsCur_ = -1, rowSumsNext_ = 0;
+  bool rowNormFold_ = false;
+  void produceRowSums(Epilogue& ep, int inC, int outC);
+
   struct BNDev { const float* scale = nullptr; const float* bias = nullptr; int act = 0; int C = 0; };
 
   void* alloc(size_t bytes);                               // zero-initialised device memory

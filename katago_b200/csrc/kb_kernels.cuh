@@ -42,6 +42,12 @@ inline Geom makeGeom(int X, int Y, int n) {
 //                                                  for c in [actC0, actC1)           if outAct
 // The second form is the NEXT layer's batch norm + activation + board mask (eigenbackend.cpp:739-763)
 // applied while the accumulator is still on chip.
+// Epilogue::act value used only by the tensor-core convolution for the merged FFN up|gate projection whose output
+// channels are interleaved in groups of 16 (16 "up" channels, then their 16 "gate" channels): instead of the two
+// halves it writes h = silu(up) * gate (eigenbackend.cpp:1660-1672), 16 values per 32 accumulator columns, to outAct
+// ([rows][actStride], channel (c - actC0) / 2).  scale/bias/mask are not used.
+constexpr int KB_ACT_SWIGLU_PAIRS = 100;
+
 struct Epilogue {
   const float* biasNC = nullptr;
   const void* residual = nullptr;
@@ -55,6 +61,15 @@ struct Epilogue {
   const float* bias = nullptr;
   int act = 0;
   const float* mask = nullptr;
+  // Row-wise RMS normalisation folded around a convolution (pre-norm transformer blocks, eigenbackend.cpp:867-918;
+  // tensor-core convolution with the shared-memory staged epilogue only).  A producer of the residual stream adds the
+  // sum of squares of every row of its raw output into sumsqOut and clears the same rows of sumsqClear (the buffer
+  // the next producer adds into).  A consumer multiplies each accumulator row by rsqrt(rowSumsq/C + eps) (0 where the
+  // mask is 0) before anything else; with the norm's gain folded into its weights that equals conv(rmsnorm(x)).
+  float* sumsqOut = nullptr;
+  float* sumsqClear = nullptr;
+  const float* rowSumsq = nullptr;
+  float rowInvC = 0.0f, rowEps = 0.0f;
 };
 
 // --- SIMT kernels (any dtype) ---------------------------------------------------------------------
@@ -111,6 +126,10 @@ cudaError_t launchMaskToPadded(cudaStream_t st, const float* src, float* mask, f
 struct ConvTcPlan;  // opaque: tensor maps + tile configuration for one convolution
 // True if the tensor-core kernel can run this convolution shape.
 bool convTcEligible(int dt, int inC, int outC, int kY, int kX);
+// True if a 1x1 convolution inC -> outC takes the staged epilogue that supports sumsqOut / rowSumsq.
+bool convTcRowNormEligible(int dt, int inC, int outC);
+// True if the tensor-core kernel can run the merged up|gate projection (inC -> 2*F, interleaved) with the SwiGLU epilogue.
+bool convTcSwigluEligible(int dt, int inC, int F);
 // in: [rowsPadMax][inStride] activations, w: [kY*kX][outC][inC] in dtype dt (K-major per tap).
 ConvTcPlan* convTcCreate(
   int dt, const void* in, int inStride, int inC, const void* w, int outC, int kY, int kX, int X, int Y, int rowsPadMax);
@@ -158,8 +177,10 @@ struct AttnTcPlan;
 bool attentionTcEligible(int dt, int dq, int dv, int X, int Y, int stride, int qOff, int kOff, int vOff, int outStride);
 AttnTcPlan* attentionTcCreate(int dt, const void* qkv, int stride, int totalCols, int rowsPadMax);
 void attentionTcDestroy(AttnTcPlan* p);
+// ropeCos/ropeSin ([tableHeads][32][S], or NULL): the rotary embedding is applied to Q and K inside the kernel, so the
+// QKV matrix holds the unrotated projections.
 cudaError_t launchAttentionTc(
   cudaStream_t st, const AttnTcPlan* p, int qOff, int kOff, int vOff, int heads, int kvHeads, const float* mask, void* out,
-  int outStride, Geom g, int* statusWord);
+  int outStride, Geom g, int* statusWord, const float* ropeCos, const float* ropeSin, int tableHeads);
 
 }  // namespace kb

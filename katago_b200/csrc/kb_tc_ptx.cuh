@@ -187,6 +187,18 @@ __device__ __forceinline__ void tmemLd32(uint32_t taddr, uint32_t (&r)[32]) {
     : "memory");
 }
 __device__ __forceinline__ void tmemLdWait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Same wait, naming the 32 destination registers of an earlier load as in/out operands: when the load was issued ahead
+// of other work, this ties every later use of the registers to the wait in the compiler's eyes.
+__device__ __forceinline__ void tmemLdWaitFor(uint32_t (&r)[32]) {
+  asm volatile(
+    "tcgen05.wait::ld.sync.aligned;"
+    : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+      "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),
+      "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+      "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+    :
+    : "memory");
+}
 
 // Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows 128 B apart, 8-row groups
 // 1024 B apart (stride byte offset), descriptor version 1 (Blackwell).  The swizzle is a function of the

@@ -166,22 +166,24 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_
     for(int j = 0; j < 3; j++) tmaLoad2d(smemU32(sV + j * AT_TILE_BYTES), &tmQKV, a.vOff + kvh * AT_D, boardRow + j * 128, smemU32(&bars[4]));
   }
 
-  AT_TRACE(0);
-  for(int qt = 0; qt < numQTiles; qt++) {
-    AT_TRACE(1 + qt * 8);
+  // Shared-memory descriptors as 32-bit low words (start address, leading offset) plus the common high word, so that the
+  // issuing thread spends an add per MMA
+  const uint32_t descHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);  // stride offset | version | SWIZZLE_128B
+  auto descLo = [](uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); };
+
+  // Rotates Q of tile qt (and K, for the first tile) in shared memory if asked to, then has thread 0 issue S = Q K^T.
+  auto issueScores = [&](int qt) {
     const uint32_t ph = (uint32_t)qt & 1u;
-    const int q0 = qt * 128;
     bool landed = true;
     if(a.ropeCos) {
-      // every thread waits for the tiles, rotates its share of K (first tile only) and Q in shared memory, and the
-      // rotated operands are made visible to the tensor core before the MMAs are issued
+      // every thread waits for the tiles and rotates its share; the rotated operands are made visible to the tensor core
       landed = (qt > 0 || mbarWait(smemU32(&bars[0]), 0u, abortFlag)) && mbarWait(smemU32(&bars[1]), ph, abortFlag);
       if(landed) {
         if(qt == 0) {
           const int thK = kvh * a.tableHeads / a.kvHeads;
           for(int j = 0; j < 3; j++) ropeTileInPlace<T>(sK + j * AT_TILE_BYTES, j * 128, thK, a.ropeCos, a.ropeSin, a.g, tid);
         }
-        ropeTileInPlace<T>(sQ, q0, h * a.tableHeads / a.heads, a.ropeCos, a.ropeSin, a.g, tid);
+        ropeTileInPlace<T>(sQ, qt * 128, h * a.tableHeads / a.heads, a.ropeCos, a.ropeSin, a.g, tid);
       }
       fenceProxyAsync();
       __syncthreads();
@@ -191,15 +193,24 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_
       bool ok = landed && (qt > 0 || mbarWait(smemU32(&bars[0]), 0u, abortFlag)) && mbarWait(smemU32(&bars[1]), ph, abortFlag);
       if(ok) {
         tcFenceAfter();
+        const uint32_t qLo = descLo(smemU32(sQ));
         for(int j = 0; j < 3; j++) {
+          const uint32_t kLo = descLo(smemU32(sK + j * AT_TILE_BYTES));
 #pragma unroll
-          for(int k = 0; k < AT_D / 16; k++)
-            umma(tmemS + (uint32_t)(j * 128), makeSmemDesc(smemU32(sQ) + k * 32), makeSmemDesc(smemU32(sK + j * AT_TILE_BYTES) + k * 32), a.idescS, k > 0 ? 1u : 0u);
+          for(int k = 0; k < AT_D / 16; k++) ummaLoHi(tmemS + (uint32_t)(j * 128), qLo + 2 * k, kLo + 2 * k, descHi, a.idescS, k > 0 ? 1u : 0u);
         }
         ummaCommit(smemU32(&bars[2]));
       }
       else if(!*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, AT_ERR_TIMEOUT); }
     }
+  };
+
+  AT_TRACE(0);
+  issueScores(0);
+  for(int qt = 0; qt < numQTiles; qt++) {
+    AT_TRACE(1 + qt * 8);
+    const uint32_t ph = (uint32_t)qt & 1u;
+    const int q0 = qt * 128;
     // ---- softmax: two warps per query row quarter, each over half of the keys ----
     const float qMask = (q0 + row < a.keysValid) ? a.mask[boardRow + q0 + row] : 0.0f;
     bool ok = mbarWait(smemU32(&bars[2]), ph, abortFlag);
@@ -289,16 +300,20 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_
       tcFenceAfter();
       uint32_t acc = 0;
       for(int kc = 0; kc < AT_SK / 64; kc++) {
+        const uint32_t pLo = descLo(smemU32(sP + (size_t)kc * AT_TILE_BYTES));          // 64 keys of P: one swizzle atom per row
+        const uint32_t vLo = descLo(smemU32(sV) + (uint32_t)(kc * 64) * 128u);         // the same 64 key rows of V
 #pragma unroll
         for(int k = 0; k < 4; k++) {
-          const uint32_t pAddr = smemU32(sP + (size_t)kc * AT_TILE_BYTES) + k * 32;  // 16 keys further along K inside the atom
-          const uint32_t vAddr = smemU32(sV) + (uint32_t)(kc * 64 + k * 16) * 128u;   // 16 key rows further
-          umma(tmemO, makeSmemDesc(pAddr), makeSmemDescMN(vAddr), a.idescO, acc);
+          // 16 keys further: 32 bytes along K inside P's atom, 16 rows (2048 bytes) down in V
+          ummaLoHi(tmemO, pLo + 2 * k, vLo + (uint32_t)k * 128u, descHi, a.idescO, acc);
           acc = 1;
         }
       }
       ummaCommit(smemU32(&bars[3]));
     }
+    // S of this tile has been consumed and its MMAs for O are queued: rotate the next Q tile and queue its S = Q K^T
+    // behind them, so that both run while the threads read O out
+    if(qt + 1 < numQTiles) issueScores(qt + 1);
     AT_TRACE(6 + qt * 8);
     ok = !*abortFlag && mbarWait(smemU32(&bars[3]), ph, abortFlag);
     AT_TRACE(7 + qt * 8);
@@ -323,11 +338,11 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_
       }
     }
     AT_TRACE(8 + qt * 8);
-    // every warp has finished reading S and O of this tile before the next tile's MMAs overwrite them
-    tcFenceBefore();
-    __syncthreads();
-    tcFenceAfter();
+    // No barrier here: the next tile's P is written only after this wait on the O barrier, and its O MMAs are issued
+    // behind the softmax barriers, which every thread reaches after it has read this tile's O.
   }
+  tcFenceBefore();
+  __syncthreads();
   if(warp == 0) { tcFenceAfter(); tmemDealloc(tmemBase, 512); }
 }
 

@@ -50,6 +50,10 @@ WORKLOADS = {
                         metric="NN evals/sec, transformer trunk 12x(6x64, SwiGLU 1024) fp16 batch 128 19x19",
                         text="3x3 stem to d=384, 12 pre-norm layers (6 heads x 64, learnable RoPE, SwiGLU 1024), fp16, 19x19, batch 128 per GPU",
                         dominant="attention"),
+    "transformer_relbias": dict(builder="make_transformer_relbias", precision="fp16", batch=128, sizes=None,
+                                metric="NN evals/sec, transformer trunk 12x(6x64, relative-position bias, SwiGLU 1024) fp16 batch 128 19x19",
+                                text="3x3 stem to d=384, 12 pre-norm layers (6 heads x 64, learned per-head 19x19 relative-position bias, SwiGLU 1024), fp16, 19x19, batch 128 per GPU",
+                                dominant="attention"),
     "mixed": dict(builder="make_b18c384nbt", precision="fp16", batch=128, sizes=[9, 13, 19, 19],
                   metric="NN evals/sec, b18c384nbt fp16 mixed 9/13/19 boards padded to 19x19, batch 128 per GPU",
                   text="b18c384nbt, fp16, boards 9x9/13x13/19x19 in ratio 1:1:2 zero-padded to 19x19 with the on-board mask, batch 128 per GPU (1024 over 8)",

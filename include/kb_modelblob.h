@@ -21,6 +21,10 @@
  *                | BLOCK_GPOOL BN CONV(regular) CONV(gpool) BN(gpool) MATMUL BN(mid) CONV(final)
  *                | BLOCK_NESTED{numInner} BN CONV block*numInner BN CONV
  *                | BLOCK_ATTN{heads,kvHeads,qDim,vDim,useRope,learnableRope,ropePairs}[theta, freqs...]
+ *                  TRMSNORM MATMUL(q) MATMUL(k) MATMUL(v) MATMUL(out) [ATTNBIAS{heads,Y,X}[heads*(2Y-1)*(2X-1)]]
+ *                  (ATTNBIAS: optional learned relative-position bias, added to the scaled scores of query (yq,xq)
+ *                  and key (yk,xk) as table[head][yk-yq+Y-1][xk-xq+X-1]; an extension of this library, the
+ *                  reference's model files cannot carry it)
  *                      TRMSNORM MATMUL(q) MATMUL(k) MATMUL(v) MATMUL(out)
  *                | BLOCK_FFN{C,ffnC,useSwiGLU} TRMSNORM MATMUL(1) [MATMUL(gate)] MATMUL(2)
  *   policyhead  := POLICYHEAD{modelVersion,policyC,hasPassMlp} CONV(p1) CONV(g1) BN(g1) MATMUL(gpoolToBias)
@@ -59,6 +63,7 @@ enum {
   KB_TAG_BLOCK_FFN = 14,
   KB_TAG_RMSNORM = 15,
   KB_TAG_TRMSNORM = 16,
+  KB_TAG_ATTNBIAS = 17,
   KB_TAG_POLICYHEAD = 20,
   KB_TAG_VALUEHEAD = 21,
   KB_TAG_END = 99

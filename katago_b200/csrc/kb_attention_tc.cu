@@ -49,6 +49,7 @@ struct AttnTcArgs {
   const float* ropeCos;   // rotary tables [tableHeads][AT_D/2][S], or NULL: Q and K are used as stored
   const float* ropeSin;
   int tableHeads;
+  const float* scoreBias; // [heads][S][AT_SK] additive bias on the scaled scores (BIAS kernels only)
   int* status;
 };
 
@@ -73,6 +74,7 @@ template <> struct AtUnpack<__nv_bfloat16> {
 // angle whose cosine and sine are table[(tableHead * 32 + p) * S + xy].  Rows that are not board points are left
 // alone (they are masked out of the softmax, and their outputs are written as zeros).  Lanes take consecutive rows,
 // so the table reads coalesce and the 16-byte shared-memory accesses of a quarter warp fall into distinct banks.
+static_assert(AT_SK == KB_ATTN_TC_KEYS, "the expanded score bias is laid out for AT_SK keys");
 static_assert(AT_THREADS == 256, "ropeTileInPlace maps 256 threads onto 128 rows x 2 chunk phases");
 template <typename T>
 __device__ __forceinline__ void ropeTileInPlace(
@@ -118,7 +120,7 @@ __device__ __forceinline__ uint64_t makeSmemDescMN(uint32_t saddr) {
   return d;
 }
 
-template <typename T>
+template <typename T, bool BIAS>
 __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs a) {
   extern __shared__ uint8_t smemRaw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~(uintptr_t)1023);
@@ -213,6 +215,12 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_
     const int q0 = qt * 128;
     // ---- softmax: two warps per query row quarter, each over half of the keys ----
     const float qMask = (q0 + row < a.keysValid) ? a.mask[boardRow + q0 + row] : 0.0f;
+    // this query's row of the score bias (queries that are not board points produce zeros anyway and skip it)
+    const float4* qb4 = nullptr;
+    if(BIAS) {
+      const int qr = q0 + row, qy = qr / a.g.RW, qx = qr - qy * a.g.RW;
+      if(qy < a.g.Y && qx < a.g.X) qb4 = reinterpret_cast<const float4*>(a.scoreBias + ((size_t)h * a.g.S + (size_t)(qy * a.g.X + qx)) * AT_SK + half * (AT_SK / 2));
+    }
     bool ok = mbarWait(smemU32(&bars[2]), ph, abortFlag);
     if(!ok && !*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, AT_ERR_TIMEOUT); }
     if(tid == 0 && ok && qt + 1 < numQTiles) {
@@ -239,11 +247,17 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_
         if(i + 1 < NCH) tmemLd32(tS + (uint32_t)((i + 1) * 32), r[(i + 1) & 1]);
 #pragma unroll
         for(int j = 0; j < 8; j++) {
-          const float4 b = kb4[i * 8 + j];
-          m4[0] = fmaxf(m4[0], __uint_as_float(r[i & 1][4 * j]) + b.x);
-          m4[1] = fmaxf(m4[1], __uint_as_float(r[i & 1][4 * j + 1]) + b.y);
-          m4[2] = fmaxf(m4[2], __uint_as_float(r[i & 1][4 * j + 2]) + b.z);
-          m4[3] = fmaxf(m4[3], __uint_as_float(r[i & 1][4 * j + 3]) + b.w);
+          // everything in the base-2 exponent domain: t = score * scale * log2(e) + key bias (+ score bias * log2(e))
+          float4 b = kb4[i * 8 + j];
+          if(BIAS && qb4) {
+            const float4 e = __ldg(qb4 + i * 8 + j);
+            b.x = fmaf(e.x, 1.4426950408889634f, b.x); b.y = fmaf(e.y, 1.4426950408889634f, b.y);
+            b.z = fmaf(e.z, 1.4426950408889634f, b.z); b.w = fmaf(e.w, 1.4426950408889634f, b.w);
+          }
+          m4[0] = fmaxf(m4[0], fmaf(__uint_as_float(r[i & 1][4 * j]), a.scaleLog2e, b.x));
+          m4[1] = fmaxf(m4[1], fmaf(__uint_as_float(r[i & 1][4 * j + 1]), a.scaleLog2e, b.y));
+          m4[2] = fmaxf(m4[2], fmaf(__uint_as_float(r[i & 1][4 * j + 2]), a.scaleLog2e, b.z));
+          m4[3] = fmaxf(m4[3], fmaf(__uint_as_float(r[i & 1][4 * j + 3]), a.scaleLog2e, b.w));
         }
         if(i + 1 < NCH) tmemLdWaitFor(r[(i + 1) & 1]);
       }
@@ -257,7 +271,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_
     float sum = 0.0f;
     if(ok) {
       const int sw = row & 7;
-      const float mxs = mx * a.scaleLog2e;
+      const float mxs = mx;  // the maximum is already in the exponent domain
       uint32_t r[2][32];
       float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       tmemLd32(tS, r[0]);
@@ -274,7 +288,12 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_
           float p[8];
 #pragma unroll
           for(int k = 0; k < 2; k++) {
-            const float4 b = kb4[i * 8 + 2 * jj + k];
+            float4 b = kb4[i * 8 + 2 * jj + k];
+            if(BIAS && qb4) {
+              const float4 e = __ldg(qb4 + i * 8 + 2 * jj + k);
+              b.x = fmaf(e.x, 1.4426950408889634f, b.x); b.y = fmaf(e.y, 1.4426950408889634f, b.y);
+              b.z = fmaf(e.z, 1.4426950408889634f, b.z); b.w = fmaf(e.w, 1.4426950408889634f, b.w);
+            }
             p[4 * k] = ex2Approx(fmaf(__uint_as_float(r[i & 1][8 * jj + 4 * k]), a.scaleLog2e, b.x - mxs));
             p[4 * k + 1] = ex2Approx(fmaf(__uint_as_float(r[i & 1][8 * jj + 4 * k + 1]), a.scaleLog2e, b.y - mxs));
             p[4 * k + 2] = ex2Approx(fmaf(__uint_as_float(r[i & 1][8 * jj + 4 * k + 2]), a.scaleLog2e, b.z - mxs));
@@ -387,8 +406,10 @@ AttnTcPlan* attentionTcCreate(int dt, const void* qkv, int stride, int totalCols
     box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if(r != CUDA_SUCCESS) { delete p; return nullptr; }
   p->smemBytes = 13 * (size_t)AT_TILE_BYTES + (AT_SK + 256) * sizeof(float) + 5 * 8 + 16 + 1024;
-  cudaError_t e1 = cudaFuncSetAttribute(attentionTcKernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p->smemBytes);
-  cudaError_t e2 = cudaFuncSetAttribute(attentionTcKernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p->smemBytes);
+  cudaError_t e1 = cudaFuncSetAttribute(attentionTcKernel<__half, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p->smemBytes);
+  cudaError_t e2 = cudaFuncSetAttribute(attentionTcKernel<__nv_bfloat16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p->smemBytes);
+  if(e1 == cudaSuccess) e1 = cudaFuncSetAttribute(attentionTcKernel<__half, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p->smemBytes);
+  if(e2 == cudaSuccess) e2 = cudaFuncSetAttribute(attentionTcKernel<__nv_bfloat16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p->smemBytes);
   if(e1 != cudaSuccess || e2 != cudaSuccess) { delete p; return nullptr; }
   return p;
 }
@@ -397,7 +418,7 @@ void attentionTcDestroy(AttnTcPlan* p) { delete p; }
 
 cudaError_t launchAttentionTc(
   cudaStream_t st, const AttnTcPlan* p, int qOff, int kOff, int vOff, int heads, int kvHeads, const float* mask, void* out,
-  int outStride, Geom g, int* statusWord, const float* ropeCos, const float* ropeSin, int tableHeads) {
+  int outStride, Geom g, int* statusWord, const float* ropeCos, const float* ropeSin, int tableHeads, const float* scoreBias) {
   AttnTcArgs a;
   a.g = g; a.heads = heads; a.kvHeads = kvHeads; a.qOff = qOff; a.kOff = kOff; a.vOff = vOff;
   a.keysValid = g.Y * g.RW;
@@ -408,9 +429,16 @@ cudaError_t launchAttentionTc(
   a.scaleLog2e = 1.4426950408889634f / sqrtf((float)AT_D);
   a.status = statusWord;
   a.ropeCos = ropeCos; a.ropeSin = ropeSin; a.tableHeads = tableHeads;
+  a.scoreBias = scoreBias;
   dim3 grid(g.n * heads);
-  if(p->dt == DT_F16) attentionTcKernel<__half><<<grid, AT_THREADS, p->smemBytes, st>>>(p->tmQKV, a);
-  else attentionTcKernel<__nv_bfloat16><<<grid, AT_THREADS, p->smemBytes, st>>>(p->tmQKV, a);
+  if(scoreBias) {
+    if(p->dt == DT_F16) attentionTcKernel<__half, true><<<grid, AT_THREADS, p->smemBytes, st>>>(p->tmQKV, a);
+    else attentionTcKernel<__nv_bfloat16, true><<<grid, AT_THREADS, p->smemBytes, st>>>(p->tmQKV, a);
+  }
+  else {
+    if(p->dt == DT_F16) attentionTcKernel<__half, false><<<grid, AT_THREADS, p->smemBytes, st>>>(p->tmQKV, a);
+    else attentionTcKernel<__nv_bfloat16, false><<<grid, AT_THREADS, p->smemBytes, st>>>(p->tmQKV, a);
+  }
   return cudaGetLastError();
 }
 

@@ -165,9 +165,11 @@ cudaError_t launchRope(
 // Masked softmax attention over the board points of each board (eigenbackend.cpp:1455-1560).  qkv: [rowsPad][stride]
 // with Q at column qOff (heads*dq), K at kOff (kvHeads*dq), V at vOff (kvHeads*dv).  out: [rowsPad][outStride]
 // (heads*dv); rows of masked or padding points are written as zeros.
+// relBias (or NULL): learned relative-position bias [heads][2*relY-1][2*relX-1], added to the scaled score of query
+// (yq,xq) and key (yk,xk) at [head][yk-yq+relY-1][xk-xq+relX-1].
 cudaError_t launchAttention(
   cudaStream_t st, int dt, const void* qkv, int stride, int qOff, int kOff, int vOff, int heads, int kvHeads, int dq, int dv,
-  const float* mask, void* out, int outStride, Geom g);
+  const float* mask, void* out, int outStride, Geom g, const float* relBias = nullptr, int relY = 0, int relX = 0);
 
 // SwiGLU (eigenbackend.cpp:1660-1672): out[r][c] = silu(in[r][c]) * in[r][C + c].
 cudaError_t launchSwiGLU(cudaStream_t st, int dt, const void* in, int inStride, void* out, int outStride, int C, Geom g);
@@ -181,6 +183,9 @@ void attentionTcDestroy(AttnTcPlan* p);
 // QKV matrix holds the unrotated projections.
 cudaError_t launchAttentionTc(
   cudaStream_t st, const AttnTcPlan* p, int qOff, int kOff, int vOff, int heads, int kvHeads, const float* mask, void* out,
-  int outStride, Geom g, int* statusWord, const float* ropeCos, const float* ropeSin, int tableHeads);
+  int outStride, Geom g, int* statusWord, const float* ropeCos, const float* ropeSin, int tableHeads, const float* scoreBias = nullptr);
+// scoreBias (or NULL): additive score bias [heads][X*Y queries][384 keys in padded-row order] in fp32, e.g. a
+// relative-position bias expanded for this board size.
+constexpr int KB_ATTN_TC_KEYS = 384;
 
 }  // namespace kb

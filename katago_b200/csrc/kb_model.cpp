@@ -112,6 +112,14 @@ void parseBlock(Reader& rd, BlockW& b) {
     if(b.q.inC != b.preLN.C || b.k.inC != b.preLN.C || b.v.inC != b.preLN.C || b.q.outC != b.heads * b.qDim ||
        b.k.outC != b.kvHeads * b.qDim || b.v.outC != b.kvHeads * b.vDim || b.out.inC != b.heads * b.vDim || b.out.outC != b.preLN.C)
       fail("attention block: projection shape mismatch");
+    if(!rd.atEnd() && rd.peekTag() == KB_TAG_ATTNBIAS) {
+      Record rb = rd.expect(KB_TAG_ATTNBIAS, 3, "ATTNBIAS");
+      b.relBiasY = rb.ints[1]; b.relBiasX = rb.ints[2];
+      if(rb.ints[0] != b.heads || b.relBiasY < 1 || b.relBiasX < 1 || b.relBiasY > 64 || b.relBiasX > 64 ||
+         rb.nFloats != (uint32_t)(b.heads * (2 * b.relBiasY - 1) * (2 * b.relBiasX - 1)))
+        fail("attention block: relative-position bias has the wrong shape");
+      b.relBias.assign(rb.floats, rb.floats + rb.nFloats);
+    }
   }
   else if(tag == KB_TAG_BLOCK_FFN) {
     Record r = rd.expect(KB_TAG_BLOCK_FFN, 3, "BLOCK_FFN");

@@ -53,6 +53,9 @@ struct BlockW {
   int heads = 0, kvHeads = 0, qDim = 0, vDim = 0, useRope = 0, learnableRope = 0;
   float ropeTheta = 0.0f;
   std::vector<float> ropeFreqs;
+  // optional relative-position bias [heads][2*relBiasY-1][2*relBiasX-1] (empty: none)
+  std::vector<float> relBias;
+  int relBiasY = 0, relBiasX = 0;
   TRMSNormW preLN;
   MatMulW q, k, v, out;
   // ffn (eigenbackend.cpp:1592-1707)

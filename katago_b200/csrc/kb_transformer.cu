@@ -193,7 +193,7 @@ cudaError_t launchRope(
 template <typename T>
 __global__ void __launch_bounds__(256) attentionKernel(
   const T* __restrict__ qkv, int stride, int qOff, int kOff, int vOff, int heads, int kvHeads, int dq, int dv,
-  const float* __restrict__ mask, T* __restrict__ out, int outStride, Geom g) {
+  const float* __restrict__ mask, T* __restrict__ out, int outStride, Geom g, const float* __restrict__ relBias, int relY, int relX) {
   extern __shared__ float sm[];
   const int S = g.S;
   const int kp = dq + 1, vp = dv + 1;
@@ -242,6 +242,10 @@ __global__ void __launch_bounds__(256) attentionKernel(
         float dot = 0.0f;
         for(int d = 0; d < dq; d++) dot = fmaf(myQ[d], kr[d], dot);
         s = dot * scale;
+        if(relBias) {
+          const int ky = k / g.X, kx = k - ky * g.X;
+          s += relBias[((size_t)h * (2 * relY - 1) + (ky - y + relY - 1)) * (2 * relX - 1) + (kx - x + relX - 1)];
+        }
       }
       myP[k] = s;
       mx = fmaxf(mx, s);
@@ -267,7 +271,7 @@ __global__ void __launch_bounds__(256) attentionKernel(
 
 cudaError_t launchAttention(
   cudaStream_t st, int dt, const void* qkv, int stride, int qOff, int kOff, int vOff, int heads, int kvHeads, int dq, int dv,
-  const float* mask, void* out, int outStride, Geom g) {
+  const float* mask, void* out, int outStride, Geom g, const float* relBias, int relY, int relX) {
   const size_t smem = ((size_t)g.S * (dq + 1) + (size_t)g.S * (dv + 1) + g.S + 8 * (size_t)g.S + 8 * (size_t)dq) * sizeof(float);
   if(smem > 227 * 1024) return cudaErrorInvalidValue;
   dim3 grid((g.S + 31) / 32, g.n * heads);
@@ -277,7 +281,7 @@ cudaError_t launchAttention(
     default: cudaFuncSetAttribute(attentionKernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); break;
   }
   KBT_DISPATCH_DT(dt, (attentionKernel<T><<<grid, 256, smem, st>>>(
-    (const T*)qkv, stride, qOff, kOff, vOff, heads, kvHeads, dq, dv, mask, (T*)out, outStride, g)));
+    (const T*)qkv, stride, qOff, kOff, vOff, heads, kvHeads, dq, dv, mask, (T*)out, outStride, g, relBias, relY, relX)));
   return cudaGetLastError();
 }
 

@@ -30,6 +30,7 @@ _ACT_CODES = {v: k for k, v in _ACT_NAMES.items()}
 
 TAG_MODEL, TAG_TRUNK, TAG_CONV, TAG_BN, TAG_MATMUL, TAG_MATBIAS, TAG_ACT = 1, 2, 3, 4, 5, 6, 7
 TAG_BLOCK_ORDINARY, TAG_BLOCK_GPOOL, TAG_BLOCK_NESTED, TAG_BLOCK_ATTN, TAG_BLOCK_FFN = 10, 11, 12, 13, 14
+TAG_ATTNBIAS = 17
 TAG_RMSNORM, TAG_TRMSNORM, TAG_POLICYHEAD, TAG_VALUEHEAD, TAG_END = 15, 16, 20, 21, 99
 BLOB_MAGIC = 0x314D424B
 
@@ -358,6 +359,8 @@ def _write_blocks(w: _Writer, blocks, v):
             _write_blocks(w, b["blocks"], v)
             _write_bn(w, b["postBN"]); _write_act(w, b["postAct"], v); _write_conv(w, b["postConv"])
         elif k == "transformer_attention_block":
+            if b.get("relBias") is not None:
+                raise ValueError("the reference's model file format has no field for a relative-position attention bias; use to_blob")
             w.ln(b["heads"], b["kvHeads"], b["qDim"], b["vDim"], b["useRope"], b["learnableRope"])
             _write_trmsnorm(w, b["preLN"])
             for key in ("q", "k", "v", "out"):
@@ -504,6 +507,10 @@ def _b_blocks(o: _Blob, blocks):
             _b_trms(o, b["preLN"])
             for key in ("q", "k", "v", "out"):
                 _b_matmul(o, b[key])
+            if b.get("relBias") is not None:
+                # learned relative-position bias [heads][2Y-1][2X-1]: an extension carried by the blob only
+                rb = np.asarray(b["relBias"], np.float32)
+                o.rec(TAG_ATTNBIAS, (rb.shape[0], (rb.shape[1] + 1) // 2, (rb.shape[2] + 1) // 2), rb.reshape(-1))
         elif k == "transformer_ffn_block":
             o.rec(TAG_BLOCK_FFN, (b["C"], b["ffnC"], b["swiglu"]))
             _b_trms(o, b["preLN"]); _b_matmul(o, b["linear1"])
@@ -682,9 +689,11 @@ def make_b28c512nbt(seed=1002, num_blocks=28):
     return make_nbt("b28c512nbt-random", seed, num_blocks, 512, 256, 64, (64, 64, 128, 144))
 
 
-def make_transformer(seed=1003, layers=12, d=384, heads=6, head_dim=64, ffn=1024, rope="learnable"):
+def make_transformer(seed=1003, layers=12, d=384, heads=6, head_dim=64, ffn=1024, rope="learnable", rel_bias=False):
     """BASELINE configs[3]: conv stem to d, `layers` pre-norm (attention, SwiGLU FFN) pairs, standard heads.
-    Weights N(0, 0.02).  The positional scheme is RoPE, the one the reference's file format can express."""
+    Weights N(0, 0.02).  The positional scheme is RoPE, the one the reference's file format can express; rel_bias adds
+    a learned per-head relative-position bias table [heads][37][37] ~ N(0, 0.2) to every attention block, which only
+    the blob (to_blob) can carry."""
     g = _Gen(seed, std_override=0.02)
     v = 17
     sp, gl = num_features(v)
@@ -701,6 +710,8 @@ def make_transformer(seed=1003, layers=12, d=384, heads=6, head_dim=64, ffn=1024
             a["ropeFreqs"] = g.rng.uniform(-1.0, 1.0, heads * (head_dim // 2) * 2).astype(np.float32)
         elif rope == "fixed":
             a["ropeTheta"] = np.float32(100.0)
+        if rel_bias:
+            a["relBias"] = (g.rng.standard_normal((heads, 37, 37)) * 0.2).astype(np.float32)
         blocks.append(a)
         blocks.append(dict(kind="transformer_ffn_block", name=g.name("ffn"), C=d, ffnC=ffn, swiglu=1, preLN=g.trms(d),
                            linear1=g.matmul(d, ffn), gate=g.matmul(d, ffn), linear2=g.matmul(ffn, d)))
@@ -710,6 +721,12 @@ def make_transformer(seed=1003, layers=12, d=384, heads=6, head_dim=64, ffn=1024
     m["trunk"] = t
     _gen_heads(g, m, d, 48, 48, 96, 128, ACT_SILU)
     return m
+
+
+def make_transformer_relbias(seed=1004, layers=12):
+    """BASELINE configs[3] as worded: 12 pre-norm layers of 6 heads x 64 with a learned per-head relative-position bias
+    (no RoPE), SwiGLU 1024.  Only the blob can carry the bias."""
+    return make_transformer(seed=seed, layers=layers, rope="none", rel_bias=True)
 
 
 # ----------------------------------------------------------------------------------------------

@@ -430,6 +430,10 @@ struct AttnBlock final : Block {
   TRMSNorm preLN; MatMul q, k, v, o;
   mutable vector<float> cosT, sinT;
   mutable int tabX = -1, tabY = -1;
+  // Optional learned relative-position bias (KB_TAG_ATTNBIAS, an extension the reference's files cannot carry):
+  // score(q,k) += relBias[h][yk-yq+relY-1][xk-xq+relX-1].
+  vector<float> relBias;
+  int relY = 0, relX = 0;
 
   void load(Reader& rd) {
     Record r = rd.expect(KB_TAG_BLOCK_ATTN, 6, "BLOCK_ATTN");
@@ -447,6 +451,13 @@ struct AttnBlock final : Block {
     if(q.inC != preLN.C || k.inC != preLN.C || v.inC != preLN.C || q.outC != H * dq || k.outC != Hkv * dq ||
        v.outC != Hkv * dv || o.inC != H * dv || o.outC != preLN.C)
       throw Fail("attention block: projection shape mismatch");
+    if(!rd.atEnd() && rd.peekTag() == KB_TAG_ATTNBIAS) {
+      Record rb = rd.expect(KB_TAG_ATTNBIAS, 3, "ATTNBIAS");
+      relY = rb.ints[1]; relX = rb.ints[2];
+      if(rb.ints[0] != H || relY < 1 || relX < 1 || rb.nFloats != (uint32_t)(H * (2 * relY - 1) * (2 * relX - 1)))
+        throw Fail("attention block: relative-position bias has the wrong shape");
+      relBias.assign(rb.floats, rb.floats + rb.nFloats);
+    }
   }
   int channels() const override { return preLN.C; }
 
@@ -521,6 +532,7 @@ struct AttnBlock final : Block {
     }
     const float scale = 1.0f / sqrtf((float)dq);
     const int group = H / Hkv;
+    if(!relBias.empty() && (cx.X > relX || cx.Y > relY)) throw Fail("attention block: board larger than the relative-position bias table");
 #pragma omp parallel for collapse(2) schedule(dynamic)
     for(int b = 0; b < cx.n; b++)
       for(int h = 0; h < H; h++) {
@@ -539,6 +551,10 @@ struct AttnBlock final : Block {
             float dot = 0.0f;
             for(int d = 0; d < dq; d++) dot += qv[d] * kv[d];
             sc[ki] = dot * scale;
+            if(!relBias.empty()) {
+              const int dy = ki / cx.X - qi / cx.X + relY - 1, dx = ki % cx.X - qi % cx.X + relX - 1;
+              sc[ki] += relBias[((size_t)h * (2 * relY - 1) + dy) * (2 * relX - 1) + dx];
+            }
             maxVal = std::max(maxVal, sc[ki]);
           }
           float sumExp = 0.0f;

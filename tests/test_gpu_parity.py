@@ -93,9 +93,16 @@ def _attn_block(g, C, heads, kv, dq, dv, rope):
     return b
 
 
+def _with_rel_bias(g, block):
+    """Adds a learned per-head relative-position bias table [heads][37][37] (the blob extension KB_TAG_ATTNBIAS)."""
+    block["relBias"] = (g.rng.standard_normal((block["heads"], 37, 37)) * 0.5).astype(np.float32)
+    return block
+
+
 @pytest.mark.parametrize("prec,tol", [(capi.PRECISION_FP32, 2e-4), (capi.PRECISION_FP16, 0.03)])
 def test_transformer_blocks_with_masks(prec, tol, oracle):
-    """Attention (plain, grouped-query, fixed and learnable RoPE) and SwiGLU FFN blocks on masked boards."""
+    """Attention (plain, grouped-query, fixed and learnable RoPE, with and without a relative-position bias) and SwiGLU FFN
+    blocks on masked boards."""
     g = mf._Gen(77)
     rng = np.random.default_rng(5)
     mask = np.zeros((3, 19, 19), np.float32)
@@ -106,6 +113,9 @@ def test_transformer_blocks_with_masks(prec, tol, oracle):
         (96, _attn_block(g, 96, 6, 3, 32, 16, "fixed")),
         (384, _attn_block(g, 384, 6, 6, 64, 64, "learnable")),
         (64, _attn_block(g, 64, 4, 4, 16, 16, "none")),
+        (384, _with_rel_bias(g, _attn_block(g, 384, 6, 6, 64, 64, "none"))),
+        (384, _with_rel_bias(g, _attn_block(g, 384, 6, 3, 64, 64, "learnable"))),
+        (64, _with_rel_bias(g, _attn_block(g, 64, 4, 2, 16, 16, "fixed"))),
         (384, dict(kind="transformer_ffn_block", name="ffn", C=384, ffnC=1024, swiglu=1, preLN=g.trms(384), linear1=g.matmul(384, 1024),
                    gate=g.matmul(384, 1024), linear2=g.matmul(1024, 384))),
         (96, dict(kind="transformer_ffn_block", name="ffn2", C=96, ffnC=160, swiglu=1, preLN=g.trms(96), linear1=g.matmul(96, 160),
@@ -123,7 +133,8 @@ def test_transformer_blocks_with_masks(prec, tol, oracle):
 def test_transformer_net_vs_oracle(prec, oracle):
     """BASELINE configs[3] architecture (conv stem to d=384, pre-norm attention + SwiGLU layers of 6 heads x 64, FFN 1024,
     RMSNorm+SiLU tip, standard heads) with 3 layers, and a small net with fixed RoPE; mixed board sizes and symmetries."""
-    for model_tree, n in [(mf.make_transformer(layers=3), 4), (mf.make_transformer(seed=9, layers=2, d=64, heads=2, head_dim=32, ffn=96, rope="fixed"), 5)]:
+    for model_tree, n in [(mf.make_transformer(layers=3), 4), (mf.make_transformer(seed=9, layers=2, d=64, heads=2, head_dim=32, ffn=96, rope="fixed"), 5),
+                          (mf.make_transformer(seed=11, layers=2, rope="none", rel_bias=True), 4)]:
         blob = mf.to_blob(model_tree)
         sizes = ([19, 13, 9, 19, 11])[:n]
         sp, gl = mf.random_positions(n, seed=2003, board_sizes=sizes)

@@ -20,6 +20,8 @@ CASES = {
     "b6c96": (lambda: mf.make_b6c96(seed=1000), 8, [19, 19, 13, 9, 19, 13, 9, 19], 2000),
     "b18c384nbt_3blocks": (lambda: mf.make_b18c384nbt(seed=1001, num_blocks=3), 6, [19, 13, 9, 19, 19, 13], 2001),
     "b28c512nbt_3blocks": (lambda: mf.make_b28c512nbt(seed=1002, num_blocks=3), 4, [19, 9, 13, 19], 2002),
+    "transformer_rope_2layers": (lambda: mf.make_transformer(seed=1003, layers=2), 4, [19, 13, 9, 19], 2003),
+    "transformer_relbias_2layers": (lambda: mf.make_transformer_relbias(seed=1004, layers=2), 4, [19, 9, 13, 19], 2004),
 }
 
 

@@ -194,6 +194,18 @@ def test_nbt_reduced_precision_matches_golden(name, prec, oracle):
     _assert_reduced_close(got, ref, mask)
 
 
+@pytest.mark.parametrize("name", ["transformer_rope_2layers", "transformer_relbias_2layers"])
+@pytest.mark.parametrize("prec", [capi.PRECISION_FP32, capi.PRECISION_FP16])
+def test_transformer_matches_golden(name, prec, oracle):
+    """BASELINE configs[3] architecture at 2 layers: RoPE (what the reference's files can carry) and the learned
+    relative-position bias (blob extension), CUDA-core path in fp32 and tcgen05 path in fp16."""
+    got, ref, mask = _run_case(name, prec, oracle)
+    if prec == capi.PRECISION_FP32:
+        _assert_fp32_close(got, ref, mask)
+    else:
+        _assert_reduced_close(got, ref, mask)
+
+
 def _fp16_conv_weights(tree):
     """The model as the device holds it in fp16 mode: every convolution weight rounded to fp16 (norms, matmuls of the
     heads and biases stay fp32 on the device)."""

@@ -25,6 +25,7 @@ constexpr int AT_SK = 384;     // keys per board handled in one pass (19x19: 19*
 constexpr int AT_D = 64;       // head dimension (q, k and v)
 constexpr int AT_THREADS = 256;
 constexpr int AT_TILE_BYTES = 128 * 128;  // 128 rows x 64 elements x 2 bytes
+constexpr int AT_REL_MAX = 1536;          // floats of one head's relative-position table: (2Y-1)(2X-1) < 4*Y*X <= 4*AT_SK
 
 enum { AT_ERR_TIMEOUT = 201 };
 
@@ -49,7 +50,8 @@ struct AttnTcArgs {
   const float* ropeCos;   // rotary tables [tableHeads][AT_D/2][S], or NULL: Q and K are used as stored
   const float* ropeSin;
   int tableHeads;
-  const float* scoreBias; // [heads][S][AT_SK] additive bias on the scaled scores (BIAS kernels only)
+  const float* relBias;   // learned relative-position bias [heads][2*relY-1][2*relX-1] (BIAS kernels only)
+  int relY, relX;
   int* status;
 };
 
@@ -74,7 +76,6 @@ template <> struct AtUnpack<__nv_bfloat16> {
 // angle whose cosine and sine are table[(tableHead * 32 + p) * S + xy].  Rows that are not board points are left
 // alone (they are masked out of the softmax, and their outputs are written as zeros).  Lanes take consecutive rows,
 // so the table reads coalesce and the 16-byte shared-memory accesses of a quarter warp fall into distinct banks.
-static_assert(AT_SK == KB_ATTN_TC_KEYS, "the expanded score bias is laid out for AT_SK keys");
 static_assert(AT_THREADS == 256, "ropeTileInPlace maps 256 threads onto 128 rows x 2 chunk phases");
 template <typename T>
 __device__ __forceinline__ void ropeTileInPlace(
@@ -130,7 +131,10 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_
   uint8_t* sP = sV + 3 * AT_TILE_BYTES;       // 6 x 16 KiB (64 keys each), K-major operand layout
   float* sKb = reinterpret_cast<float*>(sP + 6 * AT_TILE_BYTES);  // [AT_SK] additive key bias: 0 on the board, -1e30 elsewhere
   float* sRed = sKb + AT_SK;                                      // [2][128] partial row maxima, then partial row sums
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sRed + 256);         // k (all tiles), q, mma1, mma2, v
+  // BIAS only: this head's bias table times log2(e), and for every key row its offset into it (ky * (2*relX-1) + kx)
+  float* sRel = sRed + 256;                                       // [AT_REL_MAX]
+  int* sKeyOff = reinterpret_cast<int*>(sRel + (BIAS ? AT_REL_MAX : 0));  // [AT_SK]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sKeyOff + (BIAS ? AT_SK : 0));  // k (all tiles), q, mma1, mma2, v
   uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 5);
   volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
 
@@ -151,6 +155,14 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_
   }
   if(warp == 0) { tmemAlloc(smemU32(tmemSlot), 512); tmemRelinquish(); }
   for(int j = tid; j < AT_SK; j += AT_THREADS) sKb[j] = (j < a.keysValid && a.mask[boardRow + j] != 0.0f) ? 0.0f : -1e30f;
+  if(BIAS) {
+    const int W = 2 * a.relX - 1, relN = (2 * a.relY - 1) * W;
+    for(int j = tid; j < relN; j += AT_THREADS) sRel[j] = a.relBias[(size_t)h * relN + j] * 1.4426950408889634f;
+    for(int j = tid; j < AT_SK; j += AT_THREADS) {
+      const int ky = j / a.g.RW, kx = j - ky * a.g.RW;
+      sKeyOff[j] = (ky < a.g.Y && kx < a.g.X) ? ky * W + kx : 0;  // keys off the board: any valid entry, their key bias is -1e30
+    }
+  }
   tcFenceBefore();
   __syncthreads();
   tcFenceAfter();
@@ -215,12 +227,13 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_
     const int q0 = qt * 128;
     // ---- softmax: two warps per query row quarter, each over half of the keys ----
     const float qMask = (q0 + row < a.keysValid) ? a.mask[boardRow + q0 + row] : 0.0f;
-    // this query's row of the score bias (queries that are not board points produce zeros anyway and skip it)
-    const float4* qb4 = nullptr;
+    // this query's origin in the bias table (queries that are not board points produce zeros anyway and skip the bias)
+    const float* qRel = nullptr;
     if(BIAS) {
       const int qr = q0 + row, qy = qr / a.g.RW, qx = qr - qy * a.g.RW;
-      if(qy < a.g.Y && qx < a.g.X) qb4 = reinterpret_cast<const float4*>(a.scoreBias + ((size_t)h * a.g.S + (size_t)(qy * a.g.X + qx)) * AT_SK + half * (AT_SK / 2));
+      if(qy < a.g.Y && qx < a.g.X) qRel = sRel + (a.relY - 1 - qy) * (2 * a.relX - 1) + (a.relX - 1 - qx);
     }
+    const int4* ko4 = reinterpret_cast<const int4*>(sKeyOff + half * (AT_SK / 2));
     bool ok = mbarWait(smemU32(&bars[2]), ph, abortFlag);
     if(!ok && !*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, AT_ERR_TIMEOUT); }
     if(tid == 0 && ok && qt + 1 < numQTiles) {
@@ -247,12 +260,11 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_
         if(i + 1 < NCH) tmemLd32(tS + (uint32_t)((i + 1) * 32), r[(i + 1) & 1]);
 #pragma unroll
         for(int j = 0; j < 8; j++) {
-          // everything in the base-2 exponent domain: t = score * scale * log2(e) + key bias (+ score bias * log2(e))
+          // everything in the base-2 exponent domain: t = score * scale * log2(e) + key bias (+ relative bias * log2(e))
           float4 b = kb4[i * 8 + j];
-          if(BIAS && qb4) {
-            const float4 e = __ldg(qb4 + i * 8 + j);
-            b.x = fmaf(e.x, 1.4426950408889634f, b.x); b.y = fmaf(e.y, 1.4426950408889634f, b.y);
-            b.z = fmaf(e.z, 1.4426950408889634f, b.z); b.w = fmaf(e.w, 1.4426950408889634f, b.w);
+          if(BIAS && qRel) {
+            const int4 ko = ko4[i * 8 + j];
+            b.x += qRel[ko.x]; b.y += qRel[ko.y]; b.z += qRel[ko.z]; b.w += qRel[ko.w];
           }
           m4[0] = fmaxf(m4[0], fmaf(__uint_as_float(r[i & 1][4 * j]), a.scaleLog2e, b.x));
           m4[1] = fmaxf(m4[1], fmaf(__uint_as_float(r[i & 1][4 * j + 1]), a.scaleLog2e, b.y));
@@ -289,10 +301,9 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_
 #pragma unroll
           for(int k = 0; k < 2; k++) {
             float4 b = kb4[i * 8 + 2 * jj + k];
-            if(BIAS && qb4) {
-              const float4 e = __ldg(qb4 + i * 8 + 2 * jj + k);
-              b.x = fmaf(e.x, 1.4426950408889634f, b.x); b.y = fmaf(e.y, 1.4426950408889634f, b.y);
-              b.z = fmaf(e.z, 1.4426950408889634f, b.z); b.w = fmaf(e.w, 1.4426950408889634f, b.w);
+            if(BIAS && qRel) {
+              const int4 ko = ko4[i * 8 + 2 * jj + k];
+              b.x += qRel[ko.x]; b.y += qRel[ko.y]; b.z += qRel[ko.z]; b.w += qRel[ko.w];
             }
             p[4 * k] = ex2Approx(fmaf(__uint_as_float(r[i & 1][8 * jj + 4 * k]), a.scaleLog2e, b.x - mxs));
             p[4 * k + 1] = ex2Approx(fmaf(__uint_as_float(r[i & 1][8 * jj + 4 * k + 1]), a.scaleLog2e, b.y - mxs));
@@ -405,7 +416,7 @@ AttnTcPlan* attentionTcCreate(int dt, const void* qkv, int stride, int totalCols
     &p->tmQKV, dt == DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(qkv), dims, strides,
     box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if(r != CUDA_SUCCESS) { delete p; return nullptr; }
-  p->smemBytes = 13 * (size_t)AT_TILE_BYTES + (AT_SK + 256) * sizeof(float) + 5 * 8 + 16 + 1024;
+  p->smemBytes = 13 * (size_t)AT_TILE_BYTES + (AT_SK + 256 + AT_REL_MAX + AT_SK) * sizeof(float) + 5 * 8 + 16 + 1024;
   cudaError_t e1 = cudaFuncSetAttribute(attentionTcKernel<__half, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p->smemBytes);
   cudaError_t e2 = cudaFuncSetAttribute(attentionTcKernel<__nv_bfloat16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p->smemBytes);
   if(e1 == cudaSuccess) e1 = cudaFuncSetAttribute(attentionTcKernel<__half, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p->smemBytes);
@@ -418,7 +429,7 @@ void attentionTcDestroy(AttnTcPlan* p) { delete p; }
 
 cudaError_t launchAttentionTc(
   cudaStream_t st, const AttnTcPlan* p, int qOff, int kOff, int vOff, int heads, int kvHeads, const float* mask, void* out,
-  int outStride, Geom g, int* statusWord, const float* ropeCos, const float* ropeSin, int tableHeads, const float* scoreBias) {
+  int outStride, Geom g, int* statusWord, const float* ropeCos, const float* ropeSin, int tableHeads, const float* relBias, int relY, int relX) {
   AttnTcArgs a;
   a.g = g; a.heads = heads; a.kvHeads = kvHeads; a.qOff = qOff; a.kOff = kOff; a.vOff = vOff;
   a.keysValid = g.Y * g.RW;
@@ -429,9 +440,10 @@ cudaError_t launchAttentionTc(
   a.scaleLog2e = 1.4426950408889634f / sqrtf((float)AT_D);
   a.status = statusWord;
   a.ropeCos = ropeCos; a.ropeSin = ropeSin; a.tableHeads = tableHeads;
-  a.scoreBias = scoreBias;
+  a.relBias = relBias; a.relY = relY; a.relX = relX;
+  if(relBias && ((2 * relY - 1) * (2 * relX - 1) > AT_REL_MAX || g.X > relX || g.Y > relY)) return cudaErrorInvalidValue;
   dim3 grid(g.n * heads);
-  if(scoreBias) {
+  if(relBias) {
     if(p->dt == DT_F16) attentionTcKernel<__half, true><<<grid, AT_THREADS, p->smemBytes, st>>>(p->tmQKV, a);
     else attentionTcKernel<__nv_bfloat16, true><<<grid, AT_THREADS, p->smemBytes, st>>>(p->tmQKV, a);
   }

@@ -403,7 +403,8 @@ void Engine::emitBlock(const BlockW& b, int C, void* raw, void* act, const BNW* 
       ConvDev cq = makeConv({&qkvW}, normed, C, C);
       addConvOp(cq, eq, "qkv");
     }
-    const bool attnTc = !forceSimt_ && attentionTcEligible(dt_, dq, dv, X_, Y_, qkvC, 0, qC, qC + kC, oC);
+    const bool attnTc = !forceSimt_ && attentionTcEligible(dt_, dq, dv, X_, Y_, qkvC, 0, qC, qC + kC, oC) &&
+                        (b.relBias.empty() || (2 * b.relBiasY - 1) * (2 * b.relBiasX - 1) <= KB_ATTN_TC_REL_MAX);
     float* dCos = nullptr;
     float* dSin = nullptr;
     int tableHeads = 1;
@@ -421,26 +422,12 @@ void Engine::emitBlock(const BlockW& b, int C, void* raw, void* act, const BNW* 
         });
       }
     }
-    // optional learned relative-position bias (blob extension)
+    // optional learned relative-position bias (blob extension); both attention kernels take the table as it is
     const float* relBiasDev = nullptr;
-    const float* scoreBiasDev = nullptr;
     const int relY = b.relBiasY, relX = b.relBiasX;
     if(!b.relBias.empty()) {
       if(X_ > relX || Y_ > relY) throw std::runtime_error("attention block: board larger than the relative-position bias table");
-      if(attnTc) {
-        // expanded for this board: [head][query point][key row in padded order], zeros at padding keys
-        const int Sq = X_ * Y_, RW = X_ + 1;
-        std::vector<float> dense((size_t)H * Sq * KB_ATTN_TC_KEYS, 0.0f);
-        for(int h = 0; h < H; h++)
-          for(int qy = 0; qy < Y_; qy++)
-            for(int qx = 0; qx < X_; qx++)
-              for(int ky = 0; ky < Y_; ky++)
-                for(int kx = 0; kx < X_; kx++)
-                  dense[((size_t)h * Sq + (size_t)qy * X_ + qx) * KB_ATTN_TC_KEYS + (size_t)ky * RW + kx] =
-                    b.relBias[((size_t)h * (2 * relY - 1) + (ky - qy + relY - 1)) * (2 * relX - 1) + (kx - qx + relX - 1)];
-        scoreBiasDev = uploadF32(dense);
-      }
-      else relBiasDev = uploadF32(b.relBias);
+      relBiasDev = uploadF32(b.relBias);
     }
     if(attnTc) {
       AttnTcPlan* ap = attentionTcCreate(dt_, qkv, qkvC, qkvC, rowsPadMax_);
@@ -448,7 +435,7 @@ void Engine::emitBlock(const BlockW& b, int C, void* raw, void* act, const BNW* 
       attnPlans_.push_back(ap);
       int* status = statusWord_;
       addOp(b.useRope ? "attention tcgen05 +rope" : "attention tcgen05", 2.0 * S * S * (dq + dv) * H, S * (qkvC + oC) * es, [=](cudaStream_t st, const Geom& g) {
-        return launchAttentionTc(st, ap, 0, qC, qC + kC, H, Hkv, mask, attn, oC, g, status, dCos, dSin, tableHeads, scoreBiasDev);
+        return launchAttentionTc(st, ap, 0, qC, qC + kC, H, Hkv, mask, attn, oC, g, status, dCos, dSin, tableHeads, relBiasDev, relY, relX);
       });
     }
     else {

@@ -183,9 +183,10 @@ void attentionTcDestroy(AttnTcPlan* p);
 // QKV matrix holds the unrotated projections.
 cudaError_t launchAttentionTc(
   cudaStream_t st, const AttnTcPlan* p, int qOff, int kOff, int vOff, int heads, int kvHeads, const float* mask, void* out,
-  int outStride, Geom g, int* statusWord, const float* ropeCos, const float* ropeSin, int tableHeads, const float* scoreBias = nullptr);
-// scoreBias (or NULL): additive score bias [heads][X*Y queries][384 keys in padded-row order] in fp32, e.g. a
-// relative-position bias expanded for this board size.
-constexpr int KB_ATTN_TC_KEYS = 384;
+  int outStride, Geom g, int* statusWord, const float* ropeCos, const float* ropeSin, int tableHeads,
+  const float* relBias = nullptr, int relY = 0, int relX = 0);
+// relBias (or NULL): learned relative-position bias as for launchAttention; the kernel keeps one head's table in shared
+// memory, which bounds it to KB_ATTN_TC_REL_MAX entries.
+constexpr int KB_ATTN_TC_REL_MAX = 1536;
 
 }  // namespace kb

@@ -666,7 +666,7 @@ def make_convnet(name, seed, version, trunk_c, blocks, heads, act, mid_c=None, r
 
 
 def make_b6c96(seed=1000, gpool_blocks=(2,)):
-    """BASELINE configs[0]: 6 plain residual blocks of two 3x3 convs, 96 channels, gpool in the listed block(s)."""
+    """The fp32 benchmark configuration: 6 plain residual blocks of two 3x3 convs, 96 channels, gpool in the listed block(s)."""
     blocks = ["gpool" if i in gpool_blocks else "plain" for i in range(6)]
     return make_convnet("b6c96-random", seed, 15, 96, blocks, (32, 32, 32, 64), ACT_RELU, mid_c=96, regular_c=64, gpool_c=32)
 
@@ -690,7 +690,7 @@ def make_b28c512nbt(seed=1002, num_blocks=28):
 
 
 def make_transformer(seed=1003, layers=12, d=384, heads=6, head_dim=64, ffn=1024, rope="learnable", rel_bias=False):
-    """BASELINE configs[3]: conv stem to d, `layers` pre-norm (attention, SwiGLU FFN) pairs, standard heads.
+    """The transformer benchmark configuration: conv stem to d, `layers` pre-norm (attention, SwiGLU FFN) pairs, standard heads.
     Weights N(0, 0.02).  The positional scheme is RoPE, the one the reference's file format can express; rel_bias adds
     a learned per-head relative-position bias table [heads][37][37] ~ N(0, 0.2) to every attention block, which only
     the blob (to_blob) can carry."""
@@ -724,7 +724,7 @@ def make_transformer(seed=1003, layers=12, d=384, heads=6, head_dim=64, ffn=1024
 
 
 def make_transformer_relbias(seed=1004, layers=12):
-    """BASELINE configs[3] as worded: 12 pre-norm layers of 6 heads x 64 with a learned per-head relative-position bias
+    """The transformer benchmark configuration as worded: 12 pre-norm layers of 6 heads x 64 with a learned per-head relative-position bias
     (no RoPE), SwiGLU 1024.  Only the blob can carry the bias."""
     return make_transformer(seed=seed, layers=layers, rope="none", rel_bias=True)
 

@@ -7,7 +7,7 @@ build.  Models are either generated from seeds (katago_b200.modelfile) or the tr
 reference (copied next to the reference files so that they travel to the GPU box).  Everything goes to
 oracle/_ref/gpuerror/, which is not committed.
 
-    python oracle/make_gpuerror_refs.py [--reference /root/reference]
+    python oracle/make_gpuerror_refs.py [--reference <directory of the reference checkout>]
 """
 import argparse
 import json

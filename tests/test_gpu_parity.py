@@ -131,7 +131,7 @@ def test_transformer_blocks_with_masks(prec, tol, oracle):
 
 @pytest.mark.parametrize("prec", [capi.PRECISION_FP32, capi.PRECISION_FP16])
 def test_transformer_net_vs_oracle(prec, oracle):
-    """BASELINE configs[3] architecture (conv stem to d=384, pre-norm attention + SwiGLU layers of 6 heads x 64, FFN 1024,
+    """The transformer benchmark configuration's architecture (conv stem to d=384, pre-norm attention + SwiGLU layers of 6 heads x 64, FFN 1024,
     RMSNorm+SiLU tip, standard heads) with 3 layers, and a small net with fixed RoPE; mixed board sizes and symmetries."""
     for model_tree, n in [(mf.make_transformer(layers=3), 4), (mf.make_transformer(seed=9, layers=2, d=64, heads=2, head_dim=32, ffn=96, rope="fixed"), 5),
                           (mf.make_transformer(seed=11, layers=2, rope="none", rel_bias=True), 4)]:
@@ -197,7 +197,7 @@ def test_nbt_reduced_precision_matches_golden(name, prec, oracle):
 @pytest.mark.parametrize("name", ["transformer_rope_2layers", "transformer_relbias_2layers"])
 @pytest.mark.parametrize("prec", [capi.PRECISION_FP32, capi.PRECISION_FP16])
 def test_transformer_matches_golden(name, prec, oracle):
-    """BASELINE configs[3] architecture at 2 layers: RoPE (what the reference's files can carry) and the learned
+    """The transformer benchmark configuration's architecture at 2 layers: RoPE (what the reference's files can carry) and the learned
     relative-position bias (blob extension), CUDA-core path in fp32 and tcgen05 path in fp16."""
     got, ref, mask = _run_case(name, prec, oracle)
     if prec == capi.PRECISION_FP32:
@@ -226,7 +226,7 @@ def _fp16_conv_weights(tree):
 
 
 def test_full_b18c384nbt_fp16_mixed_boards_vs_oracle(oracle):
-    """BASELINE configs[1] and [4] at a batch the oracle finishes in seconds: full 18-block net, boards of
+    """The headline and mixed-board benchmark configurations at a batch the oracle finishes in seconds: full 18-block net, boards of
     9/13/19 in ratio 1:1:2, random symmetries, 64 boards so that a 99th percentile means something.
 
     Two comparisons.  (1) Against the oracle run on the weights the device actually holds (convolution weights rounded
@@ -271,7 +271,7 @@ def test_batch_size_independence_and_any_n():
 
 
 def test_large_batch_properties():
-    """BASELINE configs[1] size (batch 256): size-independent properties instead of an oracle run --
+    """The headline benchmark size (batch 256): size-independent properties instead of an oracle run --
     duplicated positions give identical rows, and a symmetry applied to the input permutes policy/ownership."""
     n = 256
     model = capi.Model(mf.to_blob(mf.make_b18c384nbt(num_blocks=4)))

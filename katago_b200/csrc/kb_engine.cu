@@ -630,6 +630,7 @@ Engine::Engine(const Model& m, int device, int maxBatch, int X, int Y, int preci
   device_ = pickDevice(device);
   dt_ = precision; X_ = X; Y_ = Y; maxBatch_ = maxBatch;
   forceSimt_ = getenv("KB_FORCE_SIMT") != nullptr && atoi(getenv("KB_FORCE_SIMT")) != 0;
+  graphsEnabled_ = getenv("KB_NO_GRAPH") == nullptr;
   chunkBoards_ = 0;  // measured on B200: 128-board chunks 9.5 ms vs 8.1 ms for the whole batch of 256 (per-launch overhead wins)
   if(const char* e = getenv("KB_CHUNK_BOARDS")) chunkBoards_ = atoi(e);
   cudaCheck(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate");
@@ -733,6 +734,7 @@ Engine::~Engine() {
   for(cudaEvent_t e : events_) cudaEventDestroy(e);
   for(ConvTcPlan* p : tcPlans_) convTcDestroy(p);
   for(AttnTcPlan* p : attnPlans_) attentionTcDestroy(p);
+  for(auto& kv : graphs_) if(kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
   for(void* p : allocations_) cudaFree(p);
   if(statusHost_) cudaFreeHost(statusHost_);
   if(flushBuf_) cudaFree(flushBuf_);
@@ -749,13 +751,7 @@ void Engine::sync() {
   }
 }
 
-void Engine::runOps(int n) {
-  if(n < 1 || n > maxBatch_) throw std::runtime_error("batch size out of range for this handle");
-  if(profiling_ && events_.size() < 2 * ops_.size()) {
-    size_t old = events_.size();
-    events_.resize(2 * ops_.size());
-    for(size_t i = old; i < events_.size(); i++) cudaCheck(cudaEventCreate(&events_[i]), "cudaEventCreate");
-  }
+void Engine::launchOpsEager(int n) {
   // Optionally (KB_CHUNK_BOARDS) the batch runs through the launch list in chunks of boards that reuse the same
   // activation buffers, so that tensors handed from kernel to kernel stay in the 126 MB L2.
   const int chunk = (chunkBoards_ > 0 && layerN_ == 0) ? chunkBoards_ : n;
@@ -783,6 +779,47 @@ void Engine::runOps(int n) {
     }
   }
   boardOffset_ = 0;
+}
+
+void Engine::runOps(int n) {
+  if(n < 1 || n > maxBatch_) throw std::runtime_error("batch size out of range for this handle");
+  if(profiling_ && events_.size() < 2 * ops_.size()) {
+    size_t old = events_.size();
+    events_.resize(2 * ops_.size());
+    for(size_t i = old; i < events_.size(); i++) cudaCheck(cudaEventCreate(&events_[i]), "cudaEventCreate");
+  }
+  // Whole-network runs replay a CUDA graph of the launch list from the second run of a batch size on: the kernels'
+  // arguments depend only on the batch size and on whether symmetries were uploaded.
+  const bool graphable = graphsEnabled_ && !profiling_ && layerN_ == 0 && chunkBoards_ == 0;
+  bool done = false;
+  if(graphable) {
+    GraphEntry& ge = graphs_[n * 2 + (haveSym_ ? 1 : 0)];
+    if(ge.exec) {
+      cudaCheck(cudaGraphLaunch(ge.exec, stream_), "cudaGraphLaunch");
+      done = true;
+    }
+    else if(++ge.uses >= 2 && graphs_.size() <= 128) {
+      cudaGraph_t graph = nullptr;
+      bool ok = cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+      if(ok) {
+        try { launchOpsEager(n); }
+        catch(...) { ok = false; }
+        if(cudaStreamEndCapture(stream_, &graph) != cudaSuccess) ok = false;
+      }
+      if(ok && graph && cudaGraphInstantiate(&ge.exec, graph, 0) == cudaSuccess) {
+        cudaCheck(cudaGraphLaunch(ge.exec, stream_), "cudaGraphLaunch");
+        done = true;
+      }
+      else {
+        // capture is not possible here: stay eager for good
+        ge.exec = nullptr;
+        graphsEnabled_ = false;
+        cudaGetLastError();
+      }
+      if(graph) cudaGraphDestroy(graph);
+    }
+  }
+  if(!done) launchOpsEager(n);
   cudaCheck(cudaMemcpyAsync(statusHost_, statusWord_, sizeof(int), cudaMemcpyDeviceToHost, stream_), "status copy");
   if(profiling_) sync();
 }

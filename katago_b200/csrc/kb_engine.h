@@ -78,6 +78,13 @@ class Engine {
     const void* in = nullptr;
     int inStride = 0;
   };
+  // The launch list of one batch size, captured into a CUDA graph the second time that size is run (the first run is
+  // the eager warm-up); key = n * 2 + (symmetries given).  KB_NO_GRAPH=1 keeps every run eager.
+  struct GraphEntry { int uses = 0; cudaGraphExec_t exec = nullptr; };
+  std::map<int, GraphEntry> graphs_;
+  bool graphsEnabled_ = true;
+  void launchOpsEager(int n);
+
   // RMS norms of pre-norm transformer blocks folded into the convolutions around them: two row-sum-of-squares
   // buffers that the producers of the residual stream fill alternately; rowSumsCur_ = the one describing the current
   // stream, or -1.

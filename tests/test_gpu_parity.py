@@ -270,6 +270,31 @@ def test_batch_size_independence_and_any_n():
     h.close()
 
 
+def test_repeated_forwards_replay_the_same_results():
+    """From the second run of a batch size on, the library replays a CUDA graph of the launch list: the first (eager)
+    run, the run that captures and the replays must agree bit for bit, also after new inputs and symmetries were given."""
+    model = capi.Model(mf.to_blob(mf.make_b18c384nbt(num_blocks=2)))
+    h = capi.Handle(model, 12, precision=capi.PRECISION_FP16)
+    sp, gl = mf.random_positions(12, seed=91, board_sizes=[19, 13, 9] * 4)
+    sp2, gl2 = mf.random_positions(12, seed=92, board_sizes=[9, 19, 13] * 4)
+    syms = (np.arange(12) % 8).astype(np.int32)
+    first = h.forward(sp, gl)
+    for _ in range(3):
+        again = h.forward(sp, gl)
+        for k in first:
+            assert np.array_equal(first[k], again[k]), k
+    other_first = h.forward(sp2, gl2, syms)   # symmetries given: a different graph key, eager again
+    assert not np.array_equal(other_first["value"], first["value"])
+    for _ in range(3):
+        again = h.forward(sp2, gl2, syms)
+        for k in other_first:
+            assert np.array_equal(other_first[k], again[k]), k
+    back = h.forward(sp, gl)
+    for k in first:
+        assert np.array_equal(first[k], back[k]), k
+    h.close()
+
+
 def test_large_batch_properties():
     """The headline benchmark size (batch 256): size-independent properties instead of an oracle run --
     duplicated positions give identical rows, and a symmetry applied to the input permutes policy/ownership."""

@@ -43,6 +43,8 @@ void kb_model_destroy(kb_model* m);
 
 /* info[0..8] = modelVersion, inC, inGlobalC, policyC, valueC, scoreValueC, ownershipC, trunkC, numBlocks */
 int kb_model_info(const kb_model* m, int32_t info[9]);
+/* Number of SGF metadata input channels (ModelDesc::numInputMetaChannels, desc.h; 0 for nets without the encoder). */
+int kb_model_meta_channels(const kb_model* m, int32_t* channels);
 
 /* Replaces NeuralNet::createComputeHandle / freeComputeHandle (nninterface.h:76-86):
  * binds the calling thread to `device` (-1 = current default), uploads the weights in the
@@ -68,6 +70,13 @@ int kb_handle_precision(const kb_handle* h, int* precision);
 int kb_forward_host(
   kb_handle* h, int n, const float* spatial, const float* global, const int32_t* symmetry,
   float* policy, float* policyPass, float* value, float* scoreValue, float* ownership);
+
+/* The same for nets with an SGF metadata encoder (NNResultBuf::rowMetaBuf / hasRowMeta, nninputs.h; eigenbackend.cpp
+ * 2458-2471): meta is [n][metaChannels] fp32 and must be non-NULL exactly when the model has the encoder. */
+int kb_forward_host_meta(
+  kb_handle* h, int n, const float* spatial, const float* global, const float* meta, const int32_t* symmetry,
+  float* policy, float* policyPass, float* value, float* scoreValue, float* ownership);
+int kb_upload_inputs_meta(kb_handle* h, int n, const float* spatial, const float* global, const float* meta, const int32_t* symmetry);
 
 /* The three stages of kb_forward_host as separate calls, for measurements with the inputs
  * already resident in device memory: upload (host->device, asynchronous on the handle's stream),

@@ -16,7 +16,10 @@
  *   model       := MODEL{modelVersion,inC,inGlobalC,inMetaC,policyC,valueC,scoreValueC,ownershipC}
  *                  trunk policyhead valuehead END
  *   trunk       := TRUNK{numBlocks,trunkC,midC,regularC,gpoolC,normKind}
- *                  CONV MATMUL block*numBlocks (BN | RMSNORM)
+ *                  CONV MATMUL [inMetaC > 0: METAENC{metaEncoderVersion,inMetaC} MATMUL MATBIAS ACT MATMUL MATBIAS ACT MATMUL]
+ *                  block*numBlocks (BN | RMSNORM)
+ *                  (METAENC: the SGF metadata encoder of human-SL nets, desc.cpp:1476-1522; its output [n][trunkC] is
+ *                  added to the trunk like the global-feature bias, eigenbackend.cpp:1917-1920)
  *   block       := BLOCK_ORDINARY BN CONV BN CONV
  *                | BLOCK_GPOOL BN CONV(regular) CONV(gpool) BN(gpool) MATMUL BN(mid) CONV(final)
  *                | BLOCK_NESTED{numInner} BN CONV block*numInner BN CONV
@@ -25,7 +28,6 @@
  *                  (ATTNBIAS: optional learned relative-position bias, added to the scaled scores of query (yq,xq)
  *                  and key (yk,xk) as table[head][yk-yq+Y-1][xk-xq+X-1]; an extension of this library, the
  *                  reference's model files cannot carry it)
- *                      TRMSNORM MATMUL(q) MATMUL(k) MATMUL(v) MATMUL(out)
  *                | BLOCK_FFN{C,ffnC,useSwiGLU} TRMSNORM MATMUL(1) [MATMUL(gate)] MATMUL(2)
  *   policyhead  := POLICYHEAD{modelVersion,policyC,hasPassMlp} CONV(p1) CONV(g1) BN(g1) MATMUL(gpoolToBias)
  *                  BN(p1) CONV(p2) MATMUL(pass) [hasPassMlp: MATBIAS ACT MATMUL(pass2)]
@@ -66,6 +68,7 @@ enum {
   KB_TAG_ATTNBIAS = 17,
   KB_TAG_POLICYHEAD = 20,
   KB_TAG_VALUEHEAD = 21,
+  KB_TAG_METAENC = 22,
   KB_TAG_END = 99
 };
 

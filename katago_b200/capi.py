@@ -16,7 +16,7 @@ _lib = None
 # Every symbol include/katab200.h declares.
 EXPORTED_SYMBOLS = [
     "kb_last_error", "kb_version", "kb_device_count", "kb_device_name", "kb_model_create", "kb_model_destroy",
-    "kb_model_info", "kb_handle_create", "kb_handle_destroy", "kb_handle_precision", "kb_forward_host",
+    "kb_model_info", "kb_model_meta_channels", "kb_forward_host_meta", "kb_upload_inputs_meta", "kb_handle_create", "kb_handle_destroy", "kb_handle_precision", "kb_forward_host",
     "kb_upload_inputs", "kb_forward_resident", "kb_download_outputs", "kb_time_forward_resident", "kb_time_forward_steps",
     "kb_profile_enable", "kb_profile_reset", "kb_profile_read", "kb_launches_per_forward", "kb_debug_read_trunk",
     "kb_eval_layer", "kb_host_alloc", "kb_host_free", "kb_conv_noalloc", "kb_conv_noalloc_last_error",
@@ -54,6 +54,9 @@ def lib():
         L.kb_model_create.argtypes = [vp, sz, ctypes.POINTER(vp)]
         L.kb_model_destroy.argtypes = [vp]
         L.kb_model_info.argtypes = [vp, ctypes.POINTER(ctypes.c_int32)]
+        L.kb_model_meta_channels.argtypes = [vp, ctypes.POINTER(ctypes.c_int32)]
+        L.kb_forward_host_meta.argtypes = [vp, ci] + [vp] * 9
+        L.kb_upload_inputs_meta.argtypes = [vp, ci, vp, vp, vp, vp]
         L.kb_handle_create.argtypes = [vp, ci, ci, ci, ci, ci, ci, ctypes.POINTER(vp)]
         L.kb_handle_destroy.argtypes = [vp]
         L.kb_handle_precision.argtypes = [vp, ctypes.POINTER(ci)]
@@ -128,6 +131,9 @@ class Model:
         _check(lib().kb_model_info(self.h, info), "kb_model_info")
         (self.version, self.in_c, self.in_global_c, self.policy_c, self.value_c, self.score_c, self.own_c,
          self.trunk_c, self.num_blocks) = list(info)
+        mc = ctypes.c_int32(0)
+        _check(lib().kb_model_meta_channels(self.h, ctypes.byref(mc)), "kb_model_meta_channels")
+        self.meta_c = int(mc.value)
 
     def __del__(self):
         if getattr(self, "h", None):
@@ -157,23 +163,35 @@ class Handle:
                       scoreValue=(n, m.score_c), ownership=(n, S))
         return {k: np.empty(s, np.float32) for k, s in shapes.items()}
 
-    def forward(self, spatial: np.ndarray, glob: np.ndarray, symmetry=None, out=None):
-        """The call getOutput makes: host buffers in, host buffers out."""
+    def forward(self, spatial: np.ndarray, glob: np.ndarray, symmetry=None, out=None, meta=None):
+        """The call getOutput makes: host buffers in, host buffers out.  meta: [n][meta_c] rows for nets with an SGF
+        metadata encoder."""
         n = spatial.shape[0]
         spatial = np.ascontiguousarray(spatial, np.float32)
         glob = np.ascontiguousarray(glob, np.float32)
         sym = None if symmetry is None else np.ascontiguousarray(symmetry, np.int32)
         out = out or self._outputs(n)
+        if meta is not None:
+            meta = np.ascontiguousarray(meta, np.float32)
+            _check(lib().kb_forward_host_meta(self.h, n, _ptr(spatial), _ptr(glob), _ptr(meta), _ptr(sym), _ptr(out["policy"]),
+                                              _ptr(out["policyPass"]), _ptr(out["value"]), _ptr(out["scoreValue"]), _ptr(out["ownership"])),
+                   "kb_forward_host_meta")
+            return out
         _check(lib().kb_forward_host(self.h, n, _ptr(spatial), _ptr(glob), _ptr(sym), _ptr(out["policy"]), _ptr(out["policyPass"]),
                                      _ptr(out["value"]), _ptr(out["scoreValue"]), _ptr(out["ownership"])), "kb_forward_host")
         return out
 
-    def upload(self, spatial, glob, symmetry=None):
+    def upload(self, spatial, glob, symmetry=None, meta=None):
         n = spatial.shape[0]
         spatial = np.ascontiguousarray(spatial, np.float32)
         glob = np.ascontiguousarray(glob, np.float32)
         sym = None if symmetry is None else np.ascontiguousarray(symmetry, np.int32)
         self._keep = (spatial, glob, sym)
+        if meta is not None:
+            meta = np.ascontiguousarray(meta, np.float32)
+            self._keep = (spatial, glob, sym, meta)
+            _check(lib().kb_upload_inputs_meta(self.h, n, _ptr(spatial), _ptr(glob), _ptr(meta), _ptr(sym)), "kb_upload_inputs_meta")
+            return
         _check(lib().kb_upload_inputs(self.h, n, _ptr(spatial), _ptr(glob), _ptr(sym)), "kb_upload_inputs")
 
     def forward_resident(self, n):

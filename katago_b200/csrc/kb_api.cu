@@ -79,6 +79,10 @@ int kb_model_info(const kb_model* m, int32_t info[9]) {
   });
 }
 
+int kb_model_meta_channels(const kb_model* m, int32_t* channels) {
+  return guarded([&]() { need(m, "model"); need(channels, "channels"); *channels = m->m.inMetaC; });
+}
+
 int kb_handle_create(
   const kb_model* m, int device, int maxBatch, int nnXLen, int nnYLen, int precision, int requireExactNNLen, kb_handle** out) {
   if(out) *out = nullptr;
@@ -110,6 +114,19 @@ int kb_forward_host(
   return guarded([&]() {
     need(h, "handle");
     h->e->uploadInputs(n, spatial, global, symmetry);
+    h->e->forwardResident(n);
+    h->e->downloadOutputs(n, policy, policyPass, value, scoreValue, ownership);
+  });
+}
+int kb_upload_inputs_meta(kb_handle* h, int n, const float* spatial, const float* global, const float* meta, const int32_t* symmetry) {
+  return guarded([&]() { need(h, "handle"); h->e->uploadInputs(n, spatial, global, symmetry, meta); });
+}
+int kb_forward_host_meta(
+  kb_handle* h, int n, const float* spatial, const float* global, const float* meta, const int32_t* symmetry,
+  float* policy, float* policyPass, float* value, float* scoreValue, float* ownership) {
+  return guarded([&]() {
+    need(h, "handle");
+    h->e->uploadInputs(n, spatial, global, symmetry, meta);
     h->e->forwardResident(n);
     h->e->downloadOutputs(n, policy, policyPass, value, scoreValue, ownership);
   });

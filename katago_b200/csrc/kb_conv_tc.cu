@@ -236,6 +236,10 @@ __device__ __forceinline__ void epilogueTile(
   }
 }
 
+#ifndef KB_TC_ACT_GROUP
+#define KB_TC_ACT_GROUP 16
+#endif
+constexpr int TC_ACT_GROUP = KB_TC_ACT_GROUP;   // values per activation stage: independent chains covering the special-function latency
 constexpr int TC_UNIT_BYTES = 32 * 64;        // one staging unit: 32 rows x 32 channels (64 B rows, 64-byte swizzle)
 constexpr int TC_MAX_RING = (8 + TC_EPI_CG - 1) / TC_EPI_CG + 1;  // BN <= 256 -> 8 units over the warps of a quarter, plus one
 
@@ -368,20 +372,21 @@ __device__ __forceinline__ bool epilogueTileTma(
       const int ca = c - ep.actC0;
       const float4* sp = reinterpret_cast<const float4*>(sScale + ca);
       const float4* bp = reinterpret_cast<const float4*>(sBias + ca);
+      // all 32 values of the unit go through the activation stage by stage (TC_ACT_GROUP at a time)
 #pragma unroll
-      for(int hh = 0; hh < 2; hh++) {
-        float x[16];
+      for(int hh = 0; hh < 32 / TC_ACT_GROUP; hh++) {
+        float x[TC_ACT_GROUP];
 #pragma unroll
-        for(int k = 0; k < 4; k++) {
-          const float4 s4 = sp[4 * hh + k], b4 = bp[4 * hh + k];
-          x[4 * k] = fmaf(v[16 * hh + 4 * k], s4.x, b4.x);
-          x[4 * k + 1] = fmaf(v[16 * hh + 4 * k + 1], s4.y, b4.y);
-          x[4 * k + 2] = fmaf(v[16 * hh + 4 * k + 2], s4.z, b4.z);
-          x[4 * k + 3] = fmaf(v[16 * hh + 4 * k + 3], s4.w, b4.w);
+        for(int k = 0; k < TC_ACT_GROUP / 4; k++) {
+          const float4 s4 = sp[(TC_ACT_GROUP / 4) * hh + k], b4 = bp[(TC_ACT_GROUP / 4) * hh + k];
+          x[4 * k] = fmaf(v[TC_ACT_GROUP * hh + 4 * k], s4.x, b4.x);
+          x[4 * k + 1] = fmaf(v[TC_ACT_GROUP * hh + 4 * k + 1], s4.y, b4.y);
+          x[4 * k + 2] = fmaf(v[TC_ACT_GROUP * hh + 4 * k + 2], s4.z, b4.z);
+          x[4 * k + 3] = fmaf(v[TC_ACT_GROUP * hh + 4 * k + 3], s4.w, b4.w);
         }
-        actStaged<ACT, 16>(x);
+        actStaged<ACT, TC_ACT_GROUP>(x);
 #pragma unroll
-        for(int k = 0; k < 8; k++) actP[8 * hh + k] = on ? Pack2<T>::pack(x[2 * k], x[2 * k + 1]) : 0u;
+        for(int k = 0; k < TC_ACT_GROUP / 2; k++) actP[(TC_ACT_GROUP / 2) * hh + k] = on ? Pack2<T>::pack(x[2 * k], x[2 * k + 1]) : 0u;
       }
     }
     TRACE(threadIdx.x == 64, 1024 + (int)(tileIter & 31u) * 16 + j * 5 + 2);

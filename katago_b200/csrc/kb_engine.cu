@@ -648,6 +648,8 @@ Engine::Engine(const Model& m, int device, int maxBatch, int X, int Y, int preci
 
   dSpatial_ = static_cast<float*>(alloc((size_t)maxBatch * S * m.inC * sizeof(float)));
   dGlobal_ = static_cast<float*>(alloc((size_t)maxBatch * m.inGlobalC * sizeof(float)));
+  inMetaC_ = m.inMetaC;
+  if(inMetaC_ > 0) dMeta_ = static_cast<float*>(alloc((size_t)maxBatch * inMetaC_ * sizeof(float)));
   dSym_ = static_cast<int32_t*>(alloc((size_t)maxBatch * sizeof(int32_t)));
   mask_ = static_cast<float*>(alloc((size_t)rowsPadMax_ * sizeof(float)));
   maskSum_ = static_cast<float*>(alloc((size_t)maxBatch * sizeof(float)));
@@ -687,6 +689,23 @@ Engine::Engine(const Model& m, int device, int maxBatch, int X, int Y, int preci
     const int inG = m.inGlobalC, tc = m.trunkC;
     addOp("matmul small", 2.0 * inG * tc, 0.0, [=](cudaStream_t st, const Geom& g) {
       return launchMatMulSmall(st, dGlobal_ + (size_t)boardOffset_ * inG, inG, wG, tc, nullptr, KB_ACT_IDENTITY, gbias, g.n);
+    });
+  }
+  // SGF metadata encoder (eigenbackend.cpp:1801-1847, 1917-1920): a three-layer MLP on the metadata rows whose output is
+  // added to the per-board bias
+  if(m.inMetaC > 0) {
+    const int inM = m.inMetaC, h1 = m.metaMul1.outC, h2 = m.metaMul2.outC, tc = m.trunkC, a1 = m.metaAct1, a2 = m.metaAct2;
+    float* w1 = uploadF32(m.metaMul1.w); float* b1 = uploadF32(m.metaBias1.b);
+    float* w2 = uploadF32(m.metaMul2.w); float* b2 = uploadF32(m.metaBias2.b);
+    float* w3 = uploadF32(m.metaMul3.w);
+    float* t1 = static_cast<float*>(alloc((size_t)maxBatch * h1 * sizeof(float)));
+    float* t2 = static_cast<float*>(alloc((size_t)maxBatch * h2 * sizeof(float)));
+    addOp("matmul small", 2.0 * inM * h1, 0.0, [=](cudaStream_t st, const Geom& g) {
+      return launchMatMulSmall(st, dMeta_ + (size_t)boardOffset_ * inM, inM, w1, h1, b1, a1, t1, g.n);
+    });
+    addOp("matmul small", 2.0 * h1 * h2, 0.0, [=](cudaStream_t st, const Geom& g) { return launchMatMulSmall(st, t1, h1, w2, h2, b2, a2, t2, g.n); });
+    addOp("matmul small", 2.0 * h2 * tc, 0.0, [=](cudaStream_t st, const Geom& g) {
+      return launchMatMulSmall(st, t2, h2, w3, tc, nullptr, KB_ACT_IDENTITY, gbias, g.n, 1);
     });
   }
   // initial convolution + global bias, producing the stream and the first block's activated input
@@ -824,13 +843,16 @@ void Engine::runOps(int n) {
   if(profiling_) sync();
 }
 
-void Engine::uploadInputs(int n, const float* spatial, const float* global, const int32_t* symmetry) {
+void Engine::uploadInputs(int n, const float* spatial, const float* global, const int32_t* symmetry, const float* meta) {
   if(n < 1 || n > maxBatch_) throw std::runtime_error("batch size out of range for this handle");
   if(!spatial || !global) throw std::runtime_error("NULL input pointer");
+  if(inMetaC_ > 0 && !meta) throw std::runtime_error("this model has an SGF metadata encoder: metadata input rows are required");
+  if(inMetaC_ == 0 && meta) throw std::runtime_error("this model has no SGF metadata encoder: metadata input rows must be NULL");
   cudaCheck(cudaSetDevice(device_), "cudaSetDevice");
   const size_t S = (size_t)X_ * Y_;
   cudaCheck(cudaMemcpyAsync(dSpatial_, spatial, (size_t)n * S * inC_ * sizeof(float), cudaMemcpyHostToDevice, stream_), "H2D spatial");
   cudaCheck(cudaMemcpyAsync(dGlobal_, global, (size_t)n * inGlobalC_ * sizeof(float), cudaMemcpyHostToDevice, stream_), "H2D global");
+  if(meta) cudaCheck(cudaMemcpyAsync(dMeta_, meta, (size_t)n * inMetaC_ * sizeof(float), cudaMemcpyHostToDevice, stream_), "H2D metadata");
   haveSym_ = symmetry != nullptr;
   if(symmetry) {
     for(int i = 0; i < n; i++)

@@ -51,7 +51,9 @@ class Engine {
     return (int)ops_.size() * ((n + chunk - 1) / chunk);
   }
 
-  void uploadInputs(int n, const float* spatial, const float* global, const int32_t* symmetry);
+  // meta: [n][inMetaC] rows for nets with an SGF metadata encoder (must be non-NULL exactly for those nets)
+  void uploadInputs(int n, const float* spatial, const float* global, const int32_t* symmetry, const float* meta = nullptr);
+  int metaChannels() const { return inMetaC_; }
   void forwardResident(int n);
   void downloadOutputs(int n, float* policy, float* policyPass, float* value, float* scoreValue, float* ownership);
   float timeForwardResident(int n, int iters);
@@ -133,6 +135,8 @@ class Engine {
 
   // whole-network state
   int inC_ = 0, inCdev_ = 0, inGlobalC_ = 0, trunkC_ = 0, policyC_ = 0, valueC_ = 0, scoreValueC_ = 0;
+  float* dMeta_ = nullptr;
+  int inMetaC_ = 0;
   float *dSpatial_ = nullptr, *dGlobal_ = nullptr, *mask_ = nullptr, *maskSum_ = nullptr;
   int32_t* dSym_ = nullptr;
   bool haveSym_ = false;

@@ -214,7 +214,7 @@ constexpr int MM_KSPLIT = 4;  // the input channels are split over threadIdx.y s
 
 __global__ void matMulSmallKernel(
   const float* __restrict__ in, int inC, const float* __restrict__ w, int outC, const float* __restrict__ bias, int act,
-  float* __restrict__ out, int rows) {
+  float* __restrict__ out, int rows, int accumulate) {
   extern __shared__ float sIn[];  // [MM_ROWS][inC], then partial sums [MM_KSPLIT][MM_ROWS][blockDim.x]
   float* sPart = sIn + MM_ROWS * inC;
   const int r0 = blockIdx.x * MM_ROWS;
@@ -250,7 +250,11 @@ __global__ void matMulSmallKernel(
         float t = 0.0f;
 #pragma unroll
         for(int k = 0; k < MM_KSPLIT; k++) t += sPart[(k * MM_ROWS + r) * blockDim.x + threadIdx.x];
-        if(r < nr) out[(size_t)(r0 + r) * outC + oc] = applyActF(t + b, act);
+        if(r < nr) {
+          float* o = out + (size_t)(r0 + r) * outC + oc;
+          const float y = applyActF(t + b, act);
+          *o = accumulate ? *o + y : y;
+        }
       }
     }
     __syncthreads();
@@ -258,10 +262,10 @@ __global__ void matMulSmallKernel(
 }
 
 cudaError_t launchMatMulSmall(
-  cudaStream_t st, const float* in, int inC, const float* w, int outC, const float* bias, int act, float* out, int rows) {
+  cudaStream_t st, const float* in, int inC, const float* w, int outC, const float* bias, int act, float* out, int rows, int accumulate) {
   const int threads = outC >= 128 ? 128 : (outC > 32 ? 64 : 32);
   const size_t smem = (size_t)(MM_ROWS * inC + MM_KSPLIT * MM_ROWS * threads) * sizeof(float);
-  matMulSmallKernel<<<(rows + MM_ROWS - 1) / MM_ROWS, dim3(threads, MM_KSPLIT), smem, st>>>(in, inC, w, outC, bias, act, out, rows);
+  matMulSmallKernel<<<(rows + MM_ROWS - 1) / MM_ROWS, dim3(threads, MM_KSPLIT), smem, st>>>(in, inC, w, outC, bias, act, out, rows, accumulate);
   return cudaGetLastError();
 }
 

@@ -87,9 +87,10 @@ cudaError_t launchConvSimt(
   cudaStream_t st, int dt, const void* in, int inStride, int inC, const void* w, int outC, int kY, int kX,
   Geom g, const Epilogue& ep);
 
-// out[r][oc] = act(sum_ic in[r][ic]*w[ic][oc] + bias[oc]); fp32, small row counts (heads, gpool bias).
+// out[r][oc] (+)= act(sum_ic in[r][ic]*w[ic][oc] + bias[oc]); fp32, small row counts (heads, gpool bias, metadata encoder).
 cudaError_t launchMatMulSmall(
-  cudaStream_t st, const float* in, int inC, const float* w, int outC, const float* bias, int act, float* out, int rows);
+  cudaStream_t st, const float* in, int inC, const float* w, int outC, const float* bias, int act, float* out, int rows,
+  int accumulate = 0);
 
 // Masked global pooling (eigenbackend.cpp:152-197).  in: [rowsPad][inStride] (channels c0..c0+C), already
 // activated and masked.  out: [n][3*C] fp32.  valueHead selects the third statistic.

@@ -143,7 +143,7 @@ void parseModel(const void* blob, size_t nbytes, Model& m) {
   Record r = rd.expect(KB_TAG_MODEL, 8, "MODEL");
   m.modelVersion = r.ints[0]; m.inC = r.ints[1]; m.inGlobalC = r.ints[2]; m.inMetaC = r.ints[3];
   m.policyC = r.ints[4]; m.valueC = r.ints[5]; m.scoreValueC = r.ints[6]; m.ownershipC = r.ints[7];
-  if(m.inMetaC != 0) fail("models with an SGF metadata encoder are not supported");
+  if(m.inMetaC < 0 || m.inMetaC > 4096) fail("bad metadata channel count");
   r = rd.expect(KB_TAG_TRUNK, 6, "TRUNK");
   m.numBlocks = r.ints[0]; m.trunkC = r.ints[1]; m.normKind = r.ints[5];
   if(m.numBlocks < 1 || m.numBlocks > 4096) fail("bad trunk block count");
@@ -151,6 +151,17 @@ void parseModel(const void* blob, size_t nbytes, Model& m) {
   parseMatMul(rd, m.initialMatMul);
   if(m.initialConv.inC != m.inC || m.initialConv.outC != m.trunkC || m.initialMatMul.inC != m.inGlobalC || m.initialMatMul.outC != m.trunkC)
     fail("trunk initial layers do not match the declared channel counts");
+  if(m.inMetaC > 0) {
+    Record e = rd.expect(KB_TAG_METAENC, 2, "METAENC");
+    m.metaEncoderVersion = e.ints[0];
+    if(e.ints[1] != m.inMetaC) fail("metadata encoder: channel count differs from the model record");
+    parseMatMul(rd, m.metaMul1); parseMatBias(rd, m.metaBias1); m.metaAct1 = parseAct(rd);
+    parseMatMul(rd, m.metaMul2); parseMatBias(rd, m.metaBias2); m.metaAct2 = parseAct(rd);
+    parseMatMul(rd, m.metaMul3);
+    if(m.metaMul1.inC != m.inMetaC || m.metaMul1.outC != m.metaBias1.C || m.metaMul2.inC != m.metaMul1.outC ||
+       m.metaMul2.outC != m.metaBias2.C || m.metaMul3.inC != m.metaMul2.outC || m.metaMul3.outC != m.trunkC)
+      fail("metadata encoder shape mismatch");
+  }
   m.blocks.resize(m.numBlocks);
   for(int i = 0; i < m.numBlocks; i++) {
     parseBlock(rd, m.blocks[i]);

@@ -71,6 +71,10 @@ struct Model {
   int numBlocks = 0, trunkC = 0, normKind = 0;
   ConvW initialConv;
   MatMulW initialMatMul;
+  // SGF metadata encoder (only if inMetaC > 0): mul1 bias1 act1 mul2 bias2 act2 mul3 -> [n][trunkC] (eigenbackend.cpp:1801-1847)
+  int metaEncoderVersion = 0, metaAct1 = 0, metaAct2 = 0;
+  MatMulW metaMul1, metaMul2, metaMul3;
+  MatBiasW metaBias1, metaBias2;
   std::vector<BlockW> blocks;
   BNW tipBN;
   RMSNormW tipRMS;

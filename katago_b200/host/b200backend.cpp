@@ -176,10 +176,12 @@ struct InputBuffers {
   int maxBatchSize = 0;
   size_t singleInputElts = 0;
   size_t singleGlobalElts = 0;
+  size_t singleMetaElts = 0;  // 0 for nets without an SGF metadata encoder
   size_t S = 0;
   int policyC = 0, valueC = 0, scoreValueC = 0;
   float* spatial = nullptr;
   float* global = nullptr;
+  float* meta = nullptr;
   int32_t* symmetry = nullptr;
   float* policy = nullptr;
   float* policyPass = nullptr;
@@ -213,6 +215,8 @@ InputBuffers* NeuralNet::createInputBuffers(const LoadedModel* loadedModel, int 
   b->scoreValueC = m.numScoreValueChannels;
   b->spatial = b->pinned<float>(b->singleInputElts * maxBatchSize);
   b->global = b->pinned<float>(b->singleGlobalElts * maxBatchSize);
+  b->singleMetaElts = (size_t)m.numInputMetaChannels;
+  if(b->singleMetaElts > 0) b->meta = b->pinned<float>(b->singleMetaElts * maxBatchSize);
   b->symmetry = b->pinned<int32_t>((size_t)maxBatchSize);
   b->policy = b->pinned<float>(b->S * b->policyC * maxBatchSize);
   b->policyPass = b->pinned<float>((size_t)b->policyC * maxBatchSize);
@@ -240,8 +244,11 @@ void NeuralNet::getOutput(
   // ownership), so rows are copied as they are; only an NCHW row needs a transposition here.
   for(int row = 0; row < n; row++) {
     const NNResultBuf* buf = inputBufs[row];
-    if(buf->hasRowMeta)
-      throw StringError("B200 backend: SGF metadata inputs are not supported");
+    // metadata rows exactly for nets with the encoder (eigenbackend.cpp:2462-2472)
+    if((b->singleMetaElts > 0) != buf->hasRowMeta)
+      throw StringError("B200 backend: SGF metadata rows must be given exactly for models with a metadata encoder");
+    if(b->singleMetaElts > 0)
+      std::memcpy(b->meta + b->singleMetaElts * row, buf->rowMetaBuf.data(), b->singleMetaElts * sizeof(float));
     float* dst = b->spatial + b->singleInputElts * row;
     const float* src = buf->rowSpatialBuf.data();
     if(h->inputsUseNHWC) {
@@ -256,8 +263,9 @@ void NeuralNet::getOutput(
   }
 
   check(
-    kb_forward_host(h->handle, n, b->spatial, b->global, b->symmetry, b->policy, b->policyPass, b->value, b->scoreValue, b->ownership),
-    "kb_forward_host");
+    kb_forward_host_meta(
+      h->handle, n, b->spatial, b->global, b->meta, b->symmetry, b->policy, b->policyPass, b->value, b->scoreValue, b->ownership),
+    "kb_forward_host_meta");
 
   // Unpack.  Symmetry was already inverted on the device, so unpackRow is called with identity symmetry.
   NNResultBuf identity;

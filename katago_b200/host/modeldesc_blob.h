@@ -111,8 +111,6 @@ inline void writeBlocks(kbblob::Writer& w, const std::vector<std::pair<int, uniq
 }
 
 inline std::vector<uint32_t> modelDescToBlob(const ModelDesc& m) {
-  if(m.metaEncoderVersion > 0 || m.numInputMetaChannels > 0)
-    throw StringError("b200 backend: models with an SGF metadata encoder are not supported yet");
   kbblob::Writer w;
   w.record(
     KB_TAG_MODEL,
@@ -124,6 +122,14 @@ inline std::vector<uint32_t> modelDescToBlob(const ModelDesc& m) {
     {t.numBlocks, t.trunkNumChannels, t.midNumChannels, t.regularNumChannels, t.gpoolNumChannels, t.trunkNormKind});
   writeConv(w, t.initialConv);
   writeMatMul(w, t.initialMatMul);
+  if(m.numInputMetaChannels > 0) {
+    // SGF metadata encoder of human-SL nets (desc.h SGFMetadataEncoderDesc)
+    const SGFMetadataEncoderDesc& e = t.sgfMetadataEncoder;
+    w.record(KB_TAG_METAENC, {e.metaEncoderVersion, e.numInputMetaChannels});
+    writeMatMul(w, e.mul1); writeMatBias(w, e.bias1); writeAct(w, e.act1);
+    writeMatMul(w, e.mul2); writeMatBias(w, e.bias2); writeAct(w, e.act2);
+    writeMatMul(w, e.mul3);
+  }
   writeBlocks(w, t.blocks);
   if(t.trunkNormKind == TRUNK_NORM_KIND_STANDARD) {
     writeBN(w, t.trunkTipBN, t.trunkTipActivation.activation);

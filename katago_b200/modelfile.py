@@ -31,6 +31,7 @@ _ACT_CODES = {v: k for k, v in _ACT_NAMES.items()}
 TAG_MODEL, TAG_TRUNK, TAG_CONV, TAG_BN, TAG_MATMUL, TAG_MATBIAS, TAG_ACT = 1, 2, 3, 4, 5, 6, 7
 TAG_BLOCK_ORDINARY, TAG_BLOCK_GPOOL, TAG_BLOCK_NESTED, TAG_BLOCK_ATTN, TAG_BLOCK_FFN = 10, 11, 12, 13, 14
 TAG_ATTNBIAS = 17
+TAG_METAENC = 22
 TAG_RMSNORM, TAG_TRMSNORM, TAG_POLICYHEAD, TAG_VALUEHEAD, TAG_END = 15, 16, 20, 21, 99
 BLOB_MAGIC = 0x314D424B
 
@@ -229,8 +230,8 @@ def parse_model_bytes(data: bytes, binary: bool) -> Dict[str, Any]:
         for _ in range(7):
             if r.int() != 0:
                 raise ValueError("unknown/unsupported model option")
-    if m["metaEncoderVersion"] != 0:
-        raise ValueError("models with an SGF metadata encoder are not supported")
+    if m["metaEncoderVersion"] not in (0, 1):
+        raise ValueError("unsupported SGF metadata encoder version")
     t: Dict[str, Any] = dict(name=r.token())
     t["numBlocks"], t["trunkC"], t["midC"], t["regularC"], t["dilatedC"], t["gpoolC"] = (r.int() for _ in range(6))
     t["normKind"] = 0
@@ -241,6 +242,13 @@ def parse_model_bytes(data: bytes, binary: bool) -> Dict[str, Any]:
                 raise ValueError("unknown/unsupported trunk option")
     t["initialConv"] = _read_conv(r)
     t["initialMatMul"] = _read_matmul(r)
+    if m["metaEncoderVersion"] > 0:
+        # SGFMetadataEncoderDesc, desc.cpp:1476-1522
+        e: Dict[str, Any] = dict(name=r.token(), numInputMetaChannels=r.int())
+        e["mul1"] = _read_matmul(r); e["bias1"] = _read_matbias(r); e["act1"] = _read_act(r, v)
+        e["mul2"] = _read_matmul(r); e["bias2"] = _read_matbias(r); e["act2"] = _read_act(r, v)
+        e["mul3"] = _read_matmul(r)
+        t["metaEncoder"] = e
     t["blocks"] = _read_blocks(r, v, t["numBlocks"])
     if t["normKind"] == 0:
         t["tipBN"] = _read_bn(r)
@@ -388,7 +396,7 @@ def model_file_bytes(m: Dict[str, Any]) -> bytes:
         for x in m["postProcess"]:
             w.ln(repr(float(x)))
     if v >= 15:
-        w.ln(0)
+        w.ln(m.get("metaEncoderVersion", 0))
         for _ in range(7):
             w.ln(0)
     t = m["trunk"]
@@ -398,6 +406,12 @@ def model_file_bytes(m: Dict[str, Any]) -> bytes:
         for _ in range(5):
             w.ln(0)
     _write_conv(w, t["initialConv"]); _write_matmul(w, t["initialMatMul"])
+    if m.get("metaEncoderVersion", 0) > 0:
+        e = t["metaEncoder"]
+        w.ln(e["name"]); w.ln(e["numInputMetaChannels"])
+        _write_matmul(w, e["mul1"]); _write_matbias(w, e["bias1"]); _write_act(w, e["act1"], v)
+        _write_matmul(w, e["mul2"]); _write_matbias(w, e["bias2"]); _write_act(w, e["act2"], v)
+        _write_matmul(w, e["mul3"])
     _write_blocks(w, t["blocks"], v)
     if t["normKind"] == 0:
         _write_bn(w, t["tipBN"])
@@ -525,10 +539,16 @@ def to_blob(m: Dict[str, Any]) -> bytes:
     o = _Blob()
     v = m["version"]
     p, h, t = m["policyHead"], m["valueHead"], m["trunk"]
-    o.rec(TAG_MODEL, (v, m["numInputChannels"], m["numInputGlobalChannels"], 0, p["policyC"],
+    enc = t.get("metaEncoder") if m.get("metaEncoderVersion", 0) > 0 else None
+    o.rec(TAG_MODEL, (v, m["numInputChannels"], m["numInputGlobalChannels"], enc["numInputMetaChannels"] if enc else 0, p["policyC"],
                       h["v3Mul"]["outC"], h["sv3Mul"]["outC"], h["ownConv"]["outC"]))
     o.rec(TAG_TRUNK, (t["numBlocks"], t["trunkC"], t["midC"], t["regularC"], t["gpoolC"], t["normKind"]))
     _b_conv(o, t["initialConv"]); _b_matmul(o, t["initialMatMul"])
+    if enc:
+        o.rec(TAG_METAENC, (m["metaEncoderVersion"], enc["numInputMetaChannels"]))
+        _b_matmul(o, enc["mul1"]); _b_matbias(o, enc["bias1"]); o.rec(TAG_ACT, (enc["act1"]["act"],))
+        _b_matmul(o, enc["mul2"]); _b_matbias(o, enc["bias2"]); o.rec(TAG_ACT, (enc["act2"]["act"],))
+        _b_matmul(o, enc["mul3"])
     _b_blocks(o, t["blocks"])
     if t["normKind"] == 0:
         _b_bn(o, t["tipBN"], t["tipAct"]["act"])
@@ -679,6 +699,29 @@ def make_nbt(name, seed, num_blocks, trunk_c, mid_c, gpool_c, heads, gpool_every
         first = "gpool" if (i % gpool_every) == gpool_every - 1 and i != num_blocks - 1 else "plain"
         blocks.append(("nbt", [first, "plain"]))
     return make_convnet(name, seed, 15, trunk_c, blocks, heads, ACT_MISH, mid_c=mid_c, regular_c=mid_c - gpool_c, gpool_c=gpool_c)
+
+
+def add_meta_encoder(m: Dict[str, Any], seed=1500, hidden=(64, 48)) -> Dict[str, Any]:
+    """Adds an SGF metadata encoder (human-SL nets; desc.cpp:1476-1522, version 1 = 192 input channels) with random
+    weights to a model tree of version >= 15: 192 -> hidden[0] -> hidden[1] -> trunk channels."""
+    if m["version"] < 15:
+        raise ValueError("the metadata encoder needs model version >= 15")
+    g = _Gen(seed)
+    act = m["trunk"]["tipAct"]["act"]
+    c = m["trunk"]["trunkC"]
+    m["metaEncoderVersion"] = 1
+    m["trunk"]["metaEncoder"] = dict(
+        name="sgfmeta", numInputMetaChannels=192, mul1=g.matmul(192, hidden[0]), bias1=g.matbias(hidden[0]), act1=g.act(act),
+        mul2=g.matmul(hidden[0], hidden[1]), bias2=g.matbias(hidden[1]), act2=g.act(act), mul3=g.matmul(hidden[1], c))
+    return m
+
+
+def random_meta_rows(n, seed=2500, channels=192):
+    """Synthetic SGF metadata rows: a sparse 0/1 pattern plus a few fractional fields, as sgfmetadata.cpp fills them."""
+    rng = np.random.default_rng(seed)
+    rows = (rng.random((n, channels)) < 0.15).astype(np.float32)
+    rows[:, -8:] = rng.random((n, 8)).astype(np.float32)
+    return rows
 
 
 def make_b18c384nbt(seed=1001, num_blocks=18):

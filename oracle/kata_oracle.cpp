@@ -632,6 +632,9 @@ std::unique_ptr<Block> loadBlock(Reader& rd) {
 struct Trunk {
   int numBlocks = 0, trunkC = 0, normKind = 0;
   Conv initialConv; MatMul initialMatMul;
+  // SGF metadata encoder, neuralnet/eigenbackend.cpp:1801-1847 (parsed by desc.cpp:1476-1522); inMetaC == 0: absent
+  int inMetaC = 0, metaAct1 = 0, metaAct2 = 0;
+  MatMul metaMul1, metaMul2, metaMul3; MatBias metaBias1, metaBias2;
   vector<std::unique_ptr<Block>> blocks;
   BN tipBN; RMSNorm tipRMS;
   void load(Reader& rd) {
@@ -640,6 +643,16 @@ struct Trunk {
     if(numBlocks < 1) throw Fail("trunk: numBlocks must be positive");
     initialConv.load(rd); initialMatMul.load(rd);
     if(initialConv.outC != trunkC || initialMatMul.outC != trunkC) throw Fail("trunk: initial layer channel mismatch");
+    if(inMetaC > 0) {
+      Record e = rd.expect(KB_TAG_METAENC, 2, "METAENC");
+      if(e.ints[1] != inMetaC) throw Fail("metadata encoder: channel count differs from the model record");
+      metaMul1.load(rd); metaBias1.load(rd); metaAct1 = loadAct(rd);
+      metaMul2.load(rd); metaBias2.load(rd); metaAct2 = loadAct(rd);
+      metaMul3.load(rd);
+      if(metaMul1.inC != inMetaC || metaMul1.outC != metaBias1.C || metaMul2.inC != metaMul1.outC || metaMul2.outC != metaBias2.C ||
+         metaMul3.inC != metaMul2.outC || metaMul3.outC != trunkC)
+        throw Fail("metadata encoder: shape mismatch");
+    }
     for(int i = 0; i < numBlocks; i++) {
       blocks.push_back(loadBlock(rd));
       if(blocks.back()->channels() != trunkC) throw Fail("trunk: block channel mismatch");
@@ -648,12 +661,24 @@ struct Trunk {
     else if(normKind == 1) { tipRMS.load(rd); if(tipRMS.C != trunkC) throw Fail("trunk: tip RMSNorm channel mismatch"); }
     else throw Fail("trunk: unknown norm kind");
   }
-  void apply(const Ctx& cx, const float* input, const float* global, float* trunkOut) const {
+  void apply(const Ctx& cx, const float* input, const float* global, const float* meta, float* trunkOut) const {
     const size_t rows = cx.rows();
     vector<float> t(rows * trunkC), gbias((size_t)cx.n * trunkC);
     initialConv.apply(input, t.data(), cx.n, cx.X, cx.Y, false);
     initialMatMul.apply(global, gbias.data(), cx.n);
     addNCBias(t.data(), gbias.data(), cx.n, cx.S, trunkC);
+    if(inMetaC > 0) {
+      // eigenbackend.cpp:1917-1920: the encoder's output is a second per-sample bias on the trunk
+      vector<float> h1((size_t)cx.n * metaMul1.outC), h2((size_t)cx.n * metaMul2.outC);
+      metaMul1.apply(meta, h1.data(), cx.n);
+      metaBias1.apply(h1.data(), cx.n);
+      for(float& x : h1) x = applyAct(x, metaAct1);
+      metaMul2.apply(h1.data(), h2.data(), cx.n);
+      metaBias2.apply(h2.data(), cx.n);
+      for(float& x : h2) x = applyAct(x, metaAct2);
+      metaMul3.apply(h2.data(), gbias.data(), cx.n);
+      addNCBias(t.data(), gbias.data(), cx.n, cx.S, trunkC);
+    }
     for(auto& b : blocks) b->apply(cx, t.data());
     if(normKind == 0) tipBN.apply(t.data(), trunkOut, cx.mask, rows);
     else tipRMS.apply(t.data(), trunkOut, cx.mask, cx.n, cx.S);
@@ -767,7 +792,8 @@ int ko_model_create(const void* blob, size_t nbytes, int nnXLen, int nnYLen, ko_
     Record r = rd.expect(KB_TAG_MODEL, 8, "MODEL");
     m->modelVersion = r.ints[0]; m->inC = r.ints[1]; m->inGlobalC = r.ints[2]; m->inMetaC = r.ints[3];
     m->policyC = r.ints[4]; m->valueC = r.ints[5]; m->scoreValueC = r.ints[6]; m->ownershipC = r.ints[7];
-    if(m->inMetaC != 0) throw Fail("models with an SGF metadata encoder are not supported");
+    if(m->inMetaC < 0) throw Fail("model: bad metadata channel count");
+    m->trunk.inMetaC = m->inMetaC;
     m->trunk.load(rd); m->policyHead.load(rd); m->valueHead.load(rd);
     rd.expect(KB_TAG_END, 0, "END");
     if(m->trunk.initialConv.inC != m->inC || m->trunk.initialMatMul.inC != m->inGlobalC) throw Fail("model: input channel mismatch");
@@ -789,12 +815,26 @@ int ko_model_info(const ko_model* m, int32_t info[9]) {
   });
 }
 
+int ko_model_meta_channels(const ko_model* m, int32_t* channels) {
+  return guarded([&]() {
+    if(!m || !channels) throw Fail("ko_model_meta_channels: NULL argument");
+    *channels = m->inMetaC;
+  });
+}
+
 int ko_forward(
   const ko_model* m, int n, const float* spatial, const float* global,
+  float* policy, float* policyPass, float* value, float* scoreValue, float* ownership, float* trunkOut) {
+  return ko_forward_meta(m, n, spatial, global, nullptr, policy, policyPass, value, scoreValue, ownership, trunkOut);
+}
+
+int ko_forward_meta(
+  const ko_model* m, int n, const float* spatial, const float* global, const float* meta,
   float* policy, float* policyPass, float* value, float* scoreValue, float* ownership, float* trunkOut) {
   return guarded([&]() {
     if(!m || !spatial || !global) throw Fail("ko_forward: NULL argument");
     if(n < 1) throw Fail("ko_forward: batch size must be positive");
+    if((m->inMetaC > 0) != (meta != nullptr)) throw Fail("ko_forward: metadata rows must be given exactly for models with a metadata encoder");
     const int S = m->X * m->Y;
     const size_t rows = (size_t)n * S;
     // mask = input channel 0, maskSum = its per-sample sum (eigenbackend.cpp:2169-2170, 122-133)
@@ -807,7 +847,7 @@ int ko_forward(
     }
     Ctx cx{n, m->X, m->Y, S, mask.data(), maskSum.data()};
     vector<float> trunkBuf(rows * m->trunk.trunkC);
-    m->trunk.apply(cx, spatial, global, trunkBuf.data());
+    m->trunk.apply(cx, spatial, global, meta, trunkBuf.data());
     if(trunkOut) std::memcpy(trunkOut, trunkBuf.data(), trunkBuf.size() * sizeof(float));
     vector<float> pol(rows * m->policyC), pass((size_t)n * m->policyC), val((size_t)n * m->valueC), sv((size_t)n * m->scoreValueC), own(rows);
     m->policyHead.apply(cx, trunkBuf.data(), pol.data(), pass.data());

@@ -45,6 +45,15 @@ int ko_forward(
   float* policy, float* policyPass, float* value, float* scoreValue, float* ownership,
   float* trunkOut);
 
+/* The same for nets with an SGF metadata encoder (eigenbackend.cpp:2458-2471): meta [n][metaChannels], non-NULL exactly
+ * for those nets. */
+int ko_forward_meta(
+  const ko_model* m, int n, const float* spatial, const float* global, const float* meta,
+  float* policy, float* policyPass, float* value, float* scoreValue, float* ownership,
+  float* trunkOut);
+/* ModelDesc::numInputMetaChannels (0 without the encoder). */
+int ko_model_meta_channels(const ko_model* m, int32_t* channels);
+
 /* Single-layer evaluation for the reference's layer tests (nninterface.h:134-180).
  * The blob holds exactly one CONV, BN, BLOCK_ORDINARY or BLOCK_GPOOL construct.
  * in [n][Y][X][inC], mask [n][Y][X] (ignored for CONV), out [n][Y][X][outC]. */

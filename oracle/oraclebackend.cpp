@@ -40,7 +40,8 @@ struct ComputeHandle {
 struct InputBuffers {
   int maxBatchSize;
   size_t singleInputElts;
-  vector<float> spatial, global, scratch;
+  size_t metaChannels = 0;
+  vector<float> spatial, global, meta, scratch;
   vector<float> policy, policyPass, value, scoreValue, ownership;
 };
 
@@ -95,6 +96,8 @@ InputBuffers* NeuralNet::createInputBuffers(const LoadedModel* loadedModel, int 
   b->spatial.resize(b->singleInputElts * maxBatchSize);
   b->scratch.resize(b->singleInputElts);
   b->global.resize((size_t)m.numInputGlobalChannels * maxBatchSize);
+  b->metaChannels = (size_t)m.numInputMetaChannels;
+  b->meta.resize(b->metaChannels * maxBatchSize);
   b->policy.resize(S * m.numPolicyChannels * maxBatchSize);
   b->policyPass.resize((size_t)m.numPolicyChannels * maxBatchSize);
   b->value.resize((size_t)m.numValueChannels * maxBatchSize);
@@ -115,11 +118,18 @@ void NeuralNet::getOutput(
     kbhost::packRow(
       d, inputBufs[row], h->inputsUseNHWC, b->spatial.data() + b->singleInputElts * row,
       b->global.data() + (size_t)d.numGlobalFeatures * row, b->scratch.data());
+  // SGF metadata rows exactly for nets with the encoder (eigenbackend.cpp:2462-2472)
+  for(int row = 0; row < n; row++) {
+    if((b->metaChannels > 0) != inputBufs[row]->hasRowMeta)
+      throw StringError("oracle backend: SGF metadata rows must be given exactly for models with a metadata encoder");
+    if(b->metaChannels > 0)
+      std::copy(inputBufs[row]->rowMetaBuf.begin(), inputBufs[row]->rowMetaBuf.begin() + b->metaChannels, b->meta.begin() + b->metaChannels * row);
+  }
   check(
-    ko_forward(
-      h->model, n, b->spatial.data(), b->global.data(), b->policy.data(), b->policyPass.data(), b->value.data(),
-      b->scoreValue.data(), b->ownership.data(), nullptr),
-    "ko_forward");
+    ko_forward_meta(
+      h->model, n, b->spatial.data(), b->global.data(), b->metaChannels > 0 ? b->meta.data() : nullptr, b->policy.data(),
+      b->policyPass.data(), b->value.data(), b->scoreValue.data(), b->ownership.data(), nullptr),
+    "ko_forward_meta");
   for(int row = 0; row < n; row++)
     kbhost::unpackRow(
       d, inputBufs[row], outputs[row], b->policy.data() + S * d.numPolicyChannels * row,

@@ -32,6 +32,8 @@ def lib():
         L.ko_model_destroy.argtypes = [ctypes.c_void_p]
         L.ko_model_info.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]
         L.ko_forward.argtypes = [ctypes.c_void_p, ctypes.c_int] + [ctypes.c_void_p] * 8
+        L.ko_forward_meta.argtypes = [ctypes.c_void_p, ctypes.c_int] + [ctypes.c_void_p] * 9
+        L.ko_model_meta_channels.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]
         L.ko_eval_layer.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_int, ctypes.c_int] + [ctypes.c_void_p] * 3
         _lib = L
     return _lib
@@ -62,7 +64,8 @@ class OracleModel:
             lib().ko_model_destroy(self.h)
             self.h = None
 
-    def forward(self, spatial: np.ndarray, glob: np.ndarray, want_trunk: bool = False):
+    def forward(self, spatial: np.ndarray, glob: np.ndarray, want_trunk: bool = False, meta: np.ndarray | None = None):
+        """meta: [n][metaChannels] rows, required exactly for nets with an SGF metadata encoder."""
         n = spatial.shape[0]
         S = self.nn_x * self.nn_y
         spatial = np.ascontiguousarray(spatial, np.float32).reshape(n, S, self.in_c)
@@ -72,8 +75,10 @@ class OracleModel:
             value=np.empty((n, self.value_c), np.float32), scoreValue=np.empty((n, self.score_c), np.float32),
             ownership=np.empty((n, S), np.float32))
         trunk = np.empty((n, S, self.trunk_c), np.float32) if want_trunk else None
-        _check(lib().ko_forward(self.h, n, _ptr(spatial), _ptr(glob), _ptr(out["policy"]), _ptr(out["policyPass"]),
-                                _ptr(out["value"]), _ptr(out["scoreValue"]), _ptr(out["ownership"]), _ptr(trunk)), "ko_forward")
+        if meta is not None:
+            meta = np.ascontiguousarray(meta, np.float32)
+        _check(lib().ko_forward_meta(self.h, n, _ptr(spatial), _ptr(glob), _ptr(meta), _ptr(out["policy"]), _ptr(out["policyPass"]),
+                                     _ptr(out["value"]), _ptr(out["scoreValue"]), _ptr(out["ownership"]), _ptr(trunk)), "ko_forward_meta")
         if want_trunk:
             out["trunk"] = trunk
         return out

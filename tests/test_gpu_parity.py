@@ -256,6 +256,31 @@ def test_full_b18c384nbt_fp16_mixed_boards_vs_oracle(oracle):
     assert np.percentile(m["policy_kl"], 99) <= 1e-3, m["policy_kl"]
 
 
+@pytest.mark.parametrize("prec", [capi.PRECISION_FP32, capi.PRECISION_FP16])
+def test_sgf_metadata_encoder_net_vs_oracle(prec, oracle):
+    """Nets with an SGF metadata encoder (human-SL nets, eigenbackend.cpp:1801-1847, 1917-1920): the encoder's MLP output is
+    a second per-board bias on the trunk; metadata rows are required exactly for such nets."""
+    tree = mf.add_meta_encoder(mf.make_b18c384nbt(seed=41, num_blocks=2))
+    blob = mf.to_blob(tree)
+    n = 6
+    sp, gl = mf.random_positions(n, seed=2010, board_sizes=[19, 13, 9, 19, 19, 13])
+    meta = mf.random_meta_rows(n, seed=2011)
+    syms = (np.arange(n) * 3 % 8).astype(np.int32)
+    model = capi.Model(blob)
+    assert model.meta_c == 192
+    h = capi.Handle(model, n, precision=prec)
+    got = h.forward(sp, gl, syms, meta=meta)
+    with pytest.raises(capi.KBError):
+        h.forward(sp, gl, syms)
+    h.close()
+    ref = unsymmetrise_outputs(oracle.OracleModel(blob).forward(symmetrise_inputs(sp, syms), gl, meta=meta), syms)
+    mask = sp[..., 0].reshape(n, -1)
+    if prec == capi.PRECISION_FP32:
+        _assert_fp32_close(got, ref, mask)
+    else:
+        _assert_reduced_close(got, ref, mask)
+
+
 def test_batch_size_independence_and_any_n():
     """getOutput may be called with any 1 <= n <= maxBatch (nninterface.h:102-123); results of a row must not
     depend on the batch it travels in (the reference's runnnbatchingtest property)."""

@@ -74,3 +74,45 @@ def test_python_reader_agrees_with_reference_loader(name, oracle, tmp_path):
     oa, ob = a.forward(sp, gl), b.forward(sp, gl)
     for k in oa:
         assert np.abs(oa[k] - ob[k]).max() <= 1e-4 * max(1.0, np.abs(oa[k]).max()), k
+
+
+def _meta_model():
+    return mf.add_meta_encoder(mf.make_b18c384nbt(seed=31, num_blocks=2))
+
+
+def test_meta_encoder_roundtrip_and_oracle(oracle):
+    """SGF metadata encoder (human-SL nets): writer -> reader round trip is bit exact, the blob carries the encoder,
+    and the oracle requires metadata rows exactly for such nets."""
+    m = _meta_model()
+    raw = mf.model_file_bytes(m)
+    m2 = mf.parse_model_bytes(raw, True)
+    assert mf.to_blob(m) == mf.to_blob(m2)
+    om = oracle.OracleModel(mf.to_blob(m))
+    sp, gl = mf.random_positions(3, seed=5)
+    meta = mf.random_meta_rows(3)
+    a = om.forward(sp, gl, meta=meta)
+    b = om.forward(sp, gl, meta=np.zeros_like(meta))
+    assert np.abs(a["value"] - b["value"]).max() > 1e-4   # the rows reach the trunk
+    with pytest.raises(Exception):
+        om.forward(sp, gl)
+    plain = oracle.OracleModel(mf.to_blob(mf.make_b18c384nbt(seed=31, num_blocks=2)))
+    with pytest.raises(Exception):
+        plain.forward(sp, gl, meta=meta)
+
+
+@pytest.mark.skipif(not os.path.exists(REF_TOOL), reason="needs oracle/_ref")
+def test_reference_loader_accepts_generated_meta_encoder_file(oracle, tmp_path):
+    """A generated model file with a metadata encoder goes through the reference's own ModelDesc loader and the
+    backend's ModelDesc -> blob conversion, and evaluates like the blob made directly from the generator's tree."""
+    m = _meta_model()
+    path = tmp_path / "meta.bin.gz"
+    mf.save_model_file(m, str(path))
+    out = tmp_path / "ref.blob"
+    subprocess.run([REF_TOOL, str(path), str(out)], check=True, stdout=subprocess.DEVNULL)
+    a, b = oracle.OracleModel(out.read_bytes()), oracle.OracleModel(mf.to_blob(m))
+    sp, gl = mf.random_positions(2, seed=6, board_sizes=[19, 13])
+    meta = mf.random_meta_rows(2, seed=7)
+    oa, ob = a.forward(sp, gl, meta=meta), b.forward(sp, gl, meta=meta)
+    for k in oa:
+        assert np.abs(oa[k] - ob[k]).max() <= 1e-4 * max(1.0, np.abs(oa[k]).max()), k
+

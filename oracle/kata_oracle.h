@@ -7,7 +7,10 @@
  * Parity is pinned by running the reference's own known-answer tests against it:
  * tests/testnn.cpp (layer vectors) and tests/tinymodel.cpp (whole-net vector); the
  * recipe in oracle/Makefile links the reference's unmodified test sources with
- * oracle/oraclebackend.cpp.
+ * oracle/oraclebackend.cpp.  The transformer blocks and the SGF metadata encoder
+ * have no vector in the reference's tests: for them parity is unpinned (they follow
+ * eigenbackend.cpp line by line); the relative-position attention bias is an
+ * extension of this repository's blob and is defined here.
  *
  * All tensors are fp32, NHWC: spatial[n][y][x][c].  Models arrive as the blob
  * described in include/kb_modelblob.h.  Every function returns 0 on success and

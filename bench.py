@@ -309,6 +309,11 @@ def run_b200(args, rank, world, local, pg):
             "sample": f"{cpu['calls']} calls of 8 positions of the same net and position scheme (oracle/kata_oracle.cpp, OpenMP, fp32)"},
         "kernels": [{"name": p["name"], "launches": p["launches"], "ms": round(p["ms"], 4), "share": round(p["ms"] / total_ms, 4)}
                     for p in sorted(prof, key=lambda p: -p["ms"])[:8] if p["launches"]],
+        # bandwidth-bound classes: algorithmic bytes (each tensor read or written once) over the measured time, against
+        # the measured copy bandwidth
+        "hbm_kernels": [{"name": p["name"], "launches": p["launches"], "gb_per_s": round(p["bytes"] / (p["ms"] * 1e-3) / 1e9, 1),
+                         "frac_of_copy_peak": round(p["bytes"] / (p["ms"] * 1e-3) / 1e9 / peaks["hbm"], 3), "us_per_launch": round(p["ms"] / p["launches"] * 1e3, 2)}
+                        for p in sorted(prof, key=lambda p: -p["ms"]) if p["launches"] and p["ms"] > 0 and p["bytes"] > 0 and "conv" not in p["name"] and "attention" not in p["name"]],
     }
     print(json.dumps(line), flush=True)
 

@@ -101,9 +101,53 @@ __global__ void packInputKernel(
   }
 }
 
+// Reduced-precision variant for inC <= 32 and rows of at least 32 channels: one thread per board point reads its inC
+// floats and writes 32 channels (64 bytes) with four 16-byte stores; the rest of the row stays zero from allocation.
+template <typename T>
+__global__ void __launch_bounds__(384) packInputVecKernel(
+  const float* __restrict__ spatial, const int32_t* __restrict__ symmetry, int inC, T* __restrict__ dst, int dstStride,
+  float* __restrict__ mask, float* __restrict__ maskSum, Geom g) {
+  const int n = blockIdx.x;
+  const int sym = symmetry ? symmetry[n] : 0;
+  const float* src = spatial + (size_t)n * g.S * inC;
+  float localSum = 0.0f;
+  for(int p = threadIdx.x; p < g.S; p += blockDim.x) {
+    const int h = p / g.X, w = p - h * g.X;
+    int h2, w2;
+    symMap(sym, false, g.Y, g.X, h, w, h2, w2);
+    const size_t row = (size_t)n * g.PB + (size_t)h2 * g.RW + w2;
+    float v[32];
+#pragma unroll
+    for(int c = 0; c < 32; c++) v[c] = c < inC ? src[(size_t)p * inC + c] : 0.0f;
+    uint4 o[4];
+    T* oe = reinterpret_cast<T*>(o);
+#pragma unroll
+    for(int c = 0; c < 32; c++) oe[c] = fromF<T>(v[c]);
+    uint4* d = reinterpret_cast<uint4*>(dst + row * dstStride);
+#pragma unroll
+    for(int k = 0; k < 4; k++) d[k] = o[k];
+    mask[row] = v[0];
+    localSum += v[0];
+  }
+  __shared__ float red[32];
+  for(int o = 16; o > 0; o >>= 1) localSum += __shfl_down_sync(0xffffffffu, localSum, o);
+  if((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = localSum;
+  __syncthreads();
+  if(threadIdx.x < 32) {
+    float v = (threadIdx.x < (blockDim.x + 31) / 32) ? red[threadIdx.x] : 0.0f;
+    for(int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+    if(threadIdx.x == 0) maskSum[n] = v;
+  }
+}
+
 cudaError_t launchPackInput(
   cudaStream_t st, int dt, const float* spatial, const int32_t* symmetry, int inC, void* dst, int dstStride,
   float* mask, float* maskSum, Geom g) {
+  if(dt != DT_F32 && inC <= 32 && dstStride >= 32 && (dstStride % 8) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+    if(dt == DT_F16) packInputVecKernel<__half><<<g.n, 384, 0, st>>>(spatial, symmetry, inC, (__half*)dst, dstStride, mask, maskSum, g);
+    else packInputVecKernel<__nv_bfloat16><<<g.n, 384, 0, st>>>(spatial, symmetry, inC, (__nv_bfloat16*)dst, dstStride, mask, maskSum, g);
+    return cudaGetLastError();
+  }
   KB_DISPATCH_DT(dt, (packInputKernel<T><<<g.n, 256, 0, st>>>(spatial, symmetry, inC, (T*)dst, dstStride, mask, maskSum, g)));
   return cudaGetLastError();
 }
@@ -482,9 +526,23 @@ __global__ void headFinalKernel(
   if(policy) {
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     const T* pr = pAct + row * pStride;
-    for(int c = 0; c < P1; c++) {
-      float v = toF<T>(pr[c]);
-      for(int k = 0; k < policyC && k < 4; k++) acc[k] = fmaf(v, sW[c * policyC + k], acc[k]);
+    if(sizeof(T) == 2 && (P1 % 8) == 0 && (pStride % 8) == 0 && (reinterpret_cast<uintptr_t>(pAct) & 15) == 0) {
+      // 8 channels per 16-byte load
+      for(int c8 = 0; c8 < P1; c8 += 8) {
+        const uint4 x = *reinterpret_cast<const uint4*>(pr + c8);
+        const T* xe = reinterpret_cast<const T*>(&x);
+#pragma unroll
+        for(int j = 0; j < 8; j++) {
+          const float v = toF<T>(xe[j]);
+          for(int k = 0; k < policyC && k < 4; k++) acc[k] = fmaf(v, sW[(c8 + j) * policyC + k], acc[k]);
+        }
+      }
+    }
+    else {
+      for(int c = 0; c < P1; c++) {
+        float v = toF<T>(pr[c]);
+        for(int k = 0; k < policyC && k < 4; k++) acc[k] = fmaf(v, sW[c * policyC + k], acc[k]);
+      }
     }
     for(int k = 0; k < policyC && k < 4; k++) policy[outPos * policyC + k] = acc[k];
   }
@@ -492,7 +550,17 @@ __global__ void headFinalKernel(
     float o = 0.0f;
     const T* vr = vAct + row * vStride + v0;
     const float* wo = sW + P1 * policyC;
-    for(int c = 0; c < V1; c++) o = fmaf(toF<T>(vr[c]), wo[c], o);
+    if(sizeof(T) == 2 && (V1 % 8) == 0 && (vStride % 8) == 0 && (v0 % 8) == 0 && (reinterpret_cast<uintptr_t>(vAct) & 15) == 0) {
+      for(int c8 = 0; c8 < V1; c8 += 8) {
+        const uint4 x = *reinterpret_cast<const uint4*>(vr + c8);
+        const T* xe = reinterpret_cast<const T*>(&x);
+#pragma unroll
+        for(int j = 0; j < 8; j++) o = fmaf(toF<T>(xe[j]), wo[c8 + j], o);
+      }
+    }
+    else {
+      for(int c = 0; c < V1; c++) o = fmaf(toF<T>(vr[c]), wo[c], o);
+    }
     ownership[outPos] = o;
   }
 }

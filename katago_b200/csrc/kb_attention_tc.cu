@@ -47,8 +47,11 @@ struct AttnTcArgs {
   int outStride;
   uint32_t idescS, idescO;
   float scaleLog2e;       // 1/sqrt(dq) * log2(e)
-  const float* ropeCos;   // rotary tables [tableHeads][AT_D/2][S], or NULL: Q and K are used as stored
-  const float* ropeSin;
+  // Rotary tables in factored form, or NULL (Q and K are used as stored): the angle of pair p at point (x,y) is the sum
+  // of an x part and a y part; ropeX [tableHeads][AT_D/2][X] and ropeY [tableHeads][AT_D/2][Y] hold (cos, sin) of the
+  // parts.  A head's tables are a few KB, so they stay in L1.
+  const float2* ropeX;
+  const float2* ropeY;
   int tableHeads;
   const float* relBias;   // learned relative-position bias [heads][2*relY-1][2*relX-1] (BIAS kernels only)
   int relY, relX;
@@ -72,27 +75,26 @@ template <> struct AtUnpack<__nv_bfloat16> {
 };
 
 // Rotary embedding (eigenbackend.cpp:1415-1451) applied in place to one 128-row x 64-channel tile that TMA put into
-// shared memory with the 128-byte swizzle: channel pair (2p, 2p+1) of the row at board position xy is rotated by the
-// angle whose cosine and sine are table[(tableHead * 32 + p) * S + xy].  Rows that are not board points are left
-// alone (they are masked out of the softmax, and their outputs are written as zeros).  Lanes take consecutive rows,
-// so the table reads coalesce and the 16-byte shared-memory accesses of a quarter warp fall into distinct banks.
+// shared memory with the 128-byte swizzle: channel pair (2p, 2p+1) of the row at board point (x,y) is rotated by the
+// angle ax(p,x) + ay(p,y); cosine and sine of the sum come from the tabulated cosines and sines of the two parts.
+// Rows that are not board points are left alone (they are masked out of the softmax, and their outputs are written as
+// zeros).  The 16-byte shared-memory accesses of a quarter warp fall into distinct banks.
 static_assert(AT_THREADS == 256, "ropeTileInPlace maps 256 threads onto 128 rows x 2 chunk phases");
 template <typename T>
 __device__ __forceinline__ void ropeTileInPlace(
-  uint8_t* tile, int firstRow, int tableHead, const float* __restrict__ cosT, const float* __restrict__ sinT, const Geom& g, int tid) {
-  // 256 threads: thread -> one row and every second 16-byte chunk of it (4 chunks = 16 channel pairs); all 32 table
-  // values are requested before any is used, so a tile costs one memory latency
+  uint8_t* tile, int firstRow, int tableHead, const float2* __restrict__ ropeX, const float2* __restrict__ ropeY, const Geom& g, int tid) {
+  // thread -> one row and every second 16-byte chunk of it (4 chunks = 16 channel pairs); all table values are
+  // requested before any is used
   const int row = tid & 127, c0 = tid >> 7;
   const int br = firstRow + row;  // row inside the board's padded block
   const int y = br / g.RW, x = br - y * g.RW;
   if(y >= g.Y || x >= g.X) return;
-  const int xy = y * g.X + x;
-  float cs[16], sn[16];
+  float2 ax[16], ay[16];
 #pragma unroll
   for(int kk = 0; kk < 4; kk++) {
-    const size_t t0 = ((size_t)tableHead * (AT_D / 2) + (c0 + 2 * kk) * 4) * g.S + xy;
+    const int p0 = tableHead * (AT_D / 2) + (c0 + 2 * kk) * 4;
 #pragma unroll
-    for(int k = 0; k < 4; k++) { cs[4 * kk + k] = __ldg(cosT + t0 + (size_t)k * g.S); sn[4 * kk + k] = __ldg(sinT + t0 + (size_t)k * g.S); }
+    for(int k = 0; k < 4; k++) { ax[4 * kk + k] = __ldg(ropeX + (size_t)(p0 + k) * g.X + x); ay[4 * kk + k] = __ldg(ropeY + (size_t)(p0 + k) * g.Y + y); }
   }
 #pragma unroll
   for(int kk = 0; kk < 4; kk++) {
@@ -102,8 +104,10 @@ __device__ __forceinline__ void ropeTileInPlace(
     uint32_t w[4] = {val.x, val.y, val.z, val.w};
 #pragma unroll
     for(int k = 0; k < 4; k++) {
+      const float2 a = ax[4 * kk + k], b = ay[4 * kk + k];
+      const float cs = a.x * b.x - a.y * b.y, sn = a.y * b.x + a.x * b.y;
       const float2 v = AtUnpack<T>::unpack(w[k]);
-      w[k] = AtPack<T>::pack(v.x * cs[4 * kk + k] - v.y * sn[4 * kk + k], v.x * sn[4 * kk + k] + v.y * cs[4 * kk + k]);
+      w[k] = AtPack<T>::pack(v.x * cs - v.y * sn, v.x * sn + v.y * cs);
     }
     *p = make_uint4(w[0], w[1], w[2], w[3]);
   }
@@ -189,15 +193,15 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_
   auto issueScores = [&](int qt) {
     const uint32_t ph = (uint32_t)qt & 1u;
     bool landed = true;
-    if(a.ropeCos) {
+    if(a.ropeX) {
       // every thread waits for the tiles and rotates its share; the rotated operands are made visible to the tensor core
       landed = (qt > 0 || mbarWait(smemU32(&bars[0]), 0u, abortFlag)) && mbarWait(smemU32(&bars[1]), ph, abortFlag);
       if(landed) {
         if(qt == 0) {
           const int thK = kvh * a.tableHeads / a.kvHeads;
-          for(int j = 0; j < 3; j++) ropeTileInPlace<T>(sK + j * AT_TILE_BYTES, j * 128, thK, a.ropeCos, a.ropeSin, a.g, tid);
+          for(int j = 0; j < 3; j++) ropeTileInPlace<T>(sK + j * AT_TILE_BYTES, j * 128, thK, a.ropeX, a.ropeY, a.g, tid);
         }
-        ropeTileInPlace<T>(sQ, qt * 128, h * a.tableHeads / a.heads, a.ropeCos, a.ropeSin, a.g, tid);
+        ropeTileInPlace<T>(sQ, qt * 128, h * a.tableHeads / a.heads, a.ropeX, a.ropeY, a.g, tid);
       }
       fenceProxyAsync();
       __syncthreads();
@@ -429,7 +433,7 @@ void attentionTcDestroy(AttnTcPlan* p) { delete p; }
 
 cudaError_t launchAttentionTc(
   cudaStream_t st, const AttnTcPlan* p, int qOff, int kOff, int vOff, int heads, int kvHeads, const float* mask, void* out,
-  int outStride, Geom g, int* statusWord, const float* ropeCos, const float* ropeSin, int tableHeads, const float* relBias, int relY, int relX) {
+  int outStride, Geom g, int* statusWord, const float2* ropeX, const float2* ropeY, int tableHeads, const float* relBias, int relY, int relX) {
   AttnTcArgs a;
   a.g = g; a.heads = heads; a.kvHeads = kvHeads; a.qOff = qOff; a.kOff = kOff; a.vOff = vOff;
   a.keysValid = g.Y * g.RW;
@@ -439,7 +443,7 @@ cudaError_t launchAttentionTc(
   a.idescO = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((uint32_t)(AT_D >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
   a.scaleLog2e = 1.4426950408889634f / sqrtf((float)AT_D);
   a.status = statusWord;
-  a.ropeCos = ropeCos; a.ropeSin = ropeSin; a.tableHeads = tableHeads;
+  a.ropeX = ropeX; a.ropeY = ropeY; a.tableHeads = tableHeads;
   a.relBias = relBias; a.relY = relY; a.relX = relX;
   if(relBias && ((2 * relY - 1) * (2 * relX - 1) > AT_REL_MAX || g.X > relX || g.Y > relY)) return cudaErrorInvalidValue;
   dim3 grid(g.n * heads);

@@ -199,6 +199,33 @@ static void foldGain(ConvW& c, const std::vector<float>& gamma) {
     for(int ic = 0; ic < c.inC; ic++) c.w[(size_t)oc * c.inC + ic] *= gamma[ic];
 }
 
+// The same tables in factored form for the tensor-core attention kernel: the angle of pair p at (x,y) is an x part plus a
+// y part (learnable: x*fx + y*fy; fixed theta: the first half of the pairs turns with y, the second with x), so
+// (cos, sin) of the parts, [tableHeads][pairs][X] and [tableHeads][pairs][Y] as interleaved floats, give every angle by
+// the addition theorem.
+static void ropeFactorTables(const BlockW& b, int X, int Y, std::vector<float>& tx, std::vector<float>& ty, int& tableHeads) {
+  const int pairs = b.qDim / 2;
+  tableHeads = b.learnableRope ? b.kvHeads : 1;
+  tx.assign((size_t)tableHeads * pairs * X * 2, 0.0f);
+  ty.assign((size_t)tableHeads * pairs * Y * 2, 0.0f);
+  const int pairsPerDim = pairs / 2, dimHalf = b.qDim / 2;
+  for(int h = 0; h < tableHeads; h++)
+    for(int p = 0; p < pairs; p++) {
+      float fx, fy;
+      if(b.learnableRope) { fx = b.ropeFreqs[(h * pairs + p) * 2 + 0]; fy = b.ropeFreqs[(h * pairs + p) * 2 + 1]; }
+      else if(p < pairsPerDim) { fx = 0.0f; fy = 1.0f / powf(b.ropeTheta, (float)(2 * p) / (float)dimHalf); }
+      else { fx = 1.0f / powf(b.ropeTheta, (float)(2 * (p - pairsPerDim)) / (float)dimHalf); fy = 0.0f; }
+      for(int x = 0; x < X; x++) {
+        const double a = (double)((float)x * fx);
+        tx[(((size_t)h * pairs + p) * X + x) * 2] = (float)cos(a); tx[(((size_t)h * pairs + p) * X + x) * 2 + 1] = (float)sin(a);
+      }
+      for(int y = 0; y < Y; y++) {
+        const double a = (double)((float)y * fy);
+        ty[(((size_t)h * pairs + p) * Y + y) * 2] = (float)cos(a); ty[(((size_t)h * pairs + p) * Y + y) * 2 + 1] = (float)sin(a);
+      }
+    }
+}
+
 // The merged FFN up|gate projection with its output channels interleaved in groups of 16 (16 up, their 16 gate), the
 // order the tensor-core convolution's SwiGLU epilogue expects.
 static ConvW upGateInterleaved(const MatMulW& up, const MatMulW& gate) {
@@ -407,14 +434,22 @@ void Engine::emitBlock(const BlockW& b, int C, void* raw, void* act, const BNW* 
                         (b.relBias.empty() || (2 * b.relBiasY - 1) * (2 * b.relBiasX - 1) <= KB_ATTN_TC_REL_MAX);
     float* dCos = nullptr;
     float* dSin = nullptr;
+    const float2* dRopeX = nullptr;
+    const float2* dRopeY = nullptr;
     int tableHeads = 1;
-    if(b.useRope) {
+    if(b.useRope && attnTc) {
+      // the tensor-core attention kernel rotates Q and K itself, in shared memory, from factored tables
+      std::vector<float> tx, ty;
+      ropeFactorTables(b, X_, Y_, tx, ty, tableHeads);
+      dRopeX = reinterpret_cast<const float2*>(uploadF32(tx));
+      dRopeY = reinterpret_cast<const float2*>(uploadF32(ty));
+    }
+    else if(b.useRope) {
       std::vector<float> cosT, sinT;
       ropeTables(b, X_, Y_, cosT, sinT, tableHeads);
       dCos = uploadF32(cosT);
       dSin = uploadF32(sinT);
-      // the tensor-core attention kernel rotates Q and K itself, in shared memory
-      if(!attnTc) {
+      {
         addOp("rope", 0.0, 2.0 * S * (qC + kC) * es, [=](cudaStream_t st, const Geom& g) {
           cudaError_t e = launchRope(st, dt, qkv, qkvC, 0, H, dq, dCos, dSin, tableHeads, g);
           if(e != cudaSuccess) return e;
@@ -435,7 +470,7 @@ void Engine::emitBlock(const BlockW& b, int C, void* raw, void* act, const BNW* 
       attnPlans_.push_back(ap);
       int* status = statusWord_;
       addOp(b.useRope ? "attention tcgen05 +rope" : "attention tcgen05", 2.0 * S * S * (dq + dv) * H, S * (qkvC + oC) * es, [=](cudaStream_t st, const Geom& g) {
-        return launchAttentionTc(st, ap, 0, qC, qC + kC, H, Hkv, mask, attn, oC, g, status, dCos, dSin, tableHeads, relBiasDev, relY, relX);
+        return launchAttentionTc(st, ap, 0, qC, qC + kC, H, Hkv, mask, attn, oC, g, status, dRopeX, dRopeY, tableHeads, relBiasDev, relY, relX);
       });
     }
     else {

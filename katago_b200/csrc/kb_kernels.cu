@@ -362,6 +362,7 @@ __global__ void __launch_bounds__(256) gpoolVec8Kernel(
 #pragma unroll
   for(int j = 0; j < 8; j++) { s[j] = 0.0f; mx[j] = -1.0f; }
   if(rg < groups) {
+#pragma unroll 4
     for(int p = rg; p < g.S; p += groups) {
       const int y = p / g.X, x = p - y * g.X;
       const size_t row = (size_t)n * g.PB + (size_t)y * g.RW + x;

@@ -180,11 +180,12 @@ struct AttnTcPlan;
 bool attentionTcEligible(int dt, int dq, int dv, int X, int Y, int stride, int qOff, int kOff, int vOff, int outStride);
 AttnTcPlan* attentionTcCreate(int dt, const void* qkv, int stride, int totalCols, int rowsPadMax);
 void attentionTcDestroy(AttnTcPlan* p);
-// ropeCos/ropeSin ([tableHeads][32][S], or NULL): the rotary embedding is applied to Q and K inside the kernel, so the
-// QKV matrix holds the unrotated projections.
+// ropeX/ropeY (or NULL): the rotary embedding is applied to Q and K inside the kernel, so the QKV matrix holds the
+// unrotated projections.  The angle of pair p at point (x,y) is ax(p,x) + ay(p,y); ropeX [tableHeads][32][X] and ropeY
+// [tableHeads][32][Y] hold (cos, sin) of the two parts.
 cudaError_t launchAttentionTc(
   cudaStream_t st, const AttnTcPlan* p, int qOff, int kOff, int vOff, int heads, int kvHeads, const float* mask, void* out,
-  int outStride, Geom g, int* statusWord, const float* ropeCos, const float* ropeSin, int tableHeads,
+  int outStride, Geom g, int* statusWord, const float2* ropeX, const float2* ropeY, int tableHeads,
   const float* relBias = nullptr, int relY = 0, int relX = 0);
 // relBias (or NULL): learned relative-position bias as for launchAttention; the kernel keeps one head's table in shared
 // memory, which bounds it to KB_ATTN_TC_REL_MAX entries.

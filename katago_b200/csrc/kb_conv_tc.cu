@@ -668,11 +668,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
       tcFenceAfter();
       const uint32_t acc = tmemBase + buf * (uint32_t)a.BN;
       if(TMA_EPI) {
-        const float rowScale = a.ep.rowSumsq ? (mk == 1.0f ? rsqrtf(fmaf(a.ep.rowSumsq[m], a.ep.rowInvC, a.ep.rowEps)) : 0.0f) : 1.0f;
+        float rowScale = 1.0f;
+        if(a.ep.rowSumsq) {
+          float ss = 0.0f;
+          for(int k = 0; k < a.ep.rowSumsqSlots; k++) ss += a.ep.rowSumsq[(size_t)k * a.ep.sumsqRowStride + m];
+          rowScale = mk == 1.0f ? rsqrtf(fmaf(ss, a.ep.rowInvC, a.ep.rowEps)) : 0.0f;
+        }
         float rowSumsq = 0.0f;
         const bool ok2 = epilogueTileTma<T, ACT>(a, &tmRaw, &tmAct, acc, q, cg, lane, m0, n0, mk, biasRow, es, it, abortFlag, sScale, sBias, &tmRes, tm, rowScale, rowSumsq);
-        if(a.ep.sumsqOut && es.nU > 0) atomicAdd(a.ep.sumsqOut + m, rowSumsq);
-        if(a.ep.sumsqClear && cg == 0 && n0 == 0) a.ep.sumsqClear[m] = 0.0f;
+        // this thread's partial sum of squares of row m: its own slot, a plain store (warps without units store 0)
+        if(a.ep.sumsqOut) a.ep.sumsqOut[(size_t)(tm.nTile(t) * TC_EPI_CG + cg) * a.ep.sumsqRowStride + m] = rowSumsq;
         if(!ok2) {
           if(lane == 0 && !*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, TC_ERR_EPILOGUE_TIMEOUT); }
           break;
@@ -803,6 +808,12 @@ bool convTcEligible(int dt, int inC, int outC, int kY, int kX) {
 bool convTcRowNormEligible(int dt, int inC, int outC) {
   if(!convTcEligible(dt, inC, outC, 1, 1) || (outC % 32) != 0) return false;
   return (pickBN(1, inC, outC) % 32) == 0;
+}
+
+int convTcRowSumSlots(int k, int inC, int outC) {
+  const int bn = pickBN(k, inC, outC);
+  // the staged epilogue needs whole 32-channel units
+  return (bn > 0 && (bn % 32) == 0 && (outC % 32) == 0) ? (outC / bn) * TC_EPI_CG : 0;
 }
 
 bool convTcSwigluEligible(int dt, int inC, int F) {

@@ -280,13 +280,14 @@ static void ropeTables(const BlockW& b, int X, int Y, std::vector<float>& cosT, 
 // Block graph -> launches
 
 // Called for a convolution whose raw output becomes the residual stream of a pre-norm transformer stack.
-void Engine::produceRowSums(Epilogue& ep, int inC, int outC) {
+void Engine::produceRowSums(Epilogue& ep, int k, int inC, int outC) {
   rowSumsCur_ = -1;
-  if(!rowNormFold_ || !convTcRowNormEligible(dt_, inC, outC)) return;
-  ep.sumsqOut = rowSums_[rowSumsNext_];
-  ep.sumsqClear = rowSums_[rowSumsNext_ ^ 1];
-  rowSumsCur_ = rowSumsNext_;
-  rowSumsNext_ ^= 1;
+  if(!rowNormFold_ || (k == 1 && !convTcRowNormEligible(dt_, inC, outC))) return;
+  const int slots = convTcRowSumSlots(k, inC, outC);
+  if(slots < 1 || slots > rowSumsSlotsMax_) return;
+  ep.sumsqOut = rowSums_;
+  ep.sumsqRowStride = rowsPadMax_;
+  rowSumsCur_ = slots;
 }
 
 void Engine::emitStack(const std::vector<BlockW>& blocks, int C, void* raw, void* act, const BNW* tail, int depth, bool actValid) {
@@ -420,7 +421,7 @@ void Engine::emitBlock(const BlockW& b, int C, void* raw, void* act, const BNW* 
       // the norm is folded into the projection: it reads the stream itself and scales its rows
       foldGain(qkvW, b.preLN.weight);
       ConvDev cq = makeConv({&qkvW}, raw, C, C);
-      eq.rowSumsq = rowSums_[rowSumsCur_]; eq.rowInvC = 1.0f / (float)C; eq.rowEps = eps;
+      eq.rowSumsq = rowSums_; eq.rowSumsqSlots = rowSumsCur_; eq.sumsqRowStride = rowsPadMax_; eq.rowInvC = 1.0f / (float)C; eq.rowEps = eps;
       addConvOp(cq, eq, "norm+qkv");
     }
     else {
@@ -483,7 +484,7 @@ void Engine::emitBlock(const BlockW& b, int C, void* raw, void* act, const BNW* 
     Epilogue eo;
     finishEp(eo);
     eo.resMask = 1;
-    produceRowSums(eo, oC, C);
+    produceRowSums(eo, 1, oC, C);
     addConvOp(co, eo, "attn out +res");
   }
   else if(b.kind == BLOCK_FFN) {
@@ -510,7 +511,7 @@ void Engine::emitBlock(const BlockW& b, int C, void* raw, void* act, const BNW* 
     if(foldNorm) foldGain(upW, b.preLN.weight);
     ConvDev cu = makeConv({&upW}, ffnIn, C, C);
     Epilogue eu;
-    if(foldNorm) { eu.rowSumsq = rowSums_[rowSumsCur_]; eu.rowInvC = 1.0f / (float)C; eu.rowEps = eps; }
+    if(foldNorm) { eu.rowSumsq = rowSums_; eu.rowSumsqSlots = rowSumsCur_; eu.sumsqRowStride = rowsPadMax_; eu.rowInvC = 1.0f / (float)C; eu.rowEps = eps; }
     if(fuseSwiglu) {
       // one kernel: the projection's epilogue writes silu(up) * gate; the 2F-wide intermediate never reaches memory
       if(!cu.tc) throw std::runtime_error("internal: fused SwiGLU projection is not on the tensor-core path");
@@ -527,7 +528,7 @@ void Engine::emitBlock(const BlockW& b, int C, void* raw, void* act, const BNW* 
     Epilogue ed;
     finishEp(ed);
     ed.resMask = 1;
-    produceRowSums(ed, F, C);
+    produceRowSums(ed, 1, F, C);
     addConvOp(cd, ed, "ffn down +res");
   }
   else {
@@ -701,14 +702,8 @@ Engine::Engine(const Model& m, int device, int maxBatch, int X, int Y, int preci
   // pre-norm transformer stacks on the tensor-core path: their norms are folded into the convolutions around them
   rowNormFold_ = !forceSimt_ && dt_ != DT_F32 && !isConvBlock(m.blocks[0]) && getenv("KB_NO_NORM_FOLD") == nullptr;
   if(rowNormFold_) {
-    for(int i = 0; i < 2; i++) rowSums_[i] = static_cast<float*>(alloc((size_t)rowsPadMax_ * sizeof(float)));
-    float* s0 = rowSums_[0];
-    float* s1 = rowSums_[1];
-    const size_t nb = (size_t)rowsPadMax_ * sizeof(float);
-    addOp("clear row sums", 0.0, 0.0, [=](cudaStream_t st, const Geom&) {
-      cudaError_t e = cudaMemsetAsync(s0, 0, nb, st);
-      return e != cudaSuccess ? e : cudaMemsetAsync(s1, 0, nb, st);
-    });
+    rowSumsSlotsMax_ = 32;
+    rowSums_ = static_cast<float*>(alloc((size_t)rowSumsSlotsMax_ * rowsPadMax_ * sizeof(float)));
   }
   // input packing (symmetry, mask, maskSum)
   {
@@ -755,11 +750,7 @@ Engine::Engine(const Model& m, int device, int maxBatch, int X, int Y, int preci
     }
     else if(c0.tc && c0.kY == 3) {
       // the stem feeds a pre-norm transformer block: record the row sums of the stream it creates
-      rowSumsCur_ = -1;
-      if(rowNormFold_ && (m.trunkC % 32) == 0) {
-        e.sumsqOut = rowSums_[rowSumsNext_]; e.sumsqClear = rowSums_[rowSumsNext_ ^ 1];
-        rowSumsCur_ = rowSumsNext_; rowSumsNext_ ^= 1;
-      }
+      if((m.trunkC % 32) == 0) produceRowSums(e, c0.kY, c0.inC, m.trunkC);
     }
     addConvOp(c0, e, "initial");
   }

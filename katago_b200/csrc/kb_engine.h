@@ -87,13 +87,13 @@ class Engine {
   bool graphsEnabled_ = true;
   void launchOpsEager(int n);
 
-  // RMS norms of pre-norm transformer blocks folded into the convolutions around them: two row-sum-of-squares
-  // buffers that the producers of the residual stream fill alternately; rowSumsCur_ = the one describing the current
-  // stream, or -1.
-  float* rowSums_[2] = {nullptr, nullptr};
-  int rowSumsCur_ = -1, rowSumsNext_ = 0;
+  // RMS norms of pre-norm transformer blocks folded into the convolutions around them: the producer of the residual
+  // stream leaves per-row partial sums of squares, the consuming projection turns them into its row scale.
+  float* rowSums_ = nullptr;   // [slot][rowsPadMax] partial sums of squares of the current stream's rows
+  int rowSumsSlotsMax_ = 0;
+  int rowSumsCur_ = -1;        // number of slots the current stream's producer filled, or -1: no sums available
   bool rowNormFold_ = false;
-  void produceRowSums(Epilogue& ep, int inC, int outC);
+  void produceRowSums(Epilogue& ep, int k, int inC, int outC);
 
   struct BNDev { const float* scale = nullptr; const float* bias = nullptr; int act = 0; int C = 0; };
 

@@ -62,13 +62,16 @@ struct Epilogue {
   int act = 0;
   const float* mask = nullptr;
   // Row-wise RMS normalisation folded around a convolution (pre-norm transformer blocks, eigenbackend.cpp:867-918;
-  // tensor-core convolution with the shared-memory staged epilogue only).  A producer of the residual stream adds the
-  // sum of squares of every row of its raw output into sumsqOut and clears the same rows of sumsqClear (the buffer
-  // the next producer adds into).  A consumer multiplies each accumulator row by rsqrt(rowSumsq/C + eps) (0 where the
-  // mask is 0) before anything else; with the norm's gain folded into its weights that equals conv(rmsnorm(x)).
+  // tensor-core convolution with the shared-memory staged epilogue only).  A producer of the residual stream stores
+  // partial sums of squares of every row of its raw output: sumsqOut[slot * sumsqRowStride + row], one slot per
+  // (channel tile, epilogue warp of the row quarter), each written by exactly one thread, so the result does not depend
+  // on any ordering.  A consumer adds rowSumsqSlots partials in slot order and multiplies each accumulator row by
+  // rsqrt(sum/C + eps) (0 where the mask is 0) before anything else; with the norm's gain folded into its weights that
+  // equals conv(rmsnorm(x)).  convTcRowSumSlots gives the producer's slot count.
   float* sumsqOut = nullptr;
-  float* sumsqClear = nullptr;
   const float* rowSumsq = nullptr;
+  int rowSumsqSlots = 0;
+  int sumsqRowStride = 0;
   float rowInvC = 0.0f, rowEps = 0.0f;
 };
 
@@ -129,6 +132,8 @@ struct ConvTcPlan;  // opaque: tensor maps + tile configuration for one convolut
 bool convTcEligible(int dt, int inC, int outC, int kY, int kX);
 // True if a 1x1 convolution inC -> outC takes the staged epilogue that supports sumsqOut / rowSumsq.
 bool convTcRowNormEligible(int dt, int inC, int outC);
+// Number of partial-sum slots a convolution of this shape writes per row when Epilogue::sumsqOut is set.
+int convTcRowSumSlots(int k, int inC, int outC);
 // True if the tensor-core kernel can run the merged up|gate projection (inC -> 2*F, interleaved) with the SwiGLU epilogue.
 bool convTcSwigluEligible(int dt, int inC, int F);
 // in: [rowsPadMax][inStride] activations, w: [kY*kX][outC][inC] in dtype dt (K-major per tap).

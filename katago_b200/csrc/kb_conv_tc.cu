@@ -134,7 +134,10 @@ __device__ long long g_tcTrace[2048];
 #endif
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;
-constexpr int TC_EPI_CG = 2;                   // epilogue warps per TMEM lane quarter; each takes every third 32-channel unit
+#ifndef KB_TC_EPI_CG
+#define KB_TC_EPI_CG 2
+#endif
+constexpr int TC_EPI_CG = KB_TC_EPI_CG;                   // epilogue warps per TMEM lane quarter; each takes every third 32-channel unit
 constexpr int TC_EPI_WARPS = 4 * TC_EPI_CG;
 constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS;
 

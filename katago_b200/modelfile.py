@@ -634,9 +634,14 @@ def _gen_gpool(g: _Gen, c, regular, gpool, act):
                 midBN=g.bn(regular), midAct=g.act(act), finalConv=g.conv(3, regular, c))
 
 
-def _gen_heads(g: _Gen, m, trunk_c, p1c, g1c, v1c, v2c, act, std_bias=True):
+def _gen_heads(g: _Gen, m, trunk_c, p1c, g1c, v1c, v2c, act, std_bias=True, policy_c=None):
     v = m["version"]
-    pc = 2 if v >= 12 else 1
+    # desc.cpp:1921-1934: 1 policy channel up to v11, 2 for v12-v15, 4 for v16 (q-value channels), v17 states its own
+    pc = 4 if v == 16 else (2 if v >= 12 else 1)
+    if policy_c is not None:
+        if v < 17 and policy_c != pc:
+            raise ValueError("only model version 17 chooses its number of policy channels")
+        pc = policy_c
     p = dict(name="policyhead", policyC=pc, p1Conv=g.conv(1, trunk_c, p1c), g1Conv=g.conv(1, trunk_c, g1c), g1BN=g.bn(g1c), g1Act=g.act(act),
              gpoolToBias=g.matmul(3 * g1c, p1c), p1BN=g.bn(p1c), p1Act=g.act(act), p2Conv=g.conv(1, p1c, pc))
     if v >= 15:
@@ -653,7 +658,7 @@ def _gen_heads(g: _Gen, m, trunk_c, p1c, g1c, v1c, v2c, act, std_bias=True):
 _POST = [20.0, 20.0, 20.0, 20.0, 40.0, 0.25, 150.0]  # tdScore, scoreMean, scoreStdev, lead, varTime, stValueErr, stScoreErr
 
 
-def make_convnet(name, seed, version, trunk_c, blocks, heads, act, mid_c=None, regular_c=None, gpool_c=None):
+def make_convnet(name, seed, version, trunk_c, blocks, heads, act, mid_c=None, regular_c=None, gpool_c=None, policy_c=None):
     """blocks: list of 'plain' / 'gpool' for a plain residual net, or ('nbt', [inner kinds]) entries."""
     g = _Gen(seed)
     sp, gl = num_features(version)
@@ -681,7 +686,7 @@ def make_convnet(name, seed, version, trunk_c, blocks, heads, act, mid_c=None, r
     t["tipBN"] = g.bn(trunk_c)
     t["tipAct"] = g.act(act)
     m["trunk"] = t
-    _gen_heads(g, m, trunk_c, *heads, act)
+    _gen_heads(g, m, trunk_c, *heads, act, policy_c=policy_c)
     return m
 
 

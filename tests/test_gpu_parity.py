@@ -281,6 +281,34 @@ def test_sgf_metadata_encoder_net_vs_oracle(prec, oracle):
         _assert_reduced_close(got, ref, mask)
 
 
+@pytest.mark.parametrize("version,policy_c", [(3, None), (5, None), (8, None), (10, None), (12, None), (14, None), (16, None), (17, 4)])
+def test_model_versions_and_policy_channels(version, policy_c, oracle):
+    """Head shapes by model version (desc.cpp:1921-1934, 2156-2179): 1, 2 or 4 policy channels (v16 and optionally v17
+    carry q-value channels), pass logit with or without its MLP, 1 to 6 score-value outputs, 14 or 19 global inputs."""
+    act = mf.ACT_RELU if version < 11 else mf.ACT_MISH
+    tree = mf.make_convnet("versions", 300 + version, version, 64, ["plain", "gpool", "plain"], (16, 16, 32, 48), act,
+                           mid_c=64, regular_c=48, gpool_c=16, policy_c=policy_c)
+    blob = mf.to_blob(tree)
+    om = oracle.OracleModel(blob)
+    n = 5
+    sp, gl = mf.random_positions(n, seed=2020 + version, board_sizes=[19, 13, 9, 19, 11], num_spatial=om.in_c, num_global=om.in_global_c)
+    syms = (np.arange(n) * 3 % 8).astype(np.int32)
+    ref = unsymmetrise_outputs(om.forward(symmetrise_inputs(sp, syms), gl), syms)
+    mask = sp[..., 0].reshape(n, -1)
+    for prec in (capi.PRECISION_FP32, capi.PRECISION_FP16):
+        h = capi.Handle(capi.Model(blob), n, precision=prec)
+        got = h.forward(sp, gl, syms)
+        h.close()
+        assert got["policy"].shape == ref["policy"].shape and got["scoreValue"].shape == ref["scoreValue"].shape
+        if prec == capi.PRECISION_FP32:
+            _assert_fp32_close(got, ref, mask)
+        else:
+            m = parity_metrics(got, ref, mask)
+            assert np.percentile(m["winrate"], 99) <= 0.005 and np.percentile(m["policy_kl"], 99) <= 1e-3
+            assert np.abs(got["policy"] - ref["policy"]).max() <= 0.03 * max(3.0, np.abs(ref["policy"]).max())
+            assert np.abs(got["scoreValue"] - ref["scoreValue"]).max() <= 0.03 * max(1.0, np.abs(ref["scoreValue"]).max())
+
+
 def test_batch_size_independence_and_any_n():
     """getOutput may be called with any 1 <= n <= maxBatch (nninterface.h:102-123); results of a row must not
     depend on the batch it travels in (the reference's runnnbatchingtest property)."""

@@ -309,6 +309,64 @@ def test_model_versions_and_policy_channels(version, policy_c, oracle):
             assert np.abs(got["scoreValue"] - ref["scoreValue"]).max() <= 0.03 * max(1.0, np.abs(ref["scoreValue"]).max())
 
 
+def _rect_positions(n, ylen, xlen, seed):
+    """Random positions on an ylen x xlen buffer; every second row holds a smaller board in the top-left corner."""
+    rng = np.random.default_rng(seed)
+    sp = np.zeros((n, ylen, xlen, 22), np.float32)
+    gl = (rng.random((n, 19)) < 0.5).astype(np.float32)
+    for i in range(n):
+        by, bx = (ylen, xlen) if i % 2 == 0 else (max(2, ylen - 3 - i), max(2, xlen - 2 - i))
+        stones = rng.choice(3, size=(by, bx), p=[0.6, 0.2, 0.2])
+        sp[i, :by, :bx, 0] = 1.0
+        sp[i, :by, :bx, 1] = stones == 1
+        sp[i, :by, :bx, 2] = stones == 2
+        sp[i, :by, :bx, 3:] = rng.random((by, bx, 19)) < 0.1
+    return sp, gl
+
+
+@pytest.mark.parametrize("ylen,xlen", [(21, 25), (7, 5), (2, 2), (19, 9), (30, 37)])
+def test_other_buffer_sizes(ylen, xlen, oracle):
+    """nnXLen / nnYLen other than 19x19, rectangular, tiny and larger than a standard board (the reference allows up to
+    COMPILE_MAX_BOARD_LEN = 50 per side when compiled for it): convolution halo geometry, pooling and heads."""
+    tree = mf.make_b18c384nbt(seed=51, num_blocks=2)
+    blob = mf.to_blob(tree)
+    n = 4
+    sp, gl = _rect_positions(n, ylen, xlen, seed=ylen * 100 + xlen)
+    ref = oracle.OracleModel(blob, nn_x=xlen, nn_y=ylen).forward(sp, gl)
+    mask = sp[..., 0].reshape(n, -1)
+    for prec in (capi.PRECISION_FP32, capi.PRECISION_FP16):
+        h = capi.Handle(capi.Model(blob), n, nn_x=xlen, nn_y=ylen, precision=prec)
+        got = h.forward(sp, gl)
+        h.close()
+        if prec == capi.PRECISION_FP32:
+            _assert_fp32_close(got, ref, mask)
+        else:
+            _assert_reduced_close(got, ref, mask)
+
+
+@pytest.mark.parametrize("ylen,xlen", [(13, 13), (9, 11), (19, 18), (6, 40)])
+def test_transformer_other_buffer_sizes(ylen, xlen, oracle):
+    """The attention kernel's tiling on buffers with one, two or three 128-query tiles, rectangular included, with RoPE
+    and with the relative-position bias (its table is for 19x19, so only buffers up to 19 per side can use it)."""
+    n = 3
+    sp, gl = _rect_positions(n, ylen, xlen, seed=ylen * 100 + xlen + 7)
+    mask = sp[..., 0].reshape(n, -1)
+    trees = [mf.make_transformer(seed=61, layers=2)]
+    if ylen <= 19 and xlen <= 19:
+        trees.append(mf.make_transformer_relbias(seed=62, layers=2))
+    for tree in trees:
+        blob = mf.to_blob(tree)
+        ref = oracle.OracleModel(blob, nn_x=xlen, nn_y=ylen).forward(sp, gl)
+        for prec in (capi.PRECISION_FP32, capi.PRECISION_FP16):
+            h = capi.Handle(capi.Model(blob), n, nn_x=xlen, nn_y=ylen, precision=prec)
+            got = h.forward(sp, gl)
+            h.close()
+            if prec == capi.PRECISION_FP32:
+                _assert_fp32_close(got, ref, mask)
+            else:
+                _assert_reduced_close(got, ref, mask)
+
+
 def test_batch_size_independence_and_any_n():
     """getOutput may be called with any 1 <= n <= maxBatch (nninterface.h:102-123); results of a row must not
     depend on the batch it travels in (the reference's runnnbatchingtest property)."""

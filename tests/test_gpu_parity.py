@@ -367,6 +367,35 @@ def test_transformer_other_buffer_sizes(ylen, xlen, oracle):
                 _assert_reduced_close(got, ref, mask)
 
 
+def test_two_handles_on_two_threads():
+    """The reference runs one or two server threads per GPU, each with its own handle of the same model
+    (nneval.cpp:376-401).  Two threads evaluating concurrently must get what each gets alone."""
+    import threading
+    model = capi.Model(mf.to_blob(mf.make_b18c384nbt(num_blocks=3)))
+    data = [mf.random_positions(24, seed=70 + i, board_sizes=[19, 13, 9] * 8) for i in range(2)]
+    handles = [capi.Handle(model, 24, precision=capi.PRECISION_FP16) for _ in range(2)]
+    alone = [handles[i].forward(*data[i]) for i in range(2)]
+    results, errors = [None, None], []
+
+    def work(i):
+        try:
+            for _ in range(20):
+                results[i] = handles[i].forward(*data[i])
+        except Exception as e:  # noqa: BLE001
+            errors.append(e)
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    for i in range(2):
+        for k in alone[i]:
+            assert np.array_equal(alone[i][k], results[i][k]), (i, k)
+        handles[i].close()
+
+
 def test_batch_size_independence_and_any_n():
     """getOutput may be called with any 1 <= n <= maxBatch (nninterface.h:102-123); results of a row must not
     depend on the batch it travels in (the reference's runnnbatchingtest property)."""

@@ -114,6 +114,7 @@ struct ConvTcArgs {
   int bSlotBytes;  // BN * 128
   int numA, numB;  // ring depths
   int pair;        // 1: CTA pairs (cluster of 2, cta_group::2 MMAs over 256 rows); bSlotBytes then holds half a weight tile
+  int prefillB;    // request the first weight slots before waiting for the preceding kernels
   int residentB;   // 1x1 only: all weight tiles of this CTA's channel tile stay in shared memory for the whole kernel
   uint32_t idesc;
   uint32_t tmemCols;
@@ -521,8 +522,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
         const int n0 = (tm.first % numNTiles) * a.BN;
         for(int kc = 0; kc < a.kChunks; kc++) loadB((uint32_t)kc, kc, n0);
       }
+      // Weight ring: the first tile's first slots are requested before the wait on the preceding kernels as well (the
+      // ring starts empty, so the slots need no empty-wait); the main loop below skips those loads.
+      int prefilled = 0;
+      if(!a.residentB && a.prefillB && tm.first < numTiles) {
+        const int n0 = tm.nTile(tm.first) * a.BN;
+        const int total = a.kChunks * taps;
+        prefilled = a.numB < total ? a.numB : total;
+        for(int i = 0; i < prefilled; i++) loadB((uint32_t)i, i / taps, (i % taps) * a.outC + n0);
+      }
       // everything above touched only weights; the activations belong to the kernels before this one
       gridDepWait();
+      int issuedB = 0;  // weight slots of this CTA in issue order
       for(int t = tm.first; t < numTiles && ok; t += tm.step) {
         const int m0 = tm.m0(t), n0 = tm.nTile(t) * a.BN;
         for(int kc = 0; kc < a.kChunks && ok; kc++) {
@@ -531,9 +542,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
           loadA(sa, kc, m0);
           if(++sa == (uint32_t)a.numA) { sa = 0; phA ^= 1u; }
           if(a.residentB) continue;
-          for(int tap = 0; tap < taps; tap++) {
-            if(!mbarWait(smemU32(&emptyB[sb]), phB ^ 1u, abortFlag)) { ok = false; break; }
-            loadB(sb, kc, tap * a.outC + n0);
+          for(int tap = 0; tap < taps; tap++, issuedB++) {
+            if(issuedB >= prefilled) {
+              if(!mbarWait(smemU32(&emptyB[sb]), phB ^ 1u, abortFlag)) { ok = false; break; }
+              loadB(sb, kc, tap * a.outC + n0);
+            }
             if(++sb == (uint32_t)a.numB) { sb = 0; phB ^= 1u; }
           }
         }
@@ -963,6 +976,8 @@ cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epi
   a.inC = p->inC; a.outC = p->outC; a.kY = p->kY; a.kX = p->kX;
   a.BN = p->BN; a.kChunks = p->kChunks; a.haloPad = p->haloPad; a.aRows = p->aRows;
   a.aSlotBytes = p->aSlotBytes; a.bSlotBytes = p->bSlotBytes; a.numA = p->numA; a.numB = p->numB; a.residentB = p->residentB;
+  static const bool prefillB = getenv("KB_NO_B_PREFILL") == nullptr;
+  a.prefillB = prefillB ? 1 : 0;
   a.pair = p->pair;
   a.idesc = p->idesc; a.tmemCols = p->tmemCols;
   a.status = statusWord;

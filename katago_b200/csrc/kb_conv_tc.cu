@@ -138,13 +138,17 @@ constexpr int TC_BK = 64;
 #ifndef KB_TC_EPI_CG
 #define KB_TC_EPI_CG 2
 #endif
-constexpr int TC_EPI_CG = KB_TC_EPI_CG;                   // epilogue warps per TMEM lane quarter; each takes every third 32-channel unit
-constexpr int TC_EPI_WARPS = 4 * TC_EPI_CG;
-constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS;
+// CG = epilogue warps per TMEM lane quarter (a template parameter of the kernel): the warps of a quarter take the
+// 32-channel units of a tile in turn.  TC_EPI_CG is the default; convolutions whose epilogue is the critical path and
+// whose units divide evenly run a variant with TC_EPI_CG_WIDE.
+constexpr int TC_EPI_CG = KB_TC_EPI_CG;
+constexpr int TC_EPI_CG_WIDE = 3;
+constexpr int tcEpiWarps(int cg) { return 4 * cg; }
+constexpr int tcThreads(int cg) { return 64 + 32 * 4 * cg; }
 
 enum { TC_ERR_PRODUCER_TIMEOUT = 101, TC_ERR_MMA_TIMEOUT = 102, TC_ERR_EPILOGUE_TIMEOUT = 103 };
 
-constexpr int TC_MAX_GROUPS = (16 + TC_EPI_CG - 1) / TC_EPI_CG;  // 16-column groups per warp and tile (BN <= 256)
+constexpr int tcMaxGroups(int cg) { return (16 + cg - 1) / cg; }  // 16-column groups per warp and tile (BN <= 256)
 
 // One group of 16 output channels of one row: bias, residual (already in registers), raw store, norm+activation store.
 template <typename T, int ACT>
@@ -214,7 +218,7 @@ __device__ __forceinline__ void epilogue16(
 // All 16-column groups of one tile that belong to this warp (the warps of a quarter take the groups in turn).
 // This is the path for channel ranges that the TMA epilogue cannot express (head convolutions, odd widths); it reads the
 // residual and writes the outputs with plain vector accesses.
-template <typename T, int ACT>
+template <typename T, int ACT, int CG>
 __device__ __forceinline__ void epilogueTile(
   const ConvTcArgs& a, uint32_t tmemAcc, int q, int cg, int m, int n0, float mk, const float* sScale, const float* sBias) {
   const Epilogue& ep = a.ep;
@@ -223,8 +227,8 @@ __device__ __forceinline__ void epilogueTile(
   const int groups = a.BN / 16;
   const bool hasRes = ep.residual != nullptr;
 #pragma unroll
-  for(int j = 0; j < TC_MAX_GROUPS; j++) {
-    const int gi = cg + TC_EPI_CG * j;
+  for(int j = 0; j < tcMaxGroups(CG); j++) {
+    const int gi = cg + CG * j;
     if(gi < groups) {
       uint32_t r[16];
       tmemLd16(tmemAcc + ((uint32_t)(q * 32) << 16) + (uint32_t)(gi * 16), r);
@@ -245,7 +249,7 @@ __device__ __forceinline__ void epilogueTile(
 #endif
 constexpr int TC_ACT_GROUP = KB_TC_ACT_GROUP;   // values per activation stage: independent chains covering the special-function latency
 constexpr int TC_UNIT_BYTES = 32 * 64;        // one staging unit: 32 rows x 32 channels (64 B rows, 64-byte swizzle)
-constexpr int TC_MAX_RING = (8 + TC_EPI_CG - 1) / TC_EPI_CG + 1;  // BN <= 256 -> 8 units over the warps of a quarter, plus one
+constexpr int tcMaxRing(int cg) { return (8 + cg - 1) / cg + 1; }  // BN <= 256 -> 8 units over the warps of a quarter, plus one
 
 struct EpiWarp {
   uint8_t* sR;          // ring of `ring` units: the residual lands here, the raw output leaves from here
@@ -266,6 +270,7 @@ struct TileMap {
   __device__ __forceinline__ int nTile(int t) const { return t % numNTiles; }
 };
 
+template <int CG>
 __device__ __forceinline__ void prefetchResidual(
   const CUtensorMap* tmRes, const ConvTcArgs& a, const EpiWarp& es, uint32_t seq, const TileMap& tm, int q, int cg) {
   const int tile = tm.first + (int)(seq / (uint32_t)es.nU) * tm.step;
@@ -274,7 +279,7 @@ __device__ __forceinline__ void prefetchResidual(
   const int m0 = tm.m0(tile), n0 = tm.nTile(tile) * a.BN;
   const uint32_t b = seq % (uint32_t)es.ring;
   mbarExpectTx(smemU32(&es.resFull[b]), (uint32_t)TC_UNIT_BYTES);
-  tmaLoad2d(smemU32(es.sR + (size_t)b * TC_UNIT_BYTES), tmRes, n0 + (cg + TC_EPI_CG * j) * 32, m0 + q * 32, smemU32(&es.resFull[b]));
+  tmaLoad2d(smemU32(es.sR + (size_t)b * TC_UNIT_BYTES), tmRes, n0 + (cg + CG * j) * 32, m0 + q * 32, smemU32(&es.resFull[b]));
 }
 
 // Epilogue of one tile for one warp, staged through shared memory.  A warp owns 32 rows (its TMEM lane quarter) and
@@ -283,7 +288,7 @@ __device__ __forceinline__ void prefetchResidual(
 // TMA; the activated tensor is staged in one more unit.  A unit is computed entirely in registers first; only then
 // does the warp wait for the TMA engine to have read the previous unit's stores, so that wait is normally free.  All
 // synchronisation is inside the warp, and global memory only sees whole 64-byte row segments written by the TMA engine.
-template <typename T, int ACT>
+template <typename T, int ACT, int CG>
 __device__ __forceinline__ bool epilogueTileTma(
   const ConvTcArgs& a, const CUtensorMap* tmRaw, const CUtensorMap* tmAct, uint32_t tmemAcc, int q, int cg, int lane,
   int m0, int n0, float mk, const float* biasRow, EpiWarp& es, uint32_t tileIter, volatile int* abortFlag,
@@ -293,7 +298,7 @@ __device__ __forceinline__ bool epilogueTileTma(
   const int sw = (lane >> 1) & 3;  // 64-byte swizzle: 16-byte chunk index XOR bits 1..2 of the row
   const bool on = mk == 1.0f;
   for(int j = 0; j < es.nU; j++) {
-    const int u = cg + TC_EPI_CG * j;
+    const int u = cg + CG * j;
     const uint32_t slot = es.seq % (uint32_t)es.ring;
     TRACE(threadIdx.x == 64, 1024 + (int)(tileIter & 31u) * 16 + j * 5);
     uint32_t r[32];
@@ -399,7 +404,7 @@ __device__ __forceinline__ bool epilogueTileTma(
     if(lane == 0) {
       bulkWaitRead0();
       // the slot of the unit before this one is free now: it takes the unit ring-1 ahead of this one
-      if(hasRes && es.seq > 0) prefetchResidual(tmRes, a, es, es.seq + (uint32_t)es.ring - 1u, tm, q, cg);
+      if(hasRes && es.seq > 0) prefetchResidual<CG>(tmRes, a, es, es.seq + (uint32_t)es.ring - 1u, tm, q, cg);
     }
     __syncwarp();
     TRACE(threadIdx.x == 64, 1024 + (int)(tileIter & 31u) * 16 + j * 5 + 3);
@@ -431,10 +436,12 @@ __device__ __forceinline__ bool epilogueTileTma(
 
 // One instantiation per element type, activation and epilogue kind: the epilogue is long straight-line code, and a
 // kernel that carried every variant ran measurably slower (instruction cache).
-template <typename T, int ACT, bool TMA_EPI, bool PAIR>
-__global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
+template <typename T, int ACT, bool TMA_EPI, bool PAIR, int CG>
+__global__ void __launch_bounds__(tcThreads(CG), 1) convTcKernel(
   const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmRes,
   const __grid_constant__ CUtensorMap tmRaw, const __grid_constant__ CUtensorMap tmAct, const ConvTcArgs a) {
+  constexpr int TC_EPI_WARPS = tcEpiWarps(CG);
+  constexpr int TC_MAX_RING = tcMaxRing(CG);
   extern __shared__ uint8_t smemRaw[];
   // 1024-byte alignment for the 128-byte swizzle pattern
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~(uintptr_t)1023);
@@ -647,12 +654,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
   else {
     // ---------------- Epilogue: warps 2..; TMEM lane quarter = warp % 4 ----------------
     const int q = warp & 3;
-    const int cg = (warp - 2) >> 2;  // which of the quarter's warps: takes units cg, cg + TC_EPI_CG, ...
+    const int cg = (warp - 2) >> 2;  // which of the quarter's warps: takes units cg, cg + CG, ...
     EpiWarp es;
     es.sR = smemR + (size_t)(warp - 2) * a.epiWarpBytes;
     es.sO = es.sR + (size_t)(a.epiWarpBytes - TC_UNIT_BYTES);
     es.resFull = resFull + (warp - 2) * TC_MAX_RING;
-    es.nU = (a.BN / 32 - cg + TC_EPI_CG - 1) / TC_EPI_CG;
+    es.nU = (a.BN / 32 - cg + CG - 1) / CG;
     es.ring = a.ep.residual ? a.resRing : 2;
     es.seq = 0;
     uint32_t it = 0;
@@ -669,7 +676,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
       if(TMA_EPI) {
         if(a.ep.residual && lane == 0 && it == 0 && es.nU > 0) {
           // fill the ring; afterwards every unit that drains fetches the unit ring-1 ahead of it
-          for(int k = 0; k < es.ring; k++) prefetchResidual(&tmRes, a, es, (uint32_t)k, tm, q, cg);
+          for(int k = 0; k < es.ring; k++) prefetchResidual<CG>(&tmRes, a, es, (uint32_t)k, tm, q, cg);
         }
         __syncwarp();
       }
@@ -691,15 +698,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) convTcKernel(
           rowScale = mk == 1.0f ? rsqrtf(fmaf(ss, a.ep.rowInvC, a.ep.rowEps)) : 0.0f;
         }
         float rowSumsq = 0.0f;
-        const bool ok2 = epilogueTileTma<T, ACT>(a, &tmRaw, &tmAct, acc, q, cg, lane, m0, n0, mk, biasRow, es, it, abortFlag, sScale, sBias, &tmRes, tm, rowScale, rowSumsq);
+        const bool ok2 = epilogueTileTma<T, ACT, CG>(a, &tmRaw, &tmAct, acc, q, cg, lane, m0, n0, mk, biasRow, es, it, abortFlag, sScale, sBias, &tmRes, tm, rowScale, rowSumsq);
         // this thread's partial sum of squares of row m: its own slot, a plain store (warps without units store 0)
-        if(a.ep.sumsqOut) a.ep.sumsqOut[(size_t)(tm.nTile(t) * TC_EPI_CG + cg) * a.ep.sumsqRowStride + m] = rowSumsq;
+        if(a.ep.sumsqOut) a.ep.sumsqOut[(size_t)(tm.nTile(t) * CG + cg) * a.ep.sumsqRowStride + m] = rowSumsq;
         if(!ok2) {
           if(lane == 0 && !*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, TC_ERR_EPILOGUE_TIMEOUT); }
           break;
         }
       }
-      else epilogueTile<T, ACT>(a, acc, q, cg, m, n0, mk, sScale, sBias);
+      else epilogueTile<T, ACT, CG>(a, acc, q, cg, m, n0, mk, sScale, sBias);
       // all TMEM reads of this warp are complete (tcgen05.wait::ld inside): hand the accumulator back
       tcFenceBefore();
       __syncwarp();
@@ -753,24 +760,27 @@ static EncodeTiledFn getEncodeTiled() {
 
 // Kernel variants by (element type, activation, epilogue kind).
 typedef void (*ConvTcKernelFn)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, ConvTcArgs);
-template <typename T, bool TMA_EPI, bool PAIR>
+template <typename T, bool TMA_EPI, bool PAIR, int CG>
 static ConvTcKernelFn kernelForAct(int act) {
   switch(act) {
-    case KB_ACT_RELU: return convTcKernel<T, KB_ACT_RELU, TMA_EPI, PAIR>;
-    case KB_ACT_MISH: return convTcKernel<T, KB_ACT_MISH, TMA_EPI, PAIR>;
-    case KB_ACT_SILU: return convTcKernel<T, KB_ACT_SILU, TMA_EPI, PAIR>;
-    case KB_ACT_MISH_SCALE8: return convTcKernel<T, KB_ACT_MISH_SCALE8, TMA_EPI, PAIR>;
-    case KB_ACT_SWIGLU_PAIRS: return convTcKernel<T, KB_ACT_SWIGLU_PAIRS, TMA_EPI, PAIR>;
-    default: return convTcKernel<T, KB_ACT_IDENTITY, TMA_EPI, PAIR>;
+    case KB_ACT_RELU: return convTcKernel<T, KB_ACT_RELU, TMA_EPI, PAIR, CG>;
+    case KB_ACT_MISH: return convTcKernel<T, KB_ACT_MISH, TMA_EPI, PAIR, CG>;
+    case KB_ACT_SILU: return convTcKernel<T, KB_ACT_SILU, TMA_EPI, PAIR, CG>;
+    case KB_ACT_MISH_SCALE8: return convTcKernel<T, KB_ACT_MISH_SCALE8, TMA_EPI, PAIR, CG>;
+    // the SwiGLU epilogue exists with the default warp count only
+    case KB_ACT_SWIGLU_PAIRS: return CG == TC_EPI_CG ? convTcKernel<T, KB_ACT_SWIGLU_PAIRS, TMA_EPI, PAIR, TC_EPI_CG> : nullptr;
+    default: return convTcKernel<T, KB_ACT_IDENTITY, TMA_EPI, PAIR, CG>;
   }
 }
+// The wide-epilogue variant exists for single CTAs with the staged epilogue only.
 template <typename T>
-static ConvTcKernelFn kernelForT(int act, bool tmaEpi, bool pair) {
-  if(pair) return tmaEpi ? kernelForAct<T, true, true>(act) : kernelForAct<T, false, true>(act);
-  return tmaEpi ? kernelForAct<T, true, false>(act) : kernelForAct<T, false, false>(act);
+static ConvTcKernelFn kernelForT(int act, bool tmaEpi, bool pair, int cg) {
+  if(cg != TC_EPI_CG) return (tmaEpi && !pair && cg == TC_EPI_CG_WIDE) ? kernelForAct<T, true, false, TC_EPI_CG_WIDE>(act) : nullptr;
+  if(pair) return tmaEpi ? kernelForAct<T, true, true, TC_EPI_CG>(act) : kernelForAct<T, false, true, TC_EPI_CG>(act);
+  return tmaEpi ? kernelForAct<T, true, false, TC_EPI_CG>(act) : kernelForAct<T, false, false, TC_EPI_CG>(act);
 }
-static ConvTcKernelFn kernelFor(int dt, int act, bool tmaEpi, bool pair) {
-  return dt == DT_F16 ? kernelForT<__half>(act, tmaEpi, pair) : kernelForT<__nv_bfloat16>(act, tmaEpi, pair);
+static ConvTcKernelFn kernelFor(int dt, int act, bool tmaEpi, bool pair, int cg) {
+  return dt == DT_F16 ? kernelForT<__half>(act, tmaEpi, pair, cg) : kernelForT<__nv_bfloat16>(act, tmaEpi, pair, cg);
 }
 
 struct ConvTcPlan {
@@ -778,6 +788,7 @@ struct ConvTcPlan {
   int dt, inC, outC, kY, kX, X, Y;
   int BN, kChunks, haloPad, aRows, aSlotBytes, bSlotBytes, numA, numB, residentB;
   int pair;  // CTA pairs: 256-row tiles, half a weight tile per CTA
+  int cg;    // epilogue warps per TMEM lane quarter of the kernel variant this convolution runs
   uint32_t idesc, tmemCols;
   size_t smemBytes;
   int numSMs;
@@ -896,7 +907,7 @@ ConvTcPlan* convTcCreate(
   if((inStride % 8) != 0 || (reinterpret_cast<uintptr_t>(in) & 15) != 0 || (reinterpret_cast<uintptr_t>(w) & 15) != 0) return nullptr;
   ConvTcPlan* p = new ConvTcPlan();
   p->dt = dt; p->inC = inC; p->outC = outC; p->kY = kY; p->kX = kX; p->X = X; p->Y = Y;
-  p->rowsPadMax = rowsPadMax; p->tmaEpi = 0;
+  p->rowsPadMax = rowsPadMax; p->tmaEpi = 0; p->cg = TC_EPI_CG;
   p->BN = pickBN(kY, inC, outC);
   p->kChunks = inC / TC_BK;
   const int maxShift = (kY == 3) ? (X + 1) + 1 : 0;  // RW + 1 rows up or down
@@ -934,7 +945,7 @@ void convTcDestroy(ConvTcPlan* p) { delete p; }
 // multiple of 32 channels the residual is fetched and the outputs are written by TMA through swizzled
 // shared-memory units; otherwise the epilogue threads access global memory directly.
 bool convTcSetEpilogue(ConvTcPlan* p, const Epilogue& ep) {
-  p->tmaEpi = 0;
+  p->tmaEpi = 0; p->cg = TC_EPI_CG;
   const bool force = getenv("KB_TC_NO_TMA_EPI") != nullptr && atoi(getenv("KB_TC_NO_TMA_EPI")) != 0;
   auto aligned32 = [](int c0, int c1) { return (c0 % 32) == 0 && (c1 % 32) == 0 && c1 > c0; };
   bool ok = !force && (p->BN % 32) == 0 && p->BN <= 256;
@@ -948,11 +959,20 @@ bool convTcSetEpilogue(ConvTcPlan* p, const Epilogue& ep) {
   // With a residual the ring holds it one whole tile ahead for 1x1 convolutions, whose epilogue is the critical path;
   // a 3x3 convolution hides its epilogue behind the MMAs and does better with the shared memory spent on weight slots,
   // so it looks only one unit ahead.  Without a residual two raw units alternate (none if there is no raw output).
-  const int unitsPerWarp = (p->BN / 32 + TC_EPI_CG - 1) / TC_EPI_CG;
+  // Twelve epilogue warps instead of eight where the epilogue is the critical path and the tile's units divide by
+  // three: measured on B200, 1x1 192->384 with residual runs 11 % faster, 3x3 convolutions (which hide the epilogue
+  // and lose weight slots to the staging units) 5 % slower.  KB_TC_WIDE_EPI=0 turns the variant off, =2 uses it for
+  // every 1x1 convolution that qualifies.
+  static const int wideMode = getenv("KB_TC_WIDE_EPI") ? atoi(getenv("KB_TC_WIDE_EPI")) : 1;
+  p->cg = TC_EPI_CG;
+  if(TC_EPI_CG == 2 && wideMode > 0 && p->kY == 1 && !p->pair && !needsStaged && (p->BN / 32) % TC_EPI_CG_WIDE == 0 &&
+     (ep.residual || wideMode > 1))
+    p->cg = TC_EPI_CG_WIDE;
+  const int unitsPerWarp = (p->BN / 32 + p->cg - 1) / p->cg;
   p->resRing = (p->kY == 1) ? unitsPerWarp + 1 : 2;
   const int rawUnits = ep.residual ? p->resRing : (ep.outRaw ? 2 : 0);
   p->epiWarpBytes = (rawUnits + 1) * TC_UNIT_BYTES;
-  if(!sizeRings(p, TC_EPI_WARPS * p->epiWarpBytes)) return needsStaged ? false : sizeRings(p, 0);
+  if(!sizeRings(p, tcEpiWarps(p->cg) * p->epiWarpBytes)) { p->cg = TC_EPI_CG; return needsStaged ? false : sizeRings(p, 0); }
   const uint64_t rows = (uint64_t)p->rowsPadMax;
   const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_64B;
   bool enc = true;
@@ -961,7 +981,7 @@ bool convTcSetEpilogue(ConvTcPlan* p, const Epilogue& ep) {
   if(ep.outAct && ep.act == KB_ACT_SWIGLU_PAIRS)
     enc = enc && encode2d(&p->tmAct, p->dt, ep.outAct, (uint64_t)(ep.actC1 - ep.actC0) / 2, rows, (uint64_t)ep.actStride * 2, 16, 32, CU_TENSOR_MAP_SWIZZLE_NONE);
   else if(ep.outAct) enc = enc && encode2d(&p->tmAct, p->dt, ep.outAct, (uint64_t)(ep.actC1 - ep.actC0), rows, (uint64_t)ep.actStride * 2, 32, 32, sw);
-  if(!enc) return needsStaged ? false : sizeRings(p, 0);
+  if(!enc) { p->cg = TC_EPI_CG; return needsStaged ? false : sizeRings(p, 0); }
   p->tmaEpi = 1;
   return true;
 }
@@ -1007,7 +1027,7 @@ cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epi
   // before this one in the stream; the kernel waits for that kernel before it touches any activation.
   static const bool usePdl = getenv("KB_NO_PDL") == nullptr;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(TC_THREADS); cfg.dynamicSmemBytes = p->smemBytes; cfg.stream = st;
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(tcThreads(p->cg)); cfg.dynamicSmemBytes = p->smemBytes; cfg.stream = st;
   cudaLaunchAttribute attr[2];
   int numAttrs = 0;
   if(p->pair) {
@@ -1022,7 +1042,8 @@ cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epi
   }
   cfg.attrs = attr; cfg.numAttrs = numAttrs;
   // without an activated output the activation code is irrelevant: use the identity variant
-  ConvTcKernelFn fn = kernelFor(p->dt, ep.outAct ? ep.act : KB_ACT_IDENTITY, p->tmaEpi != 0, p->pair != 0);
+  ConvTcKernelFn fn = kernelFor(p->dt, ep.outAct ? ep.act : KB_ACT_IDENTITY, p->tmaEpi != 0, p->pair != 0, p->cg);
+  if(!fn) return cudaErrorInvalidValue;
   {
     // opt in to the large dynamic shared memory once per variant and device
     static std::mutex mu;

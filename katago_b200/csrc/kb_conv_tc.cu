@@ -71,6 +71,45 @@ __device__ __forceinline__ void actStaged(float (&x)[G]) {
   }
 }
 
+// The same on pairs of values with the packed fp32 instructions of sm_100 (two IEEE operations per instruction, half
+// the issue slots; results are bit-identical to the scalar form).  The special-function calls stay scalar.
+template <int ACT, int G2>
+__device__ __forceinline__ void actStaged2(float2 (&x)[G2]) {
+  if(ACT == KB_ACT_RELU) {
+#pragma unroll
+    for(int i = 0; i < G2; i++) { x[i].x = fmaxf(x[i].x, 0.0f); x[i].y = fmaxf(x[i].y, 0.0f); }
+  }
+  else if(ACT == KB_ACT_MISH || ACT == KB_ACT_MISH_SCALE8) {
+    const float kk = (ACT == KB_ACT_MISH ? 1.0f : 8.0f) * 1.4426950408889634f;
+    const float2 kk2 = make_float2(kk, kk), two = make_float2(2.0f, 2.0f), minusTwo = make_float2(-2.0f, -2.0f);
+    float2 n[G2];
+#pragma unroll
+    for(int i = 0; i < G2; i++) n[i] = __fmul2_rn(x[i], kk2);
+#pragma unroll
+    for(int i = 0; i < G2; i++) { n[i].x = ex2Approx(n[i].x); n[i].y = ex2Approx(n[i].y); }
+#pragma unroll
+    for(int i = 0; i < G2; i++) n[i] = __ffma2_rn(n[i], __fadd2_rn(n[i], two), two);
+#pragma unroll
+    for(int i = 0; i < G2; i++) { n[i].x = rcpApprox(n[i].x); n[i].y = rcpApprox(n[i].y); }
+#pragma unroll
+    for(int i = 0; i < G2; i++) x[i] = __ffma2_rn(minusTwo, __fmul2_rn(x[i], n[i]), x[i]);
+  }
+  else if(ACT == KB_ACT_SILU) {
+    const float2 kk2 = make_float2(-1.4426950408889634f, -1.4426950408889634f), one = make_float2(1.0f, 1.0f);
+    float2 n[G2];
+#pragma unroll
+    for(int i = 0; i < G2; i++) n[i] = __fmul2_rn(x[i], kk2);
+#pragma unroll
+    for(int i = 0; i < G2; i++) { n[i].x = ex2Approx(n[i].x); n[i].y = ex2Approx(n[i].y); }
+#pragma unroll
+    for(int i = 0; i < G2; i++) n[i] = __fadd2_rn(one, n[i]);
+#pragma unroll
+    for(int i = 0; i < G2; i++) { n[i].x = rcpApprox(n[i].x); n[i].y = rcpApprox(n[i].y); }
+#pragma unroll
+    for(int i = 0; i < G2; i++) x[i] = __fmul2_rn(x[i], n[i]);
+  }
+}
+
 template <typename T> struct Pack2;
 template <> struct Pack2<__half> {
   static __device__ __forceinline__ uint32_t pack(float a, float b) {
@@ -310,37 +349,37 @@ __device__ __forceinline__ bool epilogueTileTma(
     tmemLdWait();
     TRACE(threadIdx.x == 64, 1024 + (int)(tileIter & 31u) * 16 + j * 5 + 1);
     const int c = n0 + u * 32;  // first output channel of this unit
-    float v[32];
+    // the unit's 32 values of this row as 16 pairs: the arithmetic below uses the packed fp32 instructions
+    float2 v[16];
 #pragma unroll
-    for(int k = 0; k < 32; k++) v[k] = __uint_as_float(r[k]);
+    for(int k = 0; k < 16; k++) v[k] = make_float2(__uint_as_float(r[2 * k]), __uint_as_float(r[2 * k + 1]));
     if(ep.rowSumsq) {
+      const float2 rs = make_float2(rowScale, rowScale);
 #pragma unroll
-      for(int k = 0; k < 32; k++) v[k] *= rowScale;
+      for(int k = 0; k < 16; k++) v[k] = __fmul2_rn(v[k], rs);
     }
     if(biasRow) {
       const float4* bp = reinterpret_cast<const float4*>(biasRow + c);
 #pragma unroll
       for(int k = 0; k < 8; k++) {
-        float4 b4 = bp[k];
-        v[4 * k] += b4.x; v[4 * k + 1] += b4.y; v[4 * k + 2] += b4.z; v[4 * k + 3] += b4.w;
+        const float4 b4 = bp[k];
+        v[2 * k] = __fadd2_rn(v[2 * k], make_float2(b4.x, b4.y));
+        v[2 * k + 1] = __fadd2_rn(v[2 * k + 1], make_float2(b4.z, b4.w));
       }
     }
     uint8_t* rRow = es.sR + (size_t)slot * TC_UNIT_BYTES + lane * 64;
     if(hasRes) {
       if(ep.resMask) {
+        const float2 mk2 = make_float2(mk, mk);
 #pragma unroll
-        for(int k = 0; k < 32; k++) v[k] *= mk;
+        for(int k = 0; k < 16; k++) v[k] = __fmul2_rn(v[k], mk2);
       }
 #pragma unroll
       for(int jj = 0; jj < 4; jj++) {
         const uint4 x = *reinterpret_cast<const uint4*>(rRow + ((jj ^ sw) << 4));
         const uint32_t xu[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
-        for(int k = 0; k < 4; k++) {
-          float2 f = Pack2<T>::unpack(xu[k]);
-          v[8 * jj + 2 * k] += f.x;
-          v[8 * jj + 2 * k + 1] += f.y;
-        }
+        for(int k = 0; k < 4; k++) v[4 * jj + k] = __fadd2_rn(v[4 * jj + k], Pack2<T>::unpack(xu[k]));
       }
     }
     const bool doRaw = ep.outRaw && c >= ep.rawC0 && c < ep.rawC1;
@@ -349,16 +388,17 @@ __device__ __forceinline__ bool epilogueTileTma(
     // one the two raw units alternate and the store from this one was waited for one unit ago.
     if(doRaw) {
       if(ep.sumsqOut) {
-        float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        // four running sums over the values k = 0, 1, 2, 3 (mod 4), as two pairs
+        float2 s2[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
 #pragma unroll
-        for(int k = 0; k < 32; k++) s4[k & 3] = fmaf(v[k], v[k], s4[k & 3]);
-        rowSumsq += (s4[0] + s4[1]) + (s4[2] + s4[3]);
+        for(int k = 0; k < 16; k++) s2[k & 1] = __ffma2_rn(v[k], v[k], s2[k & 1]);
+        rowSumsq += (s2[0].x + s2[0].y) + (s2[1].x + s2[1].y);
       }
 #pragma unroll
       for(int jj = 0; jj < 4; jj++) {
         uint4 o;
-        o.x = Pack2<T>::pack(v[8 * jj], v[8 * jj + 1]); o.y = Pack2<T>::pack(v[8 * jj + 2], v[8 * jj + 3]);
-        o.z = Pack2<T>::pack(v[8 * jj + 4], v[8 * jj + 5]); o.w = Pack2<T>::pack(v[8 * jj + 6], v[8 * jj + 7]);
+        o.x = Pack2<T>::pack(v[4 * jj].x, v[4 * jj].y); o.y = Pack2<T>::pack(v[4 * jj + 1].x, v[4 * jj + 1].y);
+        o.z = Pack2<T>::pack(v[4 * jj + 2].x, v[4 * jj + 2].y); o.w = Pack2<T>::pack(v[4 * jj + 3].x, v[4 * jj + 3].y);
         *reinterpret_cast<uint4*>(rRow + ((jj ^ sw) << 4)) = o;
       }
     }
@@ -366,15 +406,20 @@ __device__ __forceinline__ bool epilogueTileTma(
     if(ACT == KB_ACT_SWIGLU_PAIRS) {
       // columns 0..15 of the unit are "up" channels, 16..31 their "gate" channels: h = silu(up) * gate
       if(doAct) {
-        float n[16];
+        const float2 kk2 = make_float2(-1.4426950408889634f, -1.4426950408889634f), one = make_float2(1.0f, 1.0f);
+        float2 n[8];
 #pragma unroll
-        for(int k = 0; k < 16; k++) n[k] = ex2Approx(v[k] * -1.4426950408889634f);
+        for(int k = 0; k < 8; k++) n[k] = __fmul2_rn(v[k], kk2);
 #pragma unroll
-        for(int k = 0; k < 16; k++) n[k] = rcpApprox(1.0f + n[k]);
+        for(int k = 0; k < 8; k++) { n[k].x = ex2Approx(n[k].x); n[k].y = ex2Approx(n[k].y); }
 #pragma unroll
-        for(int k = 0; k < 16; k++) n[k] = v[k] * n[k] * v[16 + k];
+        for(int k = 0; k < 8; k++) n[k] = __fadd2_rn(one, n[k]);
 #pragma unroll
-        for(int k = 0; k < 8; k++) actP[k] = Pack2<T>::pack(n[2 * k], n[2 * k + 1]);
+        for(int k = 0; k < 8; k++) { n[k].x = rcpApprox(n[k].x); n[k].y = rcpApprox(n[k].y); }
+#pragma unroll
+        for(int k = 0; k < 8; k++) n[k] = __fmul2_rn(__fmul2_rn(v[k], n[k]), v[8 + k]);
+#pragma unroll
+        for(int k = 0; k < 8; k++) actP[k] = Pack2<T>::pack(n[k].x, n[k].y);
       }
     }
     else if(doAct) {
@@ -382,20 +427,19 @@ __device__ __forceinline__ bool epilogueTileTma(
       const float4* sp = reinterpret_cast<const float4*>(sScale + ca);
       const float4* bp = reinterpret_cast<const float4*>(sBias + ca);
       // all 32 values of the unit go through the activation stage by stage (TC_ACT_GROUP at a time)
+      constexpr int G2 = TC_ACT_GROUP / 2;
 #pragma unroll
       for(int hh = 0; hh < 32 / TC_ACT_GROUP; hh++) {
-        float x[TC_ACT_GROUP];
+        float2 x[G2];
 #pragma unroll
-        for(int k = 0; k < TC_ACT_GROUP / 4; k++) {
-          const float4 s4 = sp[(TC_ACT_GROUP / 4) * hh + k], b4 = bp[(TC_ACT_GROUP / 4) * hh + k];
-          x[4 * k] = fmaf(v[TC_ACT_GROUP * hh + 4 * k], s4.x, b4.x);
-          x[4 * k + 1] = fmaf(v[TC_ACT_GROUP * hh + 4 * k + 1], s4.y, b4.y);
-          x[4 * k + 2] = fmaf(v[TC_ACT_GROUP * hh + 4 * k + 2], s4.z, b4.z);
-          x[4 * k + 3] = fmaf(v[TC_ACT_GROUP * hh + 4 * k + 3], s4.w, b4.w);
+        for(int k = 0; k < G2 / 2; k++) {
+          const float4 s4 = sp[(G2 / 2) * hh + k], b4 = bp[(G2 / 2) * hh + k];
+          x[2 * k] = __ffma2_rn(v[G2 * hh + 2 * k], make_float2(s4.x, s4.y), make_float2(b4.x, b4.y));
+          x[2 * k + 1] = __ffma2_rn(v[G2 * hh + 2 * k + 1], make_float2(s4.z, s4.w), make_float2(b4.z, b4.w));
         }
-        actStaged<ACT, TC_ACT_GROUP>(x);
+        actStaged2<ACT, G2>(x);
 #pragma unroll
-        for(int k = 0; k < TC_ACT_GROUP / 2; k++) actP[(TC_ACT_GROUP / 2) * hh + k] = on ? Pack2<T>::pack(x[2 * k], x[2 * k + 1]) : 0u;
+        for(int k = 0; k < G2; k++) actP[G2 * hh + k] = on ? Pack2<T>::pack(x[k].x, x[k].y) : 0u;
       }
     }
     TRACE(threadIdx.x == 64, 1024 + (int)(tileIter & 31u) * 16 + j * 5 + 2);

@@ -117,6 +117,13 @@ template <> struct Pack2<__half> {
     return *reinterpret_cast<uint32_t*>(&h);
   }
   static __device__ __forceinline__ float2 unpack(uint32_t u) { return __half22float2(*reinterpret_cast<__half2*>(&u)); }
+  // v + (the two packed values of u), with the mixed-precision add of sm_100 (exact conversion, one rounding)
+  static __device__ __forceinline__ float2 addTo(uint32_t u, float2 v) {
+    float2 o;
+    asm("{ .reg .b16 lo, hi; mov.b32 {lo, hi}, %2; add.rn.f32.f16 %0, lo, %3; add.rn.f32.f16 %1, hi, %4; }"
+        : "=f"(o.x), "=f"(o.y) : "r"(u), "f"(v.x), "f"(v.y));
+    return o;
+  }
 };
 template <> struct Pack2<__nv_bfloat16> {
   static __device__ __forceinline__ uint32_t pack(float a, float b) {
@@ -124,6 +131,12 @@ template <> struct Pack2<__nv_bfloat16> {
     return *reinterpret_cast<uint32_t*>(&h);
   }
   static __device__ __forceinline__ float2 unpack(uint32_t u) { return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u)); }
+  static __device__ __forceinline__ float2 addTo(uint32_t u, float2 v) {
+    float2 o;
+    asm("{ .reg .b16 lo, hi; mov.b32 {lo, hi}, %2; add.rn.f32.bf16 %0, lo, %3; add.rn.f32.bf16 %1, hi, %4; }"
+        : "=f"(o.x), "=f"(o.y) : "r"(u), "f"(v.x), "f"(v.y));
+    return o;
+  }
 };
 
 
@@ -379,7 +392,7 @@ __device__ __forceinline__ bool epilogueTileTma(
         const uint4 x = *reinterpret_cast<const uint4*>(rRow + ((jj ^ sw) << 4));
         const uint32_t xu[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
-        for(int k = 0; k < 4; k++) v[4 * jj + k] = __fadd2_rn(v[4 * jj + k], Pack2<T>::unpack(xu[k]));
+        for(int k = 0; k < 4; k++) v[4 * jj + k] = Pack2<T>::addTo(xu[k], v[4 * jj + k]);
       }
     }
     const bool doRaw = ep.outRaw && c >= ep.rawC0 && c < ep.rawC1;

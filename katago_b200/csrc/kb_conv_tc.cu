@@ -81,8 +81,10 @@ __device__ __forceinline__ void actStaged2(float2 (&x)[G2]) {
   }
   else if(ACT == KB_ACT_MISH || ACT == KB_ACT_MISH_SCALE8) {
     const float kk = (ACT == KB_ACT_MISH ? 1.0f : 8.0f) * 1.4426950408889634f;
-    // x - 2x / (n^2 + 2n + 2) = x - x / q with q = n^2/2 + n + 1 = n * (n/2 + 1) + 1: one operation fewer per pair
-    const float2 kk2 = make_float2(kk, kk), half2v = make_float2(0.5f, 0.5f), one = make_float2(1.0f, 1.0f);
+    // x - 2x / (n^2 + 2n + 2) = x - x / q with q = n^2/2 + n + 1 = n * (n/2 + 1) + 1.  The code computes -q (negated
+    // constants), so that the reciprocal comes out negated and the last step is one fused multiply-add without a
+    // separate negation: x + x * (-1/q).
+    const float2 kk2 = make_float2(kk, kk), half2v = make_float2(-0.5f, -0.5f), one = make_float2(-1.0f, -1.0f);
     float2 n[G2];
 #pragma unroll
     for(int i = 0; i < G2; i++) n[i] = __fmul2_rn(x[i], kk2);
@@ -93,7 +95,7 @@ __device__ __forceinline__ void actStaged2(float2 (&x)[G2]) {
 #pragma unroll
     for(int i = 0; i < G2; i++) { n[i].x = rcpApprox(n[i].x); n[i].y = rcpApprox(n[i].y); }
 #pragma unroll
-    for(int i = 0; i < G2; i++) x[i] = __ffma2_rn(make_float2(-x[i].x, -x[i].y), n[i], x[i]);
+    for(int i = 0; i < G2; i++) x[i] = __ffma2_rn(x[i], n[i], x[i]);
   }
   else if(ACT == KB_ACT_SILU) {
     const float2 kk2 = make_float2(-1.4426950408889634f, -1.4426950408889634f), one = make_float2(1.0f, 1.0f);

@@ -256,6 +256,39 @@ def test_full_b18c384nbt_fp16_mixed_boards_vs_oracle(oracle):
     assert np.percentile(m["policy_kl"], 99) <= 1e-3, m["policy_kl"]
 
 
+def test_full_b28c512nbt_fp16_vs_oracle(oracle):
+    """The 28-block net of the 8-GPU configuration at full depth (CTA-pair convolution kernels, 512/256 channels), 32
+    mixed boards, random symmetries, fp16.
+
+    This random-init net emits scores of 41-170 points, and storing its convolution weights in fp16 alone moves the fp32
+    oracle's scores by up to 0.9 points, so the 0.1-point bound that the shallower tests assert cannot hold here for any
+    fp16 backend.  The test pins what was measured instead, with a margin of about 1.7: against the oracle run on the
+    weights the device holds (arithmetic of the CUDA path only) p99 score 0.58, lead 0.54, winrate 0.05 %, policy KL
+    4.4e-3; against the fp32 oracle p99 score 1.2 (0.7 % of the output), winrate 0.2 %."""
+    model_tree = mf.make_b28c512nbt()
+    blob = mf.to_blob(model_tree)
+    n = 32
+    sizes = [9, 13, 19, 19] * (n // 4)
+    sp, gl = mf.random_positions(n, seed=2004, board_sizes=sizes)
+    syms = (np.arange(n) * 5 % 8).astype(np.int32)
+    h = capi.Handle(capi.Model(blob), n, precision=capi.PRECISION_FP16)
+    got = h.forward(sp, gl, syms)
+    h.close()
+    mask = sp[..., 0].reshape(n, -1)
+    sym_in = symmetrise_inputs(sp, syms)
+    ref_dev = unsymmetrise_outputs(oracle.OracleModel(mf.to_blob(_fp16_conv_weights(model_tree))).forward(sym_in, gl), syms)
+    m = parity_metrics(got, ref_dev, mask)
+    assert np.percentile(m["winrate"], 99) <= 0.005, m["winrate"]
+    assert np.percentile(m["score"], 99) <= 1.0, m["score"]
+    assert np.percentile(m["lead"], 99) <= 1.0, m["lead"]
+    assert np.percentile(m["policy_kl"], 99) <= 1e-2, m["policy_kl"]
+    ref = unsymmetrise_outputs(oracle.OracleModel(blob).forward(sym_in, gl), syms)
+    m = parity_metrics(got, ref, mask)
+    assert np.percentile(m["winrate"], 99) <= 0.005, m["winrate"]
+    assert np.percentile(m["score"], 99) <= 2.0, m["score"]
+    assert np.percentile(m["lead"], 99) <= 2.0, m["lead"]
+
+
 @pytest.mark.parametrize("prec", [capi.PRECISION_FP32, capi.PRECISION_FP16])
 def test_sgf_metadata_encoder_net_vs_oracle(prec, oracle):
     """Nets with an SGF metadata encoder (human-SL nets, eigenbackend.cpp:1801-1847, 1917-1920): the encoder's MLP output is

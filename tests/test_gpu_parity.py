@@ -256,6 +256,22 @@ def test_full_b18c384nbt_fp16_mixed_boards_vs_oracle(oracle):
     assert np.percentile(m["policy_kl"], 99) <= 1e-3, m["policy_kl"]
 
 
+@pytest.mark.parametrize("factory", [mf.make_transformer, mf.make_transformer_relbias], ids=["rope", "relbias"])
+def test_full_transformer_fp16_vs_oracle(factory, oracle):
+    """The transformer configuration at full depth (12 layers, 6 heads of 64, SwiGLU 1024), with rotary embeddings and
+    with the learned relative-position bias, fp16, 16 mixed boards with random symmetries, at the stated tolerance."""
+    tree = factory()
+    blob = mf.to_blob(tree)
+    n = 16
+    sp, gl = mf.random_positions(n, seed=2021, board_sizes=[9, 13, 19, 19] * (n // 4))
+    syms = (np.arange(n) * 3 % 8).astype(np.int32)
+    h = capi.Handle(capi.Model(blob), n, precision=capi.PRECISION_FP16)
+    got = h.forward(sp, gl, syms)
+    h.close()
+    ref = unsymmetrise_outputs(oracle.OracleModel(blob).forward(symmetrise_inputs(sp, syms), gl), syms)
+    _assert_reduced_close(got, ref, sp[..., 0].reshape(n, -1))
+
+
 def test_full_b28c512nbt_fp16_vs_oracle(oracle):
     """The 28-block net of the 8-GPU configuration at full depth (CTA-pair convolution kernels, 512/256 channels), 32
     mixed boards, random symmetries, fp16.

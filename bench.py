@@ -12,7 +12,17 @@ pass over one batch.  Rank 0 prints one JSON line.
             host buffers out, host<->device copies inside the timed region
   roofline  the dominant kernel (3x3 convolution 192->192 on tcgen05): algorithmic FLOPs per launch over its mean
             launch time measured with CUDA events around every launch of a second pass over the same K steps
-  cpu_baseline  the CPU oracle (port of the reference's Eigen backend) on a bounded sample, rank 0 only
+  sustained back-to-back steps for at least 3 s with their own clock samples (a short run prints a higher figure than a
+            settled one: the 1000 W power cap takes a second to pull the SM clock down)
+  cpu_baseline  the CPU oracle (port of the reference's Eigen backend) on a bounded sample, rank 0 only: all cores
+            on batches of 8, and the reference's own CPU operating point (batches of 2, one single-threaded worker per
+            core: cpp/program/setup.cpp:279-287, 330-339)
+
+--through-katago (secondary figure, (N = --gpus) GPUs in ONE process): runs the reference program's own `benchmark`
+subcommand linked with this backend (oracle/_ref/katago_b200: search threads -> NNEvaluator queue -> getOutput) with
+--server-threads-per-gpu server threads per GPU, cudaDeviceToUseThread<i> = i mod N, on a random-weight b18c384nbt model
+file, and prints its nnEvals/s.  --c-abi-threads T (also in-process) runs T host threads per GPU, each with its own
+handle, calling kb_forward_host in a loop: the same multi-GPU process model without NNEvaluator's queue.
 
 --impl reference times that CPU port alone (the reference's own CPU backend needs Eigen3, which is not
 installed on this image), on the same config and metric.
@@ -76,7 +86,13 @@ class ClockSampler:
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index):
-        self.gpu, self.lines, self.proc = gpu_index, [], None
+        # nvidia-smi numbers GPUs without regard to CUDA_VISIBLE_DEVICES: address the device by its UUID
+        self.gpu, self.lines, self.proc = str(gpu_index), [], None
+        try:
+            import torch
+            self.gpu = "GPU-" + str(torch.cuda.get_device_properties(gpu_index).uuid)
+        except Exception:
+            pass
 
     def start(self):
         try:
@@ -155,11 +171,45 @@ def _use_all_host_cores():
     os.environ["OMP_NUM_THREADS"] = str(max(1, n))
 
 
+def _host_cores():
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def cpu_reference_operating_point(budget_s, wl=None):
+    """evals/s of the CPU port run the way the reference runs its CPU backend: batches of at most 2 positions, one
+    single-threaded server thread per core (cpp/program/setup.cpp:279-287, 330-339)."""
+    from concurrent.futures import ThreadPoolExecutor
+    from katago_b200 import modelfile as mf
+    from oracle import pyoracle as po
+    wl = wl or WORKLOADS["b18"]
+    om = po.OracleModel(mf.to_blob(getattr(mf, wl["builder"])()))
+    cores = _host_cores()
+    sp, gl = mf.random_positions(2, seed=2000)
+    deadline = time.perf_counter() + budget_s
+
+    def worker(_):
+        po.set_num_threads(1)
+        done = 0
+        while True:
+            om.forward(sp, gl)
+            done += 2
+            if time.perf_counter() > deadline:
+                return done
+    t0 = time.perf_counter()
+    with ThreadPoolExecutor(cores) as ex:
+        done = sum(ex.map(worker, range(cores)))
+    return dict(value=done / (time.perf_counter() - t0), workers=cores, evals=done)
+
+
 def cpu_oracle_rate(budget_s, positions_per_call, max_calls, wl=None):
     """evals/s of the CPU port of the reference's Eigen backend on the same net and position scheme."""
     _use_all_host_cores()
     from katago_b200 import modelfile as mf
     from oracle import pyoracle as po
+    po.set_num_threads(_host_cores())  # an OpenMP runtime loaded earlier (torch under torchrun) may have fixed it at 1
     wl = wl or WORKLOADS["b18"]
     om = po.OracleModel(mf.to_blob(getattr(mf, wl["builder"])()))
     sizes = (wl["sizes"] * positions_per_call)[:positions_per_call] if wl["sizes"] else None
@@ -185,6 +235,9 @@ def run_reference(args, rank, world, pg):
     from oracle import pyoracle as po
     per_step = 8
     from katago_b200 import modelfile as mf
+    # torchrun exports OMP_NUM_THREADS=1 and torch.distributed loads the OpenMP runtime before this point, which fixes
+    # the thread count at 1 whatever the environment says later: set it through the runtime itself
+    po.set_num_threads(_host_cores())
     om = po.OracleModel(mf.to_blob(mf.make_b18c384nbt()))
     sp, gl = mf.random_positions(per_step, seed=2000)
     for _ in range(max(args.warmup, 1)):
@@ -246,6 +299,17 @@ def run_b200(args, rank, world, local, pg):
     ms_total = _max_over_ranks(pg, sum(ms_each))
     value = world * BATCH * args.steps / (ms_total * 1e-3)
 
+    # ---- sustained: back-to-back steps for at least 3 s, with their own clock samples ----
+    sust_steps = max(args.steps, int(3000.0 / max(ms_total / args.steps, 1e-3)) + 1)
+    sust_sampler = ClockSampler(device)
+    sust_sampler.start()
+    _barrier_sync(pg)
+    sust_ms = h.time_forward_steps(BATCH, sust_steps, flush)
+    _barrier_sync(pg)
+    sust_clocks = sust_sampler.stop()
+    sust_total = _max_over_ranks(pg, sum(sust_ms))
+    sustained = world * BATCH * sust_steps / (sust_total * 1e-3)
+
     # ---- end to end through the host-buffer call ----
     for _ in range(max(args.warmup, 3)):
         h.forward(pin_sp.array, pin_gl.array, pin_sym.array, out=out_arrays)
@@ -288,6 +352,13 @@ def run_b200(args, rank, world, local, pg):
     flops_per_eval = FLOPS_PER_EVAL if args.workload == "b18" else all_conv_flops / (args.steps * BATCH)
     # the CPU baseline is taken at N=1 only (at N>1 the other ranks' processes share the host cores)
     cpu = cpu_oracle_rate(budget_s=12.0, positions_per_call=8, max_calls=8, wl=wl) if world == 1 else None
+    cpu_op = cpu_reference_operating_point(budget_s=8.0, wl=wl) if world == 1 else None
+    # The timed region of the default run is a fraction of a second, which the power cap has not settled yet: the
+    # burst figure of the measured cuBLAS peak is its denominator; a timed region of a second or more takes the
+    # sustained one.  Both ratios are printed.
+    timed_s = ms_total * 1e-3
+    peak_used = peaks["burst"] if timed_s < 1.0 else peaks["tflops"]
+    peak_name = "bf16_tflops (burst: timed region %.2f s)" % timed_s if timed_s < 1.0 else "bf16_tflops_sustained (timed region %.1f s)" % timed_s
     line = {
         "metric": wl["metric"], "value": value, "unit": "evals/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_total / args.steps, "p50_batch_latency_ms": statistics.median(ms_each), "higher_is_better": True, "scaling": "weak",
@@ -296,17 +367,23 @@ def run_b200(args, rank, world, local, pg):
                    "l2": "256 MiB memset between timed steps (L2 flush); per-step activations (~0.4 GB) also exceed the 126 MB L2",
                    "weights": "random init N(0,1/fan_in), BN scale U(0.5,1.5) bias N(0,0.1), seed 1001", "positions": "seeded synthetic, empty/black/white 0.6/0.2/0.2"},
         "clocks": clocks,
+        "sustained": {"value": sustained, "unit": "evals/s", "steps": sust_steps, "seconds": sust_total * 1e-3,
+                      "ms_per_step": sust_total / sust_steps, "clocks": sust_clocks},
         "e2e": {"value": e2e, "unit": "evals/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s / args.steps * 1e3},
         "gpu_launches": launches * args.steps,
-        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak_used, "unit": "TFLOP/s", "frac": achieved / peak_used,
+                     "frac_of_sustained_peak": achieved / peaks["tflops"], "frac_of_burst_peak": achieved / peaks["burst"],
                      "traffic": traffic, "kernel": ("convTcKernel<half> 3x3 192->192 (both epilogue variants)" if args.workload in ("b18", "mixed") else wl["dominant"] + " (tcgen05)"), "launches": dom_launches,
                      "avg_launch_ms": dom_ms / dom_launches if dom_launches else None, "share_of_step": dom_ms / total_ms,
-                     "peak_source": f"MEASURED_PEAKS.json bf16_tflops_sustained ({peaks['src']}); burst {peaks['burst']}",
+                     "peak_source": f"MEASURED_PEAKS.json {peak_name} ({peaks['src']}); burst {peaks['burst']}, sustained {peaks['tflops']}",
                      "whole_step_tflops": all_conv_flops / (total_ms * 1e-3) / 1e12,
-                     "whole_step_frac_of_peak": flops_per_eval * value / world / 1e12 / peaks["tflops"]},
+                     "whole_step_frac_of_peak": flops_per_eval * value / world / 1e12 / peak_used,
+                     "sustained_step_frac_of_sustained_peak": flops_per_eval * sustained / world / 1e12 / peaks["tflops"]},
         "cpu_baseline": None if cpu is None else {
             "value": cpu["value"], "unit": "evals/s", "cores": cpu["cores"], "kind": "port",
-            "sample": f"{cpu['calls']} calls of 8 positions of the same net and position scheme (oracle/kata_oracle.cpp, OpenMP, fp32)"},
+            "sample": f"{cpu['calls']} calls of 8 positions of the same net and position scheme (oracle/kata_oracle.cpp, OpenMP, fp32)",
+            "reference_operating_point": {"value": cpu_op["value"], "unit": "evals/s", "workers": cpu_op["workers"], "batch": 2,
+                                          "sample": f"{cpu_op['evals']} evaluations in batches of 2 by {cpu_op['workers']} single-threaded workers, as the reference configures its CPU backend"}},
         "kernels": [{"name": p["name"], "launches": p["launches"], "ms": round(p["ms"], 4), "share": round(p["ms"] / total_ms, 4)}
                     for p in sorted(prof, key=lambda p: -p["ms"])[:8] if p["launches"]],
         # bandwidth-bound classes: algorithmic bytes (each tensor read or written once) over the measured time, against
@@ -318,6 +395,109 @@ def run_b200(args, rank, world, local, pg):
     print(json.dumps(line), flush=True)
 
 
+KATAGO_CFG = """logFile = /dev/null
+logToStderr = false
+logAllGTPCommunication = false
+logSearchInfo = false
+rules = tromp-taylor
+numSearchThreads = 256
+nnMaxBatchSize = 256
+nnCacheSizePowerOfTwo = 20
+nnMutexPoolSizePowerOfTwo = 14
+numNNServerThreadsPerModel = {server_threads}
+cudaUseFP16 = true
+maxVisits = {visits}
+"""
+
+
+def run_through_katago(args):
+    """The reference's `benchmark` subcommand on this backend, N GPUs in one process (setup.cpp:183-220 device map)."""
+    import re
+    import tempfile
+    from katago_b200 import modelfile as mf
+    binary = os.path.join(ROOT, "oracle", "_ref", "katago_b200")
+    if not os.path.exists(binary):
+        print(json.dumps({"impl": "b200-through-katago", "unavailable": "oracle/_ref/katago_b200 is not built (make -C oracle ref_b200 needs the reference sources)"}))
+        return
+    G, per = max(1, args.gpus), max(1, args.server_threads_per_gpu)
+    with tempfile.TemporaryDirectory() as d:
+        model = os.path.join(d, "b18c384nbt-random.bin.gz")
+        cfg = os.path.join(d, "benchmark.cfg")
+        mf.save_model_file(mf.make_b18c384nbt(), model)
+        text = KATAGO_CFG.format(visits=args.visits, server_threads=G * per)
+        for i in range(G * per):
+            text += f"cudaDeviceToUseThread{i} = {i % G}\n"
+        with open(cfg, "w") as f:
+            f.write(text)
+        env = dict(os.environ)
+        env["LD_LIBRARY_PATH"] = os.path.join(ROOT, "katago_b200") + os.pathsep + env.get("LD_LIBRARY_PATH", "")
+        cmd = [binary, "benchmark", "-model", model, "-config", cfg, "-v", str(args.visits), "-t", args.search_threads, "-n", str(args.positions)]
+        t0 = time.perf_counter()
+        r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=1800)
+        wall = time.perf_counter() - t0
+    text = (r.stdout + r.stderr).replace("\r", "\n")
+    rows = []
+    for line in text.splitlines():
+        m = re.search(r"numSearchThreads\s*=\s*(\d+):.*?([0-9.]+)\s*nnEvals/s", line)
+        if m:
+            rows.append({"search_threads": int(m.group(1)), "nn_evals_per_s": float(m.group(2)), "line": line.strip()[:200]})
+    best = max((x["nn_evals_per_s"] for x in rows), default=None)
+    print(json.dumps({"impl": "b200-through-katago", "metric": "nnEvals/s of the reference's benchmark subcommand on this backend", "value": best,
+                      "unit": "evals/s", "n_gpus": G, "server_threads_per_gpu": per, "visits": args.visits, "rows": rows, "rc": r.returncode,
+                      "wall_s": wall, "tail": None if rows else text[-1500:]}), flush=True)
+
+
+def run_c_abi_threads(args):
+    """N GPUs in one process without NNEvaluator: T host threads per GPU, one handle each (as createComputeHandle is called
+    once per server thread), each calling kb_forward_host on its own page-locked buffers in a loop for a fixed time."""
+    import katago_b200 as kb
+    from katago_b200 import capi, modelfile as mf
+    G, T = max(1, args.gpus), max(1, args.c_abi_threads)
+    wl = WORKLOADS["b18"]
+    batch = wl["batch"]
+    blob = mf.to_blob(mf.make_b18c384nbt())
+    S = 19 * 19
+    seconds = 4.0
+    counts = [0] * (G * T)
+    handles = []
+    ready = threading.Barrier(G * T + 1)
+
+    def worker(i):
+        dev = i % G
+        model = kb.Model(blob)
+        h = kb.Handle(model, batch, precision=kb.PRECISION_FP16, device=dev)
+        sp, gl = mf.random_positions(batch, seed=2000 + i)
+        pin_sp = capi.PinnedArray((batch, 19, 19, model.in_c)); pin_sp.array[...] = sp
+        pin_gl = capi.PinnedArray((batch, model.in_global_c)); pin_gl.array[...] = gl
+        pin_sym = capi.PinnedArray((batch,), np.int32); pin_sym.array[...] = 0
+        outs = {k: capi.PinnedArray(shape) for k, shape in dict(policy=(batch, S, model.policy_c), policyPass=(batch, model.policy_c), value=(batch, model.value_c),
+                                                                  scoreValue=(batch, model.score_c), ownership=(batch, S)).items()}
+        arrays = {k: v.array for k, v in outs.items()}
+        for _ in range(3):
+            h.forward(pin_sp.array, pin_gl.array, pin_sym.array, out=arrays)
+        handles.append((h, pin_sp, pin_gl, pin_sym, outs))
+        ready.wait()
+        ready.wait()
+        end = time.perf_counter() + seconds
+        while time.perf_counter() < end:
+            h.forward(pin_sp.array, pin_gl.array, pin_sym.array, out=arrays)
+            counts[i] += 1
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(G * T)]
+    for t in threads:
+        t.start()
+    ready.wait()
+    t0 = time.perf_counter()
+    ready.wait()
+    for t in threads:
+        t.join()
+    wall = time.perf_counter() - t0
+    value = sum(counts) * batch / wall
+    print(json.dumps({"impl": "b200-c-abi-threads", "metric": METRIC + ", kb_forward_host from host threads of one process", "value": value, "unit": "evals/s",
+                      "n_gpus": G, "threads_per_gpu": T, "seconds": wall, "batches_per_thread": counts}), flush=True)
+    for h, *_ in handles:
+        h.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -325,7 +505,17 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="b18", choices=sorted(WORKLOADS), help="b18 is the headline configuration; the others are for measurement of the remaining configurations")
+    ap.add_argument("--through-katago", action="store_true", help="run the reference's benchmark subcommand on this backend, --gpus GPUs in one process")
+    ap.add_argument("--server-threads-per-gpu", type=int, default=2)
+    ap.add_argument("--visits", type=int, default=30000)
+    ap.add_argument("--search-threads", default="512,1024")
+    ap.add_argument("--positions", type=int, default=4)
+    ap.add_argument("--c-abi-threads", type=int, default=0, help="T > 0: T host threads per GPU in one process, each calling kb_forward_host in a loop")
     args = ap.parse_args()
+    if args.through_katago:
+        return run_through_katago(args)
+    if args.c_abi_threads > 0:
+        return run_c_abi_threads(args)
     rank, world, local, pg = _dist()
     if args.impl == "reference":
         run_reference(args, rank, world, pg)

@@ -143,7 +143,7 @@ int kb_eval_layer(
  * Computes the same zero-padded stride-1 cross-correlation as kb_eval_layer does for a CONV record in fp32.
  * The kernels are enqueued on `stream`; the call returns without waiting for them.
  *
- * Limits (exceeding one is an error, nothing is launched): n*(nnYLen+1)*(nnXLen+1) rounded up to 128 <= 4096 rows
+ * Limits (exceeding one is an error, nothing is launched): n*(nnYLen+1)*(nnXLen+1) rounded up to a multiple of 256 <= 4096 rows
  * (10 boards of 19x19), inC <= 64, outC <= 64, kernel at most 5x5 and odd.
  * The first call on each device looks up the array's device address (with that device current); make that
  * call before starting any stream capture.  All calls share the one array and it keeps the previous call's

@@ -13,8 +13,9 @@
 // L2 -> SM path once per tile instead of nine times.  The weight tile of each (tap, chunk) streams
 // through a ring of slots.
 //
-// Persistent CTAs (one per SM), 320 threads: warp 0 issues TMA loads, warp 1 owns TMEM and issues the
-// MMAs, warps 2..13 run the epilogue (three warps per TMEM lane quarter, taking 32-channel units in turn).
+// Persistent CTAs (one per SM), 64 + 128*CG threads: warp 0 issues TMA loads, warp 1 owns TMEM and issues the
+// MMAs, the remaining 4*CG warps run the epilogue (CG warps per TMEM lane quarter, taking 32-channel units in turn;
+// CG = 2 by default, 3 for 1x1 convolutions whose epilogue is the critical path).
 // Two accumulators live in TMEM, so the epilogue of tile i overlaps the main loop of tile i+1.
 // Every wait is bounded: on time-out the kernel records a code in the status word and all roles
 // leave through the common exit, which still frees TMEM.

@@ -1,8 +1,6 @@
-/* Row packing/unpacking shared by the backends that implement the reference's
+/* Row unpacking shared by the backends that implement the reference's
  * NeuralNet::getOutput contract (cpp/neuralnet/nninterface.h:102-123).
  *
- * packRow   : NNResultBuf -> one row of the contiguous NHWC spatial / global staging arrays,
- *             applying the row's board symmetry (nninputs.cpp:529-597).
  * unpackRow : raw network outputs of one row -> NNOutput fields, following the reference's
  *             CPU backend (neuralnet/eigenbackend.cpp:2527-2615): policy-optimism blend on
  *             policy channels 0/1, inverse symmetry for policy and ownership, pass logit at
@@ -44,25 +42,6 @@ inline NetDims makeNetDims(const ModelDesc& m, int nnXLen, int nnYLen) {
   if(m.numValueChannels != 3 || m.numOwnershipChannels != 1)
     throw StringError("backend: unexpected number of value or ownership channels");
   return d;
-}
-
-// inputsUseNHWC describes the layout of rowSpatialBuf; the staging row is always NHWC.
-inline void packRow(
-  const NetDims& d, const NNResultBuf* buf, bool inputsUseNHWC, float* spatialRowNHWC, float* globalRow, float* scratchRow) {
-  const int S = d.nnXLen * d.nnYLen;
-  const int C = d.numSpatialFeatures;
-  if(buf->hasRowMeta)
-    throw StringError("backend: SGF metadata inputs are not supported");
-  std::copy(buf->rowGlobalBuf.begin(), buf->rowGlobalBuf.begin() + d.numGlobalFeatures, globalRow);
-  if(inputsUseNHWC) {
-    SymmetryHelpers::copyInputsWithSymmetry(buf->rowSpatialBuf.data(), spatialRowNHWC, 1, d.nnYLen, d.nnXLen, C, true, buf->symmetry);
-  }
-  else {
-    SymmetryHelpers::copyInputsWithSymmetry(buf->rowSpatialBuf.data(), scratchRow, 1, d.nnYLen, d.nnXLen, C, false, buf->symmetry);
-    for(int c = 0; c < C; c++)
-      for(int s = 0; s < S; s++)
-        spatialRowNHWC[(size_t)s * C + c] = scratchRow[(size_t)c * S + s];
-  }
 }
 
 // policy: [S][policyC] of this row; policyPass: [policyC]; value: [3]; scoreValue: [scoreValueC]; ownership: [S].

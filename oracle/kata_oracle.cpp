@@ -29,6 +29,39 @@ namespace {
 
 thread_local std::string g_lastError;
 
+// ------------------------------------------------------------------------------------------------
+// Storage emulation (ko_set_storage_emulation): NOT part of the reference's arithmetic.  It rounds selected tensors to
+// fp16 or bf16 where a reduced-precision backend stores them, everything else staying fp32, so that tests can measure
+// how far ANY backend with that storage scheme must move from the fp32 result (the floor that the tolerance tests add
+// their bound to).  Off by default; set once before a forward pass, not while one runs.
+int g_emuType = 0;   // 0 off, 1 fp16, 2 bf16
+int g_emuFlags = 0;  // KO_EMU_CONV_INPUTS | KO_EMU_STREAMS
+// Where the rounding sits (it mirrors a backend whose convolution epilogues write both the updated stream and the next
+// layer's activated tensor from the fp32 accumulator): activated tensors are rounded where a convolution (or a pooling
+// layer) reads them; a residual stream is rounded just before the next branch is added to it, so the norm that follows
+// an update still sees the value before rounding; intermediate sums that such a backend stores before a per-board bias
+// is known (the regular path of a gpool block, the policy head's p1) are rounded at that point.
+
+inline float roundBf16(float x) {
+  uint32_t u;
+  std::memcpy(&u, &x, 4);
+  if((u & 0x7f800000u) == 0x7f800000u) return x;
+  u += 0x7fffu + ((u >> 16) & 1u);
+  u &= 0xffff0000u;
+  std::memcpy(&x, &u, 4);
+  return x;
+}
+inline float roundStorage(float x) {
+  if(g_emuType == 1) return (float)(_Float16)x;
+  if(g_emuType == 2) return roundBf16(x);
+  return x;
+}
+void roundTensor(float* p, size_t count) {
+#pragma omp parallel for schedule(static)
+  for(size_t i = 0; i < count; i++) p[i] = roundStorage(p[i]);
+}
+inline bool emuOn(int flag) { return g_emuType != 0 && (g_emuFlags & flag) != 0; }
+
 struct Fail : std::runtime_error {
   using std::runtime_error::runtime_error;
 };
@@ -88,6 +121,14 @@ struct Conv {
     const int S = X * Y;
     const int padY = kY / 2, padX = kX / 2;
     const int PB = 4;
+    vector<float> roundedIn;
+    // the stored residual stream is what the next update adds to; the value before rounding fed the norm that follows it
+    if(accumulate && emuOn(KO_EMU_STREAMS)) roundTensor(out, (size_t)n * S * outC);
+    if(emuOn(KO_EMU_CONV_INPUTS)) {
+      roundedIn.assign(in, in + (size_t)n * S * inC);
+      roundTensor(roundedIn.data(), roundedIn.size());
+      in = roundedIn.data();
+    }
 #pragma omp parallel for collapse(2) schedule(static)
     for(int b = 0; b < n; b++) {
       for(int y = 0; y < Y; y++) {
@@ -383,8 +424,10 @@ struct GPoolBlock final : Block {
     vector<float> gpoolConcat((size_t)cx.n * 3 * gpoolConv.outC), gpoolBias((size_t)cx.n * regularConv.outC);
     preBN.apply(trunk, scratch.data(), cx.mask, rows);
     regularConv.apply(scratch.data(), regularOut.data(), cx.n, cx.X, cx.Y, false);
+    if(emuOn(KO_EMU_CONV_INPUTS)) roundTensor(regularOut.data(), regularOut.size());  // stored before the pooled bias is known
     gpoolConv.apply(scratch.data(), gpoolOut.data(), cx.n, cx.X, cx.Y, false);
     gpoolBN.apply(gpoolOut.data(), gpoolOut2.data(), cx.mask, rows);
+    if(emuOn(KO_EMU_CONV_INPUTS)) roundTensor(gpoolOut2.data(), gpoolOut2.size());
     poolRowsGPool(gpoolOut2.data(), gpoolConcat.data(), cx.mask, cx.maskSum, cx.n, cx.S, gpoolConv.outC);
     gpoolToBias.apply(gpoolConcat.data(), gpoolBias.data(), cx.n);
     addNCBias(regularOut.data(), gpoolBias.data(), cx.n, cx.S, regularConv.outC);
@@ -661,7 +704,8 @@ struct Trunk {
     else if(normKind == 1) { tipRMS.load(rd); if(tipRMS.C != trunkC) throw Fail("trunk: tip RMSNorm channel mismatch"); }
     else throw Fail("trunk: unknown norm kind");
   }
-  void apply(const Ctx& cx, const float* input, const float* global, const float* meta, float* trunkOut) const {
+  // streams (optional): [numBlocks + 1][rows][trunkC], the residual stream entering each block and leaving the last
+  void apply(const Ctx& cx, const float* input, const float* global, const float* meta, float* trunkOut, float* streams = nullptr) const {
     const size_t rows = cx.rows();
     vector<float> t(rows * trunkC), gbias((size_t)cx.n * trunkC);
     initialConv.apply(input, t.data(), cx.n, cx.X, cx.Y, false);
@@ -679,7 +723,12 @@ struct Trunk {
       metaMul3.apply(h2.data(), gbias.data(), cx.n);
       addNCBias(t.data(), gbias.data(), cx.n, cx.S, trunkC);
     }
-    for(auto& b : blocks) b->apply(cx, t.data());
+    for(size_t i = 0; i < blocks.size(); i++) {
+      if(streams) std::memcpy(streams + i * t.size(), t.data(), t.size() * sizeof(float));
+      blocks[i]->apply(cx, t.data());
+    }
+    if(streams) std::memcpy(streams + blocks.size() * t.size(), t.data(), t.size() * sizeof(float));
+    if(!trunkOut) return;
     if(normKind == 0) tipBN.apply(t.data(), trunkOut, cx.mask, rows);
     else tipRMS.apply(t.data(), trunkOut, cx.mask, cx.n, cx.S);
   }
@@ -707,6 +756,7 @@ struct PolicyHead {
     p1Conv.apply(trunk, p1.data(), cx.n, cx.X, cx.Y, false);
     g1Conv.apply(trunk, g1.data(), cx.n, cx.X, cx.Y, false);
     g1BN.apply(g1.data(), g1b.data(), cx.mask, rows);
+    if(emuOn(KO_EMU_CONV_INPUTS)) { roundTensor(g1b.data(), g1b.size()); roundTensor(p1.data(), p1.size()); }
     poolRowsGPool(g1b.data(), concat.data(), cx.mask, cx.maskSum, cx.n, cx.S, g1Conv.outC);
     gpoolToBias.apply(concat.data(), bias.data(), cx.n);
     addNCBias(p1.data(), bias.data(), cx.n, cx.S, p1Conv.outC);
@@ -740,6 +790,7 @@ struct ValueHead {
     vector<float> v1(rows * v1Conv.outC), v1b(rows * v1Conv.outC), mean((size_t)cx.n * 3 * v1Conv.outC), v2((size_t)cx.n * v2Mul.outC);
     v1Conv.apply(trunk, v1.data(), cx.n, cx.X, cx.Y, false);
     v1BN.apply(v1.data(), v1b.data(), cx.mask, rows);
+    if(emuOn(KO_EMU_CONV_INPUTS)) roundTensor(v1b.data(), v1b.size());
     poolRowsValueHead(v1b.data(), mean.data(), cx.maskSum, cx.n, cx.S, v1Conv.outC);
     v2Mul.apply(mean.data(), v2.data(), cx.n);
     v2Bias.apply(v2.data(), cx.n);
@@ -772,6 +823,23 @@ int guarded(F&& f) {
 extern "C" {
 
 const char* ko_last_error(void) { return g_lastError.c_str(); }
+
+int ko_set_storage_emulation(int storageType, int flags) {
+  if(storageType < 0 || storageType > 2) return 1;
+  g_emuType = storageType;
+  g_emuFlags = flags;
+  return 0;
+}
+
+int ko_set_num_threads(int n) {
+#ifdef _OPENMP
+  if(n < 1) return 1;
+  omp_set_num_threads(n);
+  return 0;
+#else
+  return n == 1 ? 0 : 1;
+#endif
+}
 
 int ko_num_threads(void) {
 #ifdef _OPENMP
@@ -857,6 +925,25 @@ int ko_forward_meta(
     if(value) std::memcpy(value, val.data(), val.size() * sizeof(float));
     if(scoreValue) std::memcpy(scoreValue, sv.data(), sv.size() * sizeof(float));
     if(ownership) std::memcpy(ownership, own.data(), own.size() * sizeof(float));
+  });
+}
+
+int ko_trunk_streams(const ko_model* m, int n, const float* spatial, const float* global, const float* meta, float* streams) {
+  return guarded([&]() {
+    if(!m || !spatial || !global || !streams) throw Fail("ko_trunk_streams: NULL argument");
+    if(n < 1) throw Fail("ko_trunk_streams: batch size must be positive");
+    if((m->inMetaC > 0) != (meta != nullptr)) throw Fail("ko_trunk_streams: metadata rows must be given exactly for models with a metadata encoder");
+    const int S = m->X * m->Y;
+    const size_t rows = (size_t)n * S;
+    vector<float> mask(rows), maskSum(n);
+    for(size_t r = 0; r < rows; r++) mask[r] = spatial[r * m->inC];
+    for(int b = 0; b < n; b++) {
+      float s = 0.0f;
+      for(int p = 0; p < S; p++) s += mask[(size_t)b * S + p];
+      maskSum[b] = s;
+    }
+    Ctx cx{n, m->X, m->Y, S, mask.data(), maskSum.data()};
+    m->trunk.apply(cx, spatial, global, meta, nullptr, streams);
   });
 }
 

@@ -54,6 +54,9 @@ int ko_forward_meta(
   const ko_model* m, int n, const float* spatial, const float* global, const float* meta,
   float* policy, float* policyPass, float* value, float* scoreValue, float* ownership,
   float* trunkOut);
+/* The residual stream of the trunk (eigenbackend.cpp:1851-1936) as it enters each block and as it leaves the last one:
+ * streams [numBlocks + 1][n][Y*X][trunkC].  Lets a test hand one block of a deep net its true input. */
+int ko_trunk_streams(const ko_model* m, int n, const float* spatial, const float* global, const float* meta, float* streams);
 /* ModelDesc::numInputMetaChannels (0 without the encoder). */
 int ko_model_meta_channels(const ko_model* m, int32_t* channels);
 
@@ -64,8 +67,21 @@ int ko_eval_layer(
   const void* blob, size_t nbytes, int n, int nnXLen, int nnYLen,
   const float* in, const float* mask, float* out);
 
+/* Storage emulation, for measuring precision floors only (no counterpart in the reference): rounds the chosen tensors
+ * of the convolutional blocks to storageType (0 = off, 1 = fp16, 2 = bf16) where a reduced-precision backend stores
+ * them, all arithmetic staying fp32.  KO_EMU_CONV_INPUTS: every convolution's input (the activated tensors that feed
+ * the matrix units, the pooling layers' inputs and the sums stored ahead of a per-board bias); KO_EMU_STREAMS: the residual streams as the
+ * next update reads them.  Weights are rounded by the caller (in
+ * the blob).  Process-wide; set it before a forward pass, never during one. */
+#define KO_EMU_CONV_INPUTS 1
+#define KO_EMU_STREAMS 2
+int ko_set_storage_emulation(int storageType, int flags);
+
 /* Number of OpenMP threads the oracle will use (for reporting CPU baselines). */
 int ko_num_threads(void);
+/* Sets the number of OpenMP threads for forward passes started by the calling thread from now on (an OpenMP runtime
+ * that another library initialised first may have fixed it at 1 from the environment). */
+int ko_set_num_threads(int n);
 
 #ifdef __cplusplus
 }

@@ -45,7 +45,7 @@ CASES = [
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("KATAGO_REFERENCE", "/root/reference"))
     args = ap.parse_args()
     from katago_b200 import modelfile as mf
     katago = os.path.join(HERE, "_ref", "katago_oracle")

@@ -107,6 +107,24 @@ InputBuffers* NeuralNet::createInputBuffers(const LoadedModel* loadedModel, int 
 }
 void NeuralNet::freeInputBuffers(InputBuffers* buffers) { delete buffers; }
 
+// NNResultBuf -> one row of the contiguous NHWC spatial / global staging arrays, applying the row's board symmetry on the
+// host (nninputs.cpp:529-597).  inputsUseNHWC describes the layout of rowSpatialBuf; the staging row is always NHWC.
+static void packRow(
+  const kbhost::NetDims& d, const NNResultBuf* buf, bool inputsUseNHWC, float* spatialRowNHWC, float* globalRow, float* scratchRow) {
+  const int S = d.nnXLen * d.nnYLen;
+  const int C = d.numSpatialFeatures;
+  std::copy(buf->rowGlobalBuf.begin(), buf->rowGlobalBuf.begin() + d.numGlobalFeatures, globalRow);
+  if(inputsUseNHWC) {
+    SymmetryHelpers::copyInputsWithSymmetry(buf->rowSpatialBuf.data(), spatialRowNHWC, 1, d.nnYLen, d.nnXLen, C, true, buf->symmetry);
+  }
+  else {
+    SymmetryHelpers::copyInputsWithSymmetry(buf->rowSpatialBuf.data(), scratchRow, 1, d.nnYLen, d.nnXLen, C, false, buf->symmetry);
+    for(int c = 0; c < C; c++)
+      for(int s = 0; s < S; s++)
+        spatialRowNHWC[(size_t)s * C + c] = scratchRow[(size_t)c * S + s];
+  }
+}
+
 void NeuralNet::getOutput(
   ComputeHandle* h, InputBuffers* b, int numBatchEltsFilled, NNResultBuf** inputBufs, vector<NNOutput*>& outputs) {
   const int n = numBatchEltsFilled;
@@ -115,7 +133,7 @@ void NeuralNet::getOutput(
   const kbhost::NetDims& d = h->dims;
   const size_t S = (size_t)d.nnXLen * d.nnYLen;
   for(int row = 0; row < n; row++)
-    kbhost::packRow(
+    packRow(
       d, inputBufs[row], h->inputsUseNHWC, b->spatial.data() + b->singleInputElts * row,
       b->global.data() + (size_t)d.numGlobalFeatures * row, b->scratch.data());
   // SGF metadata rows exactly for nets with the encoder (eigenbackend.cpp:2462-2472)

@@ -33,6 +33,7 @@ def lib():
         L.ko_model_info.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]
         L.ko_forward.argtypes = [ctypes.c_void_p, ctypes.c_int] + [ctypes.c_void_p] * 8
         L.ko_forward_meta.argtypes = [ctypes.c_void_p, ctypes.c_int] + [ctypes.c_void_p] * 9
+        L.ko_trunk_streams.argtypes = [ctypes.c_void_p, ctypes.c_int] + [ctypes.c_void_p] * 4
         L.ko_model_meta_channels.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]
         L.ko_eval_layer.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_int, ctypes.c_int] + [ctypes.c_void_p] * 3
         _lib = L
@@ -84,6 +85,19 @@ class OracleModel:
         return out
 
 
+def trunk_streams(model: OracleModel, spatial: np.ndarray, glob: np.ndarray, meta: np.ndarray | None = None) -> np.ndarray:
+    """[numBlocks + 1][n][Y][X][trunkC]: the residual stream entering each block of the trunk and leaving the last."""
+    n = spatial.shape[0]
+    S = model.nn_x * model.nn_y
+    spatial = np.ascontiguousarray(spatial, np.float32).reshape(n, S, model.in_c)
+    glob = np.ascontiguousarray(glob, np.float32).reshape(n, model.in_global_c)
+    if meta is not None:
+        meta = np.ascontiguousarray(meta, np.float32)
+    out = np.empty((model.num_blocks + 1, n, model.nn_y, model.nn_x, model.trunk_c), np.float32)
+    _check(lib().ko_trunk_streams(model.h, n, _ptr(spatial), _ptr(glob), _ptr(meta), _ptr(out)), "ko_trunk_streams")
+    return out
+
+
 def eval_layer(blob: bytes, x: np.ndarray, mask: np.ndarray | None, out_c: int) -> np.ndarray:
     """x [n,Y,X,C] NHWC, mask [n,Y,X] -> [n,Y,X,out_c]."""
     n, ylen, xlen, _ = x.shape
@@ -96,3 +110,16 @@ def eval_layer(blob: bytes, x: np.ndarray, mask: np.ndarray | None, out_c: int) 
 
 def num_threads() -> int:
     return int(lib().ko_num_threads())
+
+
+def set_num_threads(n: int) -> None:
+    """OpenMP threads of forward passes started by the calling thread from now on."""
+    if lib().ko_set_num_threads(int(n)) != 0:
+        raise RuntimeError("ko_set_num_threads failed")
+
+
+def set_storage_emulation(storage: str | None, conv_inputs: bool = True, streams: bool = True) -> None:
+    """Rounds the chosen tensors to "fp16" / "bf16" where a reduced-precision backend stores them (None: off).  For
+    measuring precision floors only; process-wide."""
+    code = {None: 0, "fp16": 1, "bf16": 2}[storage]
+    lib().ko_set_storage_emulation(code, (1 if conv_inputs else 0) | (2 if streams else 0))

@@ -61,6 +61,39 @@ def parity_metrics(got, ref, mask, score_mult=20.0):
         kl[i] = float(np.sum(pr * (np.log(pr + 1e-30) - np.log(pg + 1e-30))))
         pmax[i] = float(np.abs(pg - pr).max())
     res["policy_kl"], res["policy_max"] = kl, pmax
-    og, orf = np.tanh(got["ownership"].astype(np.float64)), np.tanh(ref["ownership"].astype(np.float64))
-    res["ownership"] = (np.abs(og - orf) * (mask > 0.5)).max(axis=1)
+    if "ownership" in got and "ownership" in ref:
+        og, orf = np.tanh(got["ownership"].astype(np.float64)), np.tanh(ref["ownership"].astype(np.float64))
+        res["ownership"] = (np.abs(og - orf) * (mask > 0.5)).max(axis=1)
     return res
+
+
+def round_storage(a, dtype):
+    """fp32 array rounded to the nearest value of `dtype` ("fp16" or "bf16", ties to even), returned as fp32."""
+    a = np.ascontiguousarray(a, np.float32)
+    if dtype == "fp16":
+        return a.astype(np.float16).astype(np.float32)
+    if dtype == "bf16":
+        u = a.view(np.uint32).astype(np.uint64)
+        u = ((u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000).astype(np.uint32)
+        return u.view(np.float32).reshape(a.shape)
+    raise ValueError(dtype)
+
+
+def device_weights(tree, dtype):
+    """The model as the CUDA path holds it in reduced precision: the weights of every convolution that runs on the matrix
+    units rounded to `dtype`; the last 1x1 convolutions of the heads (policy p2, ownership), all norms, per-board
+    matmuls and biases stay fp32 on the device."""
+    import copy
+    t = copy.deepcopy(tree)
+
+    def walk(x, key=None):
+        if isinstance(x, dict):
+            if "kY" in x and isinstance(x.get("w"), np.ndarray) and key not in ("p2Conv", "ownConv"):
+                x["w"] = round_storage(x["w"], dtype)
+            for k, v in x.items():
+                walk(v, k)
+        elif isinstance(x, list):
+            for v in x:
+                walk(v)
+    walk(t)
+    return t

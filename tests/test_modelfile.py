@@ -7,7 +7,7 @@ import pytest
 
 from katago_b200 import modelfile as mf
 
-REF_MODELS = "/root/reference/cpp/tests/models"
+REF_MODELS = os.path.join(os.environ.get("KATAGO_REFERENCE", "/root/reference"), "cpp", "tests", "models")
 REF_TOOL = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref", "modelfile_to_blob")
 
 

@@ -11,7 +11,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def _torchrun(extra, port):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
            "--master-port", str(port), os.path.join(ROOT, "bench.py")] + extra
-    env = dict(os.environ, OMP_NUM_THREADS="2")
+    env = dict(os.environ, OMP_NUM_THREADS="1")  # what torchrun itself exports to its workers
     return subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT, env=env)
 
 
@@ -23,9 +23,11 @@ def test_reference_arm_under_torchrun_prints_one_line_from_rank0():
     d = json.loads(lines[0])
     assert d["impl"] == "reference" and d["n_gpus"] == 2 and d["unit"] == "evals/s" and d["value"] > 0
     assert d["cpu_baseline"]["kind"] == "port" and d["e2e"]["h2d_bytes_per_step"] == 0
+    # the CPU arm uses every core it may run on, also under torchrun (which starts its workers with one OpenMP thread)
+    assert d["cpu_baseline"]["cores"] == len(os.sched_getaffinity(0))
 
 
-def test_max_over_ranks_and_barrier_with_gloo():
+def test_max_over_ranks_and_barrier_with_gloo(tmp_path):
     code = (
         "import os, sys; sys.path.insert(0, %r)\n"
         "import bench\n"
@@ -35,14 +37,12 @@ def test_max_over_ranks_and_barrier_with_gloo():
         "assert world == 2 and m == 2.0, (world, m)\n"
         "pg.barrier(); pg.destroy_process_group()\n"
         "print('rank', rank, 'ok')\n" % ROOT)
-    path = os.path.join(ROOT, "_work_tmp_rank_test.py")
+    path = str(tmp_path / "rank_test.py")
     with open(path, "w") as f:
         f.write(code)
-    try:
+    if True:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
                "--master-port", "29633", path]
         r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=ROOT)
         assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
         assert r.stdout.count("ok") == 2
-    finally:
-        os.remove(path)

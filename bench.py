@@ -438,7 +438,7 @@ def run_through_katago(args):
     text = (r.stdout + r.stderr).replace("\r", "\n")
     rows = []
     for line in text.splitlines():
-        m = re.search(r"numSearchThreads\s*=\s*(\d+):.*?([0-9.]+)\s*nnEvals/s", line)
+        m = re.search(r"numSearchThreads\s*=\s*(\d+):.*?nnEvals/s\s*=\s*([0-9.]+)", line)
         if m:
             rows.append({"search_threads": int(m.group(1)), "nn_evals_per_s": float(m.group(2)), "line": line.strip()[:200]})
     best = max((x["nn_evals_per_s"] for x in rows), default=None)

@@ -27,6 +27,7 @@
 #include <cuda.h>
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <vector>
 #include <algorithm>
@@ -170,6 +171,13 @@ struct ConvTcArgs {
   int bSlotBytes;  // BN * 128
   int numA, numB;  // ring depths
   int pair;        // 1: CTA pairs (cluster of 2, cta_group::2 MMAs over 256 rows); bSlotBytes then holds half a weight tile
+  // Per-tile dependencies (kernel variant DEPS): depCtr, if set, holds one counter per 128-row tile of the convolution
+  // launched just before this one; a tile's inputs are ready when the counters of its row tile and both neighbours have
+  // reached depTarget, and the kernel then does not wait for that whole grid.  doneCtr, if set, receives one increment
+  // per epilogue warp and tile once that warp's stores of the tile have completed.
+  const uint32_t* depCtr;
+  uint32_t depTarget;
+  uint32_t* doneCtr;
   int prefillB;    // request the first weight slots before waiting for the preceding kernels
   int residentB;   // 1x1 only: all weight tiles of this CTA's channel tile stay in shared memory for the whole kernel
   uint32_t idesc;
@@ -179,15 +187,27 @@ struct ConvTcArgs {
   int tmaEpi;      // 1: outputs and residual travel through shared memory and TMA (64-channel aligned ranges)
   int* status;     // device status word: 0 = ok
   int trace;       // timeline instrumentation requested (only in builds with KB_TC_TRACE)
+  int tlSlot;      // whole-grid timeline slot + 1 (only in builds with KB_TC_TRACE)
 };
 
 // Optional timeline instrumentation (build with -DKB_TC_TRACE): CTA 0 of a launch whose shape matches the environment
 // variable KB_TC_TRACE="k:inC:outC:hasResidual" records SM cycle counts of its producer, MMA and first epilogue warp.
+// The same build also records a whole-grid timeline of up to TL_SLOTS consecutive launches (kb_debug_timeline_arm): per
+// CTA the global-timer value (ns, common to all SMs) of a few events, the SM it ran on and its tile count.
 #ifdef KB_TC_TRACE
 __device__ long long g_tcTrace[2048];
 #define TRACE(cond, slot) do { if((a.trace) && blockIdx.x == 0 && (cond)) g_tcTrace[(slot)] = clock64(); } while(0)
+constexpr int TL_SLOTS = 12, TL_CTAS = 160, TL_EVENTS = 10;
+__device__ unsigned long long g_tcTimeline[TL_SLOTS * TL_CTAS * TL_EVENTS];
+// events: 0 CTA start, 1 first dependency satisfied (producer), 2 first MMA issued, 3 last MMA committed,
+//         4 epilogue warp 2 finished its last tile, 5 CTA exit, 6 SM id, 7 tiles of this CTA,
+//         8 / 9 SM cycle counter at events 2 / 3 (with the timer values: the SM clock while the MMAs ran)
+#define TL(ev, val) do { if(a.tlSlot > 0 && blockIdx.x < TL_CTAS) g_tcTimeline[(((a.tlSlot - 1) * TL_CTAS) + blockIdx.x) * TL_EVENTS + (ev)] = (val); } while(0)
+#define TLT(ev) TL(ev, globalTimerNs())
 #else
 #define TRACE(cond, slot) do { } while(0)
+#define TL(ev, val) do { } while(0)
+#define TLT(ev) do { } while(0)
 #endif
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;
@@ -200,7 +220,8 @@ constexpr int TC_BK = 64;
 constexpr int TC_EPI_CG = KB_TC_EPI_CG;
 constexpr int TC_EPI_CG_WIDE = 3;
 constexpr int tcEpiWarps(int cg) { return 4 * cg; }
-constexpr int tcThreads(int cg) { return 64 + 32 * 4 * cg; }
+// deps: the kernel variant with per-tile dependencies carries one more warp, which polls the tile counters
+constexpr int tcThreads(int cg, bool deps = false) { return 64 + 32 * 4 * cg + (deps ? 32 : 0); }
 
 enum { TC_ERR_PRODUCER_TIMEOUT = 101, TC_ERR_MMA_TIMEOUT = 102, TC_ERR_EPILOGUE_TIMEOUT = 103 };
 
@@ -344,7 +365,11 @@ __device__ __forceinline__ void prefetchResidual(
 // TMA; the activated tensor is staged in one more unit.  A unit is computed entirely in registers first; only then
 // does the warp wait for the TMA engine to have read the previous unit's stores, so that wait is normally free.  All
 // synchronisation is inside the warp, and global memory only sees whole 64-byte row segments written by the TMA engine.
-template <typename T, int ACT, int CG>
+// CHAIN: the tile belongs to a multi-layer launch (convChainKernel): residual units are fetched only within the tile
+// (the caller requests the first ones once the tile's dependencies are known to be met), and a layer without a
+// residual still advances the phase of the ring slot's barrier, so that slot and phase stay functions of es.seq when
+// layers with and without a residual alternate.
+template <typename T, int ACT, int CG, bool CHAIN = false>
 __device__ __forceinline__ bool epilogueTileTma(
   const ConvTcArgs& a, const CUtensorMap* tmRaw, const CUtensorMap* tmAct, uint32_t tmemAcc, int q, int cg, int lane,
   int m0, int n0, float mk, const float* biasRow, EpiWarp& es, uint32_t tileIter, volatile int* abortFlag,
@@ -465,7 +490,16 @@ __device__ __forceinline__ bool epilogueTileTma(
     if(lane == 0) {
       bulkWaitRead0();
       // the slot of the unit before this one is free now: it takes the unit ring-1 ahead of this one
-      if(hasRes && es.seq > 0) prefetchResidual<CG>(tmRes, a, es, es.seq + (uint32_t)es.ring - 1u, tm, q, cg);
+      if(CHAIN) {
+        const int jn = j + es.ring - 1;
+        if(hasRes && j > 0 && jn < es.nU) {
+          const uint32_t b = (es.seq + (uint32_t)es.ring - 1u) % (uint32_t)es.ring;
+          mbarExpectTx(smemU32(&es.resFull[b]), (uint32_t)TC_UNIT_BYTES);
+          tmaLoad2d(smemU32(es.sR + (size_t)b * TC_UNIT_BYTES), tmRes, n0 + (cg + CG * jn) * 32, m0 + q * 32, smemU32(&es.resFull[b]));
+        }
+        if(!hasRes) mbarArrive(smemU32(&es.resFull[slot]));
+      }
+      else if(hasRes && es.seq > 0) prefetchResidual<CG>(tmRes, a, es, es.seq + (uint32_t)es.ring - 1u, tm, q, cg);
     }
     __syncwarp();
     TRACE(threadIdx.x == 64, 1024 + (int)(tileIter & 31u) * 16 + j * 5 + 3);
@@ -497,8 +531,8 @@ __device__ __forceinline__ bool epilogueTileTma(
 
 // One instantiation per element type, activation and epilogue kind: the epilogue is long straight-line code, and a
 // kernel that carried every variant ran measurably slower (instruction cache).
-template <typename T, int ACT, bool TMA_EPI, bool PAIR, int CG>
-__global__ void __launch_bounds__(tcThreads(CG), 1) convTcKernel(
+template <typename T, int ACT, bool TMA_EPI, bool PAIR, int CG, bool DEPS>
+__global__ void __launch_bounds__(tcThreads(CG, DEPS), 1) convTcKernel(
   const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmRes,
   const __grid_constant__ CUtensorMap tmRaw, const __grid_constant__ CUtensorMap tmAct, const ConvTcArgs a) {
   constexpr int TC_EPI_WARPS = tcEpiWarps(CG);
@@ -522,6 +556,7 @@ __global__ void __launch_bounds__(tcThreads(CG), 1) convTcKernel(
   uint64_t* resFull = accEmpty + 2;   // [TC_EPI_WARPS][TC_MAX_RING]
   uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(resFull + TC_EPI_WARPS * TC_MAX_RING);
   volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
+  volatile int* gateTiles = abortFlag + 1;  // per-tile dependencies: how many of this CTA's tiles are known to be ready
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int numNTiles = a.outC / a.BN;
@@ -540,12 +575,18 @@ __global__ void __launch_bounds__(tcThreads(CG), 1) convTcKernel(
 
   gridDepLaunch();
   if(threadIdx.x == 0) {
+    TLT(0);
+#ifdef KB_TC_TRACE
+    { unsigned smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid)); TL(6, (unsigned long long)smid); }
+    { int nt = 0; for(int t = tm.first; t < numTiles; t += tm.step) nt++; TL(7, (unsigned long long)nt); }
+#endif
     for(int s = 0; s < a.numA; s++) { mbarInit(smemU32(&fullA[s]), 1); mbarInit(smemU32(&emptyA[s]), 1); }
     for(int s = 0; s < a.numB; s++) { mbarInit(smemU32(&fullB[s]), 1); mbarInit(smemU32(&emptyB[s]), 1); }
     // the leader's accumulator-drained barrier collects the epilogue warps of both CTAs of a pair
     for(int s = 0; s < 2; s++) { mbarInit(smemU32(&accFull[s]), 1); mbarInit(smemU32(&accEmpty[s]), PAIR ? 2 * TC_EPI_WARPS : TC_EPI_WARPS); }
     for(int s = 0; s < TC_EPI_WARPS * TC_MAX_RING; s++) mbarInit(smemU32(&resFull[s]), 1);
     *abortFlag = 0;
+    *gateTiles = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -600,10 +641,23 @@ __global__ void __launch_bounds__(tcThreads(CG), 1) convTcKernel(
         for(int i = 0; i < prefilled; i++) loadB((uint32_t)i, i / taps, (i % taps) * a.outC + n0);
       }
       // everything above touched only weights; the activations belong to the kernels before this one
-      gridDepWait();
+      const bool tileDeps = DEPS && a.depCtr != nullptr;
+      if(!tileDeps) gridDepWait();
       int issuedB = 0;  // weight slots of this CTA in issue order
       for(int t = tm.first; t < numTiles && ok; t += tm.step) {
         const int m0 = tm.m0(t), n0 = tm.nTile(t) * a.BN;
+        if(tileDeps) {
+          // the dependency warp polls the counters ahead of time and publishes how many tiles are ready
+          const int need = (t - tm.first) / tm.step + 1;
+          uint32_t spins = 0;
+          while(*gateTiles < need) {
+            if((++spins & 63u) == 0u && *abortFlag) { ok = false; break; }
+          }
+          if(!ok) break;
+          asm volatile("fence.acq_rel.cta;" ::: "memory");
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
+        if(t == tm.first) TLT(1);
         for(int kc = 0; kc < a.kChunks && ok; kc++) {
           if(!mbarWait(smemU32(&emptyA[sa]), phA ^ 1u, abortFlag)) { ok = false; break; }
           TRACE(true, ((t - tm.first) / tm.step) * 16 + kc);
@@ -662,6 +716,7 @@ __global__ void __launch_bounds__(tcThreads(CG), 1) convTcKernel(
         uint32_t accumulate = 0;
         for(int kc = 0; kc < a.kChunks && ok; kc++) {
           if(!mbarWait(smemU32(&fullA[sa]), phA, abortFlag)) { ok = false; break; }
+          if(it == 0 && kc == 0) { TLT(2); TL(8, (unsigned long long)clock64()); }
           TRACE(true, 256 + it * 16 + 1 + kc);
           const uint32_t aLo = aLoBase + sa * aSlot16;
           if(taps == 9) {
@@ -707,12 +762,14 @@ __global__ void __launch_bounds__(tcThreads(CG), 1) convTcKernel(
           if(++sa == (uint32_t)a.numA) { sa = 0; phA ^= 1u; }
         }
         if(ok) commit(&accFull[buf]);
+        TLT(3);
+        TL(9, (unsigned long long)clock64());
         TRACE(true, 256 + it * 16 + 15);
       }
       if(!ok && !*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, TC_ERR_MMA_TIMEOUT); }
     }
   }
-  else {
+  else if(warp < 2 + TC_EPI_WARPS) {
     // ---------------- Epilogue: warps 2..; TMEM lane quarter = warp % 4 ----------------
     const int q = warp & 3;
     const int cg = (warp - 2) >> 2;  // which of the quarter's warps: takes units cg, cg + CG, ...
@@ -724,7 +781,11 @@ __global__ void __launch_bounds__(tcThreads(CG), 1) convTcKernel(
     es.ring = a.ep.residual ? a.resRing : 2;
     es.seq = 0;
     uint32_t it = 0;
-    gridDepWait();  // mask, per-board bias, residual and the output buffers belong to the kernels before this one
+    // mask, per-board bias, residual and the output buffers belong to the kernels before this one; with per-tile
+    // dependencies nothing of a tile is written before the producer has seen its row tiles done (the accumulator
+    // only fills after that), and the residual comes from a kernel further back, which has completed
+    if(!(DEPS && a.depCtr != nullptr)) gridDepWait();
+    int prevRowTile = -1;  // tile whose completion this warp still has to report
     for(int t = tm.first; t < numTiles; t += tm.step, it++) {
       const uint32_t buf = it & 1u;
       const int m0 = tm.m0(t), n0 = tm.nTile(t) * a.BN;
@@ -776,11 +837,51 @@ __global__ void __launch_bounds__(tcThreads(CG), 1) convTcKernel(
         if(PAIR) mbarArriveCluster(pairLeaderAddr(smemU32(&accEmpty[buf])));
         else mbarArrive(smemU32(&accEmpty[buf]));
       }
+      if(DEPS && TMA_EPI && a.doneCtr != nullptr && lane == 0) {
+        if(a.kY == 3) {
+          // a 3x3 convolution's epilogue warps idle until the next accumulator is full: wait here for this tile's
+          // stores to reach memory and report the tile at once
+          bulkWaitAll();
+          redReleaseGpuAdd(a.doneCtr + m0 / TC_BM, 1u);
+        }
+        else {
+          // epilogue-bound kernels report one tile late: this tile's es.nU store groups may still be in flight,
+          // everything older has reached memory
+          if(prevRowTile >= 0) {
+            bulkWaitPending(es.nU);
+            redReleaseGpuAdd(a.doneCtr + prevRowTile, 1u);
+          }
+          prevRowTile = m0 / TC_BM;
+        }
+      }
     }
     if(lane == 0) bulkWaitAll();  // outstanding tile stores must complete before the CTA's shared memory goes away
+    if(threadIdx.x == 64) TLT(4);
+    if(DEPS && TMA_EPI && a.doneCtr != nullptr && lane == 0 && prevRowTile >= 0) {
+      redReleaseGpuAdd(a.doneCtr + prevRowTile, 1u);
+    }
+  }
+  else if(DEPS && lane == 0 && a.depCtr != nullptr) {
+    // ---------------- dependency gate (its own warp: a thread that spins on global memory shares no instruction stream
+    // with the producer) ----------------
+    // The rows a tile reads (halo included) and the rows it will overwrite were last touched by the previous
+    // convolution's row tiles rt-1 .. rt+1: wait for their counters, tile after tile, ahead of the producer.
+    const int lastRowTile = a.g.rowsPad / TC_BM - 1;
+    int ready = 0;
+    for(int t = tm.first; t < numTiles; t += tm.step) {
+      const int rt = tm.m0(t) / TC_BM;
+      if(!waitTilesDone(a.depCtr, rt > 0 ? rt - 1 : 0, rt < lastRowTile ? rt + 1 : lastRowTile, a.depTarget, abortFlag, a.status)) {
+        if(!*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, TC_ERR_PRODUCER_TIMEOUT); }
+        break;
+      }
+      asm volatile("fence.acq_rel.cta;" ::: "memory");
+      *gateTiles = ++ready;
+    }
   }
 
   // ---------------- common exit ----------------
+  // a kernel that ran on per-tile dependencies still completes only after the grid before it
+  if(DEPS && a.depCtr != nullptr && threadIdx.x == 0) gridDepWait();
   tcFenceBefore();
   __syncthreads();
   if(*abortFlag && threadIdx.x == 0) {
@@ -797,10 +898,366 @@ __global__ void __launch_bounds__(tcThreads(CG), 1) convTcKernel(
     if(PAIR) tmemDeallocPair(tmemBase, a.tmemCols);
     else tmemDealloc(tmemBase, a.tmemCols);
   }
+  if(threadIdx.x == 0) TLT(5);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Multi-layer launch ("chain"): one persistent grid runs several consecutive convolutions.
+//
+// A stand-alone launch pays, per CTA and layer, for its start-up (barriers, TMEM, first loads), for the epilogue of its
+// last tile with the tensor pipe idle, for the hand-over of the SM to the next launch, and for the round of tiles that
+// does not fill the machine.  Here a CTA never leaves: all tiles of all layers of the chain form one list that the CTAs
+// take in turn (tile i of the list belongs to CTA i mod grid), so the epilogue of a layer's last tile overlaps the
+// MMAs of the next layer's first one exactly as it does between two tiles of one layer, and the load balances over
+// the whole chain instead of over each layer.
+//
+// What replaces the launch boundary: per-tile counters in global memory.  The epilogue warps of a tile add to the
+// counter of its row tile once their stores have reached memory (red.release.gpu after cp.async.bulk.wait_group); the
+// dependency warp of the CTA that will work on row tile r of the next layer waits until the counters of row tiles
+// r-1, r, r+1 of the layer before have reached their target (the rows a 3x3 tile reads, and all readers of the rows
+// it overwrites in buffers the blocks reuse), then lets the producer request that tile's loads.  A tile only ever
+// waits for tiles earlier in the list and every CTA works through its part of the list in order, so with all CTAs
+// resident (grid <= number of SMs, one CTA per SM) the waits cannot form a cycle; all of them are bounded like every
+// other wait here.  The counters are zeroed by the host before the launch.
+//
+// Restrictions (the engine only builds chains that meet them): staged (TMA) epilogue, single CTAs, the same tile width
+// and activation in every layer, per-layer tensor maps and arguments in device memory.
+
+constexpr int CHAIN_MAX_LAYERS = 16;
+struct alignas(128) ChainLayer {
+  CUtensorMap tmA, tmB, tmRes, tmRaw, tmAct;
+  ConvTcArgs a;  // a.g is replaced by the launch's geometry; ring sizes and slot strides come from ChainCfg
+};
+struct ChainCfg {
+  int numLayers;
+  Geom g;
+  int numA, numB;        // ring depths, the same for every layer
+  int aSlotStride;       // bytes between activation slots (>= the largest layer's halo tile)
+  int bSlotStride;       // bytes between weight slots
+  int epiWarpBytes;
+  uint32_t tmemCols;
+  int* status;
+  int tlSlot;
+};
+
+template <typename T, int ACT>
+__global__ void __launch_bounds__(tcThreads(TC_EPI_CG, true), 1) convChainKernel(const ChainLayer* __restrict__ layers, const ChainCfg c) {
+  constexpr int CG = TC_EPI_CG;
+  constexpr int TC_EPI_WARPS = tcEpiWarps(CG);
+  constexpr int TC_MAX_RING = tcMaxRing(CG);
+  extern __shared__ uint8_t smemRaw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* smemA = smem;
+  uint8_t* smemB = smemA + (size_t)c.numA * c.aSlotStride;
+  uint8_t* smemR = smemB + (size_t)c.numB * c.bSlotStride;
+  ConvTcArgs* sArgs = reinterpret_cast<ConvTcArgs*>(smemR + (size_t)TC_EPI_WARPS * c.epiWarpBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sArgs + CHAIN_MAX_LAYERS);
+  uint64_t* fullA = bars;
+  uint64_t* emptyA = fullA + c.numA;
+  uint64_t* fullB = emptyA + c.numA;
+  uint64_t* emptyB = fullB + c.numB;
+  uint64_t* accFull = emptyB + c.numB;
+  uint64_t* accEmpty = accFull + 2;
+  uint64_t* resFull = accEmpty + 2;   // [TC_EPI_WARPS][TC_MAX_RING]
+  uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(resFull + TC_EPI_WARPS * TC_MAX_RING);
+  volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
+  volatile int* gateItems = abortFlag + 1;  // how many of this CTA's tiles (over all layers) have their dependencies met
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int grid = (int)gridDim.x;
+  const int rowTiles = c.g.rowsPad / TC_BM;
+#ifdef KB_TC_TRACE
+  struct { int trace, tlSlot; } a = {0, c.tlSlot};  // what the timeline macros look at
+#endif
+
+  gridDepLaunch();
+  // every layer's arguments into shared memory (the roles read them in their inner loops)
+  for(int i = threadIdx.x; i < c.numLayers * (int)(sizeof(ConvTcArgs) / 4); i += blockDim.x)
+    reinterpret_cast<uint32_t*>(sArgs)[i] = reinterpret_cast<const uint32_t*>(&layers[i / (int)(sizeof(ConvTcArgs) / 4)].a)[i % (int)(sizeof(ConvTcArgs) / 4)];
+  if(threadIdx.x == 0) {
+    TLT(0);
+#ifdef KB_TC_TRACE
+    { unsigned smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid)); TL(6, (unsigned long long)smid); }
+#endif
+    for(int s = 0; s < c.numA; s++) { mbarInit(smemU32(&fullA[s]), 1); mbarInit(smemU32(&emptyA[s]), 1); }
+    for(int s = 0; s < c.numB; s++) { mbarInit(smemU32(&fullB[s]), 1); mbarInit(smemU32(&emptyB[s]), 1); }
+    for(int s = 0; s < 2; s++) { mbarInit(smemU32(&accFull[s]), 1); mbarInit(smemU32(&accEmpty[s]), TC_EPI_WARPS); }
+    for(int s = 0; s < TC_EPI_WARPS * TC_MAX_RING; s++) mbarInit(smemU32(&resFull[s]), 1);
+    *abortFlag = 0;
+    *gateItems = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if(warp == 1) { tmemAlloc(smemU32(tmemSlot), c.tmemCols); tmemRelinquish(); }
+  tcFenceBefore();
+  __syncthreads();
+  tcFenceAfter();
+  const uint32_t tmemBase = *tmemSlot;
+
+  // The list of this CTA's tiles: for L in layers, t = first(L), first(L) + grid, ... with first(L) chosen so that the
+  // tiles of all layers, numbered through, go to the CTAs in turn.
+  auto numTilesOf = [&](int L) { return rowTiles * (sArgs[L].outC / sArgs[L].BN); };
+  auto firstOf = [&](int base) { int f = ((int)blockIdx.x - base) % grid; return f < 0 ? f + grid : f; };
+
+  if(warp == 0) {
+    // ---------------- TMA producer ----------------
+    if(lane == 0) {
+      uint32_t sa = 0, phA = 0, sb = 0, phB = 0;
+      bool ok = true;
+      int item = 0, base = 0;
+      gridDepWait();  // the chain's inputs belong to the kernels before this launch
+      for(int L = 0; L < c.numLayers && ok; L++) {
+        const ConvTcArgs& la = sArgs[L];
+        const CUtensorMap* tmA = &layers[L].tmA;
+        const CUtensorMap* tmB = &layers[L].tmB;
+        const int numTiles = numTilesOf(L), numNTiles = la.outC / la.BN, taps = la.kY * la.kX;
+        const uint32_t aBytes = (uint32_t)la.aSlotBytes, bBytes = (uint32_t)la.bSlotBytes;
+        for(int t = firstOf(base); t < numTiles && ok; t += grid, item++) {
+          const int m0 = (t / numNTiles) * TC_BM, n0 = (t % numNTiles) * la.BN;
+          {
+            uint32_t spins = 0;
+            while(*gateItems <= item) {
+              if((++spins & 63u) == 0u && *abortFlag) { ok = false; break; }
+            }
+            if(!ok) break;
+            asm volatile("fence.acq_rel.cta;" ::: "memory");
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+          }
+          if(item == 0) TLT(1);
+          for(int kc = 0; kc < la.kChunks && ok; kc++) {
+            if(!mbarWait(smemU32(&emptyA[sa]), phA ^ 1u, abortFlag)) { ok = false; break; }
+            {
+              const uint32_t bar = smemU32(&fullA[sa]);
+              mbarExpectTx(bar, aBytes);
+              tmaLoad2d(smemU32(smemA + (size_t)sa * c.aSlotStride), tmA, kc * TC_BK, m0 - la.haloPad, bar);
+            }
+            if(++sa == (uint32_t)c.numA) { sa = 0; phA ^= 1u; }
+            for(int tap = 0; tap < taps; tap++) {
+              if(!mbarWait(smemU32(&emptyB[sb]), phB ^ 1u, abortFlag)) { ok = false; break; }
+              const uint32_t bar = smemU32(&fullB[sb]);
+              mbarExpectTx(bar, bBytes);
+              tmaLoad2d(smemU32(smemB + (size_t)sb * c.bSlotStride), tmB, kc * TC_BK, tap * la.outC + n0, bar);
+              if(++sb == (uint32_t)c.numB) { sb = 0; phB ^= 1u; }
+            }
+          }
+        }
+        base += numTiles;
+      }
+      if(!ok && !*abortFlag) { *abortFlag = 1; atomicCAS(c.status, 0, TC_ERR_PRODUCER_TIMEOUT); }
+    }
+  }
+  else if(warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if(lane == 0) {
+      const uint32_t descHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
+      const uint32_t aLoBase = ((smemU32(smemA) & 0x3FFFFu) >> 4) | (1u << 16);
+      const uint32_t bLoBase = ((smemU32(smemB) & 0x3FFFFu) >> 4) | (1u << 16);
+      const uint32_t aSlot16 = (uint32_t)c.aSlotStride >> 4, bSlot16 = (uint32_t)c.bSlotStride >> 4;
+      uint32_t sa = 0, phA = 0, sb = 0, phB = 0, it = 0;
+      bool ok = true;
+      int base = 0;
+      for(int L = 0; L < c.numLayers && ok; L++) {
+        const ConvTcArgs& la = sArgs[L];
+        const int numTiles = numTilesOf(L), taps = la.kY * la.kX, kChunks = la.kChunks, BN = la.BN;
+        const uint32_t idesc = la.idesc;
+        uint32_t tapOff[9];
+#pragma unroll
+        for(int tap = 0; tap < 9; tap++) {
+          const int dy = tap / 3 - 1, dx = tap % 3 - 1;
+          tapOff[tap] = (taps == 9) ? (uint32_t)(la.haloPad + dy * c.g.RW + dx) * 8u : 0u;
+        }
+        for(int t = firstOf(base); t < numTiles && ok; t += grid, it++) {
+          const uint32_t buf = it & 1u;
+          if(!mbarWait(smemU32(&accEmpty[buf]), ((it >> 1) & 1u) ^ 1u, abortFlag)) { ok = false; break; }
+          tcFenceAfter();
+          const uint32_t dTmem = tmemBase + buf * (uint32_t)BN;
+          uint32_t accumulate = 0;
+          for(int kc = 0; kc < kChunks && ok; kc++) {
+            if(!mbarWait(smemU32(&fullA[sa]), phA, abortFlag)) { ok = false; break; }
+            if(it == 0 && kc == 0) { TLT(2); TL(8, (unsigned long long)clock64()); }
+            const uint32_t aLo = aLoBase + sa * aSlot16;
+            if(taps == 9) {
+#pragma unroll
+              for(int tap = 0; tap < 9; tap++) {
+                if(!mbarWait(smemU32(&fullB[sb]), phB, abortFlag)) { ok = false; break; }
+                tcFenceAfter();
+                const uint32_t aT = aLo + tapOff[tap], bT = bLoBase + sb * bSlot16;
+#pragma unroll
+                for(int k = 0; k < TC_BK / 16; k++) {
+                  ummaLoHi(dTmem, aT + 2 * k, bT + 2 * k, descHi, idesc, accumulate);
+                  accumulate = 1;
+                }
+                ummaCommit(smemU32(&emptyB[sb]));
+                if(++sb == (uint32_t)c.numB) { sb = 0; phB ^= 1u; }
+              }
+            }
+            else {
+              if(!mbarWait(smemU32(&fullB[sb]), phB, abortFlag)) { ok = false; break; }
+              tcFenceAfter();
+              const uint32_t bT = bLoBase + sb * bSlot16;
+#pragma unroll
+              for(int k = 0; k < TC_BK / 16; k++) {
+                ummaLoHi(dTmem, aLo + 2 * k, bT + 2 * k, descHi, idesc, accumulate);
+                accumulate = 1;
+              }
+              ummaCommit(smemU32(&emptyB[sb]));
+              if(++sb == (uint32_t)c.numB) { sb = 0; phB ^= 1u; }
+            }
+            ummaCommit(smemU32(&emptyA[sa]));
+            if(++sa == (uint32_t)c.numA) { sa = 0; phA ^= 1u; }
+          }
+          if(ok) ummaCommit(smemU32(&accFull[buf]));
+          TLT(3);
+          TL(9, (unsigned long long)clock64());
+          TL(7, (unsigned long long)(it + 1));
+        }
+        base += numTiles;
+      }
+      if(!ok && !*abortFlag) { *abortFlag = 1; atomicCAS(c.status, 0, TC_ERR_MMA_TIMEOUT); }
+    }
+  }
+  else if(warp < 2 + TC_EPI_WARPS) {
+    // ---------------- Epilogue ----------------
+    const int q = warp & 3;
+    const int cg = (warp - 2) >> 2;
+    EpiWarp es;
+    es.sR = smemR + (size_t)(warp - 2) * c.epiWarpBytes;
+    es.sO = es.sR + (size_t)(c.epiWarpBytes - TC_UNIT_BYTES);
+    es.resFull = resFull + (warp - 2) * TC_MAX_RING;
+    es.ring = 2;
+    es.seq = 0;
+    uint32_t it = 0;
+    int base = 0;
+    bool alive = true;
+    TileMap tm = {};  // not used by the chain epilogue (it fetches residual units within the tile only)
+    gridDepWait();
+    for(int L = 0; L < c.numLayers && alive; L++) {
+      const ConvTcArgs& la = sArgs[L];
+      const CUtensorMap* tmRes = &layers[L].tmRes;
+      const CUtensorMap* tmRaw = &layers[L].tmRaw;
+      const CUtensorMap* tmAct = &layers[L].tmAct;
+      const int numTiles = numTilesOf(L), numNTiles = la.outC / la.BN;
+      es.nU = (la.BN / 32 - cg + CG - 1) / CG;
+      const bool hasRes = la.ep.residual != nullptr;
+      int prevRowTile = -1;  // tile of this layer whose completion this warp still has to report
+      for(int t = firstOf(base); t < numTiles; t += grid, it++) {
+        const uint32_t buf = it & 1u;
+        const int m0 = (t / numNTiles) * TC_BM, n0 = (t % numNTiles) * la.BN;
+        const int m = m0 + q * 32 + lane;
+        const float mk = la.ep.mask ? la.ep.mask[m] : 1.0f;
+        const int bIdx = min(m / c.g.PB, c.g.n - 1);
+        const float* biasRow = la.ep.biasNC ? la.ep.biasNC + (size_t)bIdx * la.outC : nullptr;
+        if(hasRes && lane == 0 && es.nU > 0) {
+          // The residual may come from a layer of this chain: fetch it only once this tile's dependencies are known to
+          // be met (they cover every row the residual unit holds).  The staging slots must be free as well.
+          uint32_t spins = 0;
+          bool gateOk = true;
+          while(*gateItems <= (int)it) {
+            if((++spins & 63u) == 0u && *abortFlag) { gateOk = false; break; }
+          }
+          if(gateOk) {
+            asm volatile("fence.acq_rel.cta;" ::: "memory");
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            bulkWaitRead0();
+            for(int k = 0; k < es.ring && k < es.nU; k++) {
+              const uint32_t b = (es.seq + (uint32_t)k) % (uint32_t)es.ring;
+              mbarExpectTx(smemU32(&es.resFull[b]), (uint32_t)TC_UNIT_BYTES);
+              tmaLoad2d(smemU32(es.sR + (size_t)b * TC_UNIT_BYTES), tmRes, n0 + (cg + CG * k) * 32, m0 + q * 32, smemU32(&es.resFull[b]));
+            }
+          }
+        }
+        __syncwarp();
+        bool ok = mbarWait(smemU32(&accFull[buf]), (it >> 1) & 1u, abortFlag);
+        ok = __all_sync(0xffffffffu, ok);
+        if(!ok) {
+          if(lane == 0 && !*abortFlag) { *abortFlag = 1; atomicCAS(c.status, 0, TC_ERR_EPILOGUE_TIMEOUT); }
+          alive = false;
+          break;
+        }
+        tcFenceAfter();
+        const uint32_t acc = tmemBase + buf * (uint32_t)la.BN;
+        float rowSumsq = 0.0f;
+        const bool ok2 = epilogueTileTma<T, ACT, CG, true>(la, tmRaw, tmAct, acc, q, cg, lane, m0, n0, mk, biasRow, es, it, abortFlag, la.ep.scale, la.ep.bias, tmRes, tm, 1.0f, rowSumsq);
+        if(!ok2) {
+          if(lane == 0 && !*abortFlag) { *abortFlag = 1; atomicCAS(c.status, 0, TC_ERR_EPILOGUE_TIMEOUT); }
+          alive = false;
+          break;
+        }
+        tcFenceBefore();
+        __syncwarp();
+        if(lane == 0) mbarArrive(smemU32(&accEmpty[buf]));
+        if(la.doneCtr != nullptr && lane == 0) {
+          if(la.kY == 3) {
+            // epilogue warps of a 3x3 layer idle until the next accumulator is full: report the tile at once
+            bulkWaitAll();
+            redReleaseGpuAdd(la.doneCtr + m0 / TC_BM, 1u);
+          }
+          else {
+            // epilogue-bound layers report one tile late: this tile's stores may still be in flight
+            if(prevRowTile >= 0) {
+              bulkWaitPending(es.nU);
+              redReleaseGpuAdd(la.doneCtr + prevRowTile, 1u);
+            }
+            prevRowTile = m0 / TC_BM;
+          }
+        }
+      }
+      if(la.doneCtr != nullptr && lane == 0 && prevRowTile >= 0) {
+        bulkWaitAll();
+        redReleaseGpuAdd(la.doneCtr + prevRowTile, 1u);
+      }
+      base += numTiles;
+    }
+    if(lane == 0) bulkWaitAll();
+    if(threadIdx.x == 64) TLT(4);
+  }
+  else if(lane == 0) {
+    // ---------------- dependency gate ----------------
+    gridDepWait();
+    const int lastRowTile = rowTiles - 1;
+    int ready = 0, base = 0;
+    bool ok = true;
+    for(int L = 0; L < c.numLayers && ok; L++) {
+      const ConvTcArgs& la = sArgs[L];
+      const int numTiles = numTilesOf(L), numNTiles = la.outC / la.BN;
+      for(int t = firstOf(base); t < numTiles; t += grid) {
+        if(la.depCtr != nullptr) {
+          const int rt = t / numNTiles;
+          if(!waitTilesDone(la.depCtr, rt > 0 ? rt - 1 : 0, rt < lastRowTile ? rt + 1 : lastRowTile, la.depTarget, abortFlag, c.status)) {
+            if(!*abortFlag) { *abortFlag = 1; atomicCAS(c.status, 0, TC_ERR_PRODUCER_TIMEOUT); }
+            ok = false;
+            break;
+          }
+        }
+        asm volatile("fence.acq_rel.cta;" ::: "memory");
+        *gateItems = ++ready;
+      }
+      base += numTiles;
+    }
+    if(!ok) *gateItems = 1 << 30;  // release the threads that spin on the gate; they leave through the abort flag
+  }
+
+  // ---------------- common exit ----------------
+  tcFenceBefore();
+  __syncthreads();
+  if(*abortFlag && threadIdx.x == 0) {
+    const uint64_t t0 = globalTimerNs();
+    while(globalTimerNs() - t0 < 2000000ull) { __nanosleep(1000); }
+  }
+  __syncthreads();
+  if(warp == 1) {
+    tcFenceAfter();
+    tmemDealloc(tmemBase, c.tmemCols);
+  }
+  if(threadIdx.x == 0) TLT(5);
 }
 
 // ---------------------------------------------------------------------------------------------
 // Host side
+
+#ifdef KB_TC_TRACE
+static int g_tlLaunch = 0, g_tlFirst = 1 << 30;  // tensor-core convolution launches since arming; first recorded launch
+#endif
 
 typedef CUresult (*EncodeTiledFn)(
   CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -821,27 +1278,33 @@ static EncodeTiledFn getEncodeTiled() {
 
 // Kernel variants by (element type, activation, epilogue kind).
 typedef void (*ConvTcKernelFn)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, ConvTcArgs);
-template <typename T, bool TMA_EPI, bool PAIR, int CG>
+template <typename T, bool TMA_EPI, bool PAIR, int CG, bool DEPS>
 static ConvTcKernelFn kernelForAct(int act) {
   switch(act) {
-    case KB_ACT_RELU: return convTcKernel<T, KB_ACT_RELU, TMA_EPI, PAIR, CG>;
-    case KB_ACT_MISH: return convTcKernel<T, KB_ACT_MISH, TMA_EPI, PAIR, CG>;
-    case KB_ACT_SILU: return convTcKernel<T, KB_ACT_SILU, TMA_EPI, PAIR, CG>;
-    case KB_ACT_MISH_SCALE8: return convTcKernel<T, KB_ACT_MISH_SCALE8, TMA_EPI, PAIR, CG>;
-    // the SwiGLU epilogue exists with the default warp count only
-    case KB_ACT_SWIGLU_PAIRS: return CG == TC_EPI_CG ? convTcKernel<T, KB_ACT_SWIGLU_PAIRS, TMA_EPI, PAIR, TC_EPI_CG> : nullptr;
-    default: return convTcKernel<T, KB_ACT_IDENTITY, TMA_EPI, PAIR, CG>;
+    case KB_ACT_RELU: return convTcKernel<T, KB_ACT_RELU, TMA_EPI, PAIR, CG, DEPS>;
+    case KB_ACT_MISH: return convTcKernel<T, KB_ACT_MISH, TMA_EPI, PAIR, CG, DEPS>;
+    case KB_ACT_SILU: return convTcKernel<T, KB_ACT_SILU, TMA_EPI, PAIR, CG, DEPS>;
+    case KB_ACT_MISH_SCALE8: return convTcKernel<T, KB_ACT_MISH_SCALE8, TMA_EPI, PAIR, CG, DEPS>;
+    // the SwiGLU epilogue exists with the default warp count and whole-grid dependencies only
+    case KB_ACT_SWIGLU_PAIRS: return (CG == TC_EPI_CG && !DEPS) ? convTcKernel<T, KB_ACT_SWIGLU_PAIRS, TMA_EPI, PAIR, TC_EPI_CG, false> : nullptr;
+    default: return convTcKernel<T, KB_ACT_IDENTITY, TMA_EPI, PAIR, CG, DEPS>;
   }
 }
 // The wide-epilogue variant exists for single CTAs with the staged epilogue only.
+// The per-tile-dependency variant exists for single CTAs with the staged epilogue only.
 template <typename T>
-static ConvTcKernelFn kernelForT(int act, bool tmaEpi, bool pair, int cg) {
-  if(cg != TC_EPI_CG) return (tmaEpi && !pair && cg == TC_EPI_CG_WIDE) ? kernelForAct<T, true, false, TC_EPI_CG_WIDE>(act) : nullptr;
-  if(pair) return tmaEpi ? kernelForAct<T, true, true, TC_EPI_CG>(act) : kernelForAct<T, false, true, TC_EPI_CG>(act);
-  return tmaEpi ? kernelForAct<T, true, false, TC_EPI_CG>(act) : kernelForAct<T, false, false, TC_EPI_CG>(act);
+static ConvTcKernelFn kernelForT(int act, bool tmaEpi, bool pair, int cg, bool deps) {
+  if(deps) {
+    if(!tmaEpi || pair) return nullptr;
+    return cg == TC_EPI_CG_WIDE ? kernelForAct<T, true, false, TC_EPI_CG_WIDE, true>(act)
+                                : (cg == TC_EPI_CG ? kernelForAct<T, true, false, TC_EPI_CG, true>(act) : nullptr);
+  }
+  if(cg != TC_EPI_CG) return (tmaEpi && !pair && cg == TC_EPI_CG_WIDE) ? kernelForAct<T, true, false, TC_EPI_CG_WIDE, false>(act) : nullptr;
+  if(pair) return tmaEpi ? kernelForAct<T, true, true, TC_EPI_CG, false>(act) : kernelForAct<T, false, true, TC_EPI_CG, false>(act);
+  return tmaEpi ? kernelForAct<T, true, false, TC_EPI_CG, false>(act) : kernelForAct<T, false, false, TC_EPI_CG, false>(act);
 }
-static ConvTcKernelFn kernelFor(int dt, int act, bool tmaEpi, bool pair, int cg) {
-  return dt == DT_F16 ? kernelForT<__half>(act, tmaEpi, pair, cg) : kernelForT<__nv_bfloat16>(act, tmaEpi, pair, cg);
+static ConvTcKernelFn kernelFor(int dt, int act, bool tmaEpi, bool pair, int cg, bool deps) {
+  return dt == DT_F16 ? kernelForT<__half>(act, tmaEpi, pair, cg, deps) : kernelForT<__nv_bfloat16>(act, tmaEpi, pair, cg, deps);
 }
 
 struct ConvTcPlan {
@@ -1047,7 +1510,23 @@ bool convTcSetEpilogue(ConvTcPlan* p, const Epilogue& ep) {
   return true;
 }
 
-cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epilogue& ep, int* statusWord) {
+bool convTcDepsCapable(const ConvTcPlan* p) { return p && p->tmaEpi && !p->pair; }
+int convTcKernelSize(const ConvTcPlan* p) { return p->kY; }
+int convTcDoneCount(const ConvTcPlan* p) { return (p->outC / p->BN) * tcEpiWarps(p->cg); }
+int convTcGridSize(const ConvTcPlan* p, const Geom& g) {
+  const int unitRows = p->pair ? 2 * TC_BM : TC_BM;
+  const int maxUnits = p->pair ? p->numSMs / 2 : p->numSMs;
+  const int numTiles = (g.rowsPad / unitRows) * (p->outC / p->BN);
+  int units = numTiles < maxUnits ? numTiles : maxUnits;
+  if(p->residentB) {
+    const int nt = p->outC / p->BN;
+    units = units / nt * nt;
+    if(units < nt) units = nt;
+  }
+  return p->pair ? 2 * units : units;
+}
+
+cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epilogue& ep, int* statusWord, const ConvTcDeps* deps) {
   // vector accesses in the epilogue need 16-byte aligned rows and 16-channel aligned ranges
   if(ep.outRaw && ((ep.rawStride % 8) || (ep.rawC0 % 16) || (ep.rawC1 % 16))) return cudaErrorInvalidValue;
   if(ep.outAct && ((ep.actStride % 8) || (ep.actC0 % 16) || (ep.actC1 % 16) || ((ep.actC1 - ep.actC0) > 512 && ep.act != KB_ACT_SWIGLU_PAIRS))) return cudaErrorInvalidValue;
@@ -1060,10 +1539,16 @@ cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epi
   static const bool prefillB = getenv("KB_NO_B_PREFILL") == nullptr;
   a.prefillB = prefillB ? 1 : 0;
   a.pair = p->pair;
+  a.depCtr = nullptr; a.depTarget = 0; a.doneCtr = nullptr;
   a.idesc = p->idesc; a.tmemCols = p->tmemCols;
   a.status = statusWord;
   a.trace = 0;
+  a.tlSlot = 0;
 #ifdef KB_TC_TRACE
+  {
+    const int idx = g_tlLaunch++;
+    if(idx >= g_tlFirst && idx < g_tlFirst + TL_SLOTS) a.tlSlot = idx - g_tlFirst + 1;
+  }
   if(const char* e = getenv("KB_TC_TRACE")) {
     int k = 0, ic = 0, oc = 0, r = 0;
     if(sscanf(e, "%d:%d:%d:%d", &k, &ic, &oc, &r) == 4 && k == p->kY && ic == p->inC && oc == p->outC && r == (ep.residual ? 1 : 0)) a.trace = 1;
@@ -1103,7 +1588,25 @@ cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epi
   }
   cfg.attrs = attr; cfg.numAttrs = numAttrs;
   // without an activated output the activation code is irrelevant: use the identity variant
-  ConvTcKernelFn fn = kernelFor(p->dt, ep.outAct ? ep.act : KB_ACT_IDENTITY, p->tmaEpi != 0, p->pair != 0, p->cg);
+  // Per-tile dependencies: this launch reports its tiles if asked to, and waits per tile on the convolution before it
+  // if that one reports and fills every SM (its CTAs can then only all have started once the kernels before it have
+  // left the SMs, so at most these two grids overlap).
+  bool useDeps = false;
+  if(deps && convTcDepsCapable(p) && ep.act != KB_ACT_SWIGLU_PAIRS) {
+    if(deps->done) { a.doneCtr = deps->done; useDeps = true; }
+    if(deps->wait && deps->waitPlan && convTcDepsCapable(deps->waitPlan) && convTcGridSize(deps->waitPlan, g) == p->numSMs) {
+      a.depCtr = deps->wait;
+      a.depTarget = (uint32_t)convTcDoneCount(deps->waitPlan);
+      useDeps = true;
+    }
+  }
+  {
+    static const int dbg = getenv("KB_TILE_DEPS_DEBUG") ? atoi(getenv("KB_TILE_DEPS_DEBUG")) : 0;
+    if(dbg == 1) a.depCtr = nullptr;                       // report only
+    if(dbg == 2) { a.doneCtr = nullptr; a.depTarget = 0; }  // poll only (always satisfied)
+  }
+  ConvTcKernelFn fn = kernelFor(p->dt, ep.outAct ? ep.act : KB_ACT_IDENTITY, p->tmaEpi != 0, p->pair != 0, p->cg, useDeps);
+  cfg.blockDim = dim3(tcThreads(p->cg, useDeps));
   if(!fn) return cudaErrorInvalidValue;
   {
     // opt in to the large dynamic shared memory once per variant and device
@@ -1122,8 +1625,146 @@ cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epi
   return cudaLaunchKernelEx(&cfg, fn, p->tmA, p->tmB, p->tmRes, p->tmRaw, p->tmAct, a);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Multi-layer launches: host side
+
+typedef void (*ConvChainKernelFn)(const ChainLayer*, ChainCfg);
+template <typename T>
+static ConvChainKernelFn chainKernelForT(int act) {
+  switch(act) {
+    case KB_ACT_RELU: return convChainKernel<T, KB_ACT_RELU>;
+    case KB_ACT_MISH: return convChainKernel<T, KB_ACT_MISH>;
+    case KB_ACT_SILU: return convChainKernel<T, KB_ACT_SILU>;
+    case KB_ACT_MISH_SCALE8: return convChainKernel<T, KB_ACT_MISH_SCALE8>;
+    default: return convChainKernel<T, KB_ACT_IDENTITY>;
+  }
+}
+
+struct ConvChainPlan {
+  ChainLayer* dLayers = nullptr;
+  ChainCfg cfg;
+  size_t smemBytes = 0;
+  int dt = 0, act = 0, numSMs = 148, maxNTiles = 1;
+};
+
+int convTcTileWidth(const ConvTcPlan* p) { return p->BN; }
+
+bool convChainEligible(const ConvTcPlan* p, const Epilogue& ep) {
+  if(!p || !p->tmaEpi || p->pair) return false;
+  if(ep.biasNC || ep.rowSumsq || ep.sumsqOut || ep.act == KB_ACT_SWIGLU_PAIRS) return false;
+  if((p->BN % 32) != 0) return false;
+  return true;
+}
+
+ConvChainPlan* convChainCreate(const ConvChainMember* members, int n) {
+  if(n < 2 || n > CHAIN_MAX_LAYERS) return nullptr;
+  ConvChainPlan* c = new ConvChainPlan();
+  const ConvTcPlan* p0 = members[0].plan;
+  c->dt = p0->dt;
+  c->act = members[0].ep.outAct ? members[0].ep.act : KB_ACT_IDENTITY;
+  c->numSMs = p0->numSMs;
+  std::vector<ChainLayer> h((size_t)n);
+  int aStride = 0, bStride = 0;
+  for(int i = 0; i < n; i++) {
+    const ConvTcPlan* p = members[i].plan;
+    const Epilogue& ep = members[i].ep;
+    const int act = ep.outAct ? ep.act : KB_ACT_IDENTITY;
+    // layers without an activated output run any variant; the others must agree
+    if(ep.outAct && c->act == KB_ACT_IDENTITY) c->act = act;
+    if(!convChainEligible(p, ep) || p->dt != c->dt || p->BN != p0->BN || (ep.outAct && act != c->act)) { delete c; return nullptr; }
+    ChainLayer& L = h[(size_t)i];
+    std::memset(&L, 0, sizeof(L));
+    L.tmA = p->tmA; L.tmB = p->tmB; L.tmRes = p->tmRes; L.tmRaw = p->tmRaw; L.tmAct = p->tmAct;
+    ConvTcArgs& a = L.a;
+    a.ep = ep;
+    a.inC = p->inC; a.outC = p->outC; a.kY = p->kY; a.kX = p->kX;
+    a.BN = p->BN; a.kChunks = p->kChunks; a.haloPad = p->haloPad; a.aRows = p->aRows;
+    a.aSlotBytes = p->aRows * 128; a.bSlotBytes = p->BN * 128;
+    a.idesc = p->idesc;
+    a.tmaEpi = 1;
+    a.doneCtr = (i + 1 < n) ? members[i].done : nullptr;
+    a.depCtr = (i > 0) ? members[i - 1].done : nullptr;
+    a.depTarget = (i > 0) ? (uint32_t)((members[i - 1].plan->outC / members[i - 1].plan->BN) * tcEpiWarps(TC_EPI_CG)) : 0u;
+    if((i + 1 < n && !members[i].done)) { delete c; return nullptr; }
+    aStride = std::max(aStride, (a.aSlotBytes + 1023) / 1024 * 1024);
+    bStride = std::max(bStride, (a.bSlotBytes + 1023) / 1024 * 1024);
+    c->maxNTiles = std::max(c->maxNTiles, p->outC / p->BN);
+  }
+  ChainCfg& cfg = c->cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.numLayers = n;
+  cfg.numA = 2;
+  if(const char* e = getenv("KB_CHAIN_NUMA")) { int v = atoi(e); if(v >= 2 && v <= 4) cfg.numA = v; }
+  cfg.aSlotStride = aStride;
+  cfg.bSlotStride = bStride;
+  cfg.epiWarpBytes = 3 * TC_UNIT_BYTES;  // two residual/raw units and one for the activated output
+  const int fixed = (int)(CHAIN_MAX_LAYERS * sizeof(ConvTcArgs)) + 96 * 8 + 64 + 1024;
+  const int budget = 227 * 1024 - fixed - tcEpiWarps(TC_EPI_CG) * cfg.epiWarpBytes - cfg.numA * aStride;
+  int numB = budget / bStride;
+  if(numB > 12) numB = 12;
+  if(numB < 2) { delete c; return nullptr; }
+  cfg.numB = numB;
+  c->smemBytes = (size_t)cfg.numA * aStride + (size_t)numB * bStride + (size_t)tcEpiWarps(TC_EPI_CG) * cfg.epiWarpBytes + (size_t)fixed;
+  cfg.tmemCols = 32;
+  while((int)cfg.tmemCols < 2 * p0->BN) cfg.tmemCols *= 2;
+  if(cudaMalloc(&c->dLayers, sizeof(ChainLayer) * (size_t)n) != cudaSuccess) { delete c; return nullptr; }
+  if(cudaMemcpy(c->dLayers, h.data(), sizeof(ChainLayer) * (size_t)n, cudaMemcpyHostToDevice) != cudaSuccess) { cudaFree(c->dLayers); delete c; return nullptr; }
+  return c;
+}
+
+void convChainDestroy(ConvChainPlan* c) {
+  if(!c) return;
+  if(c->dLayers) cudaFree(c->dLayers);
+  delete c;
+}
+
+cudaError_t launchConvChain(cudaStream_t st, const ConvChainPlan* c, Geom g, int* statusWord) {
+  ChainCfg cfg = c->cfg;
+  cfg.g = g;
+  cfg.status = statusWord;
+  cfg.tlSlot = 0;
+#ifdef KB_TC_TRACE
+  {
+    const int idx = g_tlLaunch++;
+    if(idx >= g_tlFirst && idx < g_tlFirst + TL_SLOTS) cfg.tlSlot = idx - g_tlFirst + 1;
+  }
+#endif
+  // every CTA must be resident at the same time: one CTA per SM, never more CTAs than SMs
+  const long long totalTiles = (long long)(g.rowsPad / TC_BM) * cfg.numLayers;
+  const int grid = (int)std::min<long long>(totalTiles, (long long)c->numSMs);
+  ConvChainKernelFn fn = c->dt == DT_F16 ? chainKernelForT<__half>(c->act) : chainKernelForT<__nv_bfloat16>(c->act);
+  {
+    static std::mutex mu;
+    static std::vector<std::pair<const void*, int>> done;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lock(mu);
+    const std::pair<const void*, int> key((const void*)fn, dev);
+    if(std::find(done.begin(), done.end(), key) == done.end()) {
+      cudaError_t e = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+      if(e != cudaSuccess) return e;
+      done.push_back(key);
+    }
+  }
+  static const bool usePdl = getenv("KB_NO_PDL") == nullptr;
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(grid); lc.blockDim = dim3(tcThreads(TC_EPI_CG, true)); lc.dynamicSmemBytes = c->smemBytes; lc.stream = st;
+  cudaLaunchAttribute attr[1];
+  int numAttrs = 0;
+  if(usePdl) {
+    attr[numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[numAttrs].val.programmaticStreamSerializationAllowed = 1;
+    numAttrs++;
+  }
+  lc.attrs = attr; lc.numAttrs = numAttrs;
+  return cudaLaunchKernelEx(&lc, fn, (const ChainLayer*)c->dLayers, cfg);
+}
+
 }  // namespace kb
 
 #ifdef KB_TC_TRACE
 extern "C" int kb_debug_trace(long long* out, int n) { return (int)cudaMemcpyFromSymbol(out, kb::g_tcTrace, sizeof(long long) * n); }
+// Records the launches number first .. first + 11 (counted over tensor-core convolution launches from this call on).
+extern "C" void kb_debug_timeline_arm(int first) { kb::g_tlLaunch = 0; kb::g_tlFirst = first; }
+extern "C" int kb_debug_timeline(unsigned long long* out, int n) { return (int)cudaMemcpyFromSymbol(out, kb::g_tcTimeline, sizeof(unsigned long long) * n); }
 #endif

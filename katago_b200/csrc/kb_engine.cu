@@ -42,6 +42,7 @@ void* Engine::alloc(size_t bytes) {
   if(bytes == 0) bytes = 16;
   cudaCheck(cudaMalloc(&p, bytes), "cudaMalloc");
   allocations_.push_back(p);
+  allocationBytes_.push_back(bytes);
   cudaCheck(cudaMemsetAsync(p, 0, bytes, stream_), "cudaMemset");
   return p;
 }
@@ -163,7 +164,11 @@ void Engine::addConvOp(const ConvDev& c, Epilogue ep, const std::string& tag) {
   if(c.tc) {
     if(!convTcSetEpilogue(c.plan, ep)) throw std::runtime_error("tensor-core convolution: shared memory budget exceeded");
     const ConvTcPlan* plan = c.plan;
-    addOp(name, flops, bytes, [plan, ep, status](cudaStream_t st, const Geom& g) { return launchConvTc(st, plan, g, ep, status); });
+    std::shared_ptr<ConvTcDeps> deps = std::make_shared<ConvTcDeps>();
+    addOp(name, flops, bytes, [plan, ep, status, deps](cudaStream_t st, const Geom& g) { return launchConvTc(st, plan, g, ep, status, deps.get()); });
+    ops_.back().tcPlan = plan;
+    ops_.back().ep = ep;
+    ops_.back().deps = deps;
   }
   else {
     ConvDev cc = c;
@@ -667,6 +672,10 @@ Engine::Engine(const Model& m, int device, int maxBatch, int X, int Y, int preci
   dt_ = precision; X_ = X; Y_ = Y; maxBatch_ = maxBatch;
   forceSimt_ = getenv("KB_FORCE_SIMT") != nullptr && atoi(getenv("KB_FORCE_SIMT")) != 0;
   graphsEnabled_ = getenv("KB_NO_GRAPH") == nullptr;
+  // 0: off; 1: 3x3 convolutions report their tiles (their epilogue warps have idle time to wait for the stores in);
+  // 2: every tensor-core convolution reports
+  tileDepsMode_ = getenv("KB_TILE_DEPS") != nullptr ? atoi(getenv("KB_TILE_DEPS")) : 0;
+  tileDeps_ = tileDepsMode_ != 0;
   chunkBoards_ = 0;  // measured on B200: 128-board chunks 9.5 ms vs 8.1 ms for the whole batch of 256 (per-launch overhead wins)
   if(const char* e = getenv("KB_CHUNK_BOARDS")) chunkBoards_ = atoi(e);
   cudaCheck(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate");
@@ -770,6 +779,8 @@ Engine::Engine(const Model& m, int device, int maxBatch, int X, int Y, int preci
     });
   }
   emitHeads(m, trunkAct_);
+  planChains();
+  if(chainPlans_.empty()) planTileDeps();
   cudaCheck(cudaStreamSynchronize(stream_), "engine setup");
 }
 
@@ -779,6 +790,7 @@ Engine::~Engine() {
   for(cudaEvent_t e : events_) cudaEventDestroy(e);
   for(ConvTcPlan* p : tcPlans_) convTcDestroy(p);
   for(AttnTcPlan* p : attnPlans_) attentionTcDestroy(p);
+  for(ConvChainPlan* p : chainPlans_) convChainDestroy(p);
   for(auto& kv : graphs_) if(kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
   for(void* p : allocations_) cudaFree(p);
   if(statusHost_) cudaFreeHost(statusHost_);
@@ -796,6 +808,113 @@ void Engine::sync() {
   }
 }
 
+int Engine::allocationOf(const void* p) const {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+  for(size_t i = 0; i < allocations_.size(); i++) {
+    const uintptr_t b = reinterpret_cast<uintptr_t>(allocations_[i]);
+    if(a >= b && a < b + allocationBytes_[i]) return (int)i;
+  }
+  return -1;
+}
+
+// Decides which tensor-core convolutions wait per tile on the convolution launched just before them instead of on
+// its whole grid.  The launch itself (launchConvTc) additionally requires that the earlier convolution fills every SM.
+// Reads are safe by construction (a tile reads rows of its own and the two neighbouring row tiles of whatever the
+// earlier launch wrote, and waits for exactly those), and so are overwrites of buffers the earlier launch still
+// reads (their readers are the same three tiles).  Excluded: inputs that kernels other than convolutions produce
+// between the two (per-board bias, row sums), and a residual that the earlier launch itself wrote, because the
+// epilogue fetches the residual ahead of the producer's wait.
+// Replaces every run of two or more consecutive chainable tensor-core convolutions of the launch list by one
+// multi-layer launch (kb_conv_tc.cu, convChainKernel).  Between two members of a run nothing else is launched, so the
+// only producers of a member's inputs inside the run are the members before it, and their hand-over is per tile.
+void Engine::planChains() {
+  chainMode_ = getenv("KB_CHAIN") != nullptr ? atoi(getenv("KB_CHAIN")) : 1;
+  if(chainMode_ <= 0 || chunkBoards_ > 0 || layerN_ != 0 || forceSimt_) return;
+  const size_t tiles = (size_t)rowsPadMax_ / 128;
+  auto chainable = [&](const Op& op) {
+    return op.tcPlan && convChainEligible(op.tcPlan, op.ep) && (chainMode_ >= 2 || convTcKernelSize(op.tcPlan) == 3);
+  };
+  // counters: one array per chain member
+  size_t members = 0;
+  for(const Op& op : ops_) if(chainable(op)) members++;
+  if(members < 2) return;
+  tileCtrBytes_ = members * tiles * sizeof(uint32_t);
+  tileCtr_ = static_cast<uint32_t*>(alloc(tileCtrBytes_));
+  size_t ctrIdx = 0;
+  std::vector<Op> out;
+  size_t i = 0;
+  while(i < ops_.size()) {
+    size_t j = i;
+    while(j < ops_.size() && chainable(ops_[j]) && j - i < 16 &&
+          (j == i || (convTcTileWidth(ops_[j].tcPlan) == convTcTileWidth(ops_[i].tcPlan) &&
+                      (!ops_[j].ep.outAct || !ops_[i].ep.outAct || ops_[j].ep.act == ops_[i].ep.act))))
+      j++;
+    ConvChainPlan* plan = nullptr;
+    if(j - i >= 2) {
+      std::vector<ConvChainMember> ms;
+      for(size_t k = i; k < j; k++) {
+        ConvChainMember m;
+        m.plan = ops_[k].tcPlan;
+        m.ep = ops_[k].ep;
+        m.done = tileCtr_ + (ctrIdx++) * tiles;
+        ms.push_back(m);
+      }
+      plan = convChainCreate(ms.data(), (int)ms.size());
+    }
+    if(plan) {
+      chainPlans_.push_back(plan);
+      Op op;
+      size_t big = i;
+      for(size_t k = i; k < j; k++) {
+        op.flops += ops_[k].flops;
+        op.bytes += ops_[k].bytes;
+        if(ops_[k].flops > ops_[big].flops) big = k;
+      }
+      op.cls = classId(classes_[ops_[big].cls].name + " chain x" + std::to_string(j - i));
+      int* status = statusWord_;
+      op.run = [plan, status](cudaStream_t st, const Geom& g) { return launchConvChain(st, plan, g, status); };
+      out.push_back(std::move(op));
+      i = j;
+    }
+    else {
+      out.push_back(ops_[i]);
+      i++;
+    }
+  }
+  if(chainPlans_.empty()) return;
+  ops_ = std::move(out);
+}
+
+void Engine::planTileDeps() {
+  if(!tileDeps_ || chunkBoards_ > 0 || layerN_ != 0) return;
+  const size_t tiles = (size_t)rowsPadMax_ / 128;
+  size_t numTc = 0;
+  auto reports = [&](const Op& op) {
+    return op.tcPlan && convTcDepsCapable(op.tcPlan) && (tileDepsMode_ >= 2 || convTcKernelSize(op.tcPlan) == 3);
+  };
+  for(const Op& op : ops_) if(reports(op)) numTc++;
+  if(numTc == 0) return;
+  tileCtrBytes_ = numTc * tiles * sizeof(uint32_t);
+  tileCtr_ = static_cast<uint32_t*>(alloc(tileCtrBytes_));
+  size_t idx = 0;
+  for(Op& op : ops_)
+    if(reports(op)) op.deps->done = tileCtr_ + (idx++) * tiles;
+  for(size_t i = 1; i < ops_.size(); i++) {
+    Op& cur = ops_[i];
+    const Op& prev = ops_[i - 1];
+    if(!cur.tcPlan || !prev.tcPlan || !convTcDepsCapable(cur.tcPlan) || !prev.deps->done) continue;
+    const Epilogue& e = cur.ep;
+    if(e.biasNC || e.rowSumsq || e.sumsqOut || prev.ep.sumsqOut || prev.ep.rowSumsq) continue;
+    if(e.act == KB_ACT_SWIGLU_PAIRS || prev.ep.act == KB_ACT_SWIGLU_PAIRS) continue;  // no such kernel variant
+    if(e.residual) {
+      const int r = allocationOf(e.residual);
+      if(r < 0 || r == allocationOf(prev.ep.outRaw) || r == allocationOf(prev.ep.outAct)) continue;
+    }
+    cur.deps->wait = prev.deps->done;
+    cur.deps->waitPlan = prev.tcPlan;
+  }
+}
+
 void Engine::launchOpsEager(int n) {
   // Optionally (KB_CHUNK_BOARDS) the batch runs through the launch list in chunks of boards that reuse the same
   // activation buffers, so that tensors handed from kernel to kernel stay in the 126 MB L2.
@@ -804,6 +923,7 @@ void Engine::launchOpsEager(int n) {
     const int nc = std::min(chunk, n - c0);
     boardOffset_ = c0;
     const Geom g = makeGeom(X_, Y_, nc);
+    if(tileCtr_) cudaCheck(cudaMemsetAsync(tileCtr_, 0, tileCtrBytes_, stream_), "reset of the tile counters");
     for(size_t i = 0; i < ops_.size(); i++) {
       if(profiling_) cudaCheck(cudaEventRecord(events_[2 * i], stream_), "event record");
       cudaError_t e = ops_[i].run(stream_, g);

@@ -27,6 +27,10 @@ struct Op {
   int cls = 0;                                   // index into Engine::classes (profiling bucket)
   double flops = 0.0, bytes = 0.0;               // algorithmic, per board (scaled by n when accounted)
   std::function<cudaError_t(cudaStream_t, const Geom&)> run;
+  // tensor-core convolutions only: what the launch reads and writes, and its per-tile dependency record
+  const ConvTcPlan* tcPlan = nullptr;
+  Epilogue ep;
+  std::shared_ptr<ConvTcDeps> deps;
 };
 
 struct OpClass {
@@ -121,6 +125,20 @@ class Engine {
   int boardOffset_ = 0;   // first board of the chunk being launched
   cudaStream_t stream_ = nullptr;
   std::vector<void*> allocations_;
+  std::vector<size_t> allocationBytes_;
+  // Per-tile dependencies between consecutive tensor-core convolutions (KB_TILE_DEPS): one counter per convolution
+  // and 128-row tile, zeroed at the start of every pass through the launch list.
+  bool tileDeps_ = false;
+  int tileDepsMode_ = 0;
+  uint32_t* tileCtr_ = nullptr;
+  size_t tileCtrBytes_ = 0;
+  void planTileDeps();
+  // Multi-layer launches (KB_CHAIN: 0 off, 1 runs of 3x3 convolutions, 2 runs of any tensor-core convolutions): runs of
+  // consecutive convolutions of the launch list become one persistent launch each.
+  int chainMode_ = 0;
+  std::vector<ConvChainPlan*> chainPlans_;
+  void planChains();
+  int allocationOf(const void* p) const;
   std::map<std::string, DevBuf> scratch_;
   std::vector<ConvTcPlan*> tcPlans_;
   std::vector<AttnTcPlan*> attnPlans_;

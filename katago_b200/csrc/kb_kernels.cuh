@@ -142,7 +142,34 @@ ConvTcPlan* convTcCreate(
 void convTcDestroy(ConvTcPlan* p);
 // Binds the epilogue (output/residual tensors) to the plan; must be called once before the first launch.
 bool convTcSetEpilogue(ConvTcPlan* p, const Epilogue& ep);
-cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epilogue& ep, int* statusWord);
+// Per-tile dependencies between two tensor-core convolutions launched one after the other (see ConvTcArgs::depCtr):
+// `done` = this launch's counters (one per 128-row tile, zero before the launch), `wait` / `waitPlan` = counters and
+// plan of the convolution launched immediately before it.
+struct ConvTcDeps {
+  uint32_t* done = nullptr;
+  const uint32_t* wait = nullptr;
+  const ConvTcPlan* waitPlan = nullptr;
+};
+bool convTcDepsCapable(const ConvTcPlan* p);
+int convTcKernelSize(const ConvTcPlan* p);
+int convTcDoneCount(const ConvTcPlan* p);
+int convTcGridSize(const ConvTcPlan* p, const Geom& g);
+cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epilogue& ep, int* statusWord, const ConvTcDeps* deps = nullptr);
+
+// Several consecutive tensor-core convolutions as ONE persistent launch whose tiles hand over through per-tile counters
+// (kb_conv_tc.cu, "chain").  members[i].done: counter array of layer i (one per 128-row tile of rowsPadMax, zeroed by the
+// caller before every launch), needed for every layer but the last.  Every plan must have had its epilogue bound.
+struct ConvChainPlan;
+struct ConvChainMember {
+  const ConvTcPlan* plan = nullptr;
+  Epilogue ep;
+  uint32_t* done = nullptr;
+};
+int convTcTileWidth(const ConvTcPlan* p);
+bool convChainEligible(const ConvTcPlan* p, const Epilogue& ep);
+ConvChainPlan* convChainCreate(const ConvChainMember* members, int n);
+void convChainDestroy(ConvChainPlan* c);
+cudaError_t launchConvChain(cudaStream_t st, const ConvChainPlan* c, Geom g, int* statusWord);
 
 }  // namespace kb
 

@@ -66,6 +66,52 @@ __device__ __forceinline__ void tmaLoad2d(uint32_t dst, const CUtensorMap* tmap,
     : "memory");
 }
 
+// Tile readiness counters in global memory (per-tile dependencies between consecutive convolutions).
+__device__ __forceinline__ uint32_t ldAcquireGpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void redReleaseGpuAdd(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Waits (bounded like mbarWait) until the counters of row tiles lo..hi (at most three) have all reached `target`.
+// The polls are relaxed loads that can be in flight together; one acquire fence follows the successful poll.
+__device__ __forceinline__ uint32_t ldRelaxedGpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ bool waitTilesDone(const uint32_t* ctr, int lo, int hi, uint32_t target, volatile int* abortFlag, const volatile int* status) {
+  const int mid = lo + 1 <= hi ? lo + 1 : hi;
+  uint64_t t0 = 0;
+  uint32_t spins = 0;
+  while(true) {
+    const uint32_t v0 = ldRelaxedGpu(ctr + lo), v1 = ldRelaxedGpu(ctr + mid), v2 = ldRelaxedGpu(ctr + hi);
+    if(v0 >= target && v1 >= target && v2 >= target) {
+      asm volatile("fence.acq_rel.gpu;" ::: "memory");
+      return true;
+    }
+    if(spins == 0) t0 = globalTimerNs();
+    if((++spins & 15u) == 0u) {
+      // an earlier kernel of the stream that gave up never reports its tiles: do not wait for it
+      if(*abortFlag || *status != 0) return false;
+      if(globalTimerNs() - t0 > 2000000000ull) return false;
+    }
+    __nanosleep(64);
+  }
+}
+// All but the n most recent bulk groups of this thread have completed (their global writes included).
+__device__ __forceinline__ void bulkWaitPending(int n) {
+  switch(n) {
+    case 0: asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.bulk.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.bulk.wait_group 2;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.bulk.wait_group 3;" ::: "memory"); break;
+    default: asm volatile("cp.async.bulk.wait_group 4;" ::: "memory"); break;  // n >= 4: waits for more than asked
+  }
+}
+
 // shared -> global tile store (asynchronous, tracked by the issuing thread's bulk groups)
 __device__ __forceinline__ void tmaStore2d(const CUtensorMap* tmap, uint32_t src, int c0, int c1) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap), "r"(src), "r"(c0), "r"(c1) : "memory");
@@ -75,6 +121,8 @@ __device__ __forceinline__ void bulkWaitRead0() { asm volatile("cp.async.bulk.wa
 __device__ __forceinline__ void bulkWaitRead1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void bulkWaitAll() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fenceProxyAsync() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// orders this thread's generic-proxy accesses and its asynchronous-proxy (TMA) accesses in every state space
+__device__ __forceinline__ void fenceProxyAsyncAll() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 __device__ __forceinline__ void tmemAlloc(uint32_t dstSmem, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dstSmem), "r"(cols) : "memory");

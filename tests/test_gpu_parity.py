@@ -224,13 +224,14 @@ def test_full_depth_reduced_precision_vs_oracle(case, prec, dt):
 
     Against the fp32 oracle on unrounded weights the error of these random-init nets is that of the storage type, not of
     the backend: rounding the convolution weights alone moves the fp32 oracle itself beyond the stated bounds (the
-    fixture's `floorw` set; `floorwa` also rounds the convolution inputs, i.e. both operands of the matrix units; see
-    tests/test_oracle_pins.py::test_precision_floor_of_random_nets), and two runs of the SAME storage scheme that differ
-    only in the summation order of their fp32 accumulators differ by about half of that floor again, because a
-    rounding step of the storage type is only ~1e3 fp32 steps wide and every flipped rounding is amplified like any
-    other (`emu` is the oracle emulating this backend's storage scheme exactly: the CUDA path sits as far from it as
-    from the other sets).  So the bound is: the stated tolerance where the floor is at most half of it, otherwise
-    sqrt(2) x the larger floor (two independent rounding noises of that size) plus the stated tolerance.  (Measured: b18
+    fixture's `floorw` set; `floorwa` also rounds the convolution inputs, i.e. both operands of the matrix units; `emu`
+    also the residual streams, which is this backend's storage scheme and that of the reference's CUDA backend in
+    fp16 mode; see tests/test_oracle_pins.py::test_precision_floor_of_random_nets), and two runs of the SAME storage
+    scheme that differ only in the summation order of their fp32 accumulators differ by about half of that floor
+    again, because a rounding step of the storage type is only ~1e3 fp32 steps wide and every flipped rounding is
+    amplified like any other (measured: the CUDA path sits as far from `emu` as from the other sets).  So the bound
+    is: the stated tolerance where the largest floor is at most half of it, otherwise sqrt(2) x that floor (two
+    independent rounding noises of that size; 2 x for the KL, which is quadratic) plus the stated tolerance.  (Measured: b18
     in fp16 meets all four stated bounds against the fp32 oracle as they are, score 0.09 points.)  The tight full-depth check is
     test_every_block_at_full_depth_with_true_inputs."""
     from tests.golden.make_golden import full_case_inputs, load_full
@@ -243,13 +244,46 @@ def test_full_depth_reduced_precision_vs_oracle(case, prec, dt):
     got = dict(got, policy=got["policy"][:, :, :1], policyPass=got["policyPass"][:, :1])
     mask = sp[..., 0].reshape(n, -1)
     total = _p99(parity_metrics(got, fx["ref"], mask))
-    floor_w = _p99(parity_metrics(fx["floorw_" + dt], fx["ref"], mask))
-    floor_wa = _p99(parity_metrics(fx["floorwa_" + dt], fx["ref"], mask))
-    print(case, dt, "vs fp32 oracle", total, "floors", floor_w, floor_wa)
+    floors = {s: _p99(parity_metrics(fx[s + "_" + dt], fx["ref"], mask)) for s in ("floorw", "floorwa", "emu")}
+    print(case, dt, "vs fp32 oracle", total, "floors", floors)
     for k, tol in _STATED.items():
-        floor = max(floor_w[k], floor_wa[k])
-        bound = tol if floor <= 0.5 * tol else 2.0 ** 0.5 * floor + tol
-        assert total[k] <= bound, (k, total, floor_w, floor_wa)
+        floor = max(f[k] for f in floors.values())
+        # two independent rounding noises of the floor's size: amplitudes add in quadrature, the KL (quadratic in the
+        # amplitude) doubles
+        factor = 2.0 if k == "policy_kl" else 2.0 ** 0.5
+        bound = tol if floor <= 0.5 * tol else factor * floor + tol
+        assert total[k] <= bound, (k, total, floors)
+
+
+def test_multi_layer_launches_are_bit_identical_to_single_launches():
+    """Runs of consecutive convolutions are executed as one persistent launch whose tiles hand over through per-tile
+    counters (KB_CHAIN: 1 = runs of 3x3 convolutions, the default; 2 = runs of any tensor-core convolutions; 0 = one
+    launch per convolution).  The arithmetic of a tile does not depend on the mode, so the outputs must agree bit for
+    bit -- at the benchmark batch (every SM busy, tiles of consecutive layers in flight together), at a batch with fewer
+    tiles per layer than SMs, and on repeated runs (graph replay)."""
+    blob = mf.to_blob(mf.make_b18c384nbt(num_blocks=6))
+    old = os.environ.get("KB_CHAIN")
+    try:
+        for n in (256, 3):
+            sp, gl = mf.random_positions(n, seed=77, board_sizes=[19, 13, 9, 19] * (n // 4) + [19] * (n % 4))
+            outs = {}
+            for mode in ("0", "1", "2"):
+                os.environ["KB_CHAIN"] = mode
+                h = capi.Handle(capi.Model(blob), n, precision=capi.PRECISION_FP16)
+                runs = [h.forward(sp, gl) for _ in range(4)]
+                h.close()
+                for r in runs[1:]:
+                    for k in r:
+                        assert np.array_equal(r[k], runs[0][k]), (n, mode, k)
+                outs[mode] = runs[0]
+            for mode in ("1", "2"):
+                for k in outs["0"]:
+                    assert np.array_equal(outs[mode][k], outs["0"][k]), (n, mode, k)
+    finally:
+        if old is None:
+            os.environ.pop("KB_CHAIN", None)
+        else:
+            os.environ["KB_CHAIN"] = old
 
 
 @pytest.mark.parametrize("factory,n", [(mf.make_b18c384nbt, 8), (mf.make_b28c512nbt, 8)], ids=["b18c384nbt", "b28c512nbt"])
@@ -258,9 +292,10 @@ def test_every_block_at_full_depth_with_true_inputs(factory, n, oracle):
     (fp32, from a whole-net run on mixed 9/13/19 boards) goes through the CUDA path's block k alone, in fp16 and in bf16,
     and must give the oracle's stream leaving block k.  Unlike an end-to-end run this does not let the random-init net
     amplify one block's rounding through the blocks after it, so the bound is tight at any depth: every element within
-    the reference's reduced-precision layer tolerance 0.03 * max(|x|, |y|, 3) (cpp/tests/testnn.cpp:8-15; 0.2 for bf16's
-    8 mantissa bits), and the whole tensor within 4 units of the storage type's rounding step (2^-11 fp16, 2^-8 bf16)
-    in relative root-mean-square."""
+    the reference's reduced-precision layer tolerance 0.03 * max(|x|, |y|, floor) (cpp/tests/testnn.cpp:8-15, whose
+    floor of 3 suits tensors of order one; here 3 x the tensor's root-mean-square size; 0.2 for bf16's 8 mantissa
+    bits), and the whole tensor within 2 units of the storage type's rounding step (2^-11 fp16, 2^-8 bf16) in
+    relative root-mean-square (measured: 0.96 of one step in either type)."""
     tree = factory()
     om = oracle.OracleModel(mf.to_blob(tree))
     sp, gl = mf.random_positions(n, seed=2031, board_sizes=[9, 13, 19, 19] * (n // 4))
@@ -274,10 +309,14 @@ def test_every_block_at_full_depth_with_true_inputs(factory, n, oracle):
         ref = streams[k + 1]
         for prec, elem_tol, step in ((capi.PRECISION_FP16, 0.03, 2.0 ** -11), (capi.PRECISION_BF16, 0.2, 2.0 ** -8)):
             out = capi.eval_layer(blob, streams[k], mask, C, precision=prec)
-            assert np.all(np.abs(out - ref)[on] <= (elem_tol * np.maximum(np.maximum(np.abs(out), np.abs(ref)), 3.0))[on]), (k, prec)
-            rel = float(np.sqrt(np.mean((out - ref)[on] ** 2) / np.mean(ref[on] ** 2)))
+            # the floor 3 of the reference's tolerance assumes tensors of order one: deep in a random-init net the stream is
+            # hundreds of times larger, so the floor is taken relative to the tensor's own root-mean-square size
+            rms = float(np.sqrt(np.mean(ref[on] ** 2)))
+            floor = max(3.0, 3.0 * rms)
+            assert np.all(np.abs(out - ref)[on] <= (elem_tol * np.maximum(np.maximum(np.abs(out), np.abs(ref)), floor))[on]), (k, prec, rms)
+            rel = float(np.sqrt(np.mean((out - ref)[on] ** 2)) / rms)
             worst[prec] = max(worst.get(prec, 0.0), rel)
-            assert rel <= 4.0 * step, (k, prec, rel)
+            assert rel <= 2.0 * step, (k, prec, rel)
     print("worst relative rms per precision:", worst)
 
 

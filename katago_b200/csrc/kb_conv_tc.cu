@@ -1686,6 +1686,12 @@ ConvChainPlan* convChainCreate(const ConvChainMember* members, int n) {
     a.depCtr = (i > 0) ? members[i - 1].done : nullptr;
     a.depTarget = (i > 0) ? (uint32_t)((members[i - 1].plan->outC / members[i - 1].plan->BN) * tcEpiWarps(TC_EPI_CG)) : 0u;
     if((i + 1 < n && !members[i].done)) { delete c; return nullptr; }
+    // timing experiments only (results are wrong): 1 = no tile waits, 2 = no waits and no reports
+    if(const char* e = getenv("KB_CHAIN_DEBUG")) {
+      const int v = atoi(e);
+      if(v >= 1) a.depCtr = nullptr;
+      if(v >= 2) a.doneCtr = nullptr;
+    }
     aStride = std::max(aStride, (a.aSlotBytes + 1023) / 1024 * 1024);
     bStride = std::max(bStride, (a.bSlotBytes + 1023) / 1024 * 1024);
     c->maxNTiles = std::max(c->maxNTiles, p->outC / p->BN);

@@ -67,6 +67,14 @@ float* Engine::uploadF32(const std::vector<float>& v) {
   return p;
 }
 
+// [in][out] matmul weights stored output-major ([out][in]) for the fused per-board kernels
+float* Engine::uploadF32Transposed(const std::vector<float>& w, int inC, int outC) {
+  std::vector<float> t((size_t)inC * outC);
+  for(int ic = 0; ic < inC; ic++)
+    for(int oc = 0; oc < outC; oc++) t[(size_t)oc * inC + ic] = w[(size_t)ic * outC + oc];
+  return uploadF32(t);
+}
+
 void* Engine::uploadConvWeights(const std::vector<const ConvW*>& parts, int inCdev, bool tcLayout) {
   const int kY = parts[0]->kY, kX = parts[0]->kX, inC = parts[0]->inC;
   int outC = 0;
@@ -371,17 +379,27 @@ void Engine::emitBlock(const BlockW& b, int C, void* raw, void* act, const BNW* 
     const int dt = dt_;
     float* mask = mask_; float* maskSum = maskSum_;
     const double S = (double)X_ * Y_;
-    addOp("gpool", 0.0, S * gp * es, [=](cudaStream_t st, const Geom& g) {
-      return launchGPool(st, dt, G, gp, 0, gp, mask, maskSum, pooled, 0, g);
-    });
     float* wBias = uploadF32(b.gpoolToBias.w);
-    addOp("matmul small", 2.0 * 3 * gp * reg, 0.0, [=](cudaStream_t st, const Geom& g) {
-      return launchMatMulSmall(st, pooled, 3 * gp, wBias, reg, nullptr, KB_ACT_IDENTITY, gbias, g.n);
-    });
     BNDev mb = makeBN({&b.midBN});
-    addOp("bias+norm+act", 0.0, 2.0 * S * reg * es, [=](cudaStream_t st, const Geom& g) {
-      return launchBiasBnAct(st, dt, R, reg, gbias, mb.scale, mb.bias, mb.act, mask, Ract, reg, reg, g);
-    });
+    static const bool fuseMid = getenv("KB_NO_GPOOL_FUSE") == nullptr;
+    if(fuseMid && gpoolMidEligible(dt, gp, gp, reg, reg, reg)) {
+      // pooling, bias matmul and the bias + norm + activation pass as one launch (everything is per board)
+      float* wBiasT = uploadF32Transposed(b.gpoolToBias.w, 3 * gp, reg);
+      addOp("gpool+bias+norm+act", 2.0 * 3 * gp * reg, S * (gp + 2.0 * reg) * es, [=](cudaStream_t st, const Geom& g) {
+        return launchGPoolMid(st, dt, G, gp, gp, R, reg, reg, wBiasT, mb.scale, mb.bias, mb.act, mask, maskSum, Ract, reg, g);
+      });
+    }
+    else {
+      addOp("gpool", 0.0, S * gp * es, [=](cudaStream_t st, const Geom& g) {
+        return launchGPool(st, dt, G, gp, 0, gp, mask, maskSum, pooled, 0, g);
+      });
+      addOp("matmul small", 2.0 * 3 * gp * reg, 0.0, [=](cudaStream_t st, const Geom& g) {
+        return launchMatMulSmall(st, pooled, 3 * gp, wBias, reg, nullptr, KB_ACT_IDENTITY, gbias, g.n);
+      });
+      addOp("bias+norm+act", 0.0, 2.0 * S * reg * es, [=](cudaStream_t st, const Geom& g) {
+        return launchBiasBnAct(st, dt, R, reg, gbias, mb.scale, mb.bias, mb.act, mask, Ract, reg, reg, g);
+      });
+    }
     ConvDev c2 = makeConv({&b.conv2}, Ract, reg, reg);
     Epilogue e2;
     finishEp(e2);
@@ -582,26 +600,72 @@ void Engine::emitHeads(const Model& m, const void* trunkAct) {
     addConvOp(vc, ev, "head v1");
   }
 
+  // weights of everything after the first convolutions
+  float* wGB = uploadF32(m.gpoolToBias.w);
+  float* dPass = dPolicyPass_;
+  const int Pc = m.policyC;
+  float* wPass = uploadF32(m.passMul.w);
+  const int passH = m.hasPassMlp ? m.passMul.outC : 0;
+  float* bPass = m.hasPassMlp ? uploadF32(m.passBias.b) : nullptr;
+  float* wPass2 = m.hasPassMlp ? uploadF32(m.passMul2.w) : nullptr;
+  const int passAct = m.passAct;
+  BNDev pb = makeBN({&m.p1BN});
+  const int V2 = m.v2Mul.outC, Vc = m.valueC, Sv = m.scoreValueC;
+  float* wV2 = uploadF32(m.v2Mul.w); float* bV2 = uploadF32(m.v2Bias.b);
+  float* wV3 = uploadF32(m.v3Mul.w); float* bV3 = uploadF32(m.v3Bias.b);
+  float* wSV = uploadF32(m.sv3Mul.w); float* bSV = uploadF32(m.sv3Bias.b);
+  float* dValue = dValue_; float* dScore = dScore_;
+  const int v2Act = m.v2Act;
+  // p2Conv [oc][ic][1][1] -> [ic][oc]; ownership conv [1][ic][1][1] -> [ic]
+  std::vector<float> w2((size_t)P1 * Pc);
+  for(int oc = 0; oc < Pc; oc++)
+    for(int ic = 0; ic < P1; ic++) w2[(size_t)ic * Pc + oc] = m.p2Conv.w[(size_t)oc * P1 + ic];
+  float* dW2 = uploadF32(w2);
+  float* dWOwn = uploadF32(m.ownConv.w);
+  float* dPolicy = dPolicy_; float* dOwn = dOwnership_;
+
+  HeadsTailArgs ht;
+  std::memset(&ht, 0, sizeof(ht));
+  ht.pRaw = Praw; ht.gv = GV;
+  ht.P1 = P1; ht.G1 = G1; ht.V1 = V1; ht.Pc = Pc; ht.Vc = Vc; ht.Sv = Sv; ht.V2 = V2; ht.passH = passH;
+  ht.wGB = uploadF32Transposed(m.gpoolToBias.w, 3 * G1, P1);
+  ht.wPass = uploadF32Transposed(m.passMul.w, 3 * G1, m.passMul.outC);
+  ht.bPass = bPass; ht.passAct = passAct;
+  ht.wPass2 = m.hasPassMlp ? uploadF32Transposed(m.passMul2.w, passH, Pc) : nullptr;
+  ht.pScale = pb.scale; ht.pBias = pb.bias; ht.pAct = pb.act;
+  ht.w2 = dW2; ht.wOwn = dWOwn;
+  ht.wV2 = uploadF32Transposed(m.v2Mul.w, 3 * V1, V2); ht.bV2 = bV2; ht.v2Act = v2Act;
+  ht.wV3 = uploadF32Transposed(m.v3Mul.w, V2, Vc); ht.bV3 = bV3;
+  ht.wSV = uploadF32Transposed(m.sv3Mul.w, V2, Sv); ht.bSV = bSV;
+  ht.mask = mask; ht.maskSum = maskSum;
+  static const bool fuseTail = getenv("KB_NO_HEADS_FUSE") == nullptr;
+  if(fuseTail && headsTailEligible(dt, ht)) {
+    // poolings, policy bias, pass logits, value MLP, policy norm + activation + final convolution and the ownership
+    // convolution: one launch, one CTA per board
+    addOp("heads tail", 2.0 * S * (P1 * Pc + V1), S * (P1 + 2.0 * (G1 + V1)) * es + S * (Pc + 1) * 4.0, [=](cudaStream_t st, const Geom& g) {
+      const size_t bo = (size_t)boardOffset_;
+      HeadsTailArgs a = ht;
+      a.symmetry = haveSym_ ? dSym_ + bo : nullptr;
+      a.outPolicy = dPolicy + bo * g.S * Pc; a.outOwnership = dOwn + bo * g.S;
+      a.outPass = dPass + bo * Pc; a.outValue = dValue + bo * Vc; a.outScore = dScore + bo * Sv;
+      return launchHeadsTail(st, dt, a, g);
+    });
+    return;
+  }
+
   addOp("gpool", 0.0, S * G1 * es, [=](cudaStream_t st, const Geom& g) {
     return launchGPool(st, dt, GV, G1 + V1, 0, G1, mask, maskSum, gpooled, 0, g);
   });
   addOp("gpool", 0.0, S * V1 * es, [=](cudaStream_t st, const Geom& g) {
     return launchGPool(st, dt, GV, G1 + V1, G1, V1, mask, maskSum, vpooled, 1, g);
   });
-  float* wGB = uploadF32(m.gpoolToBias.w);
   addOp("matmul small", 2.0 * 3 * G1 * P1, 0.0, [=](cudaStream_t st, const Geom& g) {
     return launchMatMulSmall(st, gpooled, 3 * G1, wGB, P1, nullptr, KB_ACT_IDENTITY, pbias, g.n);
   });
   // pass logit (eigenbackend.cpp:2013-2022)
-  float* dPass = dPolicyPass_;
-  const int Pc = m.policyC;
-  float* wPass = uploadF32(m.passMul.w);
   if(m.hasPassMlp) {
-    const int H = m.passMul.outC;
+    const int H = passH;
     float* hidden = static_cast<float*>(scratch("headPassHidden", (size_t)maxBatch_ * H * sizeof(float)));
-    float* bPass = uploadF32(m.passBias.b);
-    float* wPass2 = uploadF32(m.passMul2.w);
-    const int passAct = m.passAct;
     addOp("matmul small", 2.0 * 3 * G1 * H, 0.0, [=](cudaStream_t st, const Geom& g) {
       return launchMatMulSmall(st, gpooled, 3 * G1, wPass, H, bPass, passAct, hidden, g.n);
     });
@@ -614,18 +678,11 @@ void Engine::emitHeads(const Model& m, const void* trunkAct) {
       return launchMatMulSmall(st, gpooled, 3 * G1, wPass, Pc, nullptr, KB_ACT_IDENTITY, dPass + (size_t)boardOffset_ * Pc, g.n);
     });
   }
-  BNDev pb = makeBN({&m.p1BN});
   addOp("bias+norm+act", 0.0, 2.0 * S * P1 * es, [=](cudaStream_t st, const Geom& g) {
     return launchBiasBnAct(st, dt, Praw, P1, pbias, pb.scale, pb.bias, pb.act, mask, Pact, P1, P1, g);
   });
   // value MLP (eigenbackend.cpp:2089-2099)
-  const int V2 = m.v2Mul.outC, Vc = m.valueC, Sv = m.scoreValueC;
   float* v2 = static_cast<float*>(scratch("headV2", (size_t)maxBatch_ * V2 * sizeof(float)));
-  float* wV2 = uploadF32(m.v2Mul.w); float* bV2 = uploadF32(m.v2Bias.b);
-  float* wV3 = uploadF32(m.v3Mul.w); float* bV3 = uploadF32(m.v3Bias.b);
-  float* wSV = uploadF32(m.sv3Mul.w); float* bSV = uploadF32(m.sv3Bias.b);
-  float* dValue = dValue_; float* dScore = dScore_;
-  const int v2Act = m.v2Act;
   addOp("matmul small", 2.0 * 3 * V1 * V2, 0.0, [=](cudaStream_t st, const Geom& g) {
     return launchMatMulSmall(st, vpooled, 3 * V1, wV2, V2, bV2, v2Act, v2, g.n);
   });
@@ -635,13 +692,6 @@ void Engine::emitHeads(const Model& m, const void* trunkAct) {
   addOp("matmul small", 2.0 * V2 * Sv, 0.0, [=](cudaStream_t st, const Geom& g) {
     return launchMatMulSmall(st, v2, V2, wSV, Sv, bSV, KB_ACT_IDENTITY, dScore + (size_t)boardOffset_ * Sv, g.n);
   });
-  // p2Conv [oc][ic][1][1] -> [ic][oc]; ownership conv [1][ic][1][1] -> [ic]
-  std::vector<float> w2((size_t)P1 * Pc);
-  for(int oc = 0; oc < Pc; oc++)
-    for(int ic = 0; ic < P1; ic++) w2[(size_t)ic * Pc + oc] = m.p2Conv.w[(size_t)oc * P1 + ic];
-  float* dW2 = uploadF32(w2);
-  float* dWOwn = uploadF32(m.ownConv.w);
-  float* dPolicy = dPolicy_; float* dOwn = dOwnership_;
   addOp("head outputs", 2.0 * S * (P1 * Pc + V1), S * (P1 + V1) * es + S * (Pc + 1) * 4.0, [=](cudaStream_t st, const Geom& g) {
     const size_t bo = (size_t)boardOffset_;
     return launchHeadFinal(

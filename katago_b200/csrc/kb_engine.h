@@ -104,6 +104,7 @@ class Engine {
   void* alloc(size_t bytes);                               // zero-initialised device memory
   void* scratch(const std::string& key, size_t bytes);     // named, reused across the plan
   float* uploadF32(const std::vector<float>& v);
+  float* uploadF32Transposed(const std::vector<float>& w, int inC, int outC);
   void* uploadConvWeights(const std::vector<const ConvW*>& parts, int inCdev, bool tcLayout);
   ConvDev makeConv(const std::vector<const ConvW*>& parts, const void* in, int inStride, int inCdev);
   BNDev makeBN(const std::vector<const BNW*>& parts);

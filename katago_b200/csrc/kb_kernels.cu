@@ -505,6 +505,160 @@ cudaError_t launchBnAct(
 }
 
 // ---------------------------------------------------------------------------------------------
+// The middle of a global-pooling block in one launch (eigenbackend.cpp:1188-1211): pooled statistics of the activated gpool
+// branch, the 3*Cg -> Cr matmul that turns them into a per-board bias, and the pass that adds that bias to the regular
+// branch and applies the next norm + activation + mask.  Everything is per board, so a board's CTAs need nothing from
+// other boards: grid (n, GPM_SPLIT); every CTA of a board computes the board's statistics and bias (the second reader of
+// the gpool branch hits L2) and then takes its share of the board's rows.
+// out[oc] = act(sum_k in[k] * wT[oc][k] + bias[oc]) for oc < outC; in and out in shared memory, all warps take part.
+// The weights are stored output-major: a warp takes an output at a time, its lanes stride over k with coalesced loads
+// that are all in flight together (a thread-per-output loop over [k][oc] weights has one dependent chain of K
+// L2-latency loads per thread, which is what made the separate small matmul launches slow), then reduce by shuffles.
+__device__ __forceinline__ void blockMatVecT(const float* in, int K, const float* __restrict__ wT, int outC, const float* __restrict__ bias, int act, float* out) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for(int oc0 = warp * 4; oc0 < outC; oc0 += nwarps * 4) {
+    float a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    // rows past the last output are read from the last one (and dropped), so that every load is unconditional and
+    // the loads of several k steps can be in flight together
+    const float* w0 = wT + (size_t)min(oc0, outC - 1) * K;
+    const float* w1 = wT + (size_t)min(oc0 + 1, outC - 1) * K;
+    const float* w2 = wT + (size_t)min(oc0 + 2, outC - 1) * K;
+    const float* w3 = wT + (size_t)min(oc0 + 3, outC - 1) * K;
+#pragma unroll 4
+    for(int k = lane; k < K; k += 32) {
+      const float x = in[k];
+      a[0] = fmaf(x, w0[k], a[0]);
+      a[1] = fmaf(x, w1[k], a[1]);
+      a[2] = fmaf(x, w2[k], a[2]);
+      a[3] = fmaf(x, w3[k], a[3]);
+    }
+#pragma unroll
+    for(int j = 0; j < 4; j++) {
+#pragma unroll
+      for(int o = 16; o > 0; o >>= 1) a[j] += __shfl_xor_sync(0xffffffffu, a[j], o);
+    }
+    if(lane < 4 && oc0 + lane < outC) {
+      const float t = (lane == 0 ? a[0] : lane == 1 ? a[1] : lane == 2 ? a[2] : a[3]) + (bias ? bias[oc0 + lane] : 0.0f);
+      out[oc0 + lane] = applyActF(t, act);
+    }
+  }
+}
+
+constexpr int GPM_SPLIT = 2;
+constexpr int GPM_THREADS = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(GPM_THREADS) gpoolMidVec8Kernel(
+  const T* __restrict__ gIn, int gStride, int Cg, const T* __restrict__ rIn, int rStride, int Cr, const float* __restrict__ wT,
+  const float* __restrict__ scale, const float* __restrict__ bias, int act, const float* __restrict__ mask,
+  const float* __restrict__ maskSum, T* __restrict__ out, int outStride, Geom g) {
+  extern __shared__ float sm[];  // [2][groups][Cg] partial sums / maxima, then pooled [3*Cg], then board bias [Cr]
+  const int n = blockIdx.x;
+  const int vecs = Cg / 8;
+  const int groups = GPM_THREADS / vecs;
+  float* sPooled = sm + 2 * groups * Cg;
+  float* sBias = sPooled + 3 * Cg;
+  {
+    const int cgv = threadIdx.x % vecs, rg = threadIdx.x / vecs;
+    float s[8], mx[8];
+#pragma unroll
+    for(int j = 0; j < 8; j++) { s[j] = 0.0f; mx[j] = -1.0f; }
+    if(rg < groups) {
+#pragma unroll 4
+      for(int p = rg; p < g.S; p += groups) {
+        const int y = p / g.X, x = p - y * g.X;
+        const size_t row = (size_t)n * g.PB + (size_t)y * g.RW + x;
+        const uint4 v4 = *reinterpret_cast<const uint4*>(gIn + row * gStride + cgv * 8);
+        const T* ve = reinterpret_cast<const T*>(&v4);
+        const float mOff = mask[row] - 1.0f;
+#pragma unroll
+        for(int j = 0; j < 8; j++) {
+          const float v = toF<T>(ve[j]);
+          s[j] += v;
+          mx[j] = fmaxf(mx[j], v + mOff);
+        }
+      }
+#pragma unroll
+      for(int j = 0; j < 8; j++) { sm[rg * Cg + cgv * 8 + j] = s[j]; sm[(groups + rg) * Cg + cgv * 8 + j] = mx[j]; }
+    }
+  }
+  __syncthreads();
+  for(int c = threadIdx.x; c < Cg; c += blockDim.x) {
+    float ss = 0.0f, mm = -1.0f;
+    for(int k = 0; k < groups; k++) { ss += sm[k * Cg + c]; mm = fmaxf(mm, sm[(groups + k) * Cg + c]); }
+    const float div = maskSum[n];
+    const float sq = sqrtf(div);
+    const float mean = ss / div;
+    sPooled[c] = mean;
+    sPooled[Cg + c] = mean * (sq - 14.0f) * 0.1f;
+    sPooled[2 * Cg + c] = mm;
+  }
+  __syncthreads();
+  blockMatVecT(sPooled, 3 * Cg, wT, Cr, nullptr, KB_ACT_IDENTITY, sBias);
+  __syncthreads();
+  // this CTA's share of the board's rows (padding rows included: they are written as zeros)
+  const int rvecs = Cr / 8;
+  const int rowsPer = (g.PB + GPM_SPLIT - 1) / GPM_SPLIT;
+  const int r0 = blockIdx.y * rowsPer, r1 = min(g.PB, r0 + rowsPer);
+  const int total = (r1 - r0) * rvecs;
+  constexpr int U = 4;
+  for(int base = threadIdx.x; base < total; base += blockDim.x * U) {
+    uint4 xs[U];
+    float mk[U];
+#pragma unroll
+    for(int u = 0; u < U; u++) {
+      const int idx = base + u * blockDim.x;
+      const int rr = min(idx, total - 1) / rvecs;
+      const int c = (min(idx, total - 1) - rr * rvecs) * 8;
+      const size_t m = (size_t)n * g.PB + r0 + rr;
+      mk[u] = mask[m];
+      xs[u] = *reinterpret_cast<const uint4*>(rIn + m * rStride + c);
+    }
+#pragma unroll
+    for(int u = 0; u < U; u++) {
+    const int idx = base + u * blockDim.x;
+    if(idx >= total) break;
+    const int rr = idx / rvecs;
+    const int c = (idx - rr * rvecs) * 8;
+    const size_t m = (size_t)n * g.PB + r0 + rr;
+    uint4 o = make_uint4(0u, 0u, 0u, 0u);
+    if(mk[u] == 1.0f) {
+      const uint4 x = xs[u];
+      const T* xe = reinterpret_cast<const T*>(&x);
+      T* oe = reinterpret_cast<T*>(&o);
+      const float4* s4 = reinterpret_cast<const float4*>(scale + c);
+      const float4* b4 = reinterpret_cast<const float4*>(bias + c);
+      const float4 s0 = s4[0], s1 = s4[1], c0 = b4[0], c1 = b4[1];
+      const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+      const float bi[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+      for(int j = 0; j < 8; j++) oe[j] = fromF<T>(fastAct(fmaf(toF<T>(xe[j]) + sBias[c + j], sc[j], bi[j]), act));
+    }
+    *reinterpret_cast<uint4*>(out + m * outStride + c) = o;
+    }
+  }
+}
+
+bool gpoolMidEligible(int dt, int Cg, int gStride, int Cr, int rStride, int outStride) {
+  return dt != DT_F32 && (Cg % 8) == 0 && (Cr % 8) == 0 && (gStride % 8) == 0 && (rStride % 8) == 0 && (outStride % 8) == 0 &&
+         Cg / 8 <= GPM_THREADS && Cg >= 8;
+}
+
+cudaError_t launchGPoolMid(
+  cudaStream_t st, int dt, const void* gIn, int gStride, int Cg, const void* rIn, int rStride, int Cr, const float* w,
+  const float* scale, const float* bias, int act, const float* mask, const float* maskSum, void* out, int outStride, Geom g) {
+  if(!gpoolMidEligible(dt, Cg, gStride, Cr, rStride, outStride)) return cudaErrorInvalidValue;
+  const int groups = GPM_THREADS / (Cg / 8);
+  const size_t smem = (size_t)(2 * groups * Cg + 3 * Cg + Cr) * sizeof(float);
+  const dim3 grid(g.n, GPM_SPLIT);
+  if(dt == DT_F16)
+    gpoolMidVec8Kernel<__half><<<grid, GPM_THREADS, smem, st>>>((const __half*)gIn, gStride, Cg, (const __half*)rIn, rStride, Cr, w, scale, bias, act, mask, maskSum, (__half*)out, outStride, g);
+  else
+    gpoolMidVec8Kernel<__nv_bfloat16><<<grid, GPM_THREADS, smem, st>>>((const __nv_bfloat16*)gIn, gStride, Cg, (const __nv_bfloat16*)rIn, rStride, Cr, w, scale, bias, act, mask, maskSum, (__nv_bfloat16*)out, outStride, g);
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
 // Head outputs: one thread per board point.
 
 template <typename T>
@@ -574,6 +728,147 @@ cudaError_t launchHeadFinal(
   size_t smem = ((size_t)P1 * policyC + V1) * sizeof(float);
   KB_DISPATCH_DT(dt, (headFinalKernel<T><<<(total + 127) / 128, 128, smem, st>>>(
     (const T*)pAct, pStride, P1, w2, policyC, (const T*)vAct, vStride, v0, V1, wOwn, symmetry, policy, ownership, g)));
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Everything of the heads after their first convolutions, one CTA per board (eigenbackend.cpp:1975-2025, 2063-2103): the two
+// poolings, the policy bias, the pass logits, the value MLP, and per board point the policy's norm + activation and
+// final 1x1 convolution and the ownership convolution, written in the caller's frame (inverse board symmetry).
+
+constexpr int HT_THREADS = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(HT_THREADS) headsTailKernel(const HeadsTailArgs a, Geom g) {
+  extern __shared__ float sm[];
+  const int n = blockIdx.x;
+  const int GV = a.G1 + a.V1;
+  const int vecs = GV / 8;
+  const int groups = HT_THREADS / vecs;
+  float* sPart = sm;                                  // [2][groups][GV]
+  float* sPoolG = sPart + 2 * groups * GV;            // [3*G1]
+  float* sPoolV = sPoolG + 3 * a.G1;                  // [3*V1]
+  float* sPBias = sPoolV + 3 * a.V1;                  // [P1]
+  float* sHidden = sPBias + a.P1;                     // [passH]
+  float* sV2 = sHidden + (a.passH > 0 ? a.passH : 1); // [V2]
+  float* sSmall = sV2 + a.V2;                         // pass [Pc], value [Vc], score [Sv]
+  float* sW2 = sSmall + a.Pc + a.Vc + a.Sv;           // [P1][Pc]
+  float* sWOwn = sW2 + a.P1 * a.Pc;                   // [V1]
+  float* sScale = sWOwn + a.V1;                       // [P1] then bias [P1]
+  for(int i = threadIdx.x; i < a.P1 * a.Pc; i += blockDim.x) sW2[i] = a.w2[i];
+  for(int i = threadIdx.x; i < a.V1; i += blockDim.x) sWOwn[i] = a.wOwn[i];
+  for(int i = threadIdx.x; i < a.P1; i += blockDim.x) { sScale[i] = a.pScale[i]; sScale[a.P1 + i] = a.pBias[i]; }
+  const T* gv = static_cast<const T*>(a.gv);
+  const T* praw = static_cast<const T*>(a.pRaw);
+  {
+    const int cv = threadIdx.x % vecs, rg = threadIdx.x / vecs;
+    float s[8], mx[8];
+#pragma unroll
+    for(int j = 0; j < 8; j++) { s[j] = 0.0f; mx[j] = -1.0f; }
+    if(rg < groups) {
+#pragma unroll 2
+      for(int p = rg; p < g.S; p += groups) {
+        const int y = p / g.X, x = p - y * g.X;
+        const size_t row = (size_t)n * g.PB + (size_t)y * g.RW + x;
+        const uint4 v4 = *reinterpret_cast<const uint4*>(gv + row * GV + cv * 8);
+        const T* ve = reinterpret_cast<const T*>(&v4);
+        const float mOff = a.mask[row] - 1.0f;
+#pragma unroll
+        for(int j = 0; j < 8; j++) {
+          const float v = toF<T>(ve[j]);
+          s[j] += v;
+          mx[j] = fmaxf(mx[j], v + mOff);
+        }
+      }
+#pragma unroll
+      for(int j = 0; j < 8; j++) { sPart[rg * GV + cv * 8 + j] = s[j]; sPart[(groups + rg) * GV + cv * 8 + j] = mx[j]; }
+    }
+  }
+  __syncthreads();
+  for(int c = threadIdx.x; c < GV; c += blockDim.x) {
+    float ss = 0.0f, mm = -1.0f;
+    for(int k = 0; k < groups; k++) { ss += sPart[k * GV + c]; mm = fmaxf(mm, sPart[(groups + k) * GV + c]); }
+    const float div = a.maskSum[n];
+    const float sq = sqrtf(div);
+    const float mean = ss / div;
+    if(c < a.G1) {
+      sPoolG[c] = mean; sPoolG[a.G1 + c] = mean * (sq - 14.0f) * 0.1f; sPoolG[2 * a.G1 + c] = mm;
+    }
+    else {
+      const int cc = c - a.G1;
+      sPoolV[cc] = mean; sPoolV[a.V1 + cc] = mean * (sq - 14.0f) * 0.1f; sPoolV[2 * a.V1 + cc] = mean * ((sq - 14.0f) * (sq - 14.0f) * 0.01f - 0.1f);
+    }
+  }
+  __syncthreads();
+  blockMatVecT(sPoolG, 3 * a.G1, a.wGB, a.P1, nullptr, KB_ACT_IDENTITY, sPBias);
+  if(a.passH > 0) blockMatVecT(sPoolG, 3 * a.G1, a.wPass, a.passH, a.bPass, a.passAct, sHidden);
+  else blockMatVecT(sPoolG, 3 * a.G1, a.wPass, a.Pc, nullptr, KB_ACT_IDENTITY, sSmall);
+  blockMatVecT(sPoolV, 3 * a.V1, a.wV2, a.V2, a.bV2, a.v2Act, sV2);
+  __syncthreads();
+  if(a.passH > 0) blockMatVecT(sHidden, a.passH, a.wPass2, a.Pc, nullptr, KB_ACT_IDENTITY, sSmall);
+  blockMatVecT(sV2, a.V2, a.wV3, a.Vc, a.bV3, KB_ACT_IDENTITY, sSmall + a.Pc);
+  blockMatVecT(sV2, a.V2, a.wSV, a.Sv, a.bSV, KB_ACT_IDENTITY, sSmall + a.Pc + a.Vc);
+  __syncthreads();
+  for(int i = threadIdx.x; i < a.Pc; i += blockDim.x) a.outPass[(size_t)n * a.Pc + i] = sSmall[i];
+  for(int i = threadIdx.x; i < a.Vc; i += blockDim.x) a.outValue[(size_t)n * a.Vc + i] = sSmall[a.Pc + i];
+  for(int i = threadIdx.x; i < a.Sv; i += blockDim.x) a.outScore[(size_t)n * a.Sv + i] = sSmall[a.Pc + a.Vc + i];
+  const int sym = a.symmetry ? a.symmetry[n] : 0;
+  for(int p = threadIdx.x; p < g.S; p += blockDim.x) {
+    const int h = p / g.X, w = p - h * g.X;
+    const size_t row = (size_t)n * g.PB + (size_t)h * g.RW + w;
+    int h2, w2p;
+    symMap(sym, true, g.Y, g.X, h, w, h2, w2p);
+    const size_t outPos = (size_t)n * g.S + (size_t)h2 * g.X + w2p;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if(a.mask[row] == 1.0f) {
+      const T* pr = praw + row * a.P1;
+      for(int c8 = 0; c8 < a.P1; c8 += 8) {
+        const uint4 x = *reinterpret_cast<const uint4*>(pr + c8);
+        const T* xe = reinterpret_cast<const T*>(&x);
+#pragma unroll
+        for(int j = 0; j < 8; j++) {
+          const int c = c8 + j;
+          // the activated value passes through the storage type, as it does where this tensor is written out
+          const float v = toF<T>(fromF<T>(fastAct(fmaf(toF<T>(xe[j]) + sPBias[c], sScale[c], sScale[a.P1 + c]), a.pAct)));
+          for(int k = 0; k < a.Pc && k < 4; k++) acc[k] = fmaf(v, sW2[c * a.Pc + k], acc[k]);
+        }
+      }
+    }
+    for(int k = 0; k < a.Pc && k < 4; k++) a.outPolicy[outPos * a.Pc + k] = acc[k];
+    float o = 0.0f;
+    const T* vr = gv + row * GV + a.G1;
+    for(int c8 = 0; c8 < a.V1; c8 += 8) {
+      const uint4 x = *reinterpret_cast<const uint4*>(vr + c8);
+      const T* xe = reinterpret_cast<const T*>(&x);
+#pragma unroll
+      for(int j = 0; j < 8; j++) o = fmaf(toF<T>(xe[j]), sWOwn[c8 + j], o);
+    }
+    a.outOwnership[outPos] = o;
+  }
+}
+
+bool headsTailEligible(int dt, const HeadsTailArgs& a) {
+  const int GV = a.G1 + a.V1;
+  return dt != DT_F32 && (a.P1 % 8) == 0 && (a.G1 % 8) == 0 && (a.V1 % 8) == 0 && a.Pc >= 1 && a.Pc <= 4 && GV / 8 <= HT_THREADS &&
+         a.P1 <= 512 && a.V2 <= 4096 && a.passH <= 4096;
+}
+
+cudaError_t launchHeadsTail(cudaStream_t st, int dt, const HeadsTailArgs& a, Geom g) {
+  if(!headsTailEligible(dt, a)) return cudaErrorInvalidValue;
+  const int GV = a.G1 + a.V1;
+  const int groups = HT_THREADS / (GV / 8);
+  const size_t floats = (size_t)2 * groups * GV + 3 * a.G1 + 3 * a.V1 + a.P1 + (a.passH > 0 ? a.passH : 1) + a.V2 + a.Pc + a.Vc + a.Sv +
+                        (size_t)a.P1 * a.Pc + a.V1 + 2 * a.P1;
+  const size_t smem = floats * sizeof(float);
+  if(smem > 200 * 1024) return cudaErrorInvalidValue;
+  if(dt == DT_F16) {
+    if(smem > 48 * 1024) cudaFuncSetAttribute(headsTailKernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    headsTailKernel<__half><<<g.n, HT_THREADS, smem, st>>>(a, g);
+  }
+  else {
+    if(smem > 48 * 1024) cudaFuncSetAttribute(headsTailKernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    headsTailKernel<__nv_bfloat16><<<g.n, HT_THREADS, smem, st>>>(a, g);
+  }
   return cudaGetLastError();
 }
 

@@ -106,6 +106,14 @@ cudaError_t launchBiasBnAct(
   cudaStream_t st, int dt, const void* in, int inStride, const float* biasNC, const float* scale, const float* bias,
   int act, const float* mask, void* out, int outStride, int C, Geom g);
 
+// The three steps between the first and the last convolution of a global-pooling block in one launch: pooled statistics
+// of gIn (activated gpool branch, Cg channels), board bias = stats [3*Cg] x w (stored output-major, [Cr][3*Cg]), out = mask ? act((rIn + bias) *
+// scale + bias) : 0 over the regular branch (Cr channels).  Reduced precision with 8-channel-aligned tensors only.
+bool gpoolMidEligible(int dt, int Cg, int gStride, int Cr, int rStride, int outStride);
+cudaError_t launchGPoolMid(
+  cudaStream_t st, int dt, const void* gIn, int gStride, int Cg, const void* rIn, int rStride, int Cr, const float* w,
+  const float* scale, const float* bias, int act, const float* mask, const float* maskSum, void* out, int outStride, Geom g);
+
 // Stand-alone batch norm + activation + mask (first layer of a block whose input was not produced by one
 // of our convolutions, and the single-layer test entry points).
 cudaError_t launchBnAct(
@@ -118,6 +126,25 @@ cudaError_t launchBnAct(
 cudaError_t launchHeadFinal(
   cudaStream_t st, int dt, const void* pAct, int pStride, int P1, const float* w2, int policyC, const void* vAct,
   int vStride, int v0, int V1, const float* wOwn, const int32_t* symmetry, float* policy, float* ownership, Geom g);
+
+// Everything of the heads after their first convolutions in one launch, one CTA per board (reduced precision, channel
+// counts that are multiples of 8).  pRaw [rowsPad][P1]: policy p1 convolution output; gv [rowsPad][G1+V1]: activated g1 |
+// v1 outputs.  Matmul weights are fp32, stored output-major ([out][in]); passH = 0: no pass MLP (wPass is then [Pc][3*G1]).  Outputs: policy
+// [n][S][Pc] and ownership [n][S] in the caller's frame (symmetry may be NULL), pass [n][Pc], value [n][Vc], score [n][Sv].
+struct HeadsTailArgs {
+  const void* pRaw; const void* gv;
+  int P1, G1, V1, Pc, Vc, Sv, V2, passH;
+  const float* wGB;
+  const float* wPass; const float* bPass; int passAct; const float* wPass2;
+  const float* pScale; const float* pBias; int pAct;
+  const float* w2; const float* wOwn;
+  const float* wV2; const float* bV2; int v2Act;
+  const float* wV3; const float* bV3; const float* wSV; const float* bSV;
+  const float* mask; const float* maskSum; const int32_t* symmetry;
+  float* outPolicy; float* outOwnership; float* outPass; float* outValue; float* outScore;
+};
+bool headsTailEligible(int dt, const HeadsTailArgs& a);
+cudaError_t launchHeadsTail(cudaStream_t st, int dt, const HeadsTailArgs& a, Geom g);
 
 // Layout conversion for the single-layer entry points: [n][Y][X][C] fp32 <-> padded rows of dtype dt.
 cudaError_t launchToPadded(cudaStream_t st, int dt, const float* src, int C, void* dst, int dstStride, Geom g);

@@ -55,6 +55,19 @@ int kb_handle_create(
   kb_handle** out);
 void kb_handle_destroy(kb_handle* h);
 
+/* Device-side weight cache.  The reference's CPU backend shares one Model between all compute handles of a net,
+ * keyed by name and hash (eigenbackend.cpp:2364-2392), so that several server threads cost one copy of the weights;
+ * here every read-only weight tensor is keyed by device and contents, reference counted, and freed with the last
+ * handle that uses it: handles created from the same model on the same device hold one replica between them.
+ * stats[0..3] = live entries, their bytes, uploads made, uploads avoided (since the process started, all devices). */
+int kb_weight_cache_stats(int64_t stats[4]);
+
+/* Self-test of the failure path of the bounded device-side waits (no counterpart in the reference): on the handle's
+ * stream a kernel waits limitNs nanoseconds (at most 1e9) on a barrier that nothing arrives at, gives up and records a
+ * status code, exactly as a convolution kernel does when one of its waits runs out.  The call then synchronises and
+ * returns the resulting error (non-zero, "a device-side wait timed out ..."); the handle stays usable. */
+int kb_selftest_wait_timeout(kb_handle* h, unsigned long long limitNs);
+
 /* Replaces NeuralNet::isUsingFP16 (nninterface.h:88): returns the precision in *precision. */
 int kb_handle_precision(const kb_handle* h, int* precision);
 

@@ -16,7 +16,7 @@ _lib = None
 # Every symbol include/katab200.h declares.
 EXPORTED_SYMBOLS = [
     "kb_last_error", "kb_version", "kb_device_count", "kb_device_name", "kb_model_create", "kb_model_destroy",
-    "kb_model_info", "kb_model_meta_channels", "kb_forward_host_meta", "kb_upload_inputs_meta", "kb_handle_create", "kb_handle_destroy", "kb_handle_precision", "kb_forward_host",
+    "kb_model_info", "kb_model_meta_channels", "kb_forward_host_meta", "kb_upload_inputs_meta", "kb_handle_create", "kb_handle_destroy", "kb_handle_precision", "kb_weight_cache_stats", "kb_selftest_wait_timeout", "kb_forward_host",
     "kb_upload_inputs", "kb_forward_resident", "kb_download_outputs", "kb_time_forward_resident", "kb_time_forward_steps",
     "kb_profile_enable", "kb_profile_reset", "kb_profile_read", "kb_launches_per_forward", "kb_debug_read_trunk",
     "kb_eval_layer", "kb_host_alloc", "kb_host_free", "kb_conv_noalloc", "kb_conv_noalloc_last_error",
@@ -60,6 +60,8 @@ def lib():
         L.kb_handle_create.argtypes = [vp, ci, ci, ci, ci, ci, ci, ctypes.POINTER(vp)]
         L.kb_handle_destroy.argtypes = [vp]
         L.kb_handle_precision.argtypes = [vp, ctypes.POINTER(ci)]
+        L.kb_weight_cache_stats.argtypes = [ctypes.POINTER(ctypes.c_int64)]
+        L.kb_selftest_wait_timeout.argtypes = [vp, ctypes.c_ulonglong]
         L.kb_forward_host.argtypes = [vp, ci] + [vp] * 8
         L.kb_upload_inputs.argtypes = [vp, ci, vp, vp, vp]
         L.kb_forward_resident.argtypes = [vp, ci]
@@ -91,6 +93,13 @@ def _check(status: int, what: str):
 
 def _ptr(a):
     return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
+
+
+def weight_cache_stats() -> dict:
+    """Counters of the device-side weight cache: live entries, their bytes, uploads made, uploads avoided."""
+    a = (ctypes.c_int64 * 4)()
+    _check(lib().kb_weight_cache_stats(a), "kb_weight_cache_stats")
+    return dict(entries=int(a[0]), bytes=int(a[1]), uploads=int(a[2]), hits=int(a[3]))
 
 
 def device_count() -> int:
@@ -193,6 +202,10 @@ class Handle:
             _check(lib().kb_upload_inputs_meta(self.h, n, _ptr(spatial), _ptr(glob), _ptr(meta), _ptr(sym)), "kb_upload_inputs_meta")
             return
         _check(lib().kb_upload_inputs(self.h, n, _ptr(spatial), _ptr(glob), _ptr(sym)), "kb_upload_inputs")
+
+    def selftest_wait_timeout(self, limit_ns: int):
+        """Makes a bounded device-side wait run out on this handle's stream; raises KBError like any such time-out."""
+        _check(lib().kb_selftest_wait_timeout(self.h, int(limit_ns)), "kb_selftest_wait_timeout")
 
     def forward_resident(self, n):
         _check(lib().kb_forward_resident(self.h, n), "kb_forward_resident")

@@ -95,6 +95,18 @@ int kb_handle_create(
 }
 void kb_handle_destroy(kb_handle* h) { delete h; }
 
+int kb_weight_cache_stats(int64_t stats[4]) {
+  return guarded([&]() {
+    need(stats, "stats");
+    const kb::WeightCacheStats s = kb::weightCacheStats();
+    stats[0] = s.entries; stats[1] = s.bytes; stats[2] = s.uploads; stats[3] = s.hits;
+  });
+}
+
+int kb_selftest_wait_timeout(kb_handle* h, unsigned long long limitNs) {
+  return guarded([&]() { need(h, "handle"); h->e->selfTestWaitTimeout(limitNs); });
+}
+
 int kb_handle_precision(const kb_handle* h, int* precision) {
   return guarded([&]() { need(h, "handle"); need(precision, "precision"); *precision = h->e->precision(); });
 }

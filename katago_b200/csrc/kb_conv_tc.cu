@@ -1766,6 +1766,31 @@ cudaError_t launchConvChain(cudaStream_t st, const ConvChainPlan* c, Geom g, int
   return cudaLaunchKernelEx(&lc, fn, (const ChainLayer*)c->dLayers, cfg);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Self-test of the bounded waits: a one-thread kernel waits, with the given limit, on a barrier that nothing ever arrives
+// at.  The wait gives up, the kernel records its code in the status word exactly as the convolution kernels do on a
+// time-out, and returns; the context stays usable.
+
+enum { TC_ERR_SELFTEST_TIMEOUT = 199 };
+
+__global__ void waitTimeoutSelfTestKernel(int* status, unsigned long long limitNs) {
+  __shared__ uint64_t bar;
+  __shared__ int abortFlag;
+  if(threadIdx.x == 0) {
+    abortFlag = 0;
+    mbarInit(smemU32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const bool arrived = mbarWait(smemU32(&bar), 0u, &abortFlag, (uint64_t)limitNs);
+    if(!arrived) atomicCAS(status, 0, TC_ERR_SELFTEST_TIMEOUT);
+  }
+}
+
+cudaError_t launchWaitTimeoutSelfTest(cudaStream_t st, int* statusWord, unsigned long long limitNs) {
+  if(limitNs > 1000000000ull) return cudaErrorInvalidValue;  // a self-test never waits longer than a second
+  waitTimeoutSelfTestKernel<<<1, 32, 0, st>>>(statusWord, limitNs);
+  return cudaGetLastError();
+}
+
 }  // namespace kb
 
 #ifdef KB_TC_TRACE

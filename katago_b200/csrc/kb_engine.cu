@@ -12,6 +12,8 @@
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
+#include <map>
+#include <mutex>
 
 namespace kb {
 
@@ -47,6 +49,82 @@ void* Engine::alloc(size_t bytes) {
   return p;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Weight cache
+
+namespace {
+struct WeightKey {
+  int device; size_t bytes; uint64_t h1, h2;
+  bool operator<(const WeightKey& o) const {
+    if(device != o.device) return device < o.device;
+    if(bytes != o.bytes) return bytes < o.bytes;
+    if(h1 != o.h1) return h1 < o.h1;
+    return h2 < o.h2;
+  }
+};
+struct WeightEntry { void* p; int refs; };
+std::mutex g_weightMu;
+std::map<WeightKey, WeightEntry> g_weights;
+std::map<const void*, WeightKey> g_weightOf;
+int64_t g_weightUploads = 0, g_weightHits = 0;
+
+// two independent 64-bit hashes of the bytes (FNV-1a and a multiply-rotate mix): 128 bits identify the contents
+void hashBytes(const void* data, size_t n, uint64_t& h1, uint64_t& h2) {
+  const uint8_t* p = static_cast<const uint8_t*>(data);
+  h1 = 1469598103934665603ull; h2 = 0x9E3779B97F4A7C15ull ^ (uint64_t)n;
+  size_t i = 0;
+  for(; i + 8 <= n; i += 8) {
+    uint64_t w;
+    std::memcpy(&w, p + i, 8);
+    h1 = (h1 ^ w) * 1099511628211ull;
+    h2 = (h2 + w) * 0xC2B2AE3D27D4EB4Full;
+    h2 = (h2 << 31) | (h2 >> 33);
+  }
+  for(; i < n; i++) { h1 = (h1 ^ p[i]) * 1099511628211ull; h2 = (h2 + p[i]) * 0x165667B19E3779F9ull; }
+}
+}  // namespace
+
+WeightCacheStats weightCacheStats() {
+  std::lock_guard<std::mutex> lock(g_weightMu);
+  WeightCacheStats s = {0, 0, g_weightUploads, g_weightHits};
+  for(const auto& kv : g_weights) { s.entries++; s.bytes += (int64_t)kv.first.bytes; }
+  return s;
+}
+
+void* Engine::uploadShared(const void* host, size_t bytes) {
+  static const bool enabled = getenv("KB_NO_WEIGHT_CACHE") == nullptr;
+  if(bytes == 0) return alloc(16);
+  WeightKey key;
+  key.device = device_; key.bytes = bytes;
+  hashBytes(host, bytes, key.h1, key.h2);
+  std::lock_guard<std::mutex> lock(g_weightMu);
+  if(enabled) {
+    auto it = g_weights.find(key);
+    if(it != g_weights.end()) {
+      it->second.refs++;
+      g_weightHits++;
+      sharedWeights_.push_back(it->second.p);
+      return it->second.p;
+    }
+  }
+  void* p = nullptr;
+  cudaCheck(cudaMalloc(&p, bytes), "cudaMalloc (weights)");
+  cudaError_t e = cudaMemcpyAsync(p, host, bytes, cudaMemcpyHostToDevice, stream_);
+  if(e == cudaSuccess) e = cudaStreamSynchronize(stream_);
+  if(e != cudaSuccess) { cudaFree(p); cudaCheck(e, "upload weights"); }
+  g_weightUploads++;
+  if(!enabled) {
+    // not shared: owned by this handle like any other allocation
+    allocations_.push_back(p);
+    allocationBytes_.push_back(bytes);
+    return p;
+  }
+  g_weights[key] = WeightEntry{p, 1};
+  g_weightOf[p] = key;
+  sharedWeights_.push_back(p);
+  return p;
+}
+
 void* Engine::scratch(const std::string& key, size_t bytes) {
   auto it = scratch_.find(key);
   if(it != scratch_.end()) {
@@ -61,10 +139,7 @@ void* Engine::scratch(const std::string& key, size_t bytes) {
 }
 
 float* Engine::uploadF32(const std::vector<float>& v) {
-  float* p = static_cast<float*>(alloc(v.size() * sizeof(float)));
-  cudaCheck(cudaMemcpyAsync(p, v.data(), v.size() * sizeof(float), cudaMemcpyHostToDevice, stream_), "upload f32");
-  cudaCheck(cudaStreamSynchronize(stream_), "upload sync");
-  return p;
+  return static_cast<float*>(uploadShared(v.data(), v.size() * sizeof(float)));
 }
 
 // [in][out] matmul weights stored output-major ([out][in]) for the fused per-board kernels
@@ -100,10 +175,7 @@ void* Engine::uploadConvWeights(const std::vector<const ConvW*>& parts, int inCd
   }
   std::vector<uint8_t> bytes;
   convertTo(dt_, packed, bytes);
-  void* d = alloc(bytes.size());
-  cudaCheck(cudaMemcpyAsync(d, bytes.data(), bytes.size(), cudaMemcpyHostToDevice, stream_), "upload conv weights");
-  cudaCheck(cudaStreamSynchronize(stream_), "upload sync");
-  return d;
+  return uploadShared(bytes.data(), bytes.size());
 }
 
 Engine::ConvDev Engine::makeConv(const std::vector<const ConvW*>& parts, const void* in, int inStride, int inCdev) {
@@ -498,6 +570,9 @@ void Engine::emitBlock(const BlockW& b, int C, void* raw, void* act, const BNW* 
       });
     }
     else {
+      if(!attentionFits(X_, Y_, dq, dv))
+        throw std::runtime_error("attention block: a board of " + std::to_string(X_) + "x" + std::to_string(Y_) + " with head sizes " +
+                                 std::to_string(dq) + "/" + std::to_string(dv) + " does not fit the attention kernel's shared memory");
       addOp("attention simt", 2.0 * S * S * (dq + dv) * H, S * (qkvC + oC) * es, [=](cudaStream_t st, const Geom& g) {
         return launchAttention(st, dt, qkv, qkvC, 0, qC, qC + kC, H, Hkv, dq, dv, mask, attn, oC, g, relBiasDev, relY, relX);
       });
@@ -843,6 +918,19 @@ Engine::~Engine() {
   for(ConvChainPlan* p : chainPlans_) convChainDestroy(p);
   for(auto& kv : graphs_) if(kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
   for(void* p : allocations_) cudaFree(p);
+  {
+    std::lock_guard<std::mutex> lock(g_weightMu);
+    for(void* p : sharedWeights_) {
+      auto ko = g_weightOf.find(p);
+      if(ko == g_weightOf.end()) continue;
+      auto it = g_weights.find(ko->second);
+      if(it != g_weights.end() && --it->second.refs == 0) {
+        cudaFree(it->second.p);
+        g_weights.erase(it);
+        g_weightOf.erase(ko);
+      }
+    }
+  }
   if(statusHost_) cudaFreeHost(statusHost_);
   if(flushBuf_) cudaFree(flushBuf_);
   if(stream_) cudaStreamDestroy(stream_);
@@ -854,7 +942,7 @@ void Engine::sync() {
     int code = *statusHost_;
     *statusHost_ = 0;
     cudaMemsetAsync(statusWord_, 0, sizeof(int), stream_);
-    throw CudaError("a device-side wait timed out in the tensor-core convolution (status " + std::to_string(code) + ")");
+    throw CudaError("a device-side wait timed out (status " + std::to_string(code) + ": 101 producer, 102 MMA issuer, 103 epilogue of a tensor-core kernel, 199 wait self-test)");
   }
 }
 
@@ -965,6 +1053,13 @@ void Engine::planTileDeps() {
   }
 }
 
+void Engine::selfTestWaitTimeout(unsigned long long limitNs) {
+  cudaCheck(cudaSetDevice(device_), "cudaSetDevice");
+  cudaCheck(launchWaitTimeoutSelfTest(stream_, statusWord_, limitNs), "wait self-test launch");
+  cudaCheck(cudaMemcpyAsync(statusHost_, statusWord_, sizeof(int), cudaMemcpyDeviceToHost, stream_), "status copy");
+  sync();
+}
+
 void Engine::launchOpsEager(int n) {
   // Optionally (KB_CHUNK_BOARDS) the batch runs through the launch list in chunks of boards that reuse the same
   // activation buffers, so that tensors handed from kernel to kernel stay in the 126 MB L2.
@@ -1013,7 +1108,7 @@ void Engine::runOps(int n) {
       cudaCheck(cudaGraphLaunch(ge.exec, stream_), "cudaGraphLaunch");
       done = true;
     }
-    else if(++ge.uses >= 2 && graphs_.size() <= 128) {
+    else if(++ge.uses >= 2 && graphsInstantiated_ < 64) {
       cudaGraph_t graph = nullptr;
       bool ok = cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
       if(ok) {
@@ -1022,6 +1117,7 @@ void Engine::runOps(int n) {
         if(cudaStreamEndCapture(stream_, &graph) != cudaSuccess) ok = false;
       }
       if(ok && graph && cudaGraphInstantiate(&ge.exec, graph, 0) == cudaSuccess) {
+        graphsInstantiated_++;
         cudaCheck(cudaGraphLaunch(ge.exec, stream_), "cudaGraphLaunch");
         done = true;
       }

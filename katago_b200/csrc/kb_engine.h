@@ -22,6 +22,11 @@ struct CudaError : std::runtime_error {
 };
 void cudaCheck(cudaError_t e, const char* what);
 
+// Counters of the device-side weight cache, summed over all devices: live entries, their bytes, uploads made and
+// uploads avoided since the process started.
+struct WeightCacheStats { int64_t entries, bytes, uploads, hits; };
+WeightCacheStats weightCacheStats();
+
 // One launch of the program.
 struct Op {
   int cls = 0;                                   // index into Engine::classes (profiling bucket)
@@ -72,6 +77,8 @@ class Engine {
   int profileRead(OpClass* out, int cap);
 
   void sync();
+  // Runs the wait self-test on this handle's stream and synchronises: throws CudaError like any timed-out wait.
+  void selfTestWaitTimeout(unsigned long long limitNs);
 
  private:
   struct DevBuf { void* p = nullptr; size_t bytes = 0; };
@@ -89,6 +96,7 @@ class Engine {
   struct GraphEntry { int uses = 0; cudaGraphExec_t exec = nullptr; };
   std::map<int, GraphEntry> graphs_;
   bool graphsEnabled_ = true;
+  int graphsInstantiated_ = 0;  // instantiated graphs (at most 64 batch sizes are captured; the others stay eager)
   void launchOpsEager(int n);
 
   // RMS norms of pre-norm transformer blocks folded into the convolutions around them: the producer of the residual
@@ -101,6 +109,12 @@ class Engine {
 
   struct BNDev { const float* scale = nullptr; const float* bias = nullptr; int act = 0; int C = 0; };
 
+  // Read-only weights go through a process-wide cache per device, keyed by their contents: handles created from the
+  // same model on the same device (the reference runs two server threads per GPU) share one copy, as the reference's
+  // CPU backend shares one Model per name and hash (eigenbackend.cpp:2364-2392).  Entries are reference counted and
+  // freed with their last handle.
+  void* uploadShared(const void* host, size_t bytes);
+  std::vector<void*> sharedWeights_;
   void* alloc(size_t bytes);                               // zero-initialised device memory
   void* scratch(const std::string& key, size_t bytes);     // named, reused across the plan
   float* uploadF32(const std::vector<float>& v);

@@ -183,6 +183,10 @@ int convTcDoneCount(const ConvTcPlan* p);
 int convTcGridSize(const ConvTcPlan* p, const Geom& g);
 cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epilogue& ep, int* statusWord, const ConvTcDeps* deps = nullptr);
 
+// Self-test of the bounded device-side waits: a kernel waits (limitNs, at most one second) on a barrier nothing arrives
+// at, gives up, and records code 199 in the status word.
+cudaError_t launchWaitTimeoutSelfTest(cudaStream_t st, int* statusWord, unsigned long long limitNs);
+
 // Several consecutive tensor-core convolutions as ONE persistent launch whose tiles hand over through per-tile counters
 // (kb_conv_tc.cu, "chain").  members[i].done: counter array of layer i (one per 128-row tile of rowsPadMax, zeroed by the
 // caller before every launch), needed for every layer but the last.  Every plan must have had its epilogue bound.
@@ -227,6 +231,8 @@ cudaError_t launchRope(
 // (heads*dv); rows of masked or padding points are written as zeros.
 // relBias (or NULL): learned relative-position bias [heads][2*relY-1][2*relX-1], added to the scaled score of query
 // (yq,xq) and key (yk,xk) at [head][yk-yq+relY-1][xk-xq+relX-1].
+// The kernel keeps K, V and a row block of the scores of one board in shared memory: true if a board of X x Y fits.
+bool attentionFits(int X, int Y, int dq, int dv);
 cudaError_t launchAttention(
   cudaStream_t st, int dt, const void* qkv, int stride, int qOff, int kOff, int vOff, int heads, int kvHeads, int dq, int dv,
   const float* mask, void* out, int outStride, Geom g, const float* relBias = nullptr, int relY = 0, int relX = 0);

@@ -39,8 +39,8 @@ __device__ __forceinline__ uint64_t globalTimerNs() {
   return t;
 }
 
-// Bounded wait (about 2 s).  Returns false on time-out or if another role already gave up.
-__device__ __forceinline__ bool mbarWait(uint32_t bar, uint32_t parity, volatile int* abortFlag) {
+// Bounded wait (about 2 s unless another limit is given).  Returns false on time-out or if another role already gave up.
+__device__ __forceinline__ bool mbarWait(uint32_t bar, uint32_t parity, volatile int* abortFlag, uint64_t limitNs = 2000000000ull) {
   if(mbarTryWait(bar, parity)) return true;
   const uint64_t t0 = globalTimerNs();
   uint32_t spins = 0;
@@ -48,7 +48,7 @@ __device__ __forceinline__ bool mbarWait(uint32_t bar, uint32_t parity, volatile
     if(mbarTryWait(bar, parity)) return true;
     if((++spins & 63u) == 0u) {
       if(*abortFlag) return false;
-      if(globalTimerNs() - t0 > 2000000000ull) return false;
+      if(globalTimerNs() - t0 > limitNs) return false;
     }
   }
 }

@@ -269,10 +269,16 @@ __global__ void __launch_bounds__(256) attentionKernel(
   }
 }
 
+size_t attentionSmemBytes(int X, int Y, int dq, int dv) {
+  const size_t S = (size_t)X * Y;
+  return (S * (dq + 1) + S * (dv + 1) + S + 8 * S + 8 * (size_t)dq) * sizeof(float);
+}
+bool attentionFits(int X, int Y, int dq, int dv) { return attentionSmemBytes(X, Y, dq, dv) <= 227 * 1024; }
+
 cudaError_t launchAttention(
   cudaStream_t st, int dt, const void* qkv, int stride, int qOff, int kOff, int vOff, int heads, int kvHeads, int dq, int dv,
   const float* mask, void* out, int outStride, Geom g, const float* relBias, int relY, int relX) {
-  const size_t smem = ((size_t)g.S * (dq + 1) + (size_t)g.S * (dv + 1) + g.S + 8 * (size_t)g.S + 8 * (size_t)dq) * sizeof(float);
+  const size_t smem = attentionSmemBytes(g.X, g.Y, dq, dv);
   if(smem > 227 * 1024) return cudaErrorInvalidValue;
   dim3 grid((g.S + 31) / 32, g.n * heads);
   switch(dt) {

@@ -255,6 +255,54 @@ def test_full_depth_reduced_precision_vs_oracle(case, prec, dt):
         assert total[k] <= bound, (k, total, floors)
 
 
+def test_timed_out_device_wait_is_reported_and_the_handle_stays_usable():
+    """The failure path of the bounded waits, made to run without faulting or hanging anything: a kernel waits one
+    millisecond on a barrier that nothing arrives at, gives up and records a status code; the next synchronisation
+    raises; the status is cleared and the same handle evaluates positions as before."""
+    blob = mf.to_blob(mf.make_b18c384nbt(num_blocks=2))
+    sp, gl = mf.random_positions(3, seed=9)
+    h = capi.Handle(capi.Model(blob), 3, precision=capi.PRECISION_FP16)
+    before = h.forward(sp, gl)
+    with pytest.raises(capi.KBError, match="wait timed out"):
+        h.selftest_wait_timeout(1_000_000)
+    after = h.forward(sp, gl)
+    for k in before:
+        assert np.array_equal(before[k], after[k]), k
+    with pytest.raises(capi.KBError):
+        h.selftest_wait_timeout(2_000_000_000)  # longer than a self-test may wait: refused, nothing launched
+    again = h.forward(sp, gl)
+    assert np.array_equal(before["value"], again["value"])
+    h.close()
+
+
+def test_handles_of_one_model_share_one_weight_replica():
+    """Two handles of the same model on the same device (the reference runs two server threads per GPU) upload the
+    weights once: the second handle finds every weight tensor in the device-side cache; both give identical results,
+    the replica outlives the first handle and is freed with the second."""
+    blob = mf.to_blob(mf.make_b18c384nbt(num_blocks=3))
+    sp, gl = mf.random_positions(4, seed=5)
+    s0 = capi.weight_cache_stats()
+    h1 = capi.Handle(capi.Model(blob), 4, precision=capi.PRECISION_FP16)
+    s1 = capi.weight_cache_stats()
+    h2 = capi.Handle(capi.Model(blob), 8, precision=capi.PRECISION_FP16)  # another batch size: activations differ, weights do not
+    s2 = capi.weight_cache_stats()
+    assert s1["uploads"] > s0["uploads"] and s1["bytes"] > s0["bytes"]
+    assert s2["uploads"] == s1["uploads"] and s2["bytes"] == s1["bytes"] and s2["entries"] == s1["entries"], (s1, s2)
+    assert s2["hits"] - s1["hits"] >= s1["uploads"] - s0["uploads"]
+    a = h1.forward(sp, gl)
+    h1.close()
+    assert capi.weight_cache_stats()["entries"] == s2["entries"]
+    b = h2.forward(sp, gl)
+    for k in a:
+        assert np.array_equal(a[k], b[k]), k
+    h2.close()
+    s3 = capi.weight_cache_stats()
+    assert s3["entries"] == s0["entries"] and s3["bytes"] == s0["bytes"], (s0, s3)
+    # another precision is another set of tensors for the convolutions (fp32 tensors such as norms are shared again)
+    h3 = capi.Handle(capi.Model(blob), 4, precision=capi.PRECISION_BF16)
+    h3.close()
+
+
 def test_multi_layer_launches_are_bit_identical_to_single_launches():
     """Runs of consecutive convolutions are executed as one persistent launch whose tiles hand over through per-tile
     counters (KB_CHAIN: 1 = runs of 3x3 convolutions, the default; 2 = runs of any tensor-core convolutions; 0 = one

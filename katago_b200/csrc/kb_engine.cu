@@ -249,6 +249,8 @@ void Engine::addConvOp(const ConvDev& c, Epilogue ep, const std::string& tag) {
     ops_.back().tcPlan = plan;
     ops_.back().ep = ep;
     ops_.back().deps = deps;
+    ops_.back().convIn = c.in; ops_.back().convW = c.w; ops_.back().convInStride = c.inStride;
+    ops_.back().convInC = c.inC; ops_.back().convOutC = c.outC; ops_.back().convK = c.kY;
   }
   else {
     ConvDev cc = c;
@@ -904,6 +906,7 @@ Engine::Engine(const Model& m, int device, int maxBatch, int X, int Y, int preci
     });
   }
   emitHeads(m, trunkAct_);
+  planPostPre();
   planChains();
   if(chainPlans_.empty()) planTileDeps();
   cudaCheck(cudaStreamSynchronize(stream_), "engine setup");
@@ -916,6 +919,7 @@ Engine::~Engine() {
   for(ConvTcPlan* p : tcPlans_) convTcDestroy(p);
   for(AttnTcPlan* p : attnPlans_) attentionTcDestroy(p);
   for(ConvChainPlan* p : chainPlans_) convChainDestroy(p);
+  for(ConvPostPrePlan* p : postPrePlans_) convPostPreDestroy(p);
   for(auto& kv : graphs_) if(kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
   for(void* p : allocations_) cudaFree(p);
   {
@@ -962,6 +966,55 @@ int Engine::allocationOf(const void* p) const {
 // reads (their readers are the same three tiles).  Excluded: inputs that kernels other than convolutions produce
 // between the two (per-board bias, row sums), and a residual that the earlier launch itself wrote, because the
 // epilogue fetches the residual ahead of the producer's wait.
+// The closing 1x1 convolution of a nested bottleneck block writes the activated trunk tensor only for the opening 1x1
+// convolution of the next block, launched right after it, to read it once.  Such a pair becomes one launch of
+// convPostPreKernel, and the activated trunk tensor is not written at all.
+void Engine::planPostPre() {
+  const bool enabled = getenv("KB_FUSE_1X1") == nullptr || atoi(getenv("KB_FUSE_1X1")) != 0;
+  if(!enabled || chunkBoards_ > 0 || layerN_ != 0 || forceSimt_) return;
+  std::vector<Op> out;
+  size_t i = 0;
+  while(i < ops_.size()) {
+    ConvPostPrePlan* plan = nullptr;
+    if(i + 1 < ops_.size()) {
+      const Op& A = ops_[i];
+      const Op& B = ops_[i + 1];
+      const Epilogue& ea = A.ep;
+      const Epilogue& eb = B.ep;
+      const bool shapeOk = A.tcPlan && B.tcPlan && A.convK == 1 && B.convK == 1 && A.convInStride == A.convInC &&
+                           B.convIn == ea.outAct && B.convInStride == A.convOutC && B.convInC == A.convOutC;
+      const bool aOk = shapeOk && ea.residual && ea.residual == ea.outRaw && ea.resStride == A.convOutC && !ea.resMask && !ea.biasNC &&
+                       ea.rawC0 == 0 && ea.rawC1 == A.convOutC && ea.rawStride == A.convOutC && ea.outAct && ea.actC0 == 0 &&
+                       ea.actC1 == A.convOutC && ea.actStride == A.convOutC && !ea.sumsqOut && !ea.rowSumsq && ea.act != KB_ACT_SWIGLU_PAIRS;
+      const bool bOk = aOk && !eb.residual && !eb.biasNC && eb.outRaw && eb.outAct && eb.rawC0 == 0 && eb.rawC1 == B.convOutC &&
+                       eb.rawStride == B.convOutC && eb.actC0 == 0 && eb.actC1 == B.convOutC && eb.actStride == B.convOutC &&
+                       !eb.sumsqOut && !eb.rowSumsq && eb.act == ea.act;
+      if(bOk && convPostPreEligible(dt_, A.convInC, A.convOutC, B.convOutC)) {
+        plan = convPostPreCreate(dt_, A.convIn, A.convInC, A.convW, ea.outRaw, A.convOutC, ea.scale, ea.bias, ea.act, B.convW, eb.outRaw,
+                                 eb.outAct, B.convOutC, eb.scale, eb.bias, eb.act, mask_, rowsPadMax_);
+      }
+    }
+    if(plan) {
+      postPrePlans_.push_back(plan);
+      Op op;
+      op.flops = ops_[i].flops + ops_[i + 1].flops;
+      const double S = (double)X_ * Y_, es = (double)dtypeSize(dt_);
+      op.bytes = S * es * (ops_[i].convInC + 2.0 * ops_[i].convOutC + 2.0 * ops_[i + 1].convOutC);
+      op.cls = classId("conv1x1 " + std::to_string(ops_[i].convInC) + "->" + std::to_string(ops_[i].convOutC) + " +res | 1x1 ->" +
+                       std::to_string(ops_[i + 1].convOutC) + " tcgen05 fused");
+      int* status = statusWord_;
+      op.run = [plan, status](cudaStream_t st, const Geom& g) { return launchConvPostPre(st, plan, g, status); };
+      out.push_back(std::move(op));
+      i += 2;
+    }
+    else {
+      out.push_back(ops_[i]);
+      i++;
+    }
+  }
+  if(!postPrePlans_.empty()) ops_ = std::move(out);
+}
+
 // Replaces every run of two or more consecutive chainable tensor-core convolutions of the launch list by one
 // multi-layer launch (kb_conv_tc.cu, convChainKernel).  Between two members of a run nothing else is launched, so the
 // only producers of a member's inputs inside the run are the members before it, and their hand-over is per tile.

@@ -35,6 +35,9 @@ struct Op {
   // tensor-core convolutions only: what the launch reads and writes, and its per-tile dependency record
   const ConvTcPlan* tcPlan = nullptr;
   Epilogue ep;
+  const void* convIn = nullptr;   // input tensor, its row stride, weights and shape of the convolution
+  const void* convW = nullptr;
+  int convInStride = 0, convInC = 0, convOutC = 0, convK = 0;
   std::shared_ptr<ConvTcDeps> deps;
 };
 
@@ -150,6 +153,9 @@ class Engine {
   void planTileDeps();
   // Multi-layer launches (KB_CHAIN: 0 off, 1 runs of 3x3 convolutions, 2 runs of any tensor-core convolutions): runs of
   // consecutive convolutions of the launch list become one persistent launch each.
+  // Pairs (closing 1x1 of a nested bottleneck block, opening 1x1 of the next) as one launch (KB_FUSE_1X1=0: off).
+  std::vector<ConvPostPrePlan*> postPrePlans_;
+  void planPostPre();
   int chainMode_ = 0;
   std::vector<ConvChainPlan*> chainPlans_;
   void planChains();

@@ -183,6 +183,18 @@ int convTcDoneCount(const ConvTcPlan* p);
 int convTcGridSize(const ConvTcPlan* p, const Geom& g);
 cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epilogue& ep, int* statusWord, const ConvTcDeps* deps = nullptr);
 
+// The closing 1x1 convolution of a nested bottleneck block fused with the opening 1x1 convolution of the next one
+// (kb_conv_fused.cu): stream += w1 * in1; raw2 = w2 * act(stream * scale1 + bias1) * mask; act2 = act(raw2 * scale2 +
+// bias2) * mask.  The activated stream itself is not written anywhere.  Dense tensors, fp16 / bf16.
+struct ConvPostPrePlan;
+bool convPostPreEligible(int dt, int Cm, int Ct, int Cn);
+ConvPostPrePlan* convPostPreCreate(
+  int dt, const void* in1, int Cm, const void* w1, void* stream, int Ct, const float* scale1, const float* bias1, int act1,
+  const void* w2, void* raw2, void* act2, int Cn, const float* scale2, const float* bias2, int act2code, const float* mask,
+  int rowsPadMax);
+void convPostPreDestroy(ConvPostPrePlan* p);
+cudaError_t launchConvPostPre(cudaStream_t st, const ConvPostPrePlan* p, Geom g, int* statusWord);
+
 // Self-test of the bounded device-side waits: a kernel waits (limitNs, at most one second) on a barrier nothing arrives
 // at, gives up, and records code 199 in the status word.
 cudaError_t launchWaitTimeoutSelfTest(cudaStream_t st, int* statusWord, unsigned long long limitNs);

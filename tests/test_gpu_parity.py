@@ -303,20 +303,22 @@ def test_handles_of_one_model_share_one_weight_replica():
     h3.close()
 
 
-def test_multi_layer_launches_are_bit_identical_to_single_launches():
-    """Runs of consecutive convolutions are executed as one persistent launch whose tiles hand over through per-tile
-    counters (KB_CHAIN: 1 = runs of 3x3 convolutions, the default; 2 = runs of any tensor-core convolutions; 0 = one
-    launch per convolution).  The arithmetic of a tile does not depend on the mode, so the outputs must agree bit for
-    bit -- at the benchmark batch (every SM busy, tiles of consecutive layers in flight together), at a batch with fewer
+def test_fused_and_multi_layer_launches_are_bit_identical_to_single_launches():
+    """Two ways of merging launches must not change a single bit of the result, because the arithmetic of a tile does not
+    depend on them.  (1) Runs of consecutive convolutions execute as one persistent launch whose tiles hand over through
+    per-tile counters (KB_CHAIN: 1 = runs of 3x3 convolutions, the default; 2 = runs of any tensor-core convolutions; 0 =
+    one launch per convolution).  (2) The closing 1x1 convolution of a nested bottleneck block and the opening one of the
+    next block execute as one kernel that keeps the activated trunk tensor in shared memory (KB_FUSE_1X1=0: two launches).
+    Checked at the benchmark batch (every SM busy, tiles of consecutive layers in flight together), at a batch with fewer
     tiles per layer than SMs, and on repeated runs (graph replay)."""
     blob = mf.to_blob(mf.make_b18c384nbt(num_blocks=6))
-    old = os.environ.get("KB_CHAIN")
+    old = {k: os.environ.get(k) for k in ("KB_CHAIN", "KB_FUSE_1X1")}
     try:
         for n in (256, 3):
             sp, gl = mf.random_positions(n, seed=77, board_sizes=[19, 13, 9, 19] * (n // 4) + [19] * (n % 4))
             outs = {}
-            for mode in ("0", "1", "2"):
-                os.environ["KB_CHAIN"] = mode
+            for mode in (("0", "0"), ("1", "1"), ("2", "1"), ("1", "0"), ("0", "1")):
+                os.environ["KB_CHAIN"], os.environ["KB_FUSE_1X1"] = mode
                 h = capi.Handle(capi.Model(blob), n, precision=capi.PRECISION_FP16)
                 runs = [h.forward(sp, gl) for _ in range(4)]
                 h.close()
@@ -324,14 +326,15 @@ def test_multi_layer_launches_are_bit_identical_to_single_launches():
                     for k in r:
                         assert np.array_equal(r[k], runs[0][k]), (n, mode, k)
                 outs[mode] = runs[0]
-            for mode in ("1", "2"):
-                for k in outs["0"]:
-                    assert np.array_equal(outs[mode][k], outs["0"][k]), (n, mode, k)
+            for mode in outs:
+                for k in outs["0", "0"]:
+                    assert np.array_equal(outs[mode][k], outs["0", "0"][k]), (n, mode, k)
     finally:
-        if old is None:
-            os.environ.pop("KB_CHAIN", None)
-        else:
-            os.environ["KB_CHAIN"] = old
+        for k, v in old.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
 
 
 @pytest.mark.parametrize("factory,n", [(mf.make_b18c384nbt, 8), (mf.make_b28c512nbt, 8)], ids=["b18c384nbt", "b28c512nbt"])

@@ -345,7 +345,10 @@ def run_b200(args, rank, world, local, pg):
     if args.workload == "b18":
         try:
             with open(os.path.join(ROOT, "profiles", "conv3x3_192_b18_n256_traffic.json")) as f:
-                traffic = json.load(f)["dram_bytes_per_launch"]
+                per = json.load(f)["dram_bytes_per_launch"]
+            # DRAM bytes per launch of the dominant class (ncu, small case of the same shapes and batch), averaged over its launches
+            num = sum(per[k] * p["launches"] for p in dom for k in per if p["name"].endswith(k))
+            traffic = num / dom_launches if dom_launches and num > 0 else None
         except Exception:
             pass
     all_conv_flops = sum(p["flops"] for p in prof)
@@ -373,7 +376,7 @@ def run_b200(args, rank, world, local, pg):
         "gpu_launches": launches * args.steps,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak_used, "unit": "TFLOP/s", "frac": achieved / peak_used,
                      "frac_of_sustained_peak": achieved / peaks["tflops"], "frac_of_burst_peak": achieved / peaks["burst"],
-                     "traffic": traffic, "kernel": ("convTcKernel<half> 3x3 192->192 (both epilogue variants)" if args.workload in ("b18", "mixed") else wl["dominant"] + " (tcgen05)"), "launches": dom_launches,
+                     "traffic": traffic, "kernel": ("convChainKernel<half>: runs of 3-4 consecutive 3x3 192->192 convolutions per launch" if args.workload in ("b18", "mixed") else wl["dominant"] + " (tcgen05)"), "launches": dom_launches,
                      "avg_launch_ms": dom_ms / dom_launches if dom_launches else None, "share_of_step": dom_ms / total_ms,
                      "peak_source": f"MEASURED_PEAKS.json {peak_name} ({peaks['src']}); burst {peaks['burst']}, sustained {peaks['tflops']}",
                      "whole_step_tflops": all_conv_flops / (total_ms * 1e-3) / 1e12,
@@ -498,6 +501,26 @@ def run_c_abi_threads(args):
         h.close()
 
 
+def run_forward_only(args):
+    """Two forward passes of a workload at reduced depth, nothing timed: the small case that profiler captures run on
+    (same kernels and shapes as the full net, a fraction of its launches and memory)."""
+    import katago_b200 as kb
+    from katago_b200 import modelfile as mf
+    wl = WORKLOADS[args.workload]
+    kwargs = {"layers": args.blocks} if "transformer" in args.workload else {"num_blocks": args.blocks}
+    model = kb.Model(mf.to_blob(getattr(mf, wl["builder"])(**kwargs)))
+    batch = wl["batch"]
+    h = kb.Handle(model, batch, precision=dict(fp16=kb.PRECISION_FP16, bf16=kb.PRECISION_BF16)[wl["precision"]], device=0)
+    sizes = (wl["sizes"] * batch)[:batch] if wl["sizes"] else None
+    sp, gl = mf.random_positions(batch, seed=2000, board_sizes=sizes)
+    h.upload(sp, gl)
+    for _ in range(2):
+        h.forward_resident(batch)
+    h.download(batch)
+    print(json.dumps({"forward_only": args.workload, "blocks": args.blocks, "batch": batch, "launches_per_forward": h.launches_per_forward()}))
+    h.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -511,7 +534,11 @@ def main():
     ap.add_argument("--search-threads", default="512,1024")
     ap.add_argument("--positions", type=int, default=4)
     ap.add_argument("--c-abi-threads", type=int, default=0, help="T > 0: T host threads per GPU in one process, each calling kb_forward_host in a loop")
+    ap.add_argument("--forward-only", action="store_true", help="two untimed forward passes of --workload at --blocks blocks (for profiler captures)")
+    ap.add_argument("--blocks", type=int, default=6)
     args = ap.parse_args()
+    if args.forward_only:
+        return run_forward_only(args)
     if args.through_katago:
         return run_through_katago(args)
     if args.c_abi_threads > 0:

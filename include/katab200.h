@@ -62,6 +62,16 @@ void kb_handle_destroy(kb_handle* h);
  * stats[0..3] = live entries, their bytes, uploads made, uploads avoided (since the process started, all devices). */
 int kb_weight_cache_stats(int64_t stats[4]);
 
+/* The tile plan of a tensor-core convolution kY x kX = k x k, inC -> outC (inC as the device sees it: padded to a multiple
+ * of 64).  Replaces the OpenCL backend's start-up autotuner (cpp/neuralnet/opencltuner.cpp) by a committed table
+ * (katago_b200/csrc/kb_tile_table.h).  Host-only.  plan[0..5] = channels per tile (N of the MMA), CTA pairs (0/1), epilogue
+ * warps per TMEM lane quarter without / with a residual, multi-layer launches (0/1), 1 if the shape has a row in the table
+ * (0: fallback rules). */
+int kb_tile_plan(int k, int inC, int outC, int32_t plan[6]);
+/* Number of rows of the tile table; row i as rows[i*8 .. i*8+7] = k, inC, outC, then the plan fields of kb_tile_plan in
+ * order (without the last).  Fills at most cap rows. */
+int kb_tile_table(int32_t* rows, int cap, int32_t* count);
+
 /* Self-test of the failure path of the bounded device-side waits (no counterpart in the reference): on the handle's
  * stream a kernel waits limitNs nanoseconds (at most 1e9) on a barrier that nothing arrives at, gives up and records a
  * status code, exactly as a convolution kernel does when one of its waits runs out.  The call then synchronises and

@@ -16,7 +16,7 @@ _lib = None
 # Every symbol include/katab200.h declares.
 EXPORTED_SYMBOLS = [
     "kb_last_error", "kb_version", "kb_device_count", "kb_device_name", "kb_model_create", "kb_model_destroy",
-    "kb_model_info", "kb_model_meta_channels", "kb_forward_host_meta", "kb_upload_inputs_meta", "kb_handle_create", "kb_handle_destroy", "kb_handle_precision", "kb_weight_cache_stats", "kb_selftest_wait_timeout", "kb_forward_host",
+    "kb_model_info", "kb_model_meta_channels", "kb_forward_host_meta", "kb_upload_inputs_meta", "kb_handle_create", "kb_handle_destroy", "kb_handle_precision", "kb_weight_cache_stats", "kb_selftest_wait_timeout", "kb_tile_plan", "kb_tile_table", "kb_forward_host",
     "kb_upload_inputs", "kb_forward_resident", "kb_download_outputs", "kb_time_forward_resident", "kb_time_forward_steps",
     "kb_profile_enable", "kb_profile_reset", "kb_profile_read", "kb_launches_per_forward", "kb_debug_read_trunk",
     "kb_eval_layer", "kb_host_alloc", "kb_host_free", "kb_conv_noalloc", "kb_conv_noalloc_last_error",
@@ -62,6 +62,8 @@ def lib():
         L.kb_handle_precision.argtypes = [vp, ctypes.POINTER(ci)]
         L.kb_weight_cache_stats.argtypes = [ctypes.POINTER(ctypes.c_int64)]
         L.kb_selftest_wait_timeout.argtypes = [vp, ctypes.c_ulonglong]
+        L.kb_tile_plan.argtypes = [ci, ci, ci, ctypes.POINTER(ctypes.c_int32)]
+        L.kb_tile_table.argtypes = [ctypes.POINTER(ctypes.c_int32), ci, ctypes.POINTER(ctypes.c_int32)]
         L.kb_forward_host.argtypes = [vp, ci] + [vp] * 8
         L.kb_upload_inputs.argtypes = [vp, ci, vp, vp, vp]
         L.kb_forward_resident.argtypes = [vp, ci]
@@ -93,6 +95,23 @@ def _check(status: int, what: str):
 
 def _ptr(a):
     return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
+
+
+def tile_plan(k: int, in_c: int, out_c: int) -> dict:
+    """Tile plan of a tensor-core convolution (in_c as the device sees it, a multiple of 64)."""
+    a = (ctypes.c_int32 * 6)()
+    _check(lib().kb_tile_plan(k, in_c, out_c, a), "kb_tile_plan")
+    return dict(bn=int(a[0]), pair=int(a[1]), epi_warps=int(a[2]), epi_warps_res=int(a[3]), chain=int(a[4]), from_table=bool(a[5]))
+
+
+def tile_table() -> list:
+    """Rows of the committed tile table: dicts with k, in_c, out_c and the plan fields."""
+    n = ctypes.c_int32()
+    _check(lib().kb_tile_table(None, 0, ctypes.byref(n)), "kb_tile_table")
+    a = (ctypes.c_int32 * (8 * n.value))()
+    _check(lib().kb_tile_table(a, n.value, ctypes.byref(n)), "kb_tile_table")
+    keys = ("k", "in_c", "out_c", "bn", "pair", "epi_warps", "epi_warps_res", "chain")
+    return [dict(zip(keys, [int(a[i * 8 + j]) for j in range(8)])) for i in range(n.value)]
 
 
 def weight_cache_stats() -> dict:

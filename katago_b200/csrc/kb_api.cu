@@ -7,6 +7,7 @@
 #include <string>
 
 #include "kb_engine.h"
+#include "kb_tile_table.h"
 
 struct kb_model {
   kb::Model m;
@@ -100,6 +101,27 @@ int kb_weight_cache_stats(int64_t stats[4]) {
     need(stats, "stats");
     const kb::WeightCacheStats s = kb::weightCacheStats();
     stats[0] = s.entries; stats[1] = s.bytes; stats[2] = s.uploads; stats[3] = s.hits;
+  });
+}
+
+int kb_tile_plan(int k, int inC, int outC, int32_t plan[6]) {
+  return guarded([&]() {
+    need(plan, "plan");
+    bool fromTable = false;
+    const kb::TileRow r = kb::tilePlanFor(k, inC, outC, &fromTable);
+    plan[0] = r.BN; plan[1] = r.pair; plan[2] = r.epiWarps; plan[3] = r.epiWarpsRes; plan[4] = r.chain; plan[5] = fromTable ? 1 : 0;
+  });
+}
+int kb_tile_table(int32_t* rows, int cap, int32_t* count) {
+  return guarded([&]() {
+    need(count, "count");
+    const int n = (int)(sizeof(kb::TILE_TABLE) / sizeof(kb::TILE_TABLE[0]));
+    *count = n;
+    for(int i = 0; i < n && i < cap && rows; i++) {
+      const kb::TileRow& r = kb::TILE_TABLE[i];
+      const int32_t v[8] = {r.k, r.inC, r.outC, r.BN, r.pair, r.epiWarps, r.epiWarpsRes, r.chain};
+      for(int j = 0; j < 8; j++) rows[i * 8 + j] = v[j];
+    }
   });
 }
 

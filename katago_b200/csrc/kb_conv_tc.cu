@@ -20,6 +20,7 @@
 // Every wait is bounded: on time-out the kernel records a code in the status word and all roles
 // leave through the common exit, which still frees TMEM.
 #include "kb_conv_dev.cuh"
+#include "kb_tile_table.h"
 
 #include <cuda.h>
 #include <cstdio>
@@ -1197,13 +1198,6 @@ struct ConvTcPlan {
   CUtensorMap tmRes, tmRaw, tmAct;
 };
 
-// Tile table: output-channel tile width per convolution shape, chosen from measurements on B200 (batch 256, 19x19).
-// Shapes that are not listed take the largest multiple of 16 that divides outC and fits one MMA (N <= 256).
-struct TileRule { int k, inC, outC, BN; };
-static const TileRule TILE_TABLE[] = {
-  {0, 0, 0, 0},
-};
-
 static int pickBN(int k, int inC, int outC) {
   // experiments: KB_TC_BN="k:inC:outC=BN,..." overrides the table
   if(const char* e = getenv("KB_TC_BN")) {
@@ -1218,11 +1212,8 @@ static int pickBN(int k, int inC, int outC) {
       if(*s == ',') s++;
     }
   }
-  for(const TileRule& r : TILE_TABLE)
-    if(r.k == k && r.inC == inC && r.outC == outC && r.BN > 0 && outC % r.BN == 0) return r.BN;
-  for(int bn = 256; bn >= 16; bn -= 16)
-    if(outC % bn == 0) return bn;
-  return 0;
+  const TileRow r = tilePlanFor(k, inC, outC);
+  return (r.BN > 0 && outC % r.BN == 0) ? r.BN : 0;
 }
 
 bool convTcEligible(int dt, int inC, int outC, int kY, int kX) {
@@ -1319,7 +1310,7 @@ ConvTcPlan* convTcCreate(
   // all 1x1 convolutions run 5-10 % slower in pairs (a 256-row MMA takes 143 cycles against 127 for 128 rows, and the
   // two CTAs move in lockstep).  KB_TC_PAIR=0/1 forces the choice for experiments.  Pairs need an even row-tile count,
   // which the padded-rows layout guarantees.
-  bool wantPair = kY == 3 && p->BN == 256;
+  bool wantPair = tilePlanFor(kY, inC, outC).pair != 0;
   if(const char* e = getenv("KB_TC_PAIR")) wantPair = atoi(e) != 0;
   p->pair = (wantPair && (rowsPadMax % (2 * TC_BM)) == 0 && (p->BN % 16) == 0) ? 1 : 0;
   p->aSlotBytes = p->aRows * 128;
@@ -1365,9 +1356,13 @@ bool convTcSetEpilogue(ConvTcPlan* p, const Epilogue& ep) {
   // every 1x1 convolution that qualifies.
   static const int wideMode = getenv("KB_TC_WIDE_EPI") ? atoi(getenv("KB_TC_WIDE_EPI")) : 1;
   p->cg = TC_EPI_CG;
-  if(TC_EPI_CG == 2 && wideMode > 0 && p->kY == 1 && !p->pair && !needsStaged && (p->BN / 32) % TC_EPI_CG_WIDE == 0 &&
-     (ep.residual || wideMode > 1))
-    p->cg = TC_EPI_CG_WIDE;
+  {
+    const TileRow row = tilePlanFor(p->kY, p->inC, p->outC);
+    const int want = wideMode > 1 ? TC_EPI_CG_WIDE : (ep.residual ? row.epiWarpsRes : row.epiWarps);
+    // the 12-warp variant exists for single CTAs, 1x1 kernels, plain staged epilogues, and tiles of 3n units
+    if(TC_EPI_CG == 2 && wideMode > 0 && want == TC_EPI_CG_WIDE && p->kY == 1 && !p->pair && !needsStaged && (p->BN / 32) % TC_EPI_CG_WIDE == 0)
+      p->cg = TC_EPI_CG_WIDE;
+  }
   const int unitsPerWarp = (p->BN / 32 + p->cg - 1) / p->cg;
   p->resRing = (p->kY == 1) ? unitsPerWarp + 1 : 2;
   const int rawUnits = ep.residual ? p->resRing : (ep.outRaw ? 2 : 0);
@@ -1388,6 +1383,7 @@ bool convTcSetEpilogue(ConvTcPlan* p, const Epilogue& ep) {
 
 bool convTcDepsCapable(const ConvTcPlan* p) { return p && p->tmaEpi && !p->pair; }
 int convTcKernelSize(const ConvTcPlan* p) { return p->kY; }
+bool convTcChainPreferred(const ConvTcPlan* p) { return tilePlanFor(p->kY, p->inC, p->outC).chain != 0; }
 int convTcDoneCount(const ConvTcPlan* p) { return (p->outC / p->BN) * tcEpiWarps(p->cg); }
 int convTcGridSize(const ConvTcPlan* p, const Geom& g) {
   const int unitRows = p->pair ? 2 * TC_BM : TC_BM;

@@ -1023,7 +1023,7 @@ void Engine::planChains() {
   if(chainMode_ <= 0 || chunkBoards_ > 0 || layerN_ != 0 || forceSimt_) return;
   const size_t tiles = (size_t)rowsPadMax_ / 128;
   auto chainable = [&](const Op& op) {
-    return op.tcPlan && convChainEligible(op.tcPlan, op.ep) && (chainMode_ >= 2 || convTcKernelSize(op.tcPlan) == 3);
+    return op.tcPlan && convChainEligible(op.tcPlan, op.ep) && (chainMode_ >= 2 || convTcChainPreferred(op.tcPlan));
   };
   // counters: one array per chain member
   size_t members = 0;

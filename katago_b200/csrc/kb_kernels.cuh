@@ -179,6 +179,8 @@ struct ConvTcDeps {
 };
 bool convTcDepsCapable(const ConvTcPlan* p);
 int convTcKernelSize(const ConvTcPlan* p);
+// True if the tile table marks this shape for multi-layer launches.
+bool convTcChainPreferred(const ConvTcPlan* p);
 int convTcDoneCount(const ConvTcPlan* p);
 int convTcGridSize(const ConvTcPlan* p, const Geom& g);
 cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epilogue& ep, int* statusWord, const ConvTcDeps* deps = nullptr);

@@ -1,0 +1,77 @@
+// Tile table of the tensor-core convolution kernels: what the reference's OpenCL backend finds with its autotuner at
+// start-up (cpp/neuralnet/opencltuner.cpp) is a committed table here, one row per convolution shape of the networks
+// this library is measured on, each chosen from measurements on B200.  Host-only code (no CUDA): the planner of
+// kb_conv_tc.cu and the C ABI (kb_tile_plan) both read it.
+//
+// A row fixes, for a convolution k x k, inC -> outC (inC as the device sees it, i.e. padded to a multiple of 64):
+//   BN        output channels per tile = N of the MMA (M is always 128 rows, K chunks are 64 channels)
+//   pair      1: CTA pairs (cta_group::2, 256-row tiles, half a weight tile per CTA)
+//   epiWarps  epilogue warps per TMEM lane quarter WITHOUT a residual / WITH a residual (2 = 8 warps, 3 = 12 warps)
+//   chain     1: runs of such convolutions execute as one persistent multi-layer launch (3x3 only)
+// Shapes without a row fall back to rules that reproduce what the rows were generalised from: BN = the largest
+// multiple of 16 that divides outC (at most 256), pairs for 3x3 with BN = 256, 12 epilogue warps for 1x1 convolutions
+// with a residual whose tile has a multiple of three 32-channel units.
+//
+// The comments give the measurement behind each row: microseconds per launch at the batch of the configuration
+// (CUDA events around every launch) and, where captured, the tensor-pipe utilisation ncu reports for that launch
+// (sm__pipe_tensor_cycles_active.avg.pct_of_peak_sustained_elapsed); the summaries are under profiles/.
+#pragma once
+
+namespace kb {
+
+struct TileRow {
+  int k, inC, outC;
+  int BN, pair, epiWarps, epiWarpsRes, chain;
+};
+
+static const TileRow TILE_TABLE[] = {
+  // ---- b18c384nbt, fp16, batch 256 (102 400 padded rows = 800 row tiles) ----
+  // 3x3 192->192: N=192 61 us, N=96 93 us, N=64 130 us (the cost of an MMA has a large part that does not shrink with
+  // N); pairs 5-10 % slower; 12 epilogue warps 5 % slower (they cost a weight slot).  In a chain 58-61 us per layer.
+  {3, 192, 192, 192, 0, 2, 2, 1},
+  // 3x3 128->192 (last convolution of a gpool block, with residual): same tile as above
+  {3, 128, 192, 192, 0, 2, 2, 1},
+  // 3x3 64->384 (stem: 22 input planes padded to 64): two channel tiles, epilogue-bound
+  {3, 64, 384, 192, 0, 2, 2, 0},
+  // 1x1 384->192 (opens a nested block; also the merged head convolution p1|g1|v1): N=192 41.5 us, N=96 44.0, N=64 57.1
+  {1, 384, 192, 192, 0, 2, 2, 0},
+  // 1x1 192->384 with residual (closes a nested block): N=192 64.1 us, N=128 78.8, N=96 74.9; 12 epilogue warps 67.8 us
+  // against 76.4 with 8.  Followed by a 384->192 it runs fused with it (kb_conv_fused.cu): 97 us for the pair against 123.
+  {1, 192, 384, 192, 0, 2, 3, 0},
+  // ---- b28c512nbt, bf16, batch 512 (204 800 padded rows) ----
+  // 3x3 256->256: N=256 with CTA pairs 179 us (1199 TFLOP/s), without 3 % slower; chains bring nothing at 10.8 rounds
+  {3, 256, 256, 256, 1, 2, 2, 0},
+  {3, 192, 256, 256, 1, 2, 2, 0},
+  {3, 64, 512, 256, 1, 2, 2, 0},
+  {1, 512, 256, 256, 0, 2, 2, 0},
+  {1, 256, 512, 256, 0, 2, 2, 0},
+  // ---- transformer 12 x (6 heads x 64, SwiGLU 1024), fp16, batch 128 (51 200 padded rows) ----
+  {1, 384, 1152, 192, 0, 2, 2, 0},   // norm + Q|K|V
+  {1, 384, 384, 192, 0, 2, 2, 0},    // attention output with residual (records row sums: 8-warp epilogue only)
+  {1, 384, 2048, 256, 0, 2, 2, 0},   // norm + up|gate with the SwiGLU epilogue (8 epilogue warps only)
+  {1, 1024, 384, 192, 0, 2, 2, 0},   // FFN down with residual (records row sums)
+};
+
+inline const TileRow* tileTableLookup(int k, int inC, int outC) {
+  for(const TileRow& r : TILE_TABLE)
+    if(r.k == k && r.inC == inC && r.outC == outC) return &r;
+  return nullptr;
+}
+
+// The plan for a shape: the table's row, or the fallback rules.  fromTable tells which.
+inline TileRow tilePlanFor(int k, int inC, int outC, bool* fromTable = nullptr) {
+  if(const TileRow* r = tileTableLookup(k, inC, outC)) {
+    if(fromTable) *fromTable = true;
+    return *r;
+  }
+  if(fromTable) *fromTable = false;
+  TileRow r = {k, inC, outC, 0, 0, 2, 2, 0};
+  for(int bn = 256; bn >= 16; bn -= 16)
+    if(outC % bn == 0) { r.BN = bn; break; }
+  r.pair = (k == 3 && r.BN == 256) ? 1 : 0;
+  r.epiWarpsRes = (k == 1 && !r.pair && r.BN > 0 && (r.BN / 32) % 3 == 0 && (r.BN % 32) == 0) ? 3 : 2;
+  r.chain = (k == 3 && !r.pair) ? 1 : 0;
+  return r;
+}
+
+}  // namespace kb

@@ -14,7 +14,7 @@
 //
 // The comments give the measurement behind each row: microseconds per launch at the batch of the configuration
 // (CUDA events around every launch) and, where captured, the tensor-pipe utilisation ncu reports for that launch
-// (sm__pipe_tensor_cycles_active.avg.pct_of_peak_sustained_elapsed); the summaries are under profiles/.
+// (sm__pipe_tensor_cycles_active.avg.pct_of_peak_sustained_elapsed, on a reduced-depth net at the same batch).
 #pragma once
 
 namespace kb {
@@ -26,30 +26,34 @@ struct TileRow {
 
 static const TileRow TILE_TABLE[] = {
   // ---- b18c384nbt, fp16, batch 256 (102 400 padded rows = 800 row tiles) ----
-  // 3x3 192->192: N=192 61 us, N=96 93 us, N=64 130 us (the cost of an MMA has a large part that does not shrink with
-  // N); pairs 5-10 % slower; 12 epilogue warps 5 % slower (they cost a weight slot).  In a chain 58-61 us per layer.
+  // 3x3 192->192: N=192 61 us, N=96 93 us, N=64 130 us per launch (the cost of an MMA has a large part that does not shrink
+  // with N); CTA pairs 5-10 % slower; 12 epilogue warps 5 % slower (they cost a weight slot).  ncu: tensor pipe 54.9 % of
+  // the launch (50.1 % with a residual); in a chain of four 55 us per layer at 66 %.
   {3, 192, 192, 192, 0, 2, 2, 1},
-  // 3x3 128->192 (last convolution of a gpool block, with residual): same tile as above
+  // 3x3 128->192 (last convolution of a gpool block, with residual): the tile of the row above; 57 us, tensor pipe 38.9 %
   {3, 128, 192, 192, 0, 2, 2, 1},
-  // 3x3 64->384 (stem: 22 input planes padded to 64): two channel tiles, epilogue-bound
+  // 3x3 64->384 (stem: 22 input planes padded to 64): two channel tiles, bound by its epilogue; 77 us, tensor pipe 27.6 %
   {3, 64, 384, 192, 0, 2, 2, 0},
-  // 1x1 384->192 (opens a nested block; also the merged head convolution p1|g1|v1): N=192 41.5 us, N=96 44.0, N=64 57.1
+  // 1x1 384->192 (opens a nested block; also the merged head convolution p1|g1|v1): N=192 41.5 us, N=96 44.0, N=64 57.1;
+  // tensor pipe 17.7 %
   {1, 384, 192, 192, 0, 2, 2, 0},
   // 1x1 192->384 with residual (closes a nested block): N=192 64.1 us, N=128 78.8, N=96 74.9; 12 epilogue warps 67.8 us
-  // against 76.4 with 8.  Followed by a 384->192 it runs fused with it (kb_conv_fused.cu): 97 us for the pair against 123.
+  // against 76.4 with 8; tensor pipe 11.1 %.  Followed by a 384->192 it runs fused with it (kb_conv_fused.cu): 81.5 us
+  // under ncu for the pair against 101.5, tensor pipe 17.3 %.
   {1, 192, 384, 192, 0, 2, 3, 0},
   // ---- b28c512nbt, bf16, batch 512 (204 800 padded rows) ----
-  // 3x3 256->256: N=256 with CTA pairs 179 us (1199 TFLOP/s), without 3 % slower; chains bring nothing at 10.8 rounds
+  // 3x3 256->256: N=256 with CTA pairs 179 us (1199 TFLOP/s; ncu: tensor pipe 80 %, 75 % with a residual), without pairs
+  // 3 % slower; multi-layer launches bring nothing at 10.8 rounds of tiles per layer (730 us for four against 4 x 180)
   {3, 256, 256, 256, 1, 2, 2, 0},
-  {3, 192, 256, 256, 1, 2, 2, 0},
-  {3, 64, 512, 256, 1, 2, 2, 0},
-  {1, 512, 256, 256, 0, 2, 2, 0},
-  {1, 256, 512, 256, 0, 2, 2, 0},
+  {3, 192, 256, 256, 1, 2, 2, 0},   // last convolution of a gpool block
+  {3, 64, 512, 256, 1, 2, 2, 0},    // stem: 191 us, tensor pipe 29.7 %
+  {1, 512, 256, 256, 0, 2, 2, 0},   // 84 us, tensor pipe 31 % (also the merged head convolution: 73 us, 36 %)
+  {1, 256, 512, 256, 0, 2, 2, 0},   // with residual: 180 us, tensor pipe 14 % (8 units per tile: no 12-warp variant)
   // ---- transformer 12 x (6 heads x 64, SwiGLU 1024), fp16, batch 128 (51 200 padded rows) ----
-  {1, 384, 1152, 192, 0, 2, 2, 0},   // norm + Q|K|V
-  {1, 384, 384, 192, 0, 2, 2, 0},    // attention output with residual (records row sums: 8-warp epilogue only)
-  {1, 384, 2048, 256, 0, 2, 2, 0},   // norm + up|gate with the SwiGLU epilogue (8 epilogue warps only)
-  {1, 1024, 384, 192, 0, 2, 2, 0},   // FFN down with residual (records row sums)
+  {1, 384, 1152, 192, 0, 2, 2, 0},   // norm + Q|K|V: 70 us, tensor pipe 31 %
+  {1, 384, 384, 192, 0, 2, 2, 0},    // attention output with residual (records row sums: 8-warp epilogue only): 35 us, 20 %
+  {1, 384, 2048, 256, 0, 2, 2, 0},   // norm + up|gate with the SwiGLU epilogue (8 epilogue warps only): 124 us, 32 %
+  {1, 1024, 384, 192, 0, 2, 2, 0},   // FFN down with residual (records row sums): 62 us, 31 %
 };
 
 inline const TileRow* tileTableLookup(int k, int inC, int outC) {

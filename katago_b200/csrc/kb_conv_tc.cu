@@ -255,6 +255,13 @@ __device__ __forceinline__ bool epilogueTileTma(
   const bool hasRes = ep.residual != nullptr;
   const int sw = (lane >> 1) & 3;  // 64-byte swizzle: 16-byte chunk index XOR bits 1..2 of the row
   const bool on = mk == 1.0f;
+  // rotary embedding: this thread's board point; rows that are not board points turn by the angle of (0,0), which is 0
+  float ropePx = 0.0f, ropePy = 0.0f;
+  if(ACT == KB_ACT_ROPE_QK) {
+    const int br = (m0 + q * 32 + lane) % a.g.PB;
+    const int y = br / a.g.RW, x = br - y * a.g.RW;
+    if(y < a.g.Y && x < a.g.X) { ropePx = (float)x; ropePy = (float)y; }
+  }
   for(int j = 0; j < es.nU; j++) {
     const int u = cg + CG * j;
     const uint32_t slot = es.seq % (uint32_t)es.ring;
@@ -299,6 +306,21 @@ __device__ __forceinline__ bool epilogueTileTma(
         const uint32_t xu[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
         for(int k = 0; k < 4; k++) v[4 * jj + k] = Pack2<T>::addTo(xu[k], v[4 * jj + k]);
+      }
+    }
+    if(ACT == KB_ACT_ROPE_QK && c < ep.ropeC1) {
+      // v[k] is output channel pair c/2 + k; its two frequencies lie in shared memory (sScale holds ropeFreq), the
+      // same address for every lane
+      const float4* fq = reinterpret_cast<const float4*>(sScale + c);
+#pragma unroll
+      for(int k = 0; k < 8; k++) {
+        const float4 f = fq[k];
+        float sn0, cs0, sn1, cs1;
+        __sincosf(fmaf(ropePy, f.y, ropePx * f.x), &sn0, &cs0);
+        __sincosf(fmaf(ropePy, f.w, ropePx * f.z), &sn1, &cs1);
+        const float2 t0 = v[2 * k], t1 = v[2 * k + 1];
+        v[2 * k] = make_float2(t0.x * cs0 - t0.y * sn0, t0.x * sn0 + t0.y * cs0);
+        v[2 * k + 1] = make_float2(t1.x * cs1 - t1.y * sn1, t1.x * sn1 + t1.y * cs1);
       }
     }
     const bool doRaw = ep.outRaw && c >= ep.rawC0 && c < ep.rawC1;
@@ -475,6 +497,10 @@ __global__ void __launch_bounds__(tcThreads(CG, DEPS), 1) convTcKernel(
   if(a.ep.outAct && a.ep.scale) {
     const int nAct = a.ep.actC1 - a.ep.actC0;
     for(int i = threadIdx.x; i < nAct; i += blockDim.x) { sScale[i] = a.ep.scale[i]; sBias[i] = a.ep.bias[i]; }
+  }
+  if(ACT == KB_ACT_ROPE_QK) {
+    // rotary frequencies of the query and key channels (up to 1024 floats: the scale and bias arrays together)
+    for(int i = threadIdx.x; i < a.ep.ropeC1; i += blockDim.x) sScale[i] = a.ep.ropeFreq[i];
   }
   tcFenceBefore();
   __syncthreads();
@@ -1164,6 +1190,8 @@ static ConvTcKernelFn kernelForAct(int act) {
     case KB_ACT_MISH_SCALE8: return convTcKernel<T, KB_ACT_MISH_SCALE8, TMA_EPI, PAIR, CG, DEPS>;
     // the SwiGLU epilogue exists with the default warp count and whole-grid dependencies only
     case KB_ACT_SWIGLU_PAIRS: return (CG == TC_EPI_CG && !DEPS) ? convTcKernel<T, KB_ACT_SWIGLU_PAIRS, TMA_EPI, PAIR, TC_EPI_CG, false> : nullptr;
+    // so does the rotary epilogue, for single CTAs with the staged epilogue
+    case KB_ACT_ROPE_QK: return (TMA_EPI && !PAIR && CG == TC_EPI_CG && !DEPS) ? convTcKernel<T, KB_ACT_ROPE_QK, true, false, TC_EPI_CG, false> : nullptr;
     default: return convTcKernel<T, KB_ACT_IDENTITY, TMA_EPI, PAIR, CG, DEPS>;
   }
 }
@@ -1232,6 +1260,13 @@ int convTcRowSumSlots(int k, int inC, int outC) {
   const int bn = pickBN(k, inC, outC);
   // the staged epilogue needs whole 32-channel units
   return (bn > 0 && (bn % 32) == 0 && (outC % 32) == 0) ? (outC / bn) * TC_EPI_CG : 0;
+}
+
+bool convTcRopeEligible(int dt, int inC, int outC, int ropeC1) {
+  // whole 32-channel units, frequencies in the kernel's 1024 floats of parameter space, single CTAs (the variant does
+  // not exist for CTA pairs)
+  if(!convTcRowNormEligible(dt, inC, outC) || ropeC1 <= 0 || ropeC1 > 1024 || (ropeC1 % 32) != 0) return false;
+  return tilePlanFor(1, inC, outC).pair == 0;
 }
 
 bool convTcSwigluEligible(int dt, int inC, int F) {
@@ -1343,7 +1378,7 @@ bool convTcSetEpilogue(ConvTcPlan* p, const Epilogue& ep) {
   if(ep.outRaw) ok = ok && aligned32(ep.rawC0, ep.rawC1) && (ep.rawStride % 8) == 0 && (reinterpret_cast<uintptr_t>(ep.outRaw) & 15) == 0;
   if(ep.outAct) ok = ok && aligned32(ep.actC0, ep.actC1) && (ep.actStride % 8) == 0 && (reinterpret_cast<uintptr_t>(ep.outAct) & 15) == 0;
   if(ep.residual) ok = ok && (ep.resStride % 8) == 0 && ep.resStride >= p->outC && (reinterpret_cast<uintptr_t>(ep.residual) & 15) == 0;
-  const bool needsStaged = ep.act == KB_ACT_SWIGLU_PAIRS || ep.sumsqOut || ep.rowSumsq;
+  const bool needsStaged = ep.act == KB_ACT_SWIGLU_PAIRS || ep.act == KB_ACT_ROPE_QK || ep.sumsqOut || ep.rowSumsq;
   if(!ok || (!ep.outRaw && !ep.outAct)) return needsStaged ? false : sizeRings(p, 0);
   // per warp: the residual/raw ring (one tile of this warp's units plus one with a residual, else two units) and one
   // unit for the activated output
@@ -1366,7 +1401,7 @@ bool convTcSetEpilogue(ConvTcPlan* p, const Epilogue& ep) {
   const int unitsPerWarp = (p->BN / 32 + p->cg - 1) / p->cg;
   p->resRing = (p->kY == 1) ? unitsPerWarp + 1 : 2;
   const int rawUnits = ep.residual ? p->resRing : (ep.outRaw ? 2 : 0);
-  p->epiWarpBytes = (rawUnits + 1) * TC_UNIT_BYTES;
+  p->epiWarpBytes = (rawUnits + (ep.outAct ? 1 : 0)) * TC_UNIT_BYTES;
   if(!sizeRings(p, tcEpiWarps(p->cg) * p->epiWarpBytes)) { p->cg = TC_EPI_CG; return needsStaged ? false : sizeRings(p, 0); }
   const uint64_t rows = (uint64_t)p->rowsPadMax;
   const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_64B;
@@ -1464,7 +1499,7 @@ cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epi
   // if that one reports and fills every SM (its CTAs can then only all have started once the kernels before it have
   // left the SMs, so at most these two grids overlap).
   bool useDeps = false;
-  if(deps && convTcDepsCapable(p) && ep.act != KB_ACT_SWIGLU_PAIRS) {
+  if(deps && convTcDepsCapable(p) && ep.act != KB_ACT_SWIGLU_PAIRS && ep.act != KB_ACT_ROPE_QK) {
     if(deps->done) { a.doneCtr = deps->done; useDeps = true; }
     if(deps->wait && deps->waitPlan && convTcDepsCapable(deps->waitPlan) && convTcGridSize(deps->waitPlan, g) == p->numSMs) {
       a.depCtr = deps->wait;
@@ -1477,7 +1512,8 @@ cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epi
     if(dbg == 1) a.depCtr = nullptr;                       // report only
     if(dbg == 2) { a.doneCtr = nullptr; a.depTarget = 0; }  // poll only (always satisfied)
   }
-  ConvTcKernelFn fn = kernelFor(p->dt, ep.outAct ? ep.act : KB_ACT_IDENTITY, p->tmaEpi != 0, p->pair != 0, p->cg, useDeps);
+  const int actVariant = ep.act == KB_ACT_ROPE_QK ? KB_ACT_ROPE_QK : (ep.outAct ? ep.act : KB_ACT_IDENTITY);
+  ConvTcKernelFn fn = kernelFor(p->dt, actVariant, p->tmaEpi != 0, p->pair != 0, p->cg, useDeps);
   cfg.blockDim = dim3(tcThreads(p->cg, useDeps));
   if(!fn) return cudaErrorInvalidValue;
   {
@@ -1523,7 +1559,7 @@ int convTcTileWidth(const ConvTcPlan* p) { return p->BN; }
 
 bool convChainEligible(const ConvTcPlan* p, const Epilogue& ep) {
   if(!p || !p->tmaEpi || p->pair) return false;
-  if(ep.biasNC || ep.rowSumsq || ep.sumsqOut || ep.act == KB_ACT_SWIGLU_PAIRS) return false;
+  if(ep.biasNC || ep.rowSumsq || ep.sumsqOut || ep.act == KB_ACT_SWIGLU_PAIRS || ep.act == KB_ACT_ROPE_QK) return false;
   if((p->BN % 32) != 0) return false;
   return true;
 }

@@ -330,6 +330,25 @@ static ConvW upGateInterleaved(const MatMulW& up, const MatMulW& gate) {
   return c;
 }
 
+// The rotary frequencies per output channel pair of the merged Q|K projection: entries 2i and 2i+1 are the x and y
+// frequency of channel pair (2i, 2i+1), query heads first, then key heads (a query head uses the frequencies of its
+// key-value head; fixed theta: the first half of a head's pairs turns with y, the second with x).
+static std::vector<float> ropeChannelFreqs(const BlockW& b) {
+  const int pairs = b.qDim / 2, pairsPerDim = pairs / 2, dimHalf = b.qDim / 2;
+  std::vector<float> f((size_t)(b.heads + b.kvHeads) * b.qDim, 0.0f);
+  for(int hh = 0; hh < b.heads + b.kvHeads; hh++) {
+    const int kvh = hh < b.heads ? hh / (b.heads / b.kvHeads) : hh - b.heads;
+    for(int p = 0; p < pairs; p++) {
+      float fx, fy;
+      if(b.learnableRope) { fx = b.ropeFreqs[(kvh * pairs + p) * 2 + 0]; fy = b.ropeFreqs[(kvh * pairs + p) * 2 + 1]; }
+      else if(p < pairsPerDim) { fx = 0.0f; fy = 1.0f / powf(b.ropeTheta, (float)(2 * p) / (float)dimHalf); }
+      else { fx = 1.0f / powf(b.ropeTheta, (float)(2 * (p - pairsPerDim)) / (float)dimHalf); fy = 0.0f; }
+      f[((size_t)hh * pairs + p) * 2] = fx; f[((size_t)hh * pairs + p) * 2 + 1] = fy;
+    }
+  }
+  return f;
+}
+
 // cos/sin tables of the rotary embedding, [tableHeads][pairs][S] (desc.cpp:1212-1275 computeRopeCosSin).
 static void ropeTables(const BlockW& b, int X, int Y, std::vector<float>& cosT, std::vector<float>& sinT, int& tableHeads) {
   const int S = X * Y, pairs = b.qDim / 2;
@@ -511,23 +530,6 @@ void Engine::emitBlock(const BlockW& b, int C, void* raw, void* act, const BNW* 
     void* attn = scratch("tfAttn" + d + "_c" + std::to_string(oC), (size_t)rowsPadMax_ * oC * es);
     float* gamma = uploadF32(b.preLN.weight);
     const float eps = b.preLN.eps;
-    ConvW qkvW = matmulsAsConv({&b.q, &b.k, &b.v});
-    Epilogue eq;
-    eq.outRaw = qkv; eq.rawStride = qkvC; eq.rawC0 = 0; eq.rawC1 = qkvC;
-    if(rowSumsCur_ >= 0 && convTcRowNormEligible(dt_, C, qkvC)) {
-      // the norm is folded into the projection: it reads the stream itself and scales its rows
-      foldGain(qkvW, b.preLN.weight);
-      ConvDev cq = makeConv({&qkvW}, raw, C, C);
-      eq.rowSumsq = rowSums_; eq.rowSumsqSlots = rowSumsCur_; eq.sumsqRowStride = rowsPadMax_; eq.rowInvC = 1.0f / (float)C; eq.rowEps = eps;
-      addConvOp(cq, eq, "norm+qkv");
-    }
-    else {
-      addOp("rmsnorm", 0.0, 2.0 * S * C * es, [=](cudaStream_t st, const Geom& g) {
-        return launchRmsNorm(st, dt, raw, C, gamma, nullptr, eps, 0, mask, normed, C, C, g);
-      });
-      ConvDev cq = makeConv({&qkvW}, normed, C, C);
-      addConvOp(cq, eq, "qkv");
-    }
     const bool attnTc = !forceSimt_ && attentionTcEligible(dt_, dq, dv, X_, Y_, qkvC, 0, qC, qC + kC, oC) &&
                         (b.relBias.empty() || (2 * b.relBiasY - 1) * (2 * b.relBiasX - 1) <= KB_ATTN_TC_REL_MAX);
     float* dCos = nullptr;
@@ -536,13 +538,43 @@ void Engine::emitBlock(const BlockW& b, int C, void* raw, void* act, const BNW* 
     const float2* dRopeY = nullptr;
     int tableHeads = 1;
     if(b.useRope && attnTc) {
-      // the tensor-core attention kernel rotates Q and K itself, in shared memory, from factored tables
+      // rotation from factored tables: in the projection's epilogue where that variant exists, else by the attention
+      // kernel itself, in shared memory
       std::vector<float> tx, ty;
       ropeFactorTables(b, X_, Y_, tx, ty, tableHeads);
       dRopeX = reinterpret_cast<const float2*>(uploadF32(tx));
       dRopeY = reinterpret_cast<const float2*>(uploadF32(ty));
     }
-    else if(b.useRope) {
+    static const bool ropeFuseOff = getenv("KB_NO_ROPE_FUSE") != nullptr && atoi(getenv("KB_NO_ROPE_FUSE")) != 0;
+    bool ropeInProjection = false;
+    ConvW qkvW = matmulsAsConv({&b.q, &b.k, &b.v});
+    Epilogue eq;
+    eq.outRaw = qkv; eq.rawStride = qkvC; eq.rawC0 = 0; eq.rawC1 = qkvC;
+    auto ropeEpilogue = [&](const ConvDev& cq) {
+      if(!dRopeX || ropeFuseOff || !cq.tc || (dq % 2) != 0 || !convTcRopeEligible(dt_, C, qkvC, qC + kC)) return;
+      eq.act = KB_ACT_ROPE_QK;
+      eq.ropeFreq = uploadF32(ropeChannelFreqs(b));
+      eq.ropeC1 = qC + kC;
+      ropeInProjection = true;
+    };
+    if(rowSumsCur_ >= 0 && convTcRowNormEligible(dt_, C, qkvC)) {
+      // the norm is folded into the projection: it reads the stream itself and scales its rows
+      foldGain(qkvW, b.preLN.weight);
+      ConvDev cq = makeConv({&qkvW}, raw, C, C);
+      eq.rowSumsq = rowSums_; eq.rowSumsqSlots = rowSumsCur_; eq.sumsqRowStride = rowsPadMax_; eq.rowInvC = 1.0f / (float)C; eq.rowEps = eps;
+      ropeEpilogue(cq);
+      addConvOp(cq, eq, ropeInProjection ? "norm+qkv+rope" : "norm+qkv");
+    }
+    else {
+      addOp("rmsnorm", 0.0, 2.0 * S * C * es, [=](cudaStream_t st, const Geom& g) {
+        return launchRmsNorm(st, dt, raw, C, gamma, nullptr, eps, 0, mask, normed, C, C, g);
+      });
+      ConvDev cq = makeConv({&qkvW}, normed, C, C);
+      ropeEpilogue(cq);
+      addConvOp(cq, eq, ropeInProjection ? "qkv+rope" : "qkv");
+    }
+    if(ropeInProjection) { dRopeX = nullptr; dRopeY = nullptr; }
+    else if(b.useRope && !attnTc) {
       std::vector<float> cosT, sinT;
       ropeTables(b, X_, Y_, cosT, sinT, tableHeads);
       dCos = uploadF32(cosT);
@@ -567,7 +599,7 @@ void Engine::emitBlock(const BlockW& b, int C, void* raw, void* act, const BNW* 
       if(!ap) throw std::runtime_error("failed to create the tensor-core attention plan (TMA descriptor encoding)");
       attnPlans_.push_back(ap);
       int* status = statusWord_;
-      addOp(b.useRope ? "attention tcgen05 +rope" : "attention tcgen05", 2.0 * S * S * (dq + dv) * H, S * (qkvC + oC) * es, [=](cudaStream_t st, const Geom& g) {
+      addOp(dRopeX ? "attention tcgen05 +rope" : "attention tcgen05", 2.0 * S * S * (dq + dv) * H, S * (qkvC + oC) * es, [=](cudaStream_t st, const Geom& g) {
         return launchAttentionTc(st, ap, 0, qC, qC + kC, H, Hkv, mask, attn, oC, g, status, dRopeX, dRopeY, tableHeads, relBiasDev, relY, relX);
       });
     }
@@ -1097,6 +1129,7 @@ void Engine::planTileDeps() {
     const Epilogue& e = cur.ep;
     if(e.biasNC || e.rowSumsq || e.sumsqOut || prev.ep.sumsqOut || prev.ep.rowSumsq) continue;
     if(e.act == KB_ACT_SWIGLU_PAIRS || prev.ep.act == KB_ACT_SWIGLU_PAIRS) continue;  // no such kernel variant
+    if(e.act == KB_ACT_ROPE_QK || prev.ep.act == KB_ACT_ROPE_QK) continue;
     if(e.residual) {
       const int r = allocationOf(e.residual);
       if(r < 0 || r == allocationOf(prev.ep.outRaw) || r == allocationOf(prev.ep.outAct)) continue;

@@ -47,6 +47,11 @@ inline Geom makeGeom(int X, int Y, int n) {
 // halves it writes h = silu(up) * gate (eigenbackend.cpp:1660-1672), 16 values per 32 accumulator columns, to outAct
 // ([rows][actStride], channel (c - actC0) / 2).  scale/bias/mask are not used.
 constexpr int KB_ACT_SWIGLU_PAIRS = 100;
+// Epilogue::act value used only by the tensor-core convolution for the merged Q|K|V projection of an attention block:
+// the rotary embedding (eigenbackend.cpp:1415-1451) is applied to the query and key heads while the accumulators are
+// still fp32 registers, so the attention kernel finds Q and K rotated and rounded once.  There is no activated output;
+// outRaw receives the rotated values.  See ropeFreq / ropeC1 of Epilogue.
+constexpr int KB_ACT_ROPE_QK = 101;
 
 struct Epilogue {
   const float* biasNC = nullptr;
@@ -73,6 +78,13 @@ struct Epilogue {
   int rowSumsqSlots = 0;
   int sumsqRowStride = 0;
   float rowInvC = 0.0f, rowEps = 0.0f;
+  // act == KB_ACT_ROPE_QK: output channels [0, ropeC1) are the query and key heads (ropeC1 <= 1024, a multiple of 32).
+  // Channel pair (2i, 2i+1), at board point (x,y), turns by the angle x * ropeFreq[2i] + y * ropeFreq[2i+1]
+  // (desc.cpp:1212-1275: the head's frequencies, expanded per output channel pair by the caller).  Sine and cosine come
+  // from the special-function unit (absolute error about 2e-6 at the largest angles of a 19x19 board with frequencies
+  // up to 1, two orders of magnitude below the rounding of the stored fp16/bf16 value).
+  const float* ropeFreq = nullptr;
+  int ropeC1 = 0;
 };
 
 // --- SIMT kernels (any dtype) ---------------------------------------------------------------------
@@ -163,6 +175,8 @@ bool convTcRowNormEligible(int dt, int inC, int outC);
 int convTcRowSumSlots(int k, int inC, int outC);
 // True if the tensor-core kernel can run the merged up|gate projection (inC -> 2*F, interleaved) with the SwiGLU epilogue.
 bool convTcSwigluEligible(int dt, int inC, int F);
+// the merged Q|K|V projection can apply the rotary embedding in its epilogue (Epilogue::act == KB_ACT_ROPE_QK)
+bool convTcRopeEligible(int dt, int inC, int outC, int ropeC1);
 // in: [rowsPadMax][inStride] activations, w: [kY*kX][outC][inC] in dtype dt (K-major per tap).
 ConvTcPlan* convTcCreate(
   int dt, const void* in, int inStride, int inC, const void* w, int outC, int kY, int kX, int X, int Y, int rowsPadMax);

@@ -31,10 +31,17 @@ enum { AT_ERR_TIMEOUT = 201 };
 
 // Optional timeline instrumentation (build with -DKB_TC_TRACE): thread 0 of CTA 0 records SM cycle counts.
 #ifdef KB_TC_TRACE
-__device__ long long g_atTrace[64];
+__device__ long long g_atTrace[256];
 #define AT_TRACE(slot) do { if(blockIdx.x == 0 && threadIdx.x == 0) g_atTrace[(slot)] = clock64(); } while(0)
+// threads 0, 32 and 160 (warps 0, 1 and 5) of CTA 0, while `cond` holds: 48 slots each from slot 64
+#define AT_TRACE_W(cond, slot) do { if(blockIdx.x == 0 && (cond) && (threadIdx.x == 0 || threadIdx.x == 32 || threadIdx.x == 160)) \
+  g_atTrace[64 + (threadIdx.x == 0 ? 0 : (threadIdx.x == 32 ? 48 : 96)) + (slot)] = clock64(); } while(0)
+// the issuing thread of CTA 0: slots from 208
+#define AT_TRACE_I(cond, slot) do { if(blockIdx.x == 0 && (cond)) g_atTrace[208 + (slot)] = clock64(); } while(0)
 #else
 #define AT_TRACE(slot) do { } while(0)
+#define AT_TRACE_W(cond, slot) do { } while(0)
+#define AT_TRACE_I(cond, slot) do { } while(0)
 #endif
 
 struct AttnTcArgs {
@@ -381,6 +388,408 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_
 }
 
 // ---------------------------------------------------------------------------------------------
+// Pipelined variant, used when Q and K arrive already rotated (the projection's epilogue applied the rotary embedding)
+// or the block has no rotary embedding.  Same arithmetic as attentionTcKernel, instruction for instruction, so the two
+// produce identical bits; what differs is who does what when:
+//   * persistent CTAs: the (board, head, query tile) units are split into equal contiguous ranges, one per CTA, so all
+//     SMs finish together; K and V of a (board, kv head) stay in shared memory while consecutive units use them, and
+//     the next unit's Q (and K) are fetched as soon as the MMAs that read the buffers have completed;
+//   * a ninth warp issues every TMA load and every MMA (its warpgroup hands most of its registers to the softmax
+//     warpgroups, whose two passes want more than an even split of the register file gives them); the eight softmax warps never issue one and never meet it at a
+//     CTA-wide barrier (they synchronise among themselves on named barrier 1 and with the issuer through mbarriers);
+//   * O has two TMEM buffers, so a unit's output is read out of TMEM one unit later, after the second softmax pass of
+//     the next unit, while the tensor core computes the S = Q K^T after that; O = P V of unit i runs behind S of unit
+//     i+1, under unit i+1's softmax passes, and releases P to the second pass chunk by chunk (64 keys at a time).
+// Order on the tensor core: S(0), S(1), PV(0), S(2), PV(1), ...  S(i+1) is issued when every softmax warp has left the
+// second pass of unit i (S consumed, P complete).  Per unit a softmax warp: wait S | pass 1 (maximum) | pass 2 (exp,
+// P, sum) | signal | row sums | read out O of the unit before.
+constexpr int AP_THREADS = 384;  // two warpgroups of softmax warps and the issuer's warpgroup (one of its warps works)
+enum {
+  AP_K_FULL = 0, AP_V_FULL, AP_Q_FULL, AP_S_FULL, AP_SM_DONE, AP_O_FULL, AP_O_FREE = AP_O_FULL + 2,
+  AP_P_FREE = AP_O_FREE + 2,                // one per 64-key chunk of P: O = P V of the unit before has read it
+  AP_NUM_BARS = AP_P_FREE + AT_SK / 64
+};
+
+__device__ __forceinline__ void softmaxWarpsSync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+template <typename T, bool BIAS>
+__global__ void __launch_bounds__(AP_THREADS, 1) attentionPipeKernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcArgs a) {
+  extern __shared__ uint8_t smemRaw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;                         // 16 KiB
+  uint8_t* sK = sQ + AT_TILE_BYTES;           // 3 x 16 KiB (128 keys each)
+  uint8_t* sV = sK + 3 * AT_TILE_BYTES;       // 3 x 16 KiB
+  uint8_t* sP = sV + 3 * AT_TILE_BYTES;       // 6 x 16 KiB (64 keys each), K-major operand layout
+  float* sKb = reinterpret_cast<float*>(sP + 6 * AT_TILE_BYTES);  // [AT_SK] additive key bias: 0 on the board, -1e30 elsewhere
+  float* sMax = sKb + AT_SK;                                      // [2][128] partial row maxima
+  float* sSum = sMax + 256;                                       // [2][128] partial row sums
+  float* sRel = sSum + 256;                                       // [AT_REL_MAX] (BIAS) this head's bias table times log2(e)
+  int* sKeyOff = reinterpret_cast<int*>(sRel + (BIAS ? AT_REL_MAX : 0));  // [AT_SK] (BIAS) offset of every key row into it
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sKeyOff + (BIAS ? AT_SK : 0));
+  uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + AP_NUM_BARS);
+  volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  AT_TRACE(0);
+  if(tid == 0) {
+    for(int i = 0; i < AP_NUM_BARS; i++) mbarInit(smemU32(&bars[i]), (i == AP_SM_DONE || (i >= AP_O_FREE && i < AP_P_FREE)) ? 8 : 1);
+    *abortFlag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if(warp == 0) { tmemAlloc(smemU32(tmemSlot), 512); tmemRelinquish(); }
+  if(BIAS) {
+    const int W = 2 * a.relX - 1;
+    for(int j = tid; j < AT_SK; j += AP_THREADS) {
+      const int ky = j / a.g.RW, kx = j - ky * a.g.RW;
+      sKeyOff[j] = (ky < a.g.Y && kx < a.g.X) ? ky * W + kx : 0;  // keys off the board: any valid entry, their key bias is -1e30
+    }
+  }
+  tcFenceBefore();
+  __syncthreads();
+  tcFenceAfter();
+  const uint32_t tmemBase = *tmemSlot;
+  const uint32_t tmemS = tmemBase, tmemO = tmemBase + AT_SK;  // O buffer b at tmemO + 64 b
+
+  // this CTA's units: unit u = (item, query tile), item = (board, head)
+  const int numQTiles = (a.keysValid + 127) / 128;
+  const int units = a.g.n * a.heads * numQTiles;
+  const int u0 = (int)((long long)blockIdx.x * units / gridDim.x), u1 = (int)((long long)(blockIdx.x + 1) * units / gridDim.x);
+  const int headsPerKv = a.heads / a.kvHeads;
+  auto giveUp = [&]() { if(!*abortFlag) { *abortFlag = 1; atomicCAS(a.status, 0, AT_ERR_TIMEOUT); } };
+
+  if(warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
+    if(warp == 8 && lane == 0 && u1 > u0) {
+      // ---------------- issuer: every TMA load and every MMA ----------------
+      const uint32_t descHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);  // stride offset | version | SWIZZLE_128B
+      auto descLo = [](uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); };
+      bool ok = true;
+      uint32_t kWaited = 0, vWaited = 0, qWaited = 0;   // completed phases of the K, V and Q barriers this thread has consumed
+      bool kPending = false, vPending = false, qPending = false;
+      int kKey = -1, vKey = -1;            // (board, kv head) whose K / V is in shared memory or on its way
+      auto decode = [&](int u, int& n, int& h, int& qt) {
+        const int item = u / numQTiles;
+        qt = u - item * numQTiles; n = item / a.heads; h = item - n * a.heads;
+      };
+      auto loadK = [&](int n, int kvh) {
+        mbarExpectTx(smemU32(&bars[AP_K_FULL]), 3u * AT_TILE_BYTES);
+        for(int j = 0; j < 3; j++) tmaLoad2d(smemU32(sK + j * AT_TILE_BYTES), &tmQKV, a.kOff + kvh * AT_D, n * a.g.PB + j * 128, smemU32(&bars[AP_K_FULL]));
+        kPending = true; kKey = n * a.kvHeads + kvh;
+      };
+      auto loadV = [&](int n, int kvh) {
+        mbarExpectTx(smemU32(&bars[AP_V_FULL]), 3u * AT_TILE_BYTES);
+        for(int j = 0; j < 3; j++) tmaLoad2d(smemU32(sV + j * AT_TILE_BYTES), &tmQKV, a.vOff + kvh * AT_D, n * a.g.PB + j * 128, smemU32(&bars[AP_V_FULL]));
+        vPending = true; vKey = n * a.kvHeads + kvh;
+      };
+      auto loadQ = [&](int n, int h, int qt) {
+        mbarExpectTx(smemU32(&bars[AP_Q_FULL]), (uint32_t)AT_TILE_BYTES);
+        tmaLoad2d(smemU32(sQ), &tmQKV, a.qOff + h * AT_D, n * a.g.PB + qt * 128, smemU32(&bars[AP_Q_FULL]));
+        qPending = true;
+      };
+      // O = P V of the unit with local index j (every softmax warp has left its second pass)
+      auto issuePV = [&](int j) {
+        const int b = j & 1;
+        if(ok && vPending) {
+          if(mbarWait(smemU32(&bars[AP_V_FULL]), vWaited & 1u, abortFlag)) { vWaited++; vPending = false; }
+          else ok = false;
+        }
+        // the softmax warps have read this O buffer's previous contents (unit j-2) out of TMEM
+        ok = ok && mbarWait(smemU32(&bars[AP_O_FREE + b]), (((uint32_t)j >> 1) & 1u) ^ 1u, abortFlag);
+        if(!ok) return;
+        tcFenceAfter();
+        uint32_t acc = 0;
+        for(int kc = 0; kc < AT_SK / 64; kc++) {
+          const uint32_t pLo = descLo(smemU32(sP + (size_t)kc * AT_TILE_BYTES));   // 64 keys of P: one swizzle atom per row
+          const uint32_t vLo = descLo(smemU32(sV) + (uint32_t)(kc * 64) * 128u);  // the same 64 key rows of V
+#pragma unroll
+          for(int k = 0; k < 4; k++) {
+            // 16 keys further: 32 bytes along K inside P's atom, 16 rows (2048 bytes) down in V
+            ummaLoHi(tmemO + (uint32_t)(b * AT_D), pLo + 2 * k, vLo + (uint32_t)k * 128u, descHi, a.idescO, acc);
+            acc = 1;
+          }
+          ummaCommit(smemU32(&bars[AP_P_FREE + kc]));  // this chunk of P may be overwritten by the next unit's second pass
+        }
+        ummaCommit(smemU32(&bars[AP_O_FULL + b]));
+      };
+      {
+        int n, h, qt;
+        decode(u0, n, h, qt);
+        loadK(n, h / headsPerKv);
+        loadQ(n, h, qt);
+        loadV(n, h / headsPerKv);
+      }
+      for(int u = u0; u < u1; u++) {
+        const int i = u - u0;
+        int n, h, qt;
+        decode(u, n, h, qt);
+        const int key = n * a.kvHeads + h / headsPerKv;
+        // operands of S(i)
+        if(ok && mbarWait(smemU32(&bars[AP_Q_FULL]), qWaited & 1u, abortFlag)) { qWaited++; qPending = false; }
+        else ok = false;
+        if(ok && kPending) {
+          if(mbarWait(smemU32(&bars[AP_K_FULL]), kWaited & 1u, abortFlag)) { kWaited++; kPending = false; }
+          else ok = false;
+        }
+        // S of the unit before has been consumed and its P is complete
+        if(i > 0) ok = ok && mbarWait(smemU32(&bars[AP_SM_DONE]), (uint32_t)(i - 1) & 1u, abortFlag);
+        AT_TRACE_I(i < 6, i * 8 + 0);
+        if(ok) {
+          tcFenceAfter();
+          const uint32_t qLo = descLo(smemU32(sQ));
+          for(int j = 0; j < 3; j++) {
+            const uint32_t kLo = descLo(smemU32(sK + j * AT_TILE_BYTES));
+#pragma unroll
+            for(int k = 0; k < AT_D / 16; k++) ummaLoHi(tmemS + (uint32_t)(j * 128), qLo + 2 * k, kLo + 2 * k, descHi, a.idescS, k > 0 ? 1u : 0u);
+          }
+          ummaCommit(smemU32(&bars[AP_S_FULL]));
+        }
+        AT_TRACE_I(i < 6, i * 8 + 1);
+        if(i > 0) issuePV(i - 1);
+        AT_TRACE_I(i < 6, i * 8 + 2);
+        // S(i) has completed: the Q buffer (and K, if the next unit belongs to another board or kv head) is free
+        ok = ok && mbarWait(smemU32(&bars[AP_S_FULL]), (uint32_t)i & 1u, abortFlag);
+        AT_TRACE_I(i < 6, i * 8 + 3);
+        if(ok && u + 1 < u1) {
+          int n2, h2, qt2;
+          decode(u + 1, n2, h2, qt2);
+          loadQ(n2, h2, qt2);
+          if(n2 * a.kvHeads + h2 / headsPerKv != kKey) loadK(n2, h2 / headsPerKv);
+        }
+        // V of this unit's (board, kv head), once O = P V of the unit before has read the old one
+        if(ok && vKey != key) {
+          if(i > 0) ok = ok && mbarWait(smemU32(&bars[AP_O_FULL + ((i - 1) & 1)]), (((uint32_t)(i - 1)) >> 1) & 1u, abortFlag);
+          if(ok) loadV(n, h / headsPerKv);
+        }
+        if(!ok) break;
+      }
+      if(ok) {
+        const int last = u1 - 1 - u0;
+        ok = mbarWait(smemU32(&bars[AP_SM_DONE]), (uint32_t)last & 1u, abortFlag);
+        if(ok) issuePV(last);
+      }
+      if(!ok) {
+        giveUp();
+        // loads that were requested and never consumed: give them (bounded) time to land before the CTA exits; these
+        // waits must not return early because the CTA has given up, so they watch a flag that stays 0
+        volatile int keepWaiting = 0;
+        if(qPending) mbarWait(smemU32(&bars[AP_Q_FULL]), qWaited & 1u, &keepWaiting, 1000000ull);
+        if(kPending) mbarWait(smemU32(&bars[AP_K_FULL]), kWaited & 1u, &keepWaiting, 1000000ull);
+        if(vPending) mbarWait(smemU32(&bars[AP_V_FULL]), vWaited & 1u, &keepWaiting, 1000000ull);
+      }
+    }
+  }
+  else {
+    // ---------------- softmax warps: two per TMEM lane quarter, each over half of the keys ----------------
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    const int quarter = warp & 3;        // TMEM lane quarter this warp may read
+    const int half = warp >> 2;          // which half of the keys (softmax) / of the output columns this warp handles
+    const int row = quarter * 32 + lane; // query row inside the tile
+    constexpr int NCH = AT_SK / 2 / 32;
+    const int cBegin = half * (AT_SK / 2);
+    const uint32_t tS = tmemS + ((uint32_t)(quarter * 32) << 16) + (uint32_t)cBegin;
+    const float4* kb4 = reinterpret_cast<const float4*>(sKb + cBegin);
+    const int4* ko4 = reinterpret_cast<const int4*>(sKeyOff + half * (AT_SK / 2));
+    const float2 scale2 = make_float2(a.scaleLog2e, a.scaleLog2e);
+    int curBoard = -1, curHead = -1;
+    float invPrev = 0.0f;       // 1 / row sum of the unit whose O is still in TMEM
+    T* outWarpPrev = nullptr;   // that unit: where row 0, column 0 of this warp's 32 rows x 32 output columns goes
+    int rowsValidPrev = 0;      // that unit: how many of this warp's 32 rows lie inside the board's block of rows
+    // Reads the O buffer of the unit with local index j out of TMEM and writes the normalised values.  A thread holds
+    // its row's 32 values as four 16-byte pieces; groups of four lanes transpose them (piece c of the group's four rows
+    // ends up in lane c), so that a store instruction covers eight whole 64-byte row segments instead of 32 scattered
+    // 16-byte pieces.
+    auto writeOut = [&](int j) {
+      const int b = j & 1;
+      AT_TRACE_W(j == 2, 12);
+      bool ok = !*abortFlag && mbarWait(smemU32(&bars[AP_O_FULL + b]), ((uint32_t)j >> 1) & 1u, abortFlag);
+      if(!ok) giveUp();
+      AT_TRACE_W(j == 2, 13);
+      if(ok) {
+        tcFenceAfter();
+        uint32_t r[32];
+        tmemLd32(tmemO + (uint32_t)(b * AT_D) + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 32), r);
+        tmemLdWait();
+        AT_TRACE_W(j == 2, 14);
+        const float inv = invPrev;
+        uint4 v[4];
+#pragma unroll
+        for(int jj = 0; jj < 4; jj++) {
+          v[jj].x = AtPack<T>::pack(__uint_as_float(r[8 * jj]) * inv, __uint_as_float(r[8 * jj + 1]) * inv);
+          v[jj].y = AtPack<T>::pack(__uint_as_float(r[8 * jj + 2]) * inv, __uint_as_float(r[8 * jj + 3]) * inv);
+          v[jj].z = AtPack<T>::pack(__uint_as_float(r[8 * jj + 4]) * inv, __uint_as_float(r[8 * jj + 5]) * inv);
+          v[jj].w = AtPack<T>::pack(__uint_as_float(r[8 * jj + 6]) * inv, __uint_as_float(r[8 * jj + 7]) * inv);
+        }
+        auto xchg = [&](uint4& keepLo, uint4& keepHi, int bit) {
+          // lanes with the bit clear keep keepLo and trade keepHi for the partner's keepLo; the others the reverse
+          const bool hi = (lane & bit) != 0;
+          uint4 send = hi ? keepLo : keepHi, got;
+          got.x = __shfl_xor_sync(0xffffffffu, send.x, bit); got.y = __shfl_xor_sync(0xffffffffu, send.y, bit);
+          got.z = __shfl_xor_sync(0xffffffffu, send.z, bit); got.w = __shfl_xor_sync(0xffffffffu, send.w, bit);
+          if(hi) keepLo = got; else keepHi = got;
+        };
+        xchg(v[0], v[1], 1); xchg(v[2], v[3], 1);
+        xchg(v[0], v[2], 2); xchg(v[1], v[3], 2);
+        // now v[k] = piece (lane & 3) of the row of lane (lane & ~3) + k
+        AT_TRACE_W(j == 2, 15);
+        const int r0 = lane & ~3, c = lane & 3;
+#pragma unroll
+        for(int k = 0; k < 4; k++)
+          if(r0 + k < rowsValidPrev) *reinterpret_cast<uint4*>(outWarpPrev + (size_t)(r0 + k) * a.outStride + c * 8) = v[k];
+        AT_TRACE_W(j == 2, 16);
+      }
+      tcFenceBefore();
+      __syncwarp();
+      if(lane == 0) mbarArrive(smemU32(&bars[AP_O_FREE + b]));
+      AT_TRACE_W(j == 2, 17);
+    };
+    for(int u = u0; u < u1; u++) {
+      const int i = u - u0;
+      const int item = u / numQTiles, qt = u - item * numQTiles, n = item / a.heads, h = item - n * a.heads;
+      const int boardRow = n * a.g.PB, q0 = qt * 128;
+      // per-board key mask and per-head bias table; every softmax warp has left the previous unit's second pass (the
+      // row-sum exchange lies in between)
+      const bool newBoard = n != curBoard, newHead = BIAS && h != curHead;
+      if(newBoard) {
+        for(int j = tid; j < AT_SK; j += 256) sKb[j] = (j < a.keysValid && a.mask[boardRow + j] != 0.0f) ? 0.0f : -1e30f;
+        curBoard = n;
+      }
+      if(newHead) {
+        const int relN = (2 * a.relY - 1) * (2 * a.relX - 1);
+        for(int j = tid; j < relN; j += 256) sRel[j] = a.relBias[(size_t)h * relN + j] * 1.4426950408889634f;
+        curHead = h;
+      }
+      if(newBoard || newHead) softmaxWarpsSync();
+      const float qMask = (q0 + row < a.keysValid) ? a.mask[boardRow + q0 + row] : 0.0f;
+      // this query's origin in the bias table (queries that are not board points produce zeros anyway and skip the bias)
+      const float* qRel = nullptr;
+      if(BIAS) {
+        const int qr = q0 + row, qy = qr / a.g.RW, qx = qr - qy * a.g.RW;
+        if(qy < a.g.Y && qx < a.g.X) qRel = sRel + (a.relY - 1 - qy) * (2 * a.relX - 1) + (a.relX - 1 - qx);
+      }
+      if(i < 7) AT_TRACE(1 + i * 8);
+      bool ok = mbarWait(smemU32(&bars[AP_S_FULL]), (uint32_t)i & 1u, abortFlag);
+      if(!ok) giveUp();
+      if(i < 7) AT_TRACE(2 + i * 8);
+      AT_TRACE_W(i == 3, 0);
+      // Scores leave TMEM in chunks of 32 keys; the load of the next chunk is in flight while this one is processed.
+      // Keys off the board carry a bias of -1e30, so they lose every maximum and their exponential is 0.
+      float mx = -1e30f;
+      if(ok) {
+        tcFenceAfter();
+        uint32_t r[2][32];
+        float m4[4] = {-1e30f, -1e30f, -1e30f, -1e30f};
+        tmemLd32(tS, r[0]);
+        tmemLdWaitFor(r[0]);
+#pragma unroll
+        for(int ii = 0; ii < NCH; ii++) {
+          if(ii + 1 < NCH) tmemLd32(tS + (uint32_t)((ii + 1) * 32), r[(ii + 1) & 1]);
+#pragma unroll
+          for(int j = 0; j < 8; j++) {
+            // everything in the base-2 exponent domain: t = score * scale * log2(e) + key bias (+ relative bias * log2(e))
+            float4 b = kb4[ii * 8 + j];
+            if(BIAS && qRel) {
+              const int4 ko = ko4[ii * 8 + j];
+              b.x += qRel[ko.x]; b.y += qRel[ko.y]; b.z += qRel[ko.z]; b.w += qRel[ko.w];
+            }
+            // packed fp32 (two IEEE fused multiply-adds per instruction: the same bits as the scalar form)
+            const float2 t01 = __ffma2_rn(make_float2(__uint_as_float(r[ii & 1][4 * j]), __uint_as_float(r[ii & 1][4 * j + 1])), scale2, make_float2(b.x, b.y));
+            const float2 t23 = __ffma2_rn(make_float2(__uint_as_float(r[ii & 1][4 * j + 2]), __uint_as_float(r[ii & 1][4 * j + 3])), scale2, make_float2(b.z, b.w));
+            m4[0] = fmaxf(m4[0], t01.x); m4[1] = fmaxf(m4[1], t01.y);
+            m4[2] = fmaxf(m4[2], t23.x); m4[3] = fmaxf(m4[3], t23.y);
+          }
+          if(ii + 1 < NCH) tmemLdWaitFor(r[(ii + 1) & 1]);
+          AT_TRACE_W(i == 3, 20 + ii);
+        }
+        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      }
+      AT_TRACE_W(i == 3, 1);
+      sMax[half * 128 + row] = mx;
+      softmaxWarpsSync();
+      AT_TRACE_W(i == 3, 2);
+      mx = fmaxf(sMax[row], sMax[128 + row]);
+      if(i < 7) AT_TRACE(3 + i * 8);
+      if(i < 7) AT_TRACE(4 + i * 8);
+      AT_TRACE_W(i == 3, 3);
+      float sum = 0.0f;
+      bool pOk = true;
+      if(ok && !*abortFlag) {
+        const int sw = row & 7;
+        const float2 negMx2 = make_float2(-mx, -mx);  // the maximum is already in the exponent domain
+        uint32_t r[2][32];
+        float2 s2[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};  // four running sums, as in the scalar form
+        tmemLd32(tS, r[0]);
+        tmemLdWaitFor(r[0]);
+#pragma unroll
+        for(int ii = 0; ii < NCH; ii++) {
+          if(ii + 1 < NCH) tmemLd32(tS + (uint32_t)((ii + 1) * 32), r[(ii + 1) & 1]);
+          const int c = cBegin + ii * 32;
+          // O = P V of the unit before runs behind this unit's S = Q K^T and may still be reading P: a 64-key chunk is
+          // written once the MMAs that read it have completed
+          // (the MMAs read the chunks in order, so a chunk's barrier also covers the chunks before it: the warps of
+          // the first half of the keys wait once, for their last chunk, which is free long before they start; those
+          // of the second half wait for their first chunk and then for their last)
+          if(i > 0 && (ii == 0 || (half == 1 && ii == 2)))
+            pOk = mbarWait(smemU32(&bars[AP_P_FREE + (half == 0 ? 2 : (ii == 0 ? 3 : 5))]), (uint32_t)(i - 1) & 1u, abortFlag) && pOk;
+          // P chunk of 64 keys = one 128-byte swizzled row per query; this 32-key group is its half (c/32)&1
+          uint8_t* pRow = sP + (size_t)(c / 64) * AT_TILE_BYTES + row * 128;
+          const int halfSel = (c / 32) & 1;
+#pragma unroll
+          for(int jj = 0; jj < 4; jj++) {
+            float p[8];
+#pragma unroll
+            for(int k = 0; k < 2; k++) {
+              float4 b = kb4[ii * 8 + 2 * jj + k];
+              if(BIAS && qRel) {
+                const int4 ko = ko4[ii * 8 + 2 * jj + k];
+                b.x += qRel[ko.x]; b.y += qRel[ko.y]; b.z += qRel[ko.z]; b.w += qRel[ko.w];
+              }
+              const float2 t01 = __ffma2_rn(make_float2(__uint_as_float(r[ii & 1][8 * jj + 4 * k]), __uint_as_float(r[ii & 1][8 * jj + 4 * k + 1])), scale2,
+                                            __fadd2_rn(make_float2(b.x, b.y), negMx2));
+              const float2 t23 = __ffma2_rn(make_float2(__uint_as_float(r[ii & 1][8 * jj + 4 * k + 2]), __uint_as_float(r[ii & 1][8 * jj + 4 * k + 3])), scale2,
+                                            __fadd2_rn(make_float2(b.z, b.w), negMx2));
+              p[4 * k] = ex2Approx(t01.x); p[4 * k + 1] = ex2Approx(t01.y);
+              p[4 * k + 2] = ex2Approx(t23.x); p[4 * k + 3] = ex2Approx(t23.y);
+              s2[0] = __fadd2_rn(s2[0], make_float2(p[4 * k], p[4 * k + 1]));
+              s2[1] = __fadd2_rn(s2[1], make_float2(p[4 * k + 2], p[4 * k + 3]));
+            }
+            uint4 o;
+            o.x = AtPack<T>::pack(p[0], p[1]); o.y = AtPack<T>::pack(p[2], p[3]);
+            o.z = AtPack<T>::pack(p[4], p[5]); o.w = AtPack<T>::pack(p[6], p[7]);
+            *reinterpret_cast<uint4*>(pRow + (((halfSel * 4 + jj) ^ sw) << 4)) = o;
+          }
+          if(ii + 1 < NCH) tmemLdWaitFor(r[(ii + 1) & 1]);
+          AT_TRACE_W(i == 3, 4 + ii);
+        }
+        sum = (s2[0].x + s2[0].y) + (s2[1].x + s2[1].y);
+      }
+      if(!pOk) giveUp();
+      // this warp has consumed its part of S and written its part of P
+      fenceProxyAsync();
+      tcFenceBefore();
+      __syncwarp();
+      if(lane == 0) mbarArrive(smemU32(&bars[AP_SM_DONE]));
+      if(i < 7) AT_TRACE(5 + i * 8);
+      AT_TRACE_W(i == 3, 10);
+      sSum[half * 128 + row] = sum;
+      softmaxWarpsSync();
+      AT_TRACE_W(i == 3, 11);
+      const float rowSum = sSum[row] + sSum[128 + row];
+      // the unit before: its O = P V has long completed; reading it out now overlaps the next unit's S = Q K^T
+      if(i > 0) writeOut(i - 1);
+      invPrev = (qMask != 0.0f && rowSum > 0.0f) ? 1.0f / rowSum : 0.0f;
+      outWarpPrev = reinterpret_cast<T*>(a.out) + (size_t)(boardRow + q0 + quarter * 32) * a.outStride + h * AT_D + half * 32;
+      rowsValidPrev = a.g.PB - (q0 + quarter * 32);
+    }
+    if(u1 > u0) writeOut(u1 - 1 - u0);
+    AT_TRACE(60);
+  }
+  tcFenceBefore();
+  __syncthreads();
+  if(warp == 0) { tcFenceAfter(); tmemDealloc(tmemBase, 512); }
+}
+
+// ---------------------------------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFnA)(
   CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -389,7 +798,9 @@ typedef CUresult (*EncodeTiledFnA)(
 struct AttnTcPlan {
   CUtensorMap tmQKV;
   int dt;
-  size_t smemBytes;
+  size_t smemBytes;      // attentionTcKernel
+  size_t smemBytesPipe;  // attentionPipeKernel
+  int numSMs;
 };
 
 bool attentionTcEligible(int dt, int dq, int dv, int X, int Y, int stride, int qOff, int kOff, int vOff, int outStride) {
@@ -426,6 +837,16 @@ AttnTcPlan* attentionTcCreate(int dt, const void* qkv, int stride, int totalCols
   if(e1 == cudaSuccess) e1 = cudaFuncSetAttribute(attentionTcKernel<__half, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p->smemBytes);
   if(e2 == cudaSuccess) e2 = cudaFuncSetAttribute(attentionTcKernel<__nv_bfloat16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p->smemBytes);
   if(e1 != cudaSuccess || e2 != cudaSuccess) { delete p; return nullptr; }
+  p->smemBytesPipe = 13 * (size_t)AT_TILE_BYTES + (AT_SK + 512 + AT_REL_MAX + AT_SK) * sizeof(float) + AP_NUM_BARS * 8 + 16 + 1024;
+  const int pipeBytes = (int)p->smemBytesPipe;
+  e1 = cudaFuncSetAttribute(attentionPipeKernel<__half, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, pipeBytes);
+  e2 = cudaFuncSetAttribute(attentionPipeKernel<__nv_bfloat16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, pipeBytes);
+  if(e1 == cudaSuccess) e1 = cudaFuncSetAttribute(attentionPipeKernel<__half, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, pipeBytes);
+  if(e2 == cudaSuccess) e2 = cudaFuncSetAttribute(attentionPipeKernel<__nv_bfloat16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, pipeBytes);
+  if(e1 != cudaSuccess || e2 != cudaSuccess) { delete p; return nullptr; }
+  int dev = 0;
+  p->numSMs = 148;
+  if(cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&p->numSMs, cudaDevAttrMultiProcessorCount, dev);
   return p;
 }
 
@@ -433,7 +854,8 @@ void attentionTcDestroy(AttnTcPlan* p) { delete p; }
 
 cudaError_t launchAttentionTc(
   cudaStream_t st, const AttnTcPlan* p, int qOff, int kOff, int vOff, int heads, int kvHeads, const float* mask, void* out,
-  int outStride, Geom g, int* statusWord, const float2* ropeX, const float2* ropeY, int tableHeads, const float* relBias, int relY, int relX) {
+  int outStride, Geom g, int* statusWord, const float2* ropeX, const float2* ropeY, int tableHeads, const float* relBias, int relY, int relX,
+  int pipelined) {
   AttnTcArgs a;
   a.g = g; a.heads = heads; a.kvHeads = kvHeads; a.qOff = qOff; a.kOff = kOff; a.vOff = vOff;
   a.keysValid = g.Y * g.RW;
@@ -446,6 +868,22 @@ cudaError_t launchAttentionTc(
   a.ropeX = ropeX; a.ropeY = ropeY; a.tableHeads = tableHeads;
   a.relBias = relBias; a.relY = relY; a.relX = relX;
   if(relBias && ((2 * relY - 1) * (2 * relX - 1) > AT_REL_MAX || g.X > relX || g.Y > relY)) return cudaErrorInvalidValue;
+  // Q and K already rotated (or never rotated): the pipelined kernel, unless the caller asks for the one-CTA-per-
+  // (board, head) kernel; the two produce identical bits.
+  if(!ropeX && pipelined) {
+    const int units = g.n * heads * ((a.keysValid + 127) / 128);
+    if(units <= 0) return cudaSuccess;
+    dim3 pgrid(units < p->numSMs ? units : p->numSMs);
+    if(relBias) {
+      if(p->dt == DT_F16) attentionPipeKernel<__half, true><<<pgrid, AP_THREADS, p->smemBytesPipe, st>>>(p->tmQKV, a);
+      else attentionPipeKernel<__nv_bfloat16, true><<<pgrid, AP_THREADS, p->smemBytesPipe, st>>>(p->tmQKV, a);
+    }
+    else {
+      if(p->dt == DT_F16) attentionPipeKernel<__half, false><<<pgrid, AP_THREADS, p->smemBytesPipe, st>>>(p->tmQKV, a);
+      else attentionPipeKernel<__nv_bfloat16, false><<<pgrid, AP_THREADS, p->smemBytesPipe, st>>>(p->tmQKV, a);
+    }
+    return cudaGetLastError();
+  }
   dim3 grid(g.n * heads);
   if(relBias) {
     if(p->dt == DT_F16) attentionTcKernel<__half, true><<<grid, AT_THREADS, p->smemBytes, st>>>(p->tmQKV, a);
@@ -461,5 +899,5 @@ cudaError_t launchAttentionTc(
 }  // namespace kb
 
 #ifdef KB_TC_TRACE
-extern "C" int kb_debug_attention_trace(long long* out, int n) { return (int)cudaMemcpyFromSymbol(out, kb::g_atTrace, sizeof(long long) * n); }
+extern "C" int kb_debug_attention_trace(long long* out, int n) { return (int)cudaMemcpyFromSymbol(out, kb::g_atTrace, sizeof(long long) * (n > 256 ? 256 : n)); }
 #endif

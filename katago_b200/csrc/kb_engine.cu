@@ -545,7 +545,7 @@ void Engine::emitBlock(const BlockW& b, int C, void* raw, void* act, const BNW* 
       dRopeX = reinterpret_cast<const float2*>(uploadF32(tx));
       dRopeY = reinterpret_cast<const float2*>(uploadF32(ty));
     }
-    static const bool ropeFuseOff = getenv("KB_NO_ROPE_FUSE") != nullptr && atoi(getenv("KB_NO_ROPE_FUSE")) != 0;
+    const bool ropeFuseOff = getenv("KB_NO_ROPE_FUSE") != nullptr && atoi(getenv("KB_NO_ROPE_FUSE")) != 0;  // read per handle
     bool ropeInProjection = false;
     ConvW qkvW = matmulsAsConv({&b.q, &b.k, &b.v});
     Epilogue eq;
@@ -599,8 +599,10 @@ void Engine::emitBlock(const BlockW& b, int C, void* raw, void* act, const BNW* 
       if(!ap) throw std::runtime_error("failed to create the tensor-core attention plan (TMA descriptor encoding)");
       attnPlans_.push_back(ap);
       int* status = statusWord_;
-      addOp(dRopeX ? "attention tcgen05 +rope" : "attention tcgen05", 2.0 * S * S * (dq + dv) * H, S * (qkvC + oC) * es, [=](cudaStream_t st, const Geom& g) {
-        return launchAttentionTc(st, ap, 0, qC, qC + kC, H, Hkv, mask, attn, oC, g, status, dRopeX, dRopeY, tableHeads, relBiasDev, relY, relX);
+      // KB_ATTN_PIPE=0 (read when the handle is created): the one-CTA-per-(board, head) kernel also where the pipelined one applies
+      const int pipelined = (getenv("KB_ATTN_PIPE") != nullptr && atoi(getenv("KB_ATTN_PIPE")) == 0) ? 0 : 1;
+      addOp(dRopeX ? "attention tcgen05 +rope" : (pipelined ? "attention tcgen05 pipelined" : "attention tcgen05"), 2.0 * S * S * (dq + dv) * H, S * (qkvC + oC) * es, [=](cudaStream_t st, const Geom& g) {
+        return launchAttentionTc(st, ap, 0, qC, qC + kC, H, Hkv, mask, attn, oC, g, status, dRopeX, dRopeY, tableHeads, relBiasDev, relY, relX, pipelined);
       });
     }
     else {

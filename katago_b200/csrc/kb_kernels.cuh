@@ -279,7 +279,9 @@ void attentionTcDestroy(AttnTcPlan* p);
 cudaError_t launchAttentionTc(
   cudaStream_t st, const AttnTcPlan* p, int qOff, int kOff, int vOff, int heads, int kvHeads, const float* mask, void* out,
   int outStride, Geom g, int* statusWord, const float2* ropeX, const float2* ropeY, int tableHeads,
-  const float* relBias = nullptr, int relY = 0, int relX = 0);
+  const float* relBias = nullptr, int relY = 0, int relX = 0, int pipelined = 1);
+// pipelined: without in-kernel rotation the work runs on persistent CTAs with a dedicated issuing warp (0: one CTA per
+// (board, head), as with rotation; same bits).
 // relBias (or NULL): learned relative-position bias as for launchAttention; the kernel keeps one head's table in shared
 // memory, which bounds it to KB_ATTN_TC_REL_MAX entries.
 constexpr int KB_ATTN_TC_REL_MAX = 1536;

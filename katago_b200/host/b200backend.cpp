@@ -43,8 +43,10 @@ static void check(int status, const char* what) {
 
 struct LoadedModel {
   ModelDesc modelDesc;
+  kbhost::ModelExt ext;  // records of <model file>.kbext, if there is one (model_ext.h)
   LoadedModel(const string& fileName, const string& expectedSha256) {
     ModelDesc::loadFromFileMaybeGZipped(fileName, modelDesc, expectedSha256);
+    kbhost::loadModelExt(fileName, modelDesc.name, ext);
     // Same fp16 range trick as the reference's CUDA backend (cudabackend.cpp:3079-3082): activations of
     // Mish nets are carried at 1/8 scale, compensated by MISH_SCALE8 and postProcessParams.outputScaleMultiplier.
     // Done here because NNEvaluator copies postProcessParams right after loading (nneval.cpp:142).
@@ -114,7 +116,7 @@ ComputeContext* NeuralNet::createComputeContext(
     else throw StringError("B200 backend: cudaPrecision must be fp16, bf16 or fp32, got " + prec);
   }
   // The device library works on the flattened model; built once per context and shared by all handles.
-  std::vector<uint32_t> blob = kbhost::modelDescToBlob(loadedModel->modelDesc);
+  std::vector<uint32_t> blob = kbhost::modelDescToBlob(loadedModel->modelDesc, loadedModel->ext.empty() ? nullptr : &loadedModel->ext);
   check(kb_model_create(blob.data(), blob.size() * sizeof(uint32_t), &context->model), "kb_model_create");
   return context.release();
 }

@@ -9,8 +9,15 @@
 #include "neuralnet/desc.h"
 #include "core/global.h"
 #include "kb_modelblob.h"
+#include "model_ext.h"
 
 namespace kbhost {
+
+// Extension records (model_ext.h) to attach while flattening, and how many of them found their block.
+struct ExtAttach {
+  const ModelExt* ext = nullptr;
+  int attnBiasUsed = 0;
+};
 
 inline void writeConv(kbblob::Writer& w, const ConvLayerDesc& d) {
   w.record(KB_TAG_CONV, {d.convYSize, d.convXSize, d.inChannels, d.outChannels, d.dilationY, d.dilationX}, d.weights);
@@ -45,7 +52,7 @@ inline void writeTRMSNorm(kbblob::Writer& w, const TransformerRMSNormDesc& d) {
   w.record(KB_TAG_TRMSNORM, {d.numChannels}, f);
 }
 
-inline void writeBlocks(kbblob::Writer& w, const std::vector<std::pair<int, unique_ptr_void>>& blocks);
+inline void writeBlocks(kbblob::Writer& w, const std::vector<std::pair<int, unique_ptr_void>>& blocks, ExtAttach* ea = nullptr);
 
 inline void writeOrdinaryBlock(kbblob::Writer& w, const ResidualBlockDesc& d) {
   w.record(KB_TAG_BLOCK_ORDINARY, {});
@@ -66,16 +73,16 @@ inline void writeGPoolBlock(kbblob::Writer& w, const GlobalPoolingResidualBlockD
   writeConv(w, d.finalConv);
 }
 
-inline void writeNestedBlock(kbblob::Writer& w, const NestedBottleneckResidualBlockDesc& d) {
+inline void writeNestedBlock(kbblob::Writer& w, const NestedBottleneckResidualBlockDesc& d, ExtAttach* ea = nullptr) {
   w.record(KB_TAG_BLOCK_NESTED, {d.numBlocks});
   writeBN(w, d.preBN, d.preActivation.activation);
   writeConv(w, d.preConv);
-  writeBlocks(w, d.blocks);
+  writeBlocks(w, d.blocks, ea);
   writeBN(w, d.postBN, d.postActivation.activation);
   writeConv(w, d.postConv);
 }
 
-inline void writeAttnBlock(kbblob::Writer& w, const TransformerAttentionDesc& d) {
+inline void writeAttnBlock(kbblob::Writer& w, const TransformerAttentionDesc& d, ExtAttach* ea = nullptr) {
   std::vector<float> f;
   if(d.useRope && d.learnableRope) f = d.ropeFreqs;
   else if(d.useRope) f.push_back(d.ropeTheta);
@@ -87,6 +94,16 @@ inline void writeAttnBlock(kbblob::Writer& w, const TransformerAttentionDesc& d)
   writeMatMul(w, d.kProj);
   writeMatMul(w, d.vProj);
   writeMatMul(w, d.outProj);
+  if(ea && ea->ext) {
+    auto it = ea->ext->attnBias.find(d.name);
+    if(it != ea->ext->attnBias.end()) {
+      const AttnBiasExt& b = it->second;
+      if(b.heads != d.numHeads)
+        throw StringError("model extension: attention bias of block '" + d.name + "' has " + Global::intToString(b.heads) + " heads, the block " + Global::intToString(d.numHeads));
+      w.record(KB_TAG_ATTNBIAS, {b.heads, b.Y, b.X}, b.table);
+      ea->attnBiasUsed++;
+    }
+  }
 }
 
 inline void writeFFNBlock(kbblob::Writer& w, const TransformerFFNDesc& d) {
@@ -97,21 +114,24 @@ inline void writeFFNBlock(kbblob::Writer& w, const TransformerFFNDesc& d) {
   writeMatMul(w, d.linear2);
 }
 
-inline void writeBlocks(kbblob::Writer& w, const std::vector<std::pair<int, unique_ptr_void>>& blocks) {
+inline void writeBlocks(kbblob::Writer& w, const std::vector<std::pair<int, unique_ptr_void>>& blocks, ExtAttach* ea) {
   for(const auto& b : blocks) {
     switch(b.first) {
       case ORDINARY_BLOCK_KIND: writeOrdinaryBlock(w, *(const ResidualBlockDesc*)b.second.get()); break;
       case GLOBAL_POOLING_BLOCK_KIND: writeGPoolBlock(w, *(const GlobalPoolingResidualBlockDesc*)b.second.get()); break;
-      case NESTED_BOTTLENECK_BLOCK_KIND: writeNestedBlock(w, *(const NestedBottleneckResidualBlockDesc*)b.second.get()); break;
-      case TRANSFORMER_ATTENTION_BLOCK_KIND: writeAttnBlock(w, *(const TransformerAttentionDesc*)b.second.get()); break;
+      case NESTED_BOTTLENECK_BLOCK_KIND: writeNestedBlock(w, *(const NestedBottleneckResidualBlockDesc*)b.second.get(), ea); break;
+      case TRANSFORMER_ATTENTION_BLOCK_KIND: writeAttnBlock(w, *(const TransformerAttentionDesc*)b.second.get(), ea); break;
       case TRANSFORMER_FFN_BLOCK_KIND: writeFFNBlock(w, *(const TransformerFFNDesc*)b.second.get()); break;
       default: throw StringError("b200 backend: unknown block kind " + Global::intToString(b.first));
     }
   }
 }
 
-inline std::vector<uint32_t> modelDescToBlob(const ModelDesc& m) {
+// ext (or NULL): records of the model's extension file, attached to the blocks they name; every record must find its block.
+inline std::vector<uint32_t> modelDescToBlob(const ModelDesc& m, const ModelExt* ext = nullptr) {
   kbblob::Writer w;
+  ExtAttach ea;
+  ea.ext = ext;
   w.record(
     KB_TAG_MODEL,
     {m.modelVersion, m.numInputChannels, m.numInputGlobalChannels, m.numInputMetaChannels, m.numPolicyChannels,
@@ -130,7 +150,9 @@ inline std::vector<uint32_t> modelDescToBlob(const ModelDesc& m) {
     writeMatMul(w, e.mul2); writeMatBias(w, e.bias2); writeAct(w, e.act2);
     writeMatMul(w, e.mul3);
   }
-  writeBlocks(w, t.blocks);
+  writeBlocks(w, t.blocks, &ea);
+  if(ext && ea.attnBiasUsed != (int)ext->attnBias.size())
+    throw StringError("model extension: " + Global::intToString((int)ext->attnBias.size() - ea.attnBiasUsed) + " attention bias record(s) name a block that model '" + m.name + "' does not have");
   if(t.trunkNormKind == TRUNK_NORM_KIND_STANDARD) {
     writeBN(w, t.trunkTipBN, t.trunkTipActivation.activation);
   }

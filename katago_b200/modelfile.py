@@ -14,6 +14,7 @@ from __future__ import annotations
 
 import gzip
 import io
+import os
 import struct
 from typing import Any, Dict, List
 
@@ -292,14 +293,119 @@ def parse_model_bytes(data: bytes, binary: bool) -> Dict[str, Any]:
 
 
 def load_model_file(path: str) -> Dict[str, Any]:
-    """Reads .bin.gz / .txt.gz / .bin / .txt model files (desc.cpp:2574-2636)."""
+    """Reads .bin.gz / .txt.gz / .bin / .txt model files (desc.cpp:2574-2636), and the extension file next to it
+    (<path>.kbext, see model_ext_bytes) if there is one."""
     lower = path.lower()
     with open(path, "rb") as f:
         raw = f.read()
     if lower.endswith(".gz"):
         raw = gzip.decompress(raw)
     binary = not (lower.endswith(".txt.gz") or lower.endswith(".txt"))
-    return parse_model_bytes(raw, binary)
+    m = parse_model_bytes(raw, binary)
+    if os.path.exists(path + EXT_SUFFIX):
+        with open(path + EXT_SUFFIX, "rb") as f:
+            attach_model_ext(m, f.read())
+    return m
+
+
+# ----------------------------------------------------------------------------------------------
+# Extension file: weights the reference's model file format has no field for (katago_b200/host/model_ext.h gives the
+# encoding and is the reader the backends use).  Today: the learned relative-position attention bias, by block name.
+
+EXT_SUFFIX = ".kbext"
+_EXT_MAGIC = b"KBMDLEXT"
+_EXT_KIND_ATTNBIAS = 1
+
+
+def _attention_blocks(blocks):
+    for b in blocks:
+        if b["kind"] == "transformer_attention_block":
+            yield b
+        elif b["kind"] == "nested_bottleneck_block":
+            yield from _attention_blocks(b["blocks"])
+
+
+def _ext_str(s: str) -> bytes:
+    raw = s.encode("ascii")
+    return struct.pack("<I", len(raw)) + raw + b"\0" * (-len(raw) % 4)
+
+
+def model_ext_bytes(m: Dict[str, Any]):
+    """The extension file's content for a model, or None if the model has nothing that needs one."""
+    recs = []
+    for b in _attention_blocks(m["trunk"]["blocks"]):
+        if b.get("relBias") is None:
+            continue
+        rb = np.ascontiguousarray(b["relBias"], dtype="<f4")
+        if rb.ndim != 3 or rb.shape[0] != b["heads"] or rb.shape[1] % 2 != 1 or rb.shape[2] % 2 != 1:
+            raise ValueError(f"{b['name']}: a relative-position bias is [heads][2Y-1][2X-1]")
+        payload = _ext_str(b["name"]) + struct.pack("<III", rb.shape[0], (rb.shape[1] + 1) // 2, (rb.shape[2] + 1) // 2) + rb.tobytes()
+        recs.append(struct.pack("<II", _EXT_KIND_ATTNBIAS, len(payload)) + payload)
+    if not recs:
+        return None
+    names = [b["name"] for b in _attention_blocks(m["trunk"]["blocks"])]
+    if len(set(names)) != len(names):
+        raise ValueError("attention blocks must have distinct names for the extension file to address them")
+    return _EXT_MAGIC + struct.pack("<I", 1) + _ext_str(m["name"]) + struct.pack("<I", len(recs)) + b"".join(recs)
+
+
+def attach_model_ext(m: Dict[str, Any], data: bytes) -> None:
+    """Attaches the records of an extension file to the model tree; the same checks as the C++ reader."""
+    pos = 0
+
+    def take(n):
+        nonlocal pos
+        if pos + n > len(data):
+            raise ValueError("model extension file is truncated")
+        out = data[pos:pos + n]
+        pos += n
+        return out
+
+    def u32():
+        return struct.unpack("<I", take(4))[0]
+
+    def string():
+        n = u32()
+        if n > 4096:
+            raise ValueError("model extension file holds a malformed name")
+        raw = take((n + 3) // 4 * 4)
+        return raw[:n].decode("ascii")
+
+    if take(8) != _EXT_MAGIC:
+        raise ValueError("not a model extension file")
+    version = u32()
+    if version != 1:
+        raise ValueError(f"model extension format version {version} is not supported (this reader knows 1)")
+    name = string()
+    if name != m["name"]:
+        raise ValueError(f"model extension file written for model '{name}', but the model file holds '{m['name']}'")
+    by_name = {b["name"]: b for b in _attention_blocks(m["trunk"]["blocks"])}
+    seen = set()
+    for _ in range(u32()):
+        kind, nbytes = u32(), u32()
+        end = pos + nbytes
+        if nbytes % 4 or end > len(data):
+            raise ValueError("model extension file: record runs past the end of the file")
+        if kind != _EXT_KIND_ATTNBIAS:
+            raise ValueError(f"model extension file: unknown record kind {kind}")
+        block = string()
+        heads, Y, X = u32(), u32(), u32()
+        if not (1 <= heads <= 1024 and 1 <= Y <= 64 and 1 <= X <= 64):
+            raise ValueError(f"model extension file: attention bias of block '{block}' has an invalid shape")
+        n = heads * (2 * Y - 1) * (2 * X - 1)
+        if pos + 4 * n != end:
+            raise ValueError(f"model extension file: attention bias of block '{block}' does not match its record length")
+        table = np.frombuffer(take(4 * n), dtype="<f4").reshape(heads, 2 * Y - 1, 2 * X - 1).astype(np.float32)
+        if block not in by_name:
+            raise ValueError(f"model extension file names a block the model does not have: '{block}'")
+        if block in seen:
+            raise ValueError(f"model extension file: two attention bias records for block '{block}'")
+        if by_name[block]["heads"] != heads:
+            raise ValueError(f"model extension file: attention bias of block '{block}' has {heads} heads, the block {by_name[block]['heads']}")
+        seen.add(block)
+        by_name[block]["relBias"] = table
+    if pos != len(data):
+        raise ValueError("model extension file: bytes after the last record")
 
 
 # ----------------------------------------------------------------------------------------------
@@ -367,8 +473,7 @@ def _write_blocks(w: _Writer, blocks, v):
             _write_blocks(w, b["blocks"], v)
             _write_bn(w, b["postBN"]); _write_act(w, b["postAct"], v); _write_conv(w, b["postConv"])
         elif k == "transformer_attention_block":
-            if b.get("relBias") is not None:
-                raise ValueError("the reference's model file format has no field for a relative-position attention bias; use to_blob")
+            # a relative-position bias has no field in this format: it travels in the extension file (model_ext_bytes)
             w.ln(b["heads"], b["kvHeads"], b["qDim"], b["vDim"], b["useRope"], b["learnableRope"])
             _write_trmsnorm(w, b["preLN"])
             for key in ("q", "k", "v", "out"):
@@ -443,10 +548,18 @@ def model_file_bytes(m: Dict[str, Any]) -> bytes:
 
 
 def save_model_file(m: Dict[str, Any], path: str) -> None:
+    """Writes the model file and, if the model holds weights the format has no field for (model_ext_bytes), the
+    extension file <path>.kbext next to it; an extension file left over from another model is removed."""
     if not path.endswith(".bin.gz"):
         raise ValueError("model files are written in the .bin.gz flavour")
     with open(path, "wb") as f:
         f.write(gzip.compress(model_file_bytes(m), compresslevel=1, mtime=0))
+    ext = model_ext_bytes(m)
+    if ext is not None:
+        with open(path + EXT_SUFFIX, "wb") as f:
+            f.write(ext)
+    elif os.path.exists(path + EXT_SUFFIX):
+        os.remove(path + EXT_SUFFIX)
 
 
 # ----------------------------------------------------------------------------------------------

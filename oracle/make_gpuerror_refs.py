@@ -40,6 +40,9 @@ CASES = [
     ("b7c96h3tfrs_13", "b7c96h3tfrs-test5-cnorm.bin.gz", "13", "requireMaxBoardSize=False, maxBatchSize=5"),
     ("b4c256h4nbttflrs_rect", "b4c256h4nbttflrs-fson-silu-rsnh.bin.gz", "rectangle", "requireMaxBoardSize=False, maxBatchSize=6"),
     ("b7c96h6kv3_9", "b7c96h6kv3qk32v16tflrs-fson-bnh.bin.gz", "9", "requireMaxBoardSize=True, maxBatchSize=12"),
+    # attention with a learned relative-position bias instead of RoPE: model file + extension file (<model>.kbext,
+    # katago_b200/host/model_ext.h), which both backends pick up when they load the model
+    ("tf2_relbias_random_19", "gen:tf2relbias", "19", "requireMaxBoardSize=False, maxBatchSize=9"),
 ]
 
 
@@ -54,7 +57,8 @@ def main():
     os.makedirs(OUT, exist_ok=True)
     with open(os.path.join(OUT, "gpuerror.cfg"), "w") as f:
         f.write(CFG)
-    gen = {"b6c96": lambda: mf.make_b6c96(), "b18x4": lambda: mf.make_b18c384nbt(num_blocks=4)}
+    gen = {"b6c96": lambda: mf.make_b6c96(), "b18x4": lambda: mf.make_b18c384nbt(num_blocks=4),
+           "tf2relbias": lambda: mf.make_transformer_relbias(layers=2)}
     index = []
     for name, model, size, overrides in CASES:
         if model.startswith("gen:"):

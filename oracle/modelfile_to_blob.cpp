@@ -20,7 +20,9 @@ int main(int argc, char** argv) {
   try {
     ModelDesc desc;
     ModelDesc::loadFromFileMaybeGZipped(argv[1], desc, "");
-    std::vector<uint32_t> blob = kbhost::modelDescToBlob(desc);
+    kbhost::ModelExt ext;  // MODEL_FILE.kbext, if there is one, as the backends attach it
+    kbhost::loadModelExt(argv[1], desc.name, ext);
+    std::vector<uint32_t> blob = kbhost::modelDescToBlob(desc, ext.empty() ? nullptr : &ext);
     FILE* f = std::fopen(argv[2], "wb");
     if(f == NULL) { std::cerr << "cannot open output" << std::endl; return 1; }
     std::fwrite(blob.data(), 4, blob.size(), f);

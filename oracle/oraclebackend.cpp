@@ -20,8 +20,10 @@ using namespace std;
 
 struct LoadedModel {
   ModelDesc modelDesc;
+  kbhost::ModelExt ext;  // records of <model file>.kbext, if there is one (katago_b200/host/model_ext.h)
   LoadedModel(const string& fileName, const string& expectedSha256) {
     ModelDesc::loadFromFileMaybeGZipped(fileName, modelDesc, expectedSha256);
+    kbhost::loadModelExt(fileName, modelDesc.name, ext);
   }
 };
 
@@ -79,7 +81,7 @@ ComputeHandle* NeuralNet::createComputeHandle(
   auto handle = std::make_unique<ComputeHandle>();
   handle->dims = kbhost::makeNetDims(loadedModel->modelDesc, context->nnXLen, context->nnYLen);
   handle->inputsUseNHWC = inputsUseNHWC;
-  std::vector<uint32_t> blob = kbhost::modelDescToBlob(loadedModel->modelDesc);
+  std::vector<uint32_t> blob = kbhost::modelDescToBlob(loadedModel->modelDesc, loadedModel->ext.empty() ? nullptr : &loadedModel->ext);
   check(ko_model_create(blob.data(), blob.size() * 4, context->nnXLen, context->nnYLen, &handle->model), "ko_model_create");
   return handle.release();
 }

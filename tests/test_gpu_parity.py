@@ -337,6 +337,40 @@ def test_fused_and_multi_layer_launches_are_bit_identical_to_single_launches():
                 os.environ[k] = v
 
 
+@pytest.mark.parametrize("variant", ["learnable_rope", "fixed_rope", "rel_bias"])
+def test_attention_kernels_are_bit_identical(variant):
+    """The pipelined attention kernel (persistent CTAs, a dedicated issuing warp, the output of a query tile read out
+    one tile later) and the kernel with one CTA per (board, head) perform the same arithmetic in the same order, so
+    switching between them (KB_ATTN_PIPE=0, read when the handle is created) must not change a bit.  Checked with the
+    rotary embedding applied by the Q|K|V projection and with the relative-position bias (no rotation), at a batch
+    that gives every SM several units, at one with fewer units than SMs, on mixed board sizes, and on repeated runs."""
+    tree = dict(learnable_rope=lambda: mf.make_transformer(layers=2), fixed_rope=lambda: mf.make_transformer(layers=2, rope="fixed"),
+                rel_bias=lambda: mf.make_transformer_relbias(layers=2))[variant]()
+    blob = mf.to_blob(tree)
+    old = os.environ.get("KB_ATTN_PIPE")
+    try:
+        for n in (128, 5):
+            sp, gl = mf.random_positions(n, seed=91, board_sizes=[19, 13, 9, 19, 7] * (n // 5) + [19] * (n % 5))
+            outs = {}
+            for mode in ("1", "0"):
+                os.environ["KB_ATTN_PIPE"] = mode
+                h = capi.Handle(capi.Model(blob), n, precision=capi.PRECISION_FP16)
+                runs = [h.forward(sp, gl) for _ in range(3)]
+                h.close()
+                for r in runs[1:]:
+                    for k in r:
+                        assert np.array_equal(r[k], runs[0][k]), (n, mode, k)
+                outs[mode] = runs[0]
+            for k in outs["1"]:
+                assert np.isfinite(outs["1"][k]).all(), (n, k)
+                assert np.array_equal(outs["1"][k], outs["0"][k]), (n, k)
+    finally:
+        if old is None:
+            os.environ.pop("KB_ATTN_PIPE", None)
+        else:
+            os.environ["KB_ATTN_PIPE"] = old
+
+
 @pytest.mark.parametrize("factory,n", [(mf.make_b18c384nbt, 8), (mf.make_b28c512nbt, 8)], ids=["b18c384nbt", "b28c512nbt"])
 def test_every_block_at_full_depth_with_true_inputs(factory, n, oracle):
     """Every block of the full 18- and 28-block nets on its TRUE input: the oracle's residual stream entering block k

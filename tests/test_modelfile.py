@@ -116,3 +116,74 @@ def test_reference_loader_accepts_generated_meta_encoder_file(oracle, tmp_path):
     for k in oa:
         assert np.abs(oa[k] - ob[k]).max() <= 1e-4 * max(1.0, np.abs(oa[k]).max()), k
 
+
+
+def _relbias_model():
+    return mf.make_transformer(seed=41, layers=2, d=64, heads=2, head_dim=32, ffn=96, rope="none", rel_bias=True)
+
+
+def test_extension_file_roundtrip_and_checks(tmp_path):
+    """A net with a learned relative-position attention bias is stored as an ordinary model file plus the extension
+    file <model file>.kbext: the pair reads back to the same blob; the model file alone is the same net without the
+    bias; a model without such weights writes no extension file (and removes a stale one); malformed or mismatched
+    extension files are rejected."""
+    m = _relbias_model()
+    path = str(tmp_path / "rb.bin.gz")
+    mf.save_model_file(m, path)
+    assert os.path.exists(path + mf.EXT_SUFFIX)
+    assert mf.to_blob(mf.load_model_file(path)) == mf.to_blob(m)
+    bare = mf.parse_model_bytes(mf.model_file_bytes(m), True)
+    assert all(b.get("relBias") is None for b in bare["trunk"]["blocks"])
+    assert mf.to_blob(bare) != mf.to_blob(m)
+    ext = mf.model_ext_bytes(m)
+    # the same checks as the C++ reader (katago_b200/host/model_ext.h)
+    for bad, what in [
+        (ext[:-4], "past the end"), (ext[:10], "truncated"), (ext + b"\0\0\0\0", "after the last record"), (b"KBMDLEXX" + ext[8:], "not a model extension"),
+        (ext[:8] + (2).to_bytes(4, "little") + ext[12:], "version"),
+    ]:
+        with pytest.raises(ValueError, match=what):
+            mf.attach_model_ext(mf.parse_model_bytes(mf.model_file_bytes(m), True), bad)
+    other = mf.parse_model_bytes(mf.model_file_bytes(m), True)
+    other["name"] = "another-net"
+    with pytest.raises(ValueError, match="written for model"):
+        mf.attach_model_ext(other, ext)
+    renamed = mf.parse_model_bytes(mf.model_file_bytes(m), True)
+    renamed["trunk"]["blocks"][0]["name"] = "elsewhere"
+    with pytest.raises(ValueError, match="does not have"):
+        mf.attach_model_ext(renamed, ext)
+    plain = mf.make_b6c96()
+    assert mf.model_ext_bytes(plain) is None
+    mf.save_model_file(plain, path)
+    assert not os.path.exists(path + mf.EXT_SUFFIX)
+
+
+@pytest.mark.skipif(not os.path.exists(REF_TOOL), reason="needs oracle/_ref")
+def test_reference_loader_plus_extension_file_gives_the_generators_net(oracle, tmp_path):
+    """The route a backend takes: the reference's own loader parses the model file, the extension file's records are
+    attached by block name while the ModelDesc is flattened (katago_b200/host/modeldesc_blob.h), and the result
+    evaluates like the blob made directly from the generator's tree; without the extension file the bias is absent."""
+    m = _relbias_model()
+    path = tmp_path / "rb.bin.gz"
+    mf.save_model_file(m, str(path))
+    out = tmp_path / "ref.blob"
+    subprocess.run([REF_TOOL, str(path), str(out)], check=True, stdout=subprocess.DEVNULL)
+    with_ext = out.read_bytes()
+    assert len(with_ext) == len(mf.to_blob(m))
+    a, b = oracle.OracleModel(with_ext), oracle.OracleModel(mf.to_blob(m))
+    sp, gl = mf.random_positions(2, seed=6, board_sizes=[19, 13])
+    oa, ob = a.forward(sp, gl), b.forward(sp, gl)
+    for k in oa:
+        assert np.abs(oa[k] - ob[k]).max() <= 1e-5 * max(1.0, np.abs(oa[k]).max()), k
+    os.remove(str(path) + mf.EXT_SUFFIX)
+    subprocess.run([REF_TOOL, str(path), str(out)], check=True, stdout=subprocess.DEVNULL)
+    bias_words = sum(b["relBias"].size + 3 + 3 for b in m["trunk"]["blocks"] if b.get("relBias") is not None)
+    assert len(out.read_bytes()) == len(with_ext) - 4 * bias_words
+    oc = oracle.OracleModel(out.read_bytes()).forward(sp, gl)
+    assert np.abs(oc["policy"] - ob["policy"]).max() > 1e-5
+    # an extension file that names a block the model does not have is refused by the C++ reader too
+    renamed = _relbias_model()
+    renamed["trunk"]["blocks"][0]["name"] = "elsewhere"
+    with open(str(path) + mf.EXT_SUFFIX, "wb") as f:
+        f.write(mf.model_ext_bytes(renamed))
+    r = subprocess.run([REF_TOOL, str(path), str(out)], capture_output=True, text=True)
+    assert r.returncode != 0 and "does not have" in r.stderr

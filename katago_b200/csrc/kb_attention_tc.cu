@@ -1,18 +1,22 @@
 // Attention over the points of one board on sm_100a tensor cores (tcgen05), for head dimension 64.
 //
-// One CTA = one (board, head); it loads K and V once and walks the board's 128-query tiles.  The tokens of a board are
-// its padded rows (row = y*RW + x, kb_kernels.cuh): contiguous in memory, so Q, K and V tiles are plain 2-D TMA boxes
-// of the QKV matrix; padding rows and off-board points are excluded as keys by an additive bias of -1e30 and produce
-// zero output as queries (eigenbackend.cpp:1505-1536).  All keys of a board (<= 384 rows) are processed in one pass:
-//   rope           (optional) Q and K are rotated in place in shared memory by all 256 threads
-//   S = Q K^T      12 MMAs 128x128x16 into 384 TMEM columns (fp32)
+// The tokens of a board are its padded rows (row = y*RW + x, kb_kernels.cuh): contiguous in memory, so Q, K and V
+// tiles are plain 2-D TMA boxes of the QKV matrix; padding rows and off-board points are excluded as keys by an
+// additive bias of -1e30 and produce zero output as queries (eigenbackend.cpp:1505-1536).  All keys of a board
+// (<= 384 rows) are processed in one pass per 128-query tile:
+//   S = Q K^T      MMAs into 384 TMEM columns (fp32)
 //   softmax        two warps per query-row quarter, each over half of the keys: a pass for the maximum and a pass for
 //                  exp and sum straight out of TMEM (the next 32-key chunk is in flight while one is processed);
 //                  P is written in the activation dtype into shared memory in the K-major swizzled operand layout
 //   O = P V        24 MMAs 128x64x16; V is used as it lies in memory (dv contiguous = MN-major B operand)
 //   out = O / sum  read from TMEM, written with 16-byte stores
-// The next Q tile is fetched behind the softmax.  Waits are bounded as in the convolution kernel; on a time-out the
-// status word is set and the CTA runs through its remaining barriers without touching data.
+// Two kernels with the same arithmetic (identical bits):
+//   attentionTcKernel    one CTA per (board, head) that runs the phases one after the other; it can rotate Q and K
+//                        (rotary embedding) in place in shared memory first, for callers whose projection did not
+//   attentionPipeKernel  persistent CTAs, a dedicated warp for TMA and MMA issue, two O buffers: the tensor core works
+//                        on the neighbouring units while the softmax warps work on this one (see there)
+// Waits are bounded as in the convolution kernel; on a time-out the status word is set and the CTA runs through its
+// remaining barriers without touching data.
 #include "kb_kernels.cuh"
 #include "kb_tc_ptx.cuh"
 #include "kb_act.cuh"
@@ -52,7 +56,7 @@ struct AttnTcArgs {
   const float* mask;
   void* out;
   int outStride;
-  uint32_t idescS, idescO;
+  uint32_t idescS, idescS256, idescO;   // S = Q K^T for 128 keys, for 256 keys (the pipelined kernel), O = P V
   float scaleLog2e;       // 1/sqrt(dq) * log2(e)
   // Rotary tables in factored form, or NULL (Q and K are used as stored): the angle of pair p at point (x,y) is the sum
   // of an x part and a y part; ropeX [tableHeads][AT_D/2][X] and ropeY [tableHeads][AT_D/2][Y] hold (cos, sin) of the
@@ -536,12 +540,14 @@ __global__ void __launch_bounds__(AP_THREADS, 1) attentionPipeKernel(const __gri
         AT_TRACE_I(i < 6, i * 8 + 0);
         if(ok) {
           tcFenceAfter();
+          // the three key tiles lie back to back in the operand layout (8-key groups 1024 bytes apart throughout), so
+          // the first two go through one 256-wide MMA per 16 channels: an MMA's cost is mostly fixed (8 instead of 12)
           const uint32_t qLo = descLo(smemU32(sQ));
-          for(int j = 0; j < 3; j++) {
-            const uint32_t kLo = descLo(smemU32(sK + j * AT_TILE_BYTES));
+          const uint32_t kLo0 = descLo(smemU32(sK)), kLo2 = descLo(smemU32(sK + 2 * AT_TILE_BYTES));
 #pragma unroll
-            for(int k = 0; k < AT_D / 16; k++) ummaLoHi(tmemS + (uint32_t)(j * 128), qLo + 2 * k, kLo + 2 * k, descHi, a.idescS, k > 0 ? 1u : 0u);
-          }
+          for(int k = 0; k < AT_D / 16; k++) ummaLoHi(tmemS, qLo + 2 * k, kLo0 + 2 * k, descHi, a.idescS256, k > 0 ? 1u : 0u);
+#pragma unroll
+          for(int k = 0; k < AT_D / 16; k++) ummaLoHi(tmemS + 256u, qLo + 2 * k, kLo2 + 2 * k, descHi, a.idescS, k > 0 ? 1u : 0u);
           ummaCommit(smemU32(&bars[AP_S_FULL]));
         }
         AT_TRACE_I(i < 6, i * 8 + 1);
@@ -862,6 +868,7 @@ cudaError_t launchAttentionTc(
   a.mask = mask; a.out = out; a.outStride = outStride;
   const uint32_t fmt = p->dt == DT_F16 ? 0u : 1u;
   a.idescS = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+  a.idescS256 = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
   a.idescO = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((uint32_t)(AT_D >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
   a.scaleLog2e = 1.4426950408889634f / sqrtf((float)AT_D);
   a.status = statusWord;

@@ -50,9 +50,11 @@ static const TileRow TILE_TABLE[] = {
   {1, 512, 256, 256, 0, 2, 2, 0},   // 84 us, tensor pipe 31 % (also the merged head convolution: 73 us, 36 %)
   {1, 256, 512, 256, 0, 2, 2, 0},   // with residual: 180 us, tensor pipe 14 % (8 units per tile: no 12-warp variant)
   // ---- transformer 12 x (6 heads x 64, SwiGLU 1024), fp16, batch 128 (51 200 padded rows) ----
-  {1, 384, 1152, 192, 0, 2, 2, 0},   // norm + Q|K|V: 70 us, tensor pipe 31 %
+  // norm + Q|K|V: 66 us, tensor pipe 31 %; 83 us with the rotary embedding in its epilogue (which saves the attention
+  // kernel 45 us).  N=128 with resident weights 91 us, N=96 114 us.
+  {1, 384, 1152, 192, 0, 2, 2, 0},
   {1, 384, 384, 192, 0, 2, 2, 0},    // attention output with residual (records row sums: 8-warp epilogue only): 35 us, 20 %
-  {1, 384, 2048, 256, 0, 2, 2, 0},   // norm + up|gate with the SwiGLU epilogue (8 epilogue warps only): 124 us, 32 %
+  {1, 384, 2048, 256, 0, 2, 2, 0},   // norm + up|gate with the SwiGLU epilogue (8 epilogue warps only): 124 us, 32 %; N=128: 182 us
   {1, 1024, 384, 192, 0, 2, 2, 0},   // FFN down with residual (records row sums): 62 us, 31 %
 };
 

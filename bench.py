@@ -434,6 +434,7 @@ def run_through_katago(args):
             f.write(text)
         env = dict(os.environ)
         env["LD_LIBRARY_PATH"] = os.path.join(ROOT, "katago_b200") + os.pathsep + env.get("LD_LIBRARY_PATH", "")
+        env["KATAB200_TIMING"] = "1"  # the backend prints, per server thread, where getOutput's wall time went
         cmd = [binary, "benchmark", "-model", model, "-config", cfg, "-v", str(args.visits), "-t", args.search_threads, "-n", str(args.positions)]
         t0 = time.perf_counter()
         r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=1800)
@@ -445,7 +446,19 @@ def run_through_katago(args):
         if m:
             rows.append({"search_threads": int(m.group(1)), "nn_evals_per_s": float(m.group(2)), "line": line.strip()[:200]})
     best = max((x["nn_evals_per_s"] for x in rows), default=None)
-    print(json.dumps({"impl": "b200-through-katago", "metric": "nnEvals/s of the reference's benchmark subcommand on this backend", "value": best,
+    # host profile of the server threads: seconds spent staging rows, inside kb_forward_host, unpacking, and waiting for
+    # the NNEvaluator queue to hand over the next batch (summed over the threads)
+    prof = {"server_threads": 0, "calls": 0, "rows": 0, "staging_s": 0.0, "kb_forward_host_s": 0.0, "unpacking_s": 0.0, "waiting_s": 0.0}
+    for m in re.finditer(r"B200 backend timing: .*?: (\d+) getOutput calls, (\d+) rows .*?staging rows ([0-9.]+) s, kb_forward_host ([0-9.]+) s, "
+                         r"unpacking ([0-9.]+) s, waiting for the next batch ([0-9.]+) s", text):
+        prof["server_threads"] += 1
+        prof["calls"] += int(m.group(1)); prof["rows"] += int(m.group(2))
+        prof["staging_s"] += float(m.group(3)); prof["kb_forward_host_s"] += float(m.group(4))
+        prof["unpacking_s"] += float(m.group(5)); prof["waiting_s"] += float(m.group(6))
+    busy = prof["staging_s"] + prof["kb_forward_host_s"] + prof["unpacking_s"]
+    prof["busy_fraction"] = busy / (busy + prof["waiting_s"]) if busy + prof["waiting_s"] > 0 else None
+    prof["host_cores"] = _host_cores()
+    print(json.dumps({"impl": "b200-through-katago", "host_profile": prof, "metric": "nnEvals/s of the reference's benchmark subcommand on this backend", "value": best,
                       "unit": "evals/s", "n_gpus": G, "server_threads_per_gpu": per, "visits": args.visits, "rows": rows, "rc": r.returncode,
                       "wall_s": wall, "tail": None if rows else text[-1500:]}), flush=True)
 

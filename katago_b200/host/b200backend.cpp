@@ -29,6 +29,8 @@
 #include "modeldesc_blob.h"
 #include "nnoutput_glue.h"
 
+#include <chrono>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 
@@ -125,13 +127,38 @@ void NeuralNet::freeComputeContext(ComputeContext* computeContext) { delete comp
 
 // Handle ------------------------------------------------------------------------------------------
 
+// Host-side stage timers of getOutput (environment KATAB200_TIMING=1): where a server thread's wall time goes.  "waiting"
+// is the time between the return of one getOutput and the entry of the next, i.e. the NNEvaluator queue filling up.
+struct StageTimers {
+  typedef std::chrono::steady_clock Clock;
+  bool on = false;
+  int serverThreadIdx = 0, gpuIdx = 0;
+  long long calls = 0, rows = 0;
+  double stageS = 0.0, deviceS = 0.0, unpackS = 0.0, waitingS = 0.0;
+  Clock::time_point lastReturn;
+  bool hasLast = false;
+  static double since(Clock::time_point t0, Clock::time_point t1) { return std::chrono::duration<double>(t1 - t0).count(); }
+  void report() const {
+    if(!on || calls == 0) return;
+    std::fprintf(
+      stderr,
+      "B200 backend timing: server thread %d (GPU %d): %lld getOutput calls, %lld rows (%.1f per call); staging rows %.3f s, "
+      "kb_forward_host %.3f s, unpacking %.3f s, waiting for the next batch %.3f s\n",
+      serverThreadIdx, gpuIdx, calls, rows, (double)rows / (double)calls, stageS, deviceS, unpackS, waitingS);
+  }
+};
+
 struct ComputeHandle {
   kb_handle* handle = nullptr;
   kbhost::NetDims dims;
   int precision = KB_PRECISION_FP32;
   int maxBatchSize = 0;
   bool inputsUseNHWC = true;
-  ~ComputeHandle() { kb_handle_destroy(handle); }
+  StageTimers timers;
+  ~ComputeHandle() {
+    timers.report();
+    kb_handle_destroy(handle);
+  }
 };
 
 ComputeHandle* NeuralNet::createComputeHandle(
@@ -142,6 +169,12 @@ ComputeHandle* NeuralNet::createComputeHandle(
   handle->precision = context->precision;
   handle->maxBatchSize = maxBatchSize;
   handle->inputsUseNHWC = inputsUseNHWC;
+  {
+    const char* e = std::getenv("KATAB200_TIMING");
+    handle->timers.on = e != NULL && std::atoi(e) != 0;
+    handle->timers.serverThreadIdx = serverThreadIdx;
+    handle->timers.gpuIdx = gpuIdxForThisThread;
+  }
   check(
     kb_handle_create(
       context->model, gpuIdxForThisThread, maxBatchSize, context->nnXLen, context->nnYLen, context->precision,
@@ -241,6 +274,12 @@ void NeuralNet::getOutput(
   const kbhost::NetDims& d = h->dims;
   const size_t S = b->S;
   const size_t C = (size_t)d.numSpatialFeatures;
+  StageTimers& tm = h->timers;
+  StageTimers::Clock::time_point t0, t1, t2;
+  if(tm.on) {
+    t0 = StageTimers::Clock::now();
+    if(tm.hasLast) tm.waitingS += StageTimers::since(tm.lastReturn, t0);
+  }
 
   // Stage rows.  The board symmetry is applied on the device (inputs) and inverted there (policy,
   // ownership), so rows are copied as they are; only an NCHW row needs a transposition here.
@@ -264,10 +303,12 @@ void NeuralNet::getOutput(
     b->symmetry[row] = buf->symmetry;
   }
 
+  if(tm.on) t1 = StageTimers::Clock::now();
   check(
     kb_forward_host_meta(
       h->handle, n, b->spatial, b->global, b->meta, b->symmetry, b->policy, b->policyPass, b->value, b->scoreValue, b->ownership),
     "kb_forward_host_meta");
+  if(tm.on) t2 = StageTimers::Clock::now();
 
   // Unpack.  Symmetry was already inverted on the device, so unpackRow is called with identity symmetry.
   NNResultBuf identity;
@@ -277,6 +318,12 @@ void NeuralNet::getOutput(
     kbhost::unpackRow(
       d, &identity, outputs[row], b->policy + S * d.numPolicyChannels * row, b->policyPass + (size_t)d.numPolicyChannels * row,
       b->value + (size_t)d.numValueChannels * row, b->scoreValue + (size_t)d.numScoreValueChannels * row, b->ownership + S * row);
+  }
+  if(tm.on) {
+    const StageTimers::Clock::time_point t3 = StageTimers::Clock::now();
+    tm.calls++; tm.rows += n;
+    tm.stageS += StageTimers::since(t0, t1); tm.deviceS += StageTimers::since(t1, t2); tm.unpackS += StageTimers::since(t2, t3);
+    tm.lastReturn = t3; tm.hasLast = true;
   }
 }
 

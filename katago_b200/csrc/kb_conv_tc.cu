@@ -1189,7 +1189,10 @@ static ConvTcKernelFn kernelForAct(int act) {
     case KB_ACT_SILU: return convTcKernel<T, KB_ACT_SILU, TMA_EPI, PAIR, CG, DEPS>;
     case KB_ACT_MISH_SCALE8: return convTcKernel<T, KB_ACT_MISH_SCALE8, TMA_EPI, PAIR, CG, DEPS>;
     // the SwiGLU epilogue exists with the default warp count and whole-grid dependencies only
-    case KB_ACT_SWIGLU_PAIRS: return (CG == TC_EPI_CG && !DEPS) ? convTcKernel<T, KB_ACT_SWIGLU_PAIRS, TMA_EPI, PAIR, TC_EPI_CG, false> : nullptr;
+    case KB_ACT_SWIGLU_PAIRS:
+      if(DEPS) return nullptr;
+      if(CG == TC_EPI_CG_WIDE) return (TMA_EPI && !PAIR) ? convTcKernel<T, KB_ACT_SWIGLU_PAIRS, true, false, TC_EPI_CG_WIDE, false> : nullptr;
+      return convTcKernel<T, KB_ACT_SWIGLU_PAIRS, TMA_EPI, PAIR, TC_EPI_CG, false>;
     // so does the rotary epilogue, for single CTAs with the staged epilogue
     case KB_ACT_ROPE_QK: return (TMA_EPI && !PAIR && CG == TC_EPI_CG && !DEPS) ? convTcKernel<T, KB_ACT_ROPE_QK, true, false, TC_EPI_CG, false> : nullptr;
     default: return convTcKernel<T, KB_ACT_IDENTITY, TMA_EPI, PAIR, CG, DEPS>;
@@ -1394,8 +1397,13 @@ bool convTcSetEpilogue(ConvTcPlan* p, const Epilogue& ep) {
   {
     const TileRow row = tilePlanFor(p->kY, p->inC, p->outC);
     const int want = wideMode > 1 ? TC_EPI_CG_WIDE : (ep.residual ? row.epiWarpsRes : row.epiWarps);
-    // the 12-warp variant exists for single CTAs, 1x1 kernels, plain staged epilogues, and tiles of 3n units
-    if(TC_EPI_CG == 2 && wideMode > 0 && want == TC_EPI_CG_WIDE && p->kY == 1 && !p->pair && !needsStaged && (p->BN / 32) % TC_EPI_CG_WIDE == 0)
+    // the 12-warp variant exists for single CTAs and 1x1 kernels: plain staged epilogues whose tiles have 3n units
+    // (the residual ring assumes equal shares), and the SwiGLU epilogue, which has no residual and may split a tile's
+    // units unevenly (8 units: 3 + 3 + 2).  (The rotary epilogue was measured with twelve warps as well: 82 us either
+    // way, that projection is bound by its operand loads, about 1000 cycles per 40 KB chunk.)
+    const bool specialWide = ep.act == KB_ACT_SWIGLU_PAIRS && !ep.residual && !ep.sumsqOut;
+    const bool plainWide = !needsStaged && (p->BN / 32) % TC_EPI_CG_WIDE == 0;
+    if(TC_EPI_CG == 2 && wideMode > 0 && want == TC_EPI_CG_WIDE && p->kY == 1 && !p->pair && (plainWide || specialWide))
       p->cg = TC_EPI_CG_WIDE;
   }
   const int unitsPerWarp = (p->BN / 32 + p->cg - 1) / p->cg;

@@ -281,14 +281,21 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_
             const int4 ko = ko4[i * 8 + j];
             b.x += qRel[ko.x]; b.y += qRel[ko.y]; b.z += qRel[ko.z]; b.w += qRel[ko.w];
           }
-          m4[0] = fmaxf(m4[0], fmaf(__uint_as_float(r[i & 1][4 * j]), a.scaleLog2e, b.x));
-          m4[1] = fmaxf(m4[1], fmaf(__uint_as_float(r[i & 1][4 * j + 1]), a.scaleLog2e, b.y));
-          m4[2] = fmaxf(m4[2], fmaf(__uint_as_float(r[i & 1][4 * j + 2]), a.scaleLog2e, b.z));
-          m4[3] = fmaxf(m4[3], fmaf(__uint_as_float(r[i & 1][4 * j + 3]), a.scaleLog2e, b.w));
+          const float t0 = fmaf(__uint_as_float(r[i & 1][4 * j]), a.scaleLog2e, b.x), t1 = fmaf(__uint_as_float(r[i & 1][4 * j + 1]), a.scaleLog2e, b.y);
+          const float t2 = fmaf(__uint_as_float(r[i & 1][4 * j + 2]), a.scaleLog2e, b.z), t3 = fmaf(__uint_as_float(r[i & 1][4 * j + 3]), a.scaleLog2e, b.w);
+          m4[0] = fmaxf(m4[0], t0); m4[1] = fmaxf(m4[1], t1); m4[2] = fmaxf(m4[2], t2); m4[3] = fmaxf(m4[3], t3);
+          if(BIAS) {
+            r[i & 1][4 * j] = __float_as_uint(t0); r[i & 1][4 * j + 1] = __float_as_uint(t1);
+            r[i & 1][4 * j + 2] = __float_as_uint(t2); r[i & 1][4 * j + 3] = __float_as_uint(t3);
+          }
         }
+        // with a relative-position bias the scaled and biased scores go back into TMEM, so that the second pass does
+        // not gather the bias again
+        if(BIAS) tmemSt32(tS + (uint32_t)(i * 32), r[i & 1]);
         if(i + 1 < NCH) tmemLdWaitFor(r[(i + 1) & 1]);
       }
       mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      if(BIAS) tmemStWait();
     }
     AT_TRACE(4 + qt * 8);
     sRed[half * 128 + row] = mx;
@@ -315,15 +322,20 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_
           float p[8];
 #pragma unroll
           for(int k = 0; k < 2; k++) {
-            float4 b = kb4[i * 8 + 2 * jj + k];
-            if(BIAS && qRel) {
-              const int4 ko = ko4[i * 8 + 2 * jj + k];
-              b.x += qRel[ko.x]; b.y += qRel[ko.y]; b.z += qRel[ko.z]; b.w += qRel[ko.w];
+            if(BIAS) {
+              // the first pass left scale * score + bias in TMEM
+              p[4 * k] = ex2Approx(__uint_as_float(r[i & 1][8 * jj + 4 * k]) - mxs);
+              p[4 * k + 1] = ex2Approx(__uint_as_float(r[i & 1][8 * jj + 4 * k + 1]) - mxs);
+              p[4 * k + 2] = ex2Approx(__uint_as_float(r[i & 1][8 * jj + 4 * k + 2]) - mxs);
+              p[4 * k + 3] = ex2Approx(__uint_as_float(r[i & 1][8 * jj + 4 * k + 3]) - mxs);
             }
-            p[4 * k] = ex2Approx(fmaf(__uint_as_float(r[i & 1][8 * jj + 4 * k]), a.scaleLog2e, b.x - mxs));
-            p[4 * k + 1] = ex2Approx(fmaf(__uint_as_float(r[i & 1][8 * jj + 4 * k + 1]), a.scaleLog2e, b.y - mxs));
-            p[4 * k + 2] = ex2Approx(fmaf(__uint_as_float(r[i & 1][8 * jj + 4 * k + 2]), a.scaleLog2e, b.z - mxs));
-            p[4 * k + 3] = ex2Approx(fmaf(__uint_as_float(r[i & 1][8 * jj + 4 * k + 3]), a.scaleLog2e, b.w - mxs));
+            else {
+              const float4 b = kb4[i * 8 + 2 * jj + k];
+              p[4 * k] = ex2Approx(fmaf(__uint_as_float(r[i & 1][8 * jj + 4 * k]), a.scaleLog2e, b.x - mxs));
+              p[4 * k + 1] = ex2Approx(fmaf(__uint_as_float(r[i & 1][8 * jj + 4 * k + 1]), a.scaleLog2e, b.y - mxs));
+              p[4 * k + 2] = ex2Approx(fmaf(__uint_as_float(r[i & 1][8 * jj + 4 * k + 2]), a.scaleLog2e, b.z - mxs));
+              p[4 * k + 3] = ex2Approx(fmaf(__uint_as_float(r[i & 1][8 * jj + 4 * k + 3]), a.scaleLog2e, b.w - mxs));
+            }
             s4[0] += p[4 * k]; s4[1] += p[4 * k + 1]; s4[2] += p[4 * k + 2]; s4[3] += p[4 * k + 3];
           }
           uint4 o;
@@ -703,11 +715,19 @@ __global__ void __launch_bounds__(AP_THREADS, 1) attentionPipeKernel(const __gri
             const float2 t23 = __ffma2_rn(make_float2(__uint_as_float(r[ii & 1][4 * j + 2]), __uint_as_float(r[ii & 1][4 * j + 3])), scale2, make_float2(b.z, b.w));
             m4[0] = fmaxf(m4[0], t01.x); m4[1] = fmaxf(m4[1], t01.y);
             m4[2] = fmaxf(m4[2], t23.x); m4[3] = fmaxf(m4[3], t23.y);
+            if(BIAS) {
+              r[ii & 1][4 * j] = __float_as_uint(t01.x); r[ii & 1][4 * j + 1] = __float_as_uint(t01.y);
+              r[ii & 1][4 * j + 2] = __float_as_uint(t23.x); r[ii & 1][4 * j + 3] = __float_as_uint(t23.y);
+            }
           }
+          // with a relative-position bias the scaled and biased scores go back into TMEM, so that the second pass
+          // does not gather the bias again
+          if(BIAS) tmemSt32(tS + (uint32_t)(ii * 32), r[ii & 1]);
           if(ii + 1 < NCH) tmemLdWaitFor(r[(ii + 1) & 1]);
           AT_TRACE_W(i == 3, 20 + ii);
         }
         mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+        if(BIAS) tmemStWait();
       }
       AT_TRACE_W(i == 3, 1);
       sMax[half * 128 + row] = mx;
@@ -745,15 +765,19 @@ __global__ void __launch_bounds__(AP_THREADS, 1) attentionPipeKernel(const __gri
             float p[8];
 #pragma unroll
             for(int k = 0; k < 2; k++) {
-              float4 b = kb4[ii * 8 + 2 * jj + k];
-              if(BIAS && qRel) {
-                const int4 ko = ko4[ii * 8 + 2 * jj + k];
-                b.x += qRel[ko.x]; b.y += qRel[ko.y]; b.z += qRel[ko.z]; b.w += qRel[ko.w];
+              float2 t01, t23;
+              if(BIAS) {
+                // the first pass left scale * score + bias in TMEM
+                t01 = __fadd2_rn(make_float2(__uint_as_float(r[ii & 1][8 * jj + 4 * k]), __uint_as_float(r[ii & 1][8 * jj + 4 * k + 1])), negMx2);
+                t23 = __fadd2_rn(make_float2(__uint_as_float(r[ii & 1][8 * jj + 4 * k + 2]), __uint_as_float(r[ii & 1][8 * jj + 4 * k + 3])), negMx2);
               }
-              const float2 t01 = __ffma2_rn(make_float2(__uint_as_float(r[ii & 1][8 * jj + 4 * k]), __uint_as_float(r[ii & 1][8 * jj + 4 * k + 1])), scale2,
-                                            __fadd2_rn(make_float2(b.x, b.y), negMx2));
-              const float2 t23 = __ffma2_rn(make_float2(__uint_as_float(r[ii & 1][8 * jj + 4 * k + 2]), __uint_as_float(r[ii & 1][8 * jj + 4 * k + 3])), scale2,
-                                            __fadd2_rn(make_float2(b.z, b.w), negMx2));
+              else {
+                const float4 b = kb4[ii * 8 + 2 * jj + k];
+                t01 = __ffma2_rn(make_float2(__uint_as_float(r[ii & 1][8 * jj + 4 * k]), __uint_as_float(r[ii & 1][8 * jj + 4 * k + 1])), scale2,
+                                 __fadd2_rn(make_float2(b.x, b.y), negMx2));
+                t23 = __ffma2_rn(make_float2(__uint_as_float(r[ii & 1][8 * jj + 4 * k + 2]), __uint_as_float(r[ii & 1][8 * jj + 4 * k + 3])), scale2,
+                                 __fadd2_rn(make_float2(b.z, b.w), negMx2));
+              }
               p[4 * k] = ex2Approx(t01.x); p[4 * k + 1] = ex2Approx(t01.y);
               p[4 * k + 2] = ex2Approx(t23.x); p[4 * k + 3] = ex2Approx(t23.y);
               s2[0] = __fadd2_rn(s2[0], make_float2(p[4 * k], p[4 * k + 1]));

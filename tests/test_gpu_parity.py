@@ -116,6 +116,10 @@ def test_transformer_blocks_with_masks(prec, tol, oracle):
         (384, _with_rel_bias(g, _attn_block(g, 384, 6, 6, 64, 64, "none"))),
         (384, _with_rel_bias(g, _attn_block(g, 384, 6, 3, 64, 64, "learnable"))),
         (64, _with_rel_bias(g, _attn_block(g, 64, 4, 2, 16, 16, "fixed"))),
+        # grouped-query attention on the tensor-core path: three query heads share each K and V
+        (384, _attn_block(g, 384, 6, 2, 64, 64, "fixed")),
+        # 12 + 12 heads of 64: more rotary frequencies than the projection's epilogue holds (1024), so the attention kernel rotates Q and K itself
+        (768, _attn_block(g, 768, 12, 12, 64, 64, "learnable")),
         (384, dict(kind="transformer_ffn_block", name="ffn", C=384, ffnC=1024, swiglu=1, preLN=g.trms(384), linear1=g.matmul(384, 1024),
                    gate=g.matmul(384, 1024), linear2=g.matmul(1024, 384))),
         (96, dict(kind="transformer_ffn_block", name="ffn2", C=96, ffnC=160, swiglu=1, preLN=g.trms(96), linear1=g.matmul(96, 160),

@@ -1397,12 +1397,12 @@ bool convTcSetEpilogue(ConvTcPlan* p, const Epilogue& ep) {
   {
     const TileRow row = tilePlanFor(p->kY, p->inC, p->outC);
     const int want = wideMode > 1 ? TC_EPI_CG_WIDE : (ep.residual ? row.epiWarpsRes : row.epiWarps);
-    // the 12-warp variant exists for single CTAs and 1x1 kernels: plain staged epilogues whose tiles have 3n units
-    // (the residual ring assumes equal shares), and the SwiGLU epilogue, which has no residual and may split a tile's
-    // units unevenly (8 units: 3 + 3 + 2).  (The rotary epilogue was measured with twelve warps as well: 82 us either
-    // way, that projection is bound by its operand loads, about 1000 cycles per 40 KB chunk.)
+    // the 12-warp variant exists for single CTAs and 1x1 kernels, for the plain staged epilogue and the SwiGLU one.  A
+    // tile's units need not divide by three (8 units: 3 + 3 + 2): every warp walks its own unit sequence, residual
+    // ring included.  (The rotary epilogue was measured with twelve warps as well: 82 us either way, that projection
+    // is bound by its operand loads, about 1000 cycles per 40 KB chunk.)
     const bool specialWide = ep.act == KB_ACT_SWIGLU_PAIRS && !ep.residual && !ep.sumsqOut;
-    const bool plainWide = !needsStaged && (p->BN / 32) % TC_EPI_CG_WIDE == 0;
+    const bool plainWide = !needsStaged;
     if(TC_EPI_CG == 2 && wideMode > 0 && want == TC_EPI_CG_WIDE && p->kY == 1 && !p->pair && (plainWide || specialWide))
       p->cg = TC_EPI_CG_WIDE;
   }

@@ -10,7 +10,7 @@
 //   chain     1: runs of such convolutions execute as one persistent multi-layer launch (3x3 only)
 // Shapes without a row fall back to rules that reproduce what the rows were generalised from: BN = the largest
 // multiple of 16 that divides outC (at most 256), pairs for 3x3 with BN = 256, 12 epilogue warps for 1x1 convolutions
-// with a residual whose tile has a multiple of three 32-channel units.
+// with a residual.
 //
 // The comments give the measurement behind each row: microseconds per launch at the batch of the configuration
 // (CUDA events around every launch) and, where captured, the tensor-pipe utilisation ncu reports for that launch
@@ -47,8 +47,10 @@ static const TileRow TILE_TABLE[] = {
   {3, 256, 256, 256, 1, 2, 2, 0},
   {3, 192, 256, 256, 1, 2, 2, 0},   // last convolution of a gpool block
   {3, 64, 512, 256, 1, 2, 2, 0},    // stem: 191 us, tensor pipe 29.7 %
-  {1, 512, 256, 256, 0, 2, 2, 0},   // 84 us, tensor pipe 31 % (also the merged head convolution: 73 us, 36 %)
-  {1, 256, 512, 256, 0, 2, 2, 0},   // with residual: 180 us, tensor pipe 14 % (8 units per tile: no 12-warp variant)
+  {1, 512, 256, 256, 0, 3, 3, 0},   // 84 us, tensor pipe 31 % (also the merged head convolution: 73 us, 36 %); 12 epilogue warps 97 -> 95 us
+  // with residual: 180 us, tensor pipe 14 % with 8 epilogue warps; 12 warps (a tile's 8 units split 3 + 3 + 2) 212 -> 187 us
+  // in the per-launch pass of the full net
+  {1, 256, 512, 256, 0, 2, 3, 0},
   // ---- transformer 12 x (6 heads x 64, SwiGLU 1024), fp16, batch 128 (51 200 padded rows) ----
   // CTA pairs are slower for all four projections (Q|K|V 79 us against 66, attention output 41 against 36, up|gate 134
   // against 118, FFN down 68 against 66).
@@ -79,7 +81,7 @@ inline TileRow tilePlanFor(int k, int inC, int outC, bool* fromTable = nullptr) 
   for(int bn = 256; bn >= 16; bn -= 16)
     if(outC % bn == 0) { r.BN = bn; break; }
   r.pair = (k == 3 && r.BN == 256) ? 1 : 0;
-  r.epiWarpsRes = (k == 1 && !r.pair && r.BN > 0 && (r.BN / 32) % 3 == 0 && (r.BN % 32) == 0) ? 3 : 2;
+  r.epiWarpsRes = (k == 1 && !r.pair && r.BN > 0 && (r.BN % 32) == 0) ? 3 : 2;
   r.chain = (k == 3 && !r.pair) ? 1 : 0;
   return r;
 }

@@ -411,8 +411,9 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attentionTcKernel(const __grid_
 //     SMs finish together; K and V of a (board, kv head) stay in shared memory while consecutive units use them, and
 //     the next unit's Q (and K) are fetched as soon as the MMAs that read the buffers have completed;
 //   * a ninth warp issues every TMA load and every MMA (its warpgroup hands most of its registers to the softmax
-//     warpgroups, whose two passes want more than an even split of the register file gives them); the eight softmax warps never issue one and never meet it at a
-//     CTA-wide barrier (they synchronise among themselves on named barrier 1 and with the issuer through mbarriers);
+//     warpgroups, whose two passes want more than an even split of the register file gives them); the eight softmax
+//     warps never issue one and never meet it at a CTA-wide barrier (they synchronise among themselves on named
+//     barrier 1 and with the issuer through mbarriers);
 //   * O has two TMEM buffers, so a unit's output is read out of TMEM one unit later, after the second softmax pass of
 //     the next unit, while the tensor core computes the S = Q K^T after that; O = P V of unit i runs behind S of unit
 //     i+1, under unit i+1's softmax passes, and releases P to the second pass chunk by chunk (64 keys at a time).

@@ -7,10 +7,14 @@
  * Parity is pinned by running the reference's own known-answer tests against it:
  * tests/testnn.cpp (layer vectors) and tests/tinymodel.cpp (whole-net vector); the
  * recipe in oracle/Makefile links the reference's unmodified test sources with
- * oracle/oraclebackend.cpp.  The transformer blocks and the SGF metadata encoder
- * have no vector in the reference's tests: for them parity is unpinned (they follow
- * eigenbackend.cpp line by line); the relative-position attention bias is an
- * extension of this repository's blob and is defined here.
+ * oracle/oraclebackend.cpp; its printouts on the reference's shipped nets agree with
+ * the golden text files under cpp/tests/results.  The transformer blocks, the RMS norms
+ * and the SGF metadata encoder have no vector in the reference's C++ tests: they are
+ * pinned to the reference's own PyTorch definitions (python/katago/train/model_pytorch.py)
+ * through model files written by the reference's unmodified exporter and the nets' fp32
+ * outputs (tests/golden/make_torch_golden.py, tests/test_oracle_pins.py).  The
+ * relative-position attention bias is an extension of this repository's blob and is
+ * defined here: parity unpinned for that one piece.
  *
  * All tensors are fp32, NHWC: spatial[n][y][x][c].  Models arrive as the blob
  * described in include/kb_modelblob.h.  Every function returns 0 on success and

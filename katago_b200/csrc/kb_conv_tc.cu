@@ -1194,7 +1194,9 @@ static ConvTcKernelFn kernelForAct(int act) {
       if(CG == TC_EPI_CG_WIDE) return (TMA_EPI && !PAIR) ? convTcKernel<T, KB_ACT_SWIGLU_PAIRS, true, false, TC_EPI_CG_WIDE, false> : nullptr;
       return convTcKernel<T, KB_ACT_SWIGLU_PAIRS, TMA_EPI, PAIR, TC_EPI_CG, false>;
     // so does the rotary epilogue, for single CTAs with the staged epilogue
-    case KB_ACT_ROPE_QK: return (TMA_EPI && !PAIR && CG == TC_EPI_CG && !DEPS) ? convTcKernel<T, KB_ACT_ROPE_QK, true, false, TC_EPI_CG, false> : nullptr;
+    case KB_ACT_ROPE_QK:
+      if(DEPS || !TMA_EPI || PAIR) return nullptr;
+      return CG == TC_EPI_CG_WIDE ? convTcKernel<T, KB_ACT_ROPE_QK, true, false, TC_EPI_CG_WIDE, false> : convTcKernel<T, KB_ACT_ROPE_QK, true, false, TC_EPI_CG, false>;
     default: return convTcKernel<T, KB_ACT_IDENTITY, TMA_EPI, PAIR, CG, DEPS>;
   }
 }
@@ -1397,11 +1399,10 @@ bool convTcSetEpilogue(ConvTcPlan* p, const Epilogue& ep) {
   {
     const TileRow row = tilePlanFor(p->kY, p->inC, p->outC);
     const int want = wideMode > 1 ? TC_EPI_CG_WIDE : (ep.residual ? row.epiWarpsRes : row.epiWarps);
-    // the 12-warp variant exists for single CTAs and 1x1 kernels, for the plain staged epilogue and the SwiGLU one.  A
-    // tile's units need not divide by three (8 units: 3 + 3 + 2): every warp walks its own unit sequence, residual
-    // ring included.  (The rotary epilogue was measured with twelve warps as well: 82 us either way, that projection
-    // is bound by its operand loads, about 1000 cycles per 40 KB chunk.)
-    const bool specialWide = ep.act == KB_ACT_SWIGLU_PAIRS && !ep.residual && !ep.sumsqOut;
+    // the 12-warp variant exists for single CTAs and 1x1 kernels, for the plain staged epilogue and for the SwiGLU and
+    // rotary ones.  A tile's units need not divide by three (8 units: 3 + 3 + 2): every warp walks its own unit
+    // sequence, residual ring included.
+    const bool specialWide = (ep.act == KB_ACT_SWIGLU_PAIRS || ep.act == KB_ACT_ROPE_QK) && !ep.residual && !ep.sumsqOut;
     const bool plainWide = !needsStaged;
     if(TC_EPI_CG == 2 && wideMode > 0 && want == TC_EPI_CG_WIDE && p->kY == 1 && !p->pair && (plainWide || specialWide))
       p->cg = TC_EPI_CG_WIDE;

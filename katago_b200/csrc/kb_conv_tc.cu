@@ -1318,6 +1318,13 @@ static bool sizeRings(ConvTcPlan* p, int epiBytes) {
       if(n < 2) return false;
       p->numA = n;
       p->numB = n;
+      // experiments: KB_TC_RING_1X1="a:b" sets the two ring depths separately where they fit
+      if(const char* e = getenv("KB_TC_RING_1X1")) {
+        int ra = 0, rb = 0;
+        if(sscanf(e, "%d:%d", &ra, &rb) == 2 && ra >= 2 && rb >= 2 && ra <= 8 && rb <= 8 && ra * p->aSlotBytes + rb * p->bSlotBytes <= budget) {
+          p->numA = ra; p->numB = rb;
+        }
+      }
     }
   }
   else {

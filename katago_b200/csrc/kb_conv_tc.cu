@@ -57,6 +57,10 @@ struct ConvTcArgs {
   uint32_t* doneCtr;
   int prefillB;    // request the first weight slots before waiting for the preceding kernels
   int residentB;   // 1x1 only: all weight tiles of this CTA's channel tile stay in shared memory for the whole kernel
+  int jointAB;     // 1x1 with streamed weights: the activation chunk and the weight chunk of a K step share one "full"
+                   // and one "empty" barrier (the rings have the same depth and advance together), so the MMA-issuing
+                   // thread waits once and commits once per four MMAs; with a wait and a commit per operand that thread,
+                   // not the tensor pipe, set the pace (about 1000 cycles per step where the MMAs need 480)
   uint32_t idesc;
   uint32_t tmemCols;
   int epiWarpBytes; // shared memory of one epilogue warp's staging units (TMA epilogue)
@@ -537,7 +541,7 @@ __global__ void __launch_bounds__(tcThreads(CG, DEPS), 1) convTcKernel(
       // Weight ring: the first tile's first slots are requested before the wait on the preceding kernels as well (the
       // ring starts empty, so the slots need no empty-wait); the main loop below skips those loads.
       int prefilled = 0;
-      if(!a.residentB && a.prefillB && tm.first < numTiles) {
+      if(!a.residentB && a.prefillB && !a.jointAB && tm.first < numTiles) {
         const int n0 = tm.nTile(tm.first) * a.BN;
         const int total = a.kChunks * taps;
         prefilled = a.numB < total ? a.numB : total;
@@ -564,6 +568,15 @@ __global__ void __launch_bounds__(tcThreads(CG, DEPS), 1) convTcKernel(
         for(int kc = 0; kc < a.kChunks && ok; kc++) {
           if(!mbarWait(smemU32(&emptyA[sa]), phA ^ 1u, abortFlag)) { ok = false; break; }
           TRACE(true, ((t - tm.first) / tm.step) * 16 + kc);
+          if(!PAIR && a.jointAB) {
+            // both operands of the step on the activation slot's barrier; the weight slot has the same index
+            const uint32_t bar = smemU32(&fullA[sa]);
+            mbarExpectTx(bar, aBytes + bBytes);
+            tmaLoad2d(smemU32(smemA + (size_t)sa * a.aSlotBytes), &tmA, kc * TC_BK, m0 - a.haloPad, bar);
+            tmaLoad2d(smemU32(smemB + (size_t)sa * a.bSlotBytes), &tmB, kc * TC_BK, n0, bar);
+            if(++sa == (uint32_t)a.numA) { sa = 0; phA ^= 1u; }
+            continue;
+          }
           loadA(sa, kc, m0);
           if(++sa == (uint32_t)a.numA) { sa = 0; phA ^= 1u; }
           if(a.residentB) continue;
@@ -643,6 +656,16 @@ __global__ void __launch_bounds__(tcThreads(CG, DEPS), 1) convTcKernel(
             if(!mbarWait(smemU32(&fullB[kc]), 0u, abortFlag)) { ok = false; break; }
             tcFenceAfter();
             const uint32_t bT = bLoBase + (uint32_t)kc * bSlot16;
+#pragma unroll
+            for(int k = 0; k < TC_BK / 16; k++) {
+              mma(dTmem, aLo + 2 * k, bT + 2 * k, descHi, accumulate);
+              accumulate = 1;
+            }
+          }
+          else if(!PAIR && a.jointAB) {
+            // the weight chunk arrived on the same barrier as the activation chunk and is released with it below
+            tcFenceAfter();
+            const uint32_t bT = bLoBase + sa * bSlot16;
 #pragma unroll
             for(int k = 0; k < TC_BK / 16; k++) {
               mma(dTmem, aLo + 2 * k, bT + 2 * k, descHi, accumulate);
@@ -1416,6 +1439,14 @@ bool convTcSetEpilogue(ConvTcPlan* p, const Epilogue& ep) {
   }
   const int unitsPerWarp = (p->BN / 32 + p->cg - 1) / p->cg;
   p->resRing = (p->kY == 1) ? unitsPerWarp + 1 : 2;
+  // A 1x1 convolution with a long K loop (FFN down: 1024 channels = 16 steps) is bound by how many operand steps are in
+  // flight, not by its epilogue: three residual slots instead of four leave room for a fourth operand stage (measured
+  // 68.4 -> 61.6 us; two slots 63.2 us).  KB_TC_RES_RING overrides for experiments.
+  if(p->kY == 1 && p->kChunks >= 8 && p->resRing > 3) p->resRing = 3;
+  if(const char* e = getenv("KB_TC_RES_RING")) {
+    const int v = atoi(e);
+    if(p->kY == 1 && p->kChunks >= 8 && v >= 2 && v <= unitsPerWarp + 1) p->resRing = v;
+  }
   const int rawUnits = ep.residual ? p->resRing : (ep.outRaw ? 2 : 0);
   p->epiWarpBytes = (rawUnits + (ep.outAct ? 1 : 0)) * TC_UNIT_BYTES;
   if(!sizeRings(p, tcEpiWarps(p->cg) * p->epiWarpBytes)) { p->cg = TC_EPI_CG; return needsStaged ? false : sizeRings(p, 0); }
@@ -1459,6 +1490,8 @@ cudaError_t launchConvTc(cudaStream_t st, const ConvTcPlan* p, Geom g, const Epi
   a.inC = p->inC; a.outC = p->outC; a.kY = p->kY; a.kX = p->kX;
   a.BN = p->BN; a.kChunks = p->kChunks; a.haloPad = p->haloPad; a.aRows = p->aRows;
   a.aSlotBytes = p->aSlotBytes; a.bSlotBytes = p->bSlotBytes; a.numA = p->numA; a.numB = p->numB; a.residentB = p->residentB;
+  static const bool jointOff = getenv("KB_TC_NO_JOINT_AB") != nullptr && atoi(getenv("KB_TC_NO_JOINT_AB")) != 0;
+  a.jointAB = (!jointOff && p->kY == 1 && p->kX == 1 && !p->residentB && !p->pair && p->numA == p->numB) ? 1 : 0;
   static const bool prefillB = getenv("KB_NO_B_PREFILL") == nullptr;
   a.prefillB = prefillB ? 1 : 0;
   a.pair = p->pair;

@@ -62,7 +62,9 @@ static const TileRow TILE_TABLE[] = {
   // norm + up|gate with the SwiGLU epilogue, which is the critical path (4 units of about 1650 cycles per warp and tile
   // against 5.8 k cycles of MMAs): 12 epilogue warps (8 units split 3 + 3 + 2) 105 us, 8 warps 121 us at 32 %; N=128 182 us
   {1, 384, 2048, 256, 0, 3, 2, 0},
-  {1, 1024, 384, 192, 0, 2, 2, 0},   // FFN down with residual (records row sums): 62 us, 31 %
+  // FFN down with residual (records row sums): 62 us, 31 % under ncu; 72 -> 67 us with one barrier pair per K step, -> 62 us
+  // with a fourth operand stage in place of a fourth residual slot (CUDA events, full net)
+  {1, 1024, 384, 192, 0, 2, 2, 0},
 };
 
 inline const TileRow* tileTableLookup(int k, int inC, int outC) {

@@ -1445,7 +1445,7 @@ bool convTcSetEpilogue(ConvTcPlan* p, const Epilogue& ep) {
   if(p->kY == 1 && p->kChunks >= 8 && p->resRing > 3) p->resRing = 3;
   if(const char* e = getenv("KB_TC_RES_RING")) {
     const int v = atoi(e);
-    if(p->kY == 1 && p->kChunks >= 8 && v >= 2 && v <= unitsPerWarp + 1) p->resRing = v;
+    if(p->kY == 1 && v >= 2 && v <= unitsPerWarp + 1) p->resRing = v;
   }
   const int rawUnits = ep.residual ? p->resRing : (ep.outRaw ? 2 : 0);
   p->epiWarpBytes = (rawUnits + (ep.outAct ? 1 : 0)) * TC_UNIT_BYTES;

@@ -1284,6 +1284,10 @@ bool convTcRowNormEligible(int dt, int inC, int outC) {
   return (pickBN(1, inC, outC) % 32) == 0;
 }
 
+int convTcPlanRowSumSlots(const ConvTcPlan* p) {
+  return (p && p->tmaEpi && (p->BN % 32) == 0) ? (p->outC / p->BN) * p->cg : 0;
+}
+
 int convTcRowSumSlots(int k, int inC, int outC) {
   const int bn = pickBN(k, inC, outC);
   // the staged epilogue needs whole 32-channel units
@@ -1433,7 +1437,10 @@ bool convTcSetEpilogue(ConvTcPlan* p, const Epilogue& ep) {
     // rotary ones.  A tile's units need not divide by three (8 units: 3 + 3 + 2): every warp walks its own unit
     // sequence, residual ring included.
     const bool specialWide = (ep.act == KB_ACT_SWIGLU_PAIRS || ep.act == KB_ACT_ROPE_QK) && !ep.residual && !ep.sumsqOut;
-    const bool plainWide = !needsStaged;
+    // a producer of row sums writes one slot per (channel tile, epilogue warp of the quarter): the consumer learns the
+    // count from the plan (convTcPlanRowSumSlots), so the producer may have twelve warps as well
+    const bool sumsWide = ep.sumsqOut && !ep.rowSumsq && ep.act != KB_ACT_SWIGLU_PAIRS && ep.act != KB_ACT_ROPE_QK;
+    const bool plainWide = !needsStaged || sumsWide;
     if(TC_EPI_CG == 2 && wideMode > 0 && want == TC_EPI_CG_WIDE && p->kY == 1 && !p->pair && (plainWide || specialWide))
       p->cg = TC_EPI_CG_WIDE;
   }

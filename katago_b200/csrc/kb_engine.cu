@@ -243,6 +243,12 @@ void Engine::addConvOp(const ConvDev& c, Epilogue ep, const std::string& tag) {
   int* status = statusWord_;
   if(c.tc) {
     if(!convTcSetEpilogue(c.plan, ep)) throw std::runtime_error("tensor-core convolution: shared memory budget exceeded");
+    if(ep.sumsqOut) {
+      // the producer's slot count follows from the epilogue variant just chosen
+      const int slots = convTcPlanRowSumSlots(c.plan);
+      if(slots < 1 || slots > rowSumsSlotsMax_) throw std::runtime_error("internal: row-sum slots of a convolution exceed the buffer");
+      rowSumsCur_ = slots;
+    }
     const ConvTcPlan* plan = c.plan;
     std::shared_ptr<ConvTcDeps> deps = std::make_shared<ConvTcDeps>();
     addOp(name, flops, bytes, [plan, ep, status, deps](cudaStream_t st, const Geom& g) { return launchConvTc(st, plan, g, ep, status, deps.get()); });

@@ -173,6 +173,8 @@ bool convTcEligible(int dt, int inC, int outC, int kY, int kX);
 bool convTcRowNormEligible(int dt, int inC, int outC);
 // Number of partial-sum slots a convolution of this shape writes per row when Epilogue::sumsqOut is set.
 int convTcRowSumSlots(int k, int inC, int outC);
+// the slot count of a planned convolution whose epilogue has been set (it depends on the epilogue-warp variant chosen)
+int convTcPlanRowSumSlots(const struct ConvTcPlan* p);
 // True if the tensor-core kernel can run the merged up|gate projection (inC -> 2*F, interleaved) with the SwiGLU epilogue.
 bool convTcSwigluEligible(int dt, int inC, int F);
 // the merged Q|K|V projection can apply the rotary embedding in its epilogue (Epilogue::act == KB_ACT_ROPE_QK)

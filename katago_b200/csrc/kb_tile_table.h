@@ -58,7 +58,7 @@ static const TileRow TILE_TABLE[] = {
   // kernel 45 us).  N=128 with resident weights 91 us, N=96 114 us; 12 epilogue warps 84.5 us against 89.5 on one box,
   // 82.0 against 82.6 on another.
   {1, 384, 1152, 192, 0, 3, 2, 0},
-  {1, 384, 384, 192, 0, 2, 2, 0},    // attention output with residual (records row sums: 8-warp epilogue only): 35 us, 20 %
+  {1, 384, 384, 192, 0, 2, 3, 0},    // attention output with residual (records row sums): 38 us with 8 epilogue warps, 36 us with 12
   // norm + up|gate with the SwiGLU epilogue, which is the critical path (4 units of about 1650 cycles per warp and tile
   // against 5.8 k cycles of MMAs): 12 epilogue warps (8 units split 3 + 3 + 2) 105 us, 8 warps 121 us at 32 %; N=128 182 us
   {1, 384, 2048, 256, 0, 3, 2, 0},

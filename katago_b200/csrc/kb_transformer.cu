@@ -3,6 +3,7 @@
 // kernels.  All of these are memory-bound except attention, which here is a straightforward shared-memory
 // implementation on CUDA cores (one block per board, head and 32-query slice).
 #include "kb_kernels.cuh"
+#include "kb_act.cuh"
 #include "../../include/kb_modelblob.h"
 
 namespace kb {
@@ -65,10 +66,85 @@ __global__ void rmsNormKernel(
   }
 }
 
+// The same for 16-bit element types with C a multiple of 8 and at most 512: a lane keeps its one or two 8-channel
+// chunks of the row in registers between the sum of squares and the scaling, and memory sees 16-byte accesses only.
+// The arithmetic per element is that of rmsNormKernel except for the SiLU, see below.
+template <typename T>
+__global__ void rmsNormVec8Kernel(
+  const T* __restrict__ in, int inStride, const float* __restrict__ gamma, const float* __restrict__ beta, float eps, int silu,
+  const float* __restrict__ mask, const float* __restrict__ boardScale, T* __restrict__ out, int outStride, int C, Geom g) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if(row >= g.rowsPad) return;
+  const int chunks = C >> 3;
+  T* o = out + (size_t)row * outStride;
+  if(row >= g.rows || mask[row] == 0.0f) {
+    for(int j = lane; j < chunks; j += 32) *reinterpret_cast<uint4*>(o + 8 * j) = make_uint4(0u, 0u, 0u, 0u);
+    return;
+  }
+  const T* x = in + (size_t)row * inStride;
+  uint4 raw[2];
+  float ss = 0.0f;
+#pragma unroll
+  for(int k = 0; k < 2; k++) {
+    const int j = lane + 32 * k;
+    raw[k] = make_uint4(0u, 0u, 0u, 0u);
+    if(j < chunks) {
+      raw[k] = *reinterpret_cast<const uint4*>(x + 8 * j);
+      const T* e = reinterpret_cast<const T*>(&raw[k]);
+#pragma unroll
+      for(int i = 0; i < 8; i++) { const float v = tToF<T>(e[i]); ss += v * v; }
+    }
+  }
+  float rms;
+  if(boardScale) rms = boardScale[row / g.PB];
+  else rms = 1.0f / sqrtf(warpSum(ss) / (float)C + eps);
+#pragma unroll
+  for(int k = 0; k < 2; k++) {
+    const int j = lane + 32 * k;
+    if(j >= chunks) continue;
+    const T* e = reinterpret_cast<const T*>(&raw[k]);
+    const float4 g0 = *reinterpret_cast<const float4*>(gamma + 8 * j), g1 = *reinterpret_cast<const float4*>(gamma + 8 * j + 4);
+    const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+    float bb[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+    if(beta) {
+      const float4 b0 = *reinterpret_cast<const float4*>(beta + 8 * j), b1 = *reinterpret_cast<const float4*>(beta + 8 * j + 4);
+      bb[0] = b0.x; bb[1] = b0.y; bb[2] = b0.z; bb[3] = b0.w; bb[4] = b1.x; bb[5] = b1.y; bb[6] = b1.z; bb[7] = b1.w;
+    }
+    uint4 res;
+    T* r = reinterpret_cast<T*>(&res);
+#pragma unroll
+    for(int i = 0; i < 8; i++) {
+      float v = tToF<T>(e[i]) * rms * gg[i];
+      if(beta) v += bb[i];
+      // the special-function form the convolution epilogues use (kb_act.cuh): its error is far below the rounding of
+      // the 16-bit result, and the exact expf + division made this kernel compute-bound
+      if(silu) v = v * rcpApprox(1.0f + ex2Approx(v * -1.4426950408889634f));
+      r[i] = fToT<T>(v);
+    }
+    *reinterpret_cast<uint4*>(o + 8 * j) = res;
+  }
+}
+
+static bool rmsNormVec8Ok(int dt, const void* in, int inStride, const float* gamma, const float* beta, const void* out, int outStride, int C) {
+  return dt != DT_F32 && (C % 8) == 0 && C <= 512 && (inStride % 8) == 0 && (outStride % 8) == 0 &&
+         (reinterpret_cast<uintptr_t>(in) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
+         (reinterpret_cast<uintptr_t>(gamma) & 15) == 0 && (beta == nullptr || (reinterpret_cast<uintptr_t>(beta) & 15) == 0);
+}
+
 cudaError_t launchRmsNorm(
   cudaStream_t st, int dt, const void* in, int inStride, const float* gamma, const float* beta, float eps, int silu,
   const float* mask, void* out, int outStride, int C, Geom g) {
   const int warps = 8;
+  if(rmsNormVec8Ok(dt, in, inStride, gamma, beta, out, outStride, C)) {
+    if(dt == DT_F16)
+      rmsNormVec8Kernel<__half><<<(g.rowsPad + warps - 1) / warps, warps * 32, 0, st>>>(
+        (const __half*)in, inStride, gamma, beta, eps, silu, mask, nullptr, (__half*)out, outStride, C, g);
+    else
+      rmsNormVec8Kernel<__nv_bfloat16><<<(g.rowsPad + warps - 1) / warps, warps * 32, 0, st>>>(
+        (const __nv_bfloat16*)in, inStride, gamma, beta, eps, silu, mask, nullptr, (__nv_bfloat16*)out, outStride, C, g);
+    return cudaGetLastError();
+  }
   KBT_DISPATCH_DT(dt, (rmsNormKernel<T><<<(g.rowsPad + warps - 1) / warps, warps * 32, 0, st>>>(
     (const T*)in, inStride, gamma, beta, eps, silu, mask, nullptr, (T*)out, outStride, C, g)));
   return cudaGetLastError();
